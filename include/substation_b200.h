@@ -1,0 +1,251 @@
+/*
+ * substation_b200 -- C ABI of the B200 encoder-layer library.
+ *
+ * This is the boundary a host binds (ctypes, cgo, JNI ...): plain C types, raw
+ * device pointers, an opaque CUDA stream handle.  It replaces the four symbols
+ * the reference exports from pytorch_module/encoder.cu:304-318 (init,
+ * encoder_forward, encoder_backward, destroy) and adds one entry point per
+ * fused operator and one for the tensor contractions, which is what the
+ * reference's per-kernel harness (pytorch_module/benchmark.py) generates a
+ * translation unit for.
+ *
+ * Differences from the reference ABI, all deliberate:
+ *   - every function returns an sb_status instead of aborting the process
+ *     (reference: CHECK -> abort, pytorch_module/all.cuh:7-13);
+ *   - sizes, dropout probabilities and per-tensor dim orders are run-time
+ *     arguments of sb_create, not macros in a generated header
+ *     (reference: pytorch_module/encoder.py:213-376);
+ *   - work is enqueued on the caller's stream, not on a private one
+ *     (reference: pytorch_module/encoder.cu:78);
+ *   - dropout masks are uint8 tensors that the caller either supplies
+ *     (SB_MASK_EXPLICIT) or the kernels fill (SB_MASK_PHILOX).
+ *
+ * All tensors are fp16 except dropout masks (uint8, values 0/1).
+ * Strides are in elements.  No function synchronises the stream.
+ */
+#ifndef SUBSTATION_B200_H
+#define SUBSTATION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_MAX_DIMS 5
+#define SB_NUM_PARAMS 12
+#define SB_NUM_FWD_INTERM 23
+#define SB_NUM_BWD_INTERM 14
+
+typedef enum sb_status {
+  SB_OK = 0,
+  SB_ERR_ARG = 1,         /* null pointer, bad enum, non-positive size */
+  SB_ERR_LAYOUT = 2,      /* a dim-order string is not a permutation of the tensor's dims */
+  SB_ERR_UNSUPPORTED = 3, /* valid request outside what the kernels cover (message says what) */
+  SB_ERR_CUDA = 4,        /* a CUDA runtime/driver call failed (message carries its text) */
+  SB_ERR_ALIGNMENT = 5,   /* pointer or stride not aligned as the selected kernel needs */
+  SB_ERR_DEVICE = 6       /* a kernel reported a bounded wait running out */
+} sb_status;
+
+typedef enum sb_activation { SB_ACT_RELU = 0, SB_ACT_GELU = 1 } sb_activation;
+typedef enum sb_mask_mode { SB_MASK_EXPLICIT = 0, SB_MASK_PHILOX = 1 } sb_mask_mode;
+/* which contraction kernel sb_einsum uses */
+typedef enum sb_gemm_impl {
+  SB_GEMM_AUTO = 0,    /* tcgen05 when the operands qualify, else SIMT */
+  SB_GEMM_TCGEN05 = 1, /* fail with SB_ERR_UNSUPPORTED when they do not */
+  SB_GEMM_SIMT = 2
+} sb_gemm_impl;
+
+/* A strided view.  size/stride are listed in the operator's LOGICAL dim order
+ * (given per function below); any permutation of memory order is expressed
+ * through the strides. */
+typedef struct sb_tensor {
+  void* ptr;
+  int32_t ndim;
+  int64_t size[SB_MAX_DIMS];
+  int64_t stride[SB_MAX_DIMS];
+} sb_tensor;
+
+/* Dropout source for the forward operators.  In SB_MASK_PHILOX mode the mask of
+ * the element with logical linear index e is derived from Philox4x32-10 with
+ * key = seed, counter = (e >> 3, offset); it does not depend on memory layout
+ * or launch geometry.  Replaces GlobalRandomState (pytorch_module/blocks.cuh:48-51). */
+typedef struct sb_dropout {
+  float p;         /* drop probability in [0,1) */
+  int32_t mode;    /* sb_mask_mode */
+  uint64_t seed;
+  uint64_t offset; /* distinguishes dropout sites / calls */
+} sb_dropout;
+
+const char* sb_status_string(int status);
+/* Message of the most recent failure on the calling thread ("" if none). */
+const char* sb_last_error(void);
+/* Library version and the SM architecture it was built for, e.g. "0.1 sm_100a". */
+const char* sb_version(void);
+
+/* Scratch used by the operators that reduce over tokens (they write fp32
+ * partial sums there).  The caller allocates sb_workspace_bytes() of device
+ * memory, zero-fills it ONCE, and may reuse it for any sequence of calls on one
+ * stream; two calls that run concurrently need two workspaces. */
+size_t sb_workspace_bytes(void);
+
+/* ------------------------------------------------------------------------- */
+/* Fused operators.  "stream" is a cudaStream_t passed as void*.             */
+/* ------------------------------------------------------------------------- */
+
+/* out[n,p,h,b,j] = in[n,p,h,b,j] + bias[n,p,h]; n counts stacked projections.
+ * Replaces AttentionInputBiases::run, pytorch_module/block_aib.cuh:64-155.
+ * in/out: [N,P,H,B,J]; bias: [N,P,H]. */
+int sb_attention_input_biases(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                              const sb_tensor* out);
+
+/* alpha = softmax_k(scale*beta); drop = mask*alpha.  All [H,B,J,K].
+ * Replaces Softmax::run, pytorch_module/block_softmax.cuh:127-188. */
+int sb_softmax_dropout(void* stream, const sb_tensor* beta, const sb_tensor* alpha,
+                       const sb_tensor* mask, const sb_tensor* drop, float scale,
+                       const sb_dropout* dropout);
+
+/* lin = in + bias; r = mask*lin + resid; LayerNorm over the last dim:
+ * diff = r - mean, istd = rsqrt(var + 1e-5), ln = diff*istd, out = ln*gamma + beta.
+ * in, resid, mask, lin, diff, ln, out: [B,J,I]; istd: [B,J]; bias/gamma/beta: [I].
+ * lin may alias in (same strides).  Replaces BiasDropoutResidualLinearNorm::run,
+ * pytorch_module/block_bdrln.cuh:105-180 and :275-352. */
+int sb_bias_dropout_residual_layernorm(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                                       const sb_tensor* resid, const sb_tensor* gamma,
+                                       const sb_tensor* beta, const sb_tensor* mask,
+                                       const sb_tensor* lin, const sb_tensor* diff,
+                                       const sb_tensor* istd, const sb_tensor* ln,
+                                       const sb_tensor* out, const sb_dropout* dropout);
+
+/* lin1 = in + bias; drop2 = mask*act(lin1).  [B,J,U], bias [U].
+ * Replaces BiasActivationDropout::run, pytorch_module/block_bad.cuh:83-145
+ * (ReLU there; GELU is the tanh form of substation/transformer.py:11-14). */
+int sb_bias_activation_dropout(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                               const sb_tensor* mask, const sb_tensor* lin1,
+                               const sb_tensor* drop2, int activation,
+                               const sb_dropout* dropout);
+
+/* dln = dy*gamma; dgamma = sum_{b,j} dy*ln; dbeta = sum_{b,j} dy.
+ * dy, ln, dln: [B,J,I]; gamma, dgamma, dbeta: [I].
+ * Replaces BackwardScaleBias::run, pytorch_module/block_bsb_ebsb.cuh:171-216. */
+int sb_backward_scale_bias(void* stream, void* workspace, const sb_tensor* dy,
+                           const sb_tensor* ln, const sb_tensor* gamma, const sb_tensor* dln,
+                           const sb_tensor* dgamma, const sb_tensor* dbeta);
+
+/* LayerNorm backward-data from the stored diff and reciprocal std, then dropout:
+ * dresid = g*s - sum(g)*s/n - diff*sum(g*diff)*s^3/n; dlin = mask*dresid.
+ * dln, diff, mask, dresid, dlin: [B,J,I]; istd: [B,J].
+ * Replaces BackwardLayerNormResidualDropout::run, pytorch_module/block_blnrd.cuh:71-129, :195-259. */
+int sb_backward_layernorm_residual_dropout(void* stream, const sb_tensor* dln,
+                                           const sb_tensor* istd, const sb_tensor* diff,
+                                           const sb_tensor* mask, const sb_tensor* dresid,
+                                           const sb_tensor* dlin);
+
+/* dlin1 = act'(lin1)*(mask*ddrop2); dbias = sum_{b,j} dlin1.  [B,J,U], dbias [U].
+ * Replaces BackwardDropoutReluLinearBias::run, pytorch_module/block_bdrlb.cuh:98-146. */
+int sb_backward_dropout_activation_bias(void* stream, void* workspace, const sb_tensor* ddrop2,
+                                        const sb_tensor* mask, const sb_tensor* lin1,
+                                        const sb_tensor* dlin1, const sb_tensor* dbias,
+                                        int activation);
+
+/* dlinb2 = sum dlin2; g = dresid2 + dlin1_linw1; dln1 = g*gamma1;
+ * dgamma1 = sum g*ln1; dbeta1 = sum g.  3-D tensors [B,J,I], vectors [I].
+ * Replaces ExtendedBackwardScaleBias::run, pytorch_module/block_bsb_ebsb.cuh:368-420. */
+int sb_extended_backward_scale_bias(void* stream, void* workspace, const sb_tensor* ln1,
+                                    const sb_tensor* gamma1, const sb_tensor* dresid2,
+                                    const sb_tensor* dlin1_linw1, const sb_tensor* dlin2,
+                                    const sb_tensor* dln1, const sb_tensor* dgamma1,
+                                    const sb_tensor* dbeta1, const sb_tensor* dlinb2);
+
+/* dbo[i] = sum_{b,j} datt[b,j,i].
+ * Replaces BackwardAttnOutBias::run, pytorch_module/block_baob.cuh:75-97. */
+int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* datt,
+                              const sb_tensor* dbo);
+
+/* dbeta = alpha*(da - sum_k da*alpha), da = mask*dattn_drop.  All [H,B,J,K].
+ * Replaces BackwardSoftmax::run, pytorch_module/block_bs.cuh:100-156. */
+int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,
+                        const sb_tensor* dattn_drop, const sb_tensor* dbeta);
+
+/* dbias[n,p,h] = sum_{b,j} d[n,p,h,b,j].
+ * Replaces BackwardAttentionInputBiases::run, pytorch_module/block_baib.cuh:156-211. */
+int sb_backward_attention_input_biases(void* stream, const sb_tensor* d, const sb_tensor* dbias);
+
+/* dx = dxatt + dresid1.  [B,J,I].
+ * Replaces BackwardEncoderInput::run, pytorch_module/block_bei.cuh:52-106. */
+int sb_backward_encoder_input(void* stream, const sb_tensor* dxatt, const sb_tensor* dresid1,
+                              const sb_tensor* dx);
+
+/* C = alpha * einsum(A, B): a_dims/b_dims/c_dims name each operand's dims with
+ * one letter per entry of its size/stride arrays (e.g. "phbk","phbj","hbjk").
+ * Letters in all three are batch dims, letters in A and B only are summed.
+ * Each of the four letter groups must collapse to one stride in every operand,
+ * as in the reference (pytorch_module/einsumparser.h:29-37).
+ * Replaces Einsum::run / Gemm::run, pytorch_module/gemm.cuh:52-147. */
+int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims,
+              const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha,
+              int impl);
+/* Which kernel the last sb_einsum on this thread ran: SB_GEMM_TCGEN05 or SB_GEMM_SIMT. */
+int sb_einsum_last_impl(void);
+/* Every wait inside the tcgen05 kernel is bounded; when one runs out the kernel
+ * records a code (1 producer, 2 MMA issuer, 3 epilogue), drains and returns.
+ * This reads that sticky per-process flag after synchronising `stream`
+ * (0 = no wait ever ran out).  The reference has no counterpart: its CHECK
+ * macro aborts the process (pytorch_module/all.cuh:7-13). */
+int sb_device_error(void* stream, int* code);
+
+/* ------------------------------------------------------------------------- */
+/* Whole layer                                                               */
+/* ------------------------------------------------------------------------- */
+
+typedef struct sb_encoder sb_encoder;
+
+typedef struct sb_encoder_config {
+  int32_t batch;      /* B */
+  int32_t seq;        /* J = K */
+  int32_t heads;      /* H */
+  int32_t embed;      /* I; P = I/H, U = 4*I */
+  int32_t activation; /* sb_activation */
+  float p_softmax, p_resid1, p_activation, p_resid2;
+  /* Dim order of every tensor, as in the reference's layout pickle
+   * (config_selection/optimize.py:443-493): names[i] -> dims[i], for X, SB2, the 12
+   * parameters, the 23 forward and the 14 backward intermediates. */
+  int32_t n_tensors;
+  const char* const* names;
+  const char* const* dims;
+} sb_encoder_config;
+
+/* Replaces init() (pytorch_module/encoder.cu:304-306) and the code generation of
+ * pytorch_module/encoder.py:165-405.  Allocates the handle's workspace (the only
+ * device allocation the library ever makes for a layer). */
+int sb_encoder_create(const sb_encoder_config* cfg, sb_encoder** out);
+/* Replaces destroy() (pytorch_module/encoder.cu:316-318). */
+int sb_encoder_destroy(sb_encoder* enc);
+
+/* Replaces encoder_forward (pytorch_module/encoder.cu:308-310).  params, fwd: arrays of
+ * device pointers in the order of the config's parameter / forward-intermediate
+ * lists (the same order the reference passes them, pytorch_module/encoder.py:88-93).
+ * The four mask tensors inside fwd are read (explicit) or written (philox).
+ * seed/offset: Philox key and base offset; the four dropout sites use offset+0..3. */
+int sb_encoder_forward(sb_encoder* enc, void* stream, const void* x, const void* const* params,
+                       void* const* fwd, void* y, int mask_mode, uint64_t seed,
+                       uint64_t offset);
+/* Replaces encoder_backward (pytorch_module/encoder.cu:312-314); argument groups in the
+ * reference's order: dY, 12 parameter gradients, 14 backward intermediates, 12
+ * parameters, 23 forward intermediates, X, dX (pytorch_module/encoder.py:124-130). */
+int sb_encoder_backward(sb_encoder* enc, void* stream, const void* dy, void* const* dparams,
+                        void* const* bwd, const void* const* params, void* const* fwd,
+                        const void* x, void* dx);
+/* Per-operator device time of the most recent forward+backward, measured with
+ * CUDA events when timing was switched on; writes up to max (name, ms) pairs
+ * and returns the count.  Stands in for the NVTX ranges of pytorch_module/encoder.cu:32-53. */
+int sb_encoder_set_timing(sb_encoder* enc, int enabled);
+int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* ms);
+/* Number of kernels the most recent forward / backward launched. */
+int sb_encoder_launch_count(sb_encoder* enc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUBSTATION_B200_H */

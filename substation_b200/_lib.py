@@ -1,0 +1,128 @@
+"""ctypes binding of the C ABI declared in ``include/substation_b200.h``.
+
+The reference loads its generated ``encoder.so`` the same way
+(pytorch_module/encoder.py:395-405).  There is no fallback: if the library is
+missing or fails to load, importing an operator raises.
+"""
+
+import ctypes
+import os
+
+from . import build as _build
+
+SB_MAX_DIMS = 5
+SB_OK = 0
+SB_MASK_EXPLICIT, SB_MASK_PHILOX = 0, 1
+SB_ACT_RELU, SB_ACT_GELU = 0, 1
+SB_GEMM_AUTO, SB_GEMM_TCGEN05, SB_GEMM_SIMT = 0, 1, 2
+
+c_void_p, c_int, c_float, c_char_p = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_char_p
+
+
+class SbTensor(ctypes.Structure):
+    _fields_ = [('ptr', c_void_p), ('ndim', ctypes.c_int32),
+                ('size', ctypes.c_int64 * SB_MAX_DIMS), ('stride', ctypes.c_int64 * SB_MAX_DIMS)]
+
+
+class SbDropout(ctypes.Structure):
+    _fields_ = [('p', c_float), ('mode', ctypes.c_int32), ('seed', ctypes.c_uint64),
+                ('offset', ctypes.c_uint64)]
+
+
+class SbEncoderConfig(ctypes.Structure):
+    _fields_ = [('batch', ctypes.c_int32), ('seq', ctypes.c_int32), ('heads', ctypes.c_int32),
+                ('embed', ctypes.c_int32), ('activation', ctypes.c_int32),
+                ('p_softmax', c_float), ('p_resid1', c_float), ('p_activation', c_float),
+                ('p_resid2', c_float), ('n_tensors', ctypes.c_int32),
+                ('names', ctypes.POINTER(c_char_p)), ('dims', ctypes.POINTER(c_char_p))]
+
+
+class SubstationError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status, message):
+        super().__init__(f'substation_b200 status {status}: {message}')
+        self.status = status
+        self.message = message
+
+
+_T = ctypes.POINTER(SbTensor)
+_D = ctypes.POINTER(SbDropout)
+_PP = ctypes.POINTER(c_void_p)
+
+#: every exported symbol with (restype, argtypes); the CPU test suite checks the
+#: library exports exactly these
+SIGNATURES = {
+    'sb_status_string': (c_char_p, [c_int]),
+    'sb_last_error': (c_char_p, []),
+    'sb_version': (c_char_p, []),
+    'sb_workspace_bytes': (ctypes.c_size_t, []),
+    'sb_attention_input_biases': (c_int, [c_void_p, _T, _T, _T]),
+    'sb_softmax_dropout': (c_int, [c_void_p, _T, _T, _T, _T, c_float, _D]),
+    'sb_bias_dropout_residual_layernorm': (c_int, [c_void_p] + [_T] * 11 + [_D]),
+    'sb_bias_activation_dropout': (c_int, [c_void_p, _T, _T, _T, _T, _T, c_int, _D]),
+    'sb_backward_scale_bias': (c_int, [c_void_p, c_void_p] + [_T] * 6),
+    'sb_backward_layernorm_residual_dropout': (c_int, [c_void_p] + [_T] * 6),
+    'sb_backward_dropout_activation_bias': (c_int, [c_void_p, c_void_p] + [_T] * 5 + [c_int]),
+    'sb_extended_backward_scale_bias': (c_int, [c_void_p, c_void_p] + [_T] * 9),
+    'sb_backward_attn_out_bias': (c_int, [c_void_p, c_void_p, _T, _T]),
+    'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
+    'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
+    'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),
+    'sb_einsum': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, c_int]),
+    'sb_einsum_last_impl': (c_int, []),
+    'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    'sb_encoder_create': (c_int, [ctypes.POINTER(SbEncoderConfig), ctypes.POINTER(c_void_p)]),
+    'sb_encoder_destroy': (c_int, [c_void_p]),
+    'sb_encoder_forward': (c_int, [c_void_p, c_void_p, c_void_p, _PP, _PP, c_void_p, c_int,
+                                   ctypes.c_uint64, ctypes.c_uint64]),
+    'sb_encoder_backward': (c_int, [c_void_p, c_void_p, c_void_p, _PP, _PP, _PP, _PP, c_void_p,
+                                    c_void_p]),
+    'sb_encoder_set_timing': (c_int, [c_void_p, c_int]),
+    'sb_encoder_get_timing': (c_int, [c_void_p, c_int, ctypes.POINTER(c_char_p),
+                                      ctypes.POINTER(c_float)]),
+    'sb_encoder_launch_count': (c_int, [c_void_p]),
+}
+
+_lib = None
+
+
+def lib_path():
+    return _build.LIB_PATH
+
+
+def load():
+    """Load (building first if the .so is absent and nvcc is available)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        _build.build()
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)      # AttributeError if a declared symbol is missing
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status != SB_OK:
+        raise SubstationError(status, load().sb_last_error().decode())
+
+
+def tensor_desc(t, order=None):
+    """SbTensor for a torch tensor.  ``order``: permutation applied to (size, stride),
+    i.e. ``t.permute(order)`` without creating a view."""
+    d = SbTensor()
+    d.ptr = t.data_ptr()
+    dims = range(t.dim()) if order is None else order
+    sizes = [t.size(i) for i in dims]
+    strides = [t.stride(i) for i in dims]
+    d.ndim = len(sizes)
+    for i, (s, st) in enumerate(zip(sizes, strides)):
+        d.size[i] = s
+        d.stride[i] = st
+    return d

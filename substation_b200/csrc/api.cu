@@ -1,0 +1,771 @@
+// C ABI: argument validation, strided-view construction, per-operator entry
+// points and the whole-layer handle (operator sequence of the encoder layer).
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "ops.h"
+
+namespace sb {
+
+namespace {
+thread_local std::string g_error;
+}
+
+void set_error(const std::string& msg) { g_error = msg; }
+int fail(int status, const std::string& msg) {
+  g_error = msg;
+  return status;
+}
+
+namespace {
+
+bool aligned(const void* p, unsigned a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// vec flag: unit stride along `inner`, extent % 8 == 0, other strides % 8 == 0, base aligned.
+int vec_flag(const sb_tensor* t, int inner, unsigned align) {
+  if (t->stride[inner] != 1 || t->size[inner] % 8 != 0 || !aligned(t->ptr, align)) return 0;
+  for (int i = 0; i < t->ndim; ++i)
+    if (i != inner && t->size[i] > 1 && t->stride[i] % 8 != 0) return 0;
+  return 1;
+}
+
+int check_tensor(const sb_tensor* t, int ndim, const char* what) {
+  if (!t) return fail(SB_ERR_ARG, std::string(what) + ": null tensor");
+  if (t->ndim != ndim)
+    return fail(SB_ERR_ARG, std::string(what) + ": expected rank " + std::to_string(ndim) + ", got " +
+                                std::to_string(t->ndim));
+  long long n = 1;
+  for (int i = 0; i < ndim; ++i) {
+    if (t->size[i] < 0) return fail(SB_ERR_ARG, std::string(what) + ": negative extent");
+    n *= t->size[i];
+  }
+  if (n > 0 && !t->ptr) return fail(SB_ERR_ARG, std::string(what) + ": null data pointer");
+  return SB_OK;
+}
+
+int same_shape(const sb_tensor* a, const sb_tensor* b, const char* what) {
+  for (int i = 0; i < a->ndim; ++i)
+    if (a->size[i] != b->size[i]) return fail(SB_ERR_ARG, std::string(what) + ": extent mismatch between operands");
+  return SB_OK;
+}
+
+int fits_int(const sb_tensor* t, const char* what) {
+  for (int i = 0; i < t->ndim; ++i)
+    if (t->size[i] > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, std::string(what) + ": extent exceeds 2^31-1");
+  return SB_OK;
+}
+
+int to_view3(const sb_tensor* t, const sb_tensor* shape_ref, bool is_mask, const char* what, View3* v) {
+  SB_TRY(check_tensor(t, 3, what));
+  SB_TRY(fits_int(t, what));
+  if (shape_ref) SB_TRY(same_shape(shape_ref, t, what));
+  v->p = t->ptr; v->sB = t->stride[0]; v->sJ = t->stride[1]; v->sF = t->stride[2];
+  v->vec = vec_flag(t, 2, is_mask ? 8 : 16);
+  return SB_OK;
+}
+int to_view2(const sb_tensor* t, const sb_tensor* ref3, const char* what, View2* v) {
+  SB_TRY(check_tensor(t, 2, what));
+  if (t->size[0] != ref3->size[0] || t->size[1] != ref3->size[1])
+    return fail(SB_ERR_ARG, std::string(what) + ": extent mismatch between operands");
+  v->p = t->ptr; v->sB = t->stride[0]; v->sJ = t->stride[1];
+  return SB_OK;
+}
+int to_view4(const sb_tensor* t, const sb_tensor* shape_ref, bool is_mask, const char* what, View4* v) {
+  SB_TRY(check_tensor(t, 4, what));
+  SB_TRY(fits_int(t, what));
+  if (shape_ref) SB_TRY(same_shape(shape_ref, t, what));
+  v->p = t->ptr; v->sH = t->stride[0]; v->sB = t->stride[1]; v->sJ = t->stride[2]; v->sK = t->stride[3];
+  v->vec = vec_flag(t, 3, is_mask ? 8 : 16);
+  return SB_OK;
+}
+int to_view5(const sb_tensor* t, const sb_tensor* shape_ref, const char* what, View5* v) {
+  SB_TRY(check_tensor(t, 5, what));
+  SB_TRY(fits_int(t, what));
+  if (shape_ref) SB_TRY(same_shape(shape_ref, t, what));
+  v->p = t->ptr; v->sN = t->stride[0]; v->sP = t->stride[1]; v->sH = t->stride[2];
+  v->sB = t->stride[3]; v->sJ = t->stride[4];
+  v->vec = vec_flag(t, 4, 16);
+  return SB_OK;
+}
+// Per-feature vector [F]: must be contiguous.
+int to_param(const sb_tensor* t, long long F, const char* what, void** p) {
+  SB_TRY(check_tensor(t, 1, what));
+  if (t->size[0] != F) return fail(SB_ERR_ARG, std::string(what) + ": extent mismatch between operands");
+  if (F > 1 && t->stride[0] != 1) return fail(SB_ERR_UNSUPPORTED, std::string(what) + ": per-feature vectors must be contiguous");
+  *p = t->ptr;
+  return SB_OK;
+}
+
+int to_rng(const sb_dropout* d, Rng* r) {
+  if (!d) return fail(SB_ERR_ARG, "dropout: null descriptor");
+  if (!(d->p >= 0.f && d->p < 1.f)) return fail(SB_ERR_ARG, "dropout: probability must be in [0,1)");
+  if (d->mode != SB_MASK_EXPLICIT && d->mode != SB_MASK_PHILOX) return fail(SB_ERR_ARG, "dropout: unknown mask mode");
+  r->seed_lo = (uint32_t)d->seed; r->seed_hi = (uint32_t)(d->seed >> 32);
+  r->off_lo = (uint32_t)d->offset; r->off_hi = (uint32_t)(d->offset >> 32);
+  long thr = lrintf(d->p * 65536.f);
+  if (thr < 0) thr = 0;
+  if (thr > 65535) thr = 65535;
+  r->thr = (uint32_t)thr;
+  r->philox = d->mode == SB_MASK_PHILOX ? 1 : 0;
+  return SB_OK;
+}
+
+Dims3 dims3(const sb_tensor* t) { return Dims3{(int)t->size[0], (int)t->size[1], (int)t->size[2]}; }
+Dims4 dims4(const sb_tensor* t) { return Dims4{(int)t->size[0], (int)t->size[1], (int)t->size[2], (int)t->size[3]}; }
+Dims5 dims5(const sb_tensor* t) {
+  return Dims5{(int)t->size[0], (int)t->size[1], (int)t->size[2], (int)t->size[3], (int)t->size[4]};
+}
+
+int check_activation(int a) {
+  if (a != SB_ACT_RELU && a != SB_ACT_GELU) return fail(SB_ERR_ARG, "unknown activation");
+  return SB_OK;
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+// ---------------------------------------------------------------------------
+// Miscellaneous
+// ---------------------------------------------------------------------------
+extern "C" const char* sb_status_string(int status) {
+  switch (status) {
+    case SB_OK: return "ok";
+    case SB_ERR_ARG: return "invalid argument";
+    case SB_ERR_LAYOUT: return "invalid layout";
+    case SB_ERR_UNSUPPORTED: return "unsupported";
+    case SB_ERR_CUDA: return "CUDA error";
+    case SB_ERR_ALIGNMENT: return "misaligned operand";
+    case SB_ERR_DEVICE: return "device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+extern "C" const char* sb_last_error(void) { return g_error.c_str(); }
+extern "C" const char* sb_version(void) { return "0.1 sm_100a"; }
+extern "C" size_t sb_workspace_bytes(void) { return kWsBytes; }
+
+// ---------------------------------------------------------------------------
+// Fused operators
+// ---------------------------------------------------------------------------
+extern "C" int sb_attention_input_biases(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                                         const sb_tensor* out) {
+  View5 vi, vo;
+  SB_TRY(to_view5(in, nullptr, "aib.in", &vi));
+  SB_TRY(to_view5(out, in, "aib.out", &vo));
+  SB_TRY(check_tensor(bias, 3, "aib.bias"));
+  for (int i = 0; i < 3; ++i)
+    if (bias->size[i] != in->size[i]) return fail(SB_ERR_ARG, "aib.bias: extent mismatch between operands");
+  return launch_aib((cudaStream_t)stream, dims5(in), vi, bias->ptr, bias->stride[0], bias->stride[1],
+                    bias->stride[2], vo);
+}
+
+extern "C" int sb_softmax_dropout(void* stream, const sb_tensor* beta, const sb_tensor* alpha,
+                                  const sb_tensor* mask, const sb_tensor* drop, float scale,
+                                  const sb_dropout* dropout) {
+  View4 vb, va, vm, vd;
+  Rng rng;
+  SB_TRY(to_view4(beta, nullptr, false, "softmax.beta", &vb));
+  SB_TRY(to_view4(alpha, beta, false, "softmax.alpha", &va));
+  SB_TRY(to_view4(mask, beta, true, "softmax.mask", &vm));
+  SB_TRY(to_view4(drop, beta, false, "softmax.drop", &vd));
+  SB_TRY(to_rng(dropout, &rng));
+  return launch_softmax_fwd((cudaStream_t)stream, dims4(beta), vb, va, vm, vd, scale, rng);
+}
+
+extern "C" int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,
+                                   const sb_tensor* dattn_drop, const sb_tensor* dbeta) {
+  View4 va, vm, vg, vo;
+  SB_TRY(to_view4(alpha, nullptr, false, "bs.alpha", &va));
+  SB_TRY(to_view4(mask, alpha, true, "bs.mask", &vm));
+  SB_TRY(to_view4(dattn_drop, alpha, false, "bs.dattn_drop", &vg));
+  SB_TRY(to_view4(dbeta, alpha, false, "bs.dbeta", &vo));
+  return launch_softmax_bwd((cudaStream_t)stream, dims4(alpha), va, vm, vg, vo);
+}
+
+extern "C" int sb_bias_dropout_residual_layernorm(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                                                  const sb_tensor* resid, const sb_tensor* gamma,
+                                                  const sb_tensor* beta, const sb_tensor* mask,
+                                                  const sb_tensor* lin, const sb_tensor* diff,
+                                                  const sb_tensor* istd, const sb_tensor* ln,
+                                                  const sb_tensor* out, const sb_dropout* dropout) {
+  View3 vin, vres, vmask, vlin, vdiff, vln, vout;
+  View2 vistd;
+  void *pb, *pg, *pbt;
+  Rng rng;
+  SB_TRY(to_view3(in, nullptr, false, "bdrln.in", &vin));
+  SB_TRY(to_view3(resid, in, false, "bdrln.resid", &vres));
+  SB_TRY(to_view3(mask, in, true, "bdrln.mask", &vmask));
+  SB_TRY(to_view3(lin, in, false, "bdrln.lin", &vlin));
+  SB_TRY(to_view3(diff, in, false, "bdrln.diff", &vdiff));
+  SB_TRY(to_view3(ln, in, false, "bdrln.ln", &vln));
+  SB_TRY(to_view3(out, in, false, "bdrln.out", &vout));
+  SB_TRY(to_view2(istd, in, "bdrln.istd", &vistd));
+  SB_TRY(to_param(bias, in->size[2], "bdrln.bias", &pb));
+  SB_TRY(to_param(gamma, in->size[2], "bdrln.gamma", &pg));
+  SB_TRY(to_param(beta, in->size[2], "bdrln.beta", &pbt));
+  SB_TRY(to_rng(dropout, &rng));
+  if (lin->ptr == in->ptr && (vlin.sB != vin.sB || vlin.sJ != vin.sJ || vlin.sF != vin.sF))
+    return fail(SB_ERR_ARG, "bdrln: lin aliases in but has different strides");
+  return launch_bdrln((cudaStream_t)stream, dims3(in), vin, pb, vres, pg, pbt, vmask, vlin, vdiff, vistd,
+                      vln, vout, rng);
+}
+
+extern "C" int sb_bias_activation_dropout(void* stream, const sb_tensor* in, const sb_tensor* bias,
+                                          const sb_tensor* mask, const sb_tensor* lin1,
+                                          const sb_tensor* drop2, int activation,
+                                          const sb_dropout* dropout) {
+  View3 vin, vmask, vlin, vdrop;
+  void* pb;
+  Rng rng;
+  SB_TRY(check_activation(activation));
+  SB_TRY(to_view3(in, nullptr, false, "bad.in", &vin));
+  SB_TRY(to_view3(mask, in, true, "bad.mask", &vmask));
+  SB_TRY(to_view3(lin1, in, false, "bad.lin1", &vlin));
+  SB_TRY(to_view3(drop2, in, false, "bad.drop2", &vdrop));
+  SB_TRY(to_param(bias, in->size[2], "bad.bias", &pb));
+  SB_TRY(to_rng(dropout, &rng));
+  return launch_bad((cudaStream_t)stream, dims3(in), vin, pb, vmask, vlin, vdrop, activation, rng);
+}
+
+extern "C" int sb_backward_scale_bias(void* stream, void* workspace, const sb_tensor* dy, const sb_tensor* ln,
+                                      const sb_tensor* gamma, const sb_tensor* dln, const sb_tensor* dgamma,
+                                      const sb_tensor* dbeta) {
+  View3 vdy, vln, vdln;
+  void *pg, *pdg, *pdb;
+  SB_TRY(to_view3(dy, nullptr, false, "bsb.dy", &vdy));
+  SB_TRY(to_view3(ln, dy, false, "bsb.ln", &vln));
+  SB_TRY(to_view3(dln, dy, false, "bsb.dln", &vdln));
+  SB_TRY(to_param(gamma, dy->size[2], "bsb.gamma", &pg));
+  SB_TRY(to_param(dgamma, dy->size[2], "bsb.dgamma", &pdg));
+  SB_TRY(to_param(dbeta, dy->size[2], "bsb.dbeta", &pdb));
+  return launch_bsb((cudaStream_t)stream, workspace, dims3(dy), vdy, vln, pg, vdln, pdg, pdb);
+}
+
+extern "C" int sb_backward_layernorm_residual_dropout(void* stream, const sb_tensor* dln, const sb_tensor* istd,
+                                                      const sb_tensor* diff, const sb_tensor* mask,
+                                                      const sb_tensor* dresid, const sb_tensor* dlin) {
+  View3 vg, vd, vm, vr, vl;
+  View2 vs;
+  SB_TRY(to_view3(dln, nullptr, false, "blnrd.dln", &vg));
+  SB_TRY(to_view3(diff, dln, false, "blnrd.diff", &vd));
+  SB_TRY(to_view3(mask, dln, true, "blnrd.mask", &vm));
+  SB_TRY(to_view3(dresid, dln, false, "blnrd.dresid", &vr));
+  SB_TRY(to_view3(dlin, dln, false, "blnrd.dlin", &vl));
+  SB_TRY(to_view2(istd, dln, "blnrd.istd", &vs));
+  return launch_blnrd((cudaStream_t)stream, dims3(dln), vg, vs, vd, vm, vr, vl);
+}
+
+extern "C" int sb_backward_dropout_activation_bias(void* stream, void* workspace, const sb_tensor* ddrop2,
+                                                   const sb_tensor* mask, const sb_tensor* lin1,
+                                                   const sb_tensor* dlin1, const sb_tensor* dbias,
+                                                   int activation) {
+  View3 vg, vm, vx, vo;
+  void* pdb;
+  SB_TRY(check_activation(activation));
+  SB_TRY(to_view3(ddrop2, nullptr, false, "bdrlb.ddrop2", &vg));
+  SB_TRY(to_view3(mask, ddrop2, true, "bdrlb.mask", &vm));
+  SB_TRY(to_view3(lin1, ddrop2, false, "bdrlb.lin1", &vx));
+  SB_TRY(to_view3(dlin1, ddrop2, false, "bdrlb.dlin1", &vo));
+  SB_TRY(to_param(dbias, ddrop2->size[2], "bdrlb.dbias", &pdb));
+  return launch_bdrlb((cudaStream_t)stream, workspace, dims3(ddrop2), vg, vm, vx, vo, pdb, activation);
+}
+
+extern "C" int sb_extended_backward_scale_bias(void* stream, void* workspace, const sb_tensor* ln1,
+                                               const sb_tensor* gamma1, const sb_tensor* dresid2,
+                                               const sb_tensor* dlin1_linw1, const sb_tensor* dlin2,
+                                               const sb_tensor* dln1, const sb_tensor* dgamma1,
+                                               const sb_tensor* dbeta1, const sb_tensor* dlinb2) {
+  View3 vn, vr, vw, vl2, vo;
+  void *pg, *pdg, *pdb, *pdl;
+  SB_TRY(to_view3(ln1, nullptr, false, "ebsb.ln1", &vn));
+  SB_TRY(to_view3(dresid2, ln1, false, "ebsb.dresid2", &vr));
+  SB_TRY(to_view3(dlin1_linw1, ln1, false, "ebsb.dlin1_linw1", &vw));
+  SB_TRY(to_view3(dlin2, ln1, false, "ebsb.dlin2", &vl2));
+  SB_TRY(to_view3(dln1, ln1, false, "ebsb.dln1", &vo));
+  SB_TRY(to_param(gamma1, ln1->size[2], "ebsb.gamma1", &pg));
+  SB_TRY(to_param(dgamma1, ln1->size[2], "ebsb.dgamma1", &pdg));
+  SB_TRY(to_param(dbeta1, ln1->size[2], "ebsb.dbeta1", &pdb));
+  SB_TRY(to_param(dlinb2, ln1->size[2], "ebsb.dlinb2", &pdl));
+  return launch_ebsb((cudaStream_t)stream, workspace, dims3(ln1), vn, pg, vr, vw, vl2, vo, pdg, pdb, pdl);
+}
+
+extern "C" int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* datt,
+                                         const sb_tensor* dbo) {
+  View3 v;
+  void* p;
+  SB_TRY(to_view3(datt, nullptr, false, "baob.datt", &v));
+  SB_TRY(to_param(dbo, datt->size[2], "baob.dbo", &p));
+  return launch_baob((cudaStream_t)stream, workspace, dims3(datt), v, p);
+}
+
+extern "C" int sb_backward_attention_input_biases(void* stream, const sb_tensor* d, const sb_tensor* dbias) {
+  View5 v;
+  SB_TRY(to_view5(d, nullptr, "baib.d", &v));
+  SB_TRY(check_tensor(dbias, 3, "baib.dbias"));
+  for (int i = 0; i < 3; ++i)
+    if (dbias->size[i] != d->size[i]) return fail(SB_ERR_ARG, "baib.dbias: extent mismatch between operands");
+  return launch_baib((cudaStream_t)stream, dims5(d), v, dbias->ptr, dbias->stride[0], dbias->stride[1],
+                     dbias->stride[2]);
+}
+
+extern "C" int sb_backward_encoder_input(void* stream, const sb_tensor* dxatt, const sb_tensor* dresid1,
+                                         const sb_tensor* dx) {
+  View3 a, b, o;
+  SB_TRY(to_view3(dxatt, nullptr, false, "bei.dxatt", &a));
+  SB_TRY(to_view3(dresid1, dxatt, false, "bei.dresid1", &b));
+  SB_TRY(to_view3(dx, dxatt, false, "bei.dx", &o));
+  return launch_bei((cudaStream_t)stream, dims3(dxatt), a, b, o);
+}
+
+extern "C" int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims,
+                         const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha, int impl) {
+  GemmProblem g;
+  SB_TRY(plan_einsum(a_dims, a, b_dims, b, c_dims, c, alpha, &g));
+  return run_gemm((cudaStream_t)stream, g, impl);
+}
+extern "C" int sb_einsum_last_impl(void) { return g_last_gemm_impl; }
+extern "C" int sb_device_error(void* stream, int* code) {
+  if (!code) return fail(SB_ERR_ARG, "sb_device_error: null argument");
+  return gemm_device_error((cudaStream_t)stream, code);
+}
+
+// ---------------------------------------------------------------------------
+// Whole layer
+// ---------------------------------------------------------------------------
+namespace {
+
+const char* const kParamNames[SB_NUM_PARAMS] = {"WKQV", "BKQV", "WO", "BO", "S1", "B1",
+                                                "LINB1", "LINW1", "S2", "B2", "LINB2", "LINW2"};
+const char* const kFwdNames[SB_NUM_FWD_INTERM] = {
+    "KKQQVV", "WKKWQQWVV", "BETA", "ALPHA", "ATTN_DROP_MASK", "ATTN_DROP", "GAMMA", "ATT",
+    "DROP1MASK", "SB1", "SB1_LINW1", "DROP2", "LIN1", "DROP2_LINW2", "LIN2", "LN2", "LN2STD",
+    "LN2DIFF", "DROP2MASK", "DROP3MASK", "LN1", "LN1STD", "LN1DIFF"};
+const char* const kBwdNames[SB_NUM_BWD_INTERM] = {
+    "DLN2", "DRESID2", "DLIN2", "DDROP2", "DLIN1", "DLIN1_LINW1", "DLN1", "DRESID1", "DATT",
+    "DXATT", "DGAMMA", "DATTN_DROP", "DBETA", "DKKQQVV"};
+
+const std::map<std::string, std::string>& logical_dims() {
+  static const std::map<std::string, std::string> m = {
+      {"X", "BJI"}, {"SB2", "BJI"},
+      {"WKQV", "QPHI"}, {"BKQV", "QPH"}, {"WO", "IPH"}, {"BO", "I"}, {"S1", "I"}, {"B1", "I"},
+      {"S2", "I"}, {"B2", "I"}, {"LINW1", "IU"}, {"LINB1", "U"}, {"LINW2", "UI"}, {"LINB2", "I"},
+      {"KKQQVV", "QPHBJ"}, {"WKKWQQWVV", "QPHBJ"}, {"BETA", "HBJK"}, {"ALPHA", "HBJK"},
+      {"ATTN_DROP_MASK", "HBJK"}, {"ATTN_DROP", "HBJK"}, {"GAMMA", "PHBJ"}, {"ATT", "BJI"},
+      {"DROP1MASK", "BJI"}, {"SB1", "BJI"}, {"SB1_LINW1", "BJU"}, {"DROP2", "BJU"}, {"LIN1", "BJU"},
+      {"DROP2_LINW2", "BJI"}, {"LIN2", "BJI"}, {"LN2", "BJI"}, {"LN2STD", "BJ"}, {"LN2DIFF", "BJI"},
+      {"DROP2MASK", "BJU"}, {"DROP3MASK", "BJI"}, {"LN1", "BJI"}, {"LN1STD", "BJ"}, {"LN1DIFF", "BJI"},
+      {"DLN2", "BJI"}, {"DRESID2", "BJI"}, {"DLIN2", "BJI"}, {"DDROP2", "BJU"}, {"DLIN1", "BJU"},
+      {"DLIN1_LINW1", "BJI"}, {"DLN1", "BJI"}, {"DRESID1", "BJI"}, {"DATT", "BJI"}, {"DXATT", "BJI"},
+      {"DGAMMA", "PHBJ"}, {"DATTN_DROP", "HBJK"}, {"DBETA", "HBJK"}, {"DKKQQVV", "QPHBJ"}};
+  return m;
+}
+
+bool is_permutation(const std::string& a, const std::string& b) {
+  if (a.size() != b.size()) return false;
+  std::string x = a, y = b;
+  std::sort(x.begin(), x.end());
+  std::sort(y.begin(), y.end());
+  return x == y;
+}
+
+}  // namespace
+
+struct sb_encoder {
+  int B, S, H, P, I, U;
+  int activation;
+  float p_softmax, p_resid1, p_act, p_resid2;
+  std::map<std::string, std::string> layout;  // name -> dim order in memory
+  std::vector<std::string> param_order, fwd_order, bwd_order;
+  void* workspace = nullptr;
+  int device = 0;
+  int launches = 0;
+  bool timing = false;
+  std::vector<std::pair<std::string, cudaEvent_t>> marks;
+  std::vector<cudaEvent_t> event_pool;
+  std::vector<std::pair<std::string, float>> last_times;
+
+  long long extent(char c) const {
+    switch (c) {
+      case 'B': return B;
+      case 'J': case 'K': case 'S': return S;
+      case 'H': return H;
+      case 'P': return P;
+      case 'I': return I;
+      case 'U': return U;
+      case 'Q': return 3;
+      default: return -1;
+    }
+  }
+  long long numel(const std::string& dims) const {
+    long long n = 1;
+    for (char c : dims) n *= extent(c);
+    return n;
+  }
+  // Tensor in MEMORY order: dims string = layout (optionally with letters renamed), contiguous strides.
+  sb_tensor mem(const void* ptr, const std::string& dims) const {
+    sb_tensor t;
+    t.ptr = const_cast<void*>(ptr);
+    t.ndim = (int)dims.size();
+    long long st = 1;
+    for (int i = t.ndim - 1; i >= 0; --i) {
+      t.size[i] = extent(dims[i]);
+      t.stride[i] = st;
+      st *= t.size[i];
+    }
+    return t;
+  }
+  // Tensor viewed in LOGICAL order `logical`, stored contiguously as `lay`.
+  sb_tensor view(const void* ptr, const std::string& lay, const std::string& logical) const {
+    const sb_tensor m = mem(ptr, lay);
+    sb_tensor t;
+    t.ptr = m.ptr;
+    t.ndim = (int)logical.size();
+    for (int i = 0; i < t.ndim; ++i) {
+      const size_t d = lay.find(logical[i]);
+      t.size[i] = m.size[d];
+      t.stride[i] = m.stride[d];
+    }
+    return t;
+  }
+  sb_tensor view(const void* ptr, const char* name) const {
+    return view(ptr, layout.at(name), logical_dims().at(name));
+  }
+
+  void mark(cudaStream_t s, const char* name) {
+    ++launches;
+    if (!timing) return;
+    cudaEvent_t e;
+    if (event_pool.empty()) cudaEventCreate(&e);
+    else { e = event_pool.back(); event_pool.pop_back(); }
+    cudaEventRecord(e, s);
+    marks.emplace_back(name, e);
+  }
+};
+
+namespace {
+
+std::string rename(std::string s, char from, char to) {
+  for (char& c : s)
+    if (c == from) c = to;
+  return s;
+}
+
+struct Ptrs {
+  std::map<std::string, void*> p;
+  void* operator[](const char* n) const { return p.at(n); }
+};
+
+int einsum(sb_encoder* e, cudaStream_t s, const char* name, const std::string& ad, const void* a,
+           const std::string& bd, const void* b, const std::string& cd, void* c, float alpha) {
+  e->mark(s, name);
+  const sb_tensor ta = e->mem(a, ad), tb = e->mem(b, bd), tc = e->mem(c, cd);
+  GemmProblem g;
+  SB_TRY(plan_einsum(ad.c_str(), &ta, bd.c_str(), &tb, cd.c_str(), &tc, alpha, &g));
+  return run_gemm(s, g, SB_GEMM_AUTO);
+}
+
+}  // namespace
+
+extern "C" int sb_encoder_create(const sb_encoder_config* cfg, sb_encoder** out) {
+  if (!cfg || !out) return fail(SB_ERR_ARG, "sb_encoder_create: null argument");
+  *out = nullptr;
+  if (cfg->batch <= 0 || cfg->seq <= 0 || cfg->heads <= 0 || cfg->embed <= 0)
+    return fail(SB_ERR_ARG, "sb_encoder_create: sizes must be positive");
+  if (cfg->embed % cfg->heads != 0)
+    return fail(SB_ERR_ARG, "sb_encoder_create: embedding size must be a multiple of the head count");
+  SB_TRY(check_activation(cfg->activation));
+  for (float p : {cfg->p_softmax, cfg->p_resid1, cfg->p_activation, cfg->p_resid2})
+    if (!(p >= 0.f && p < 1.f)) return fail(SB_ERR_ARG, "sb_encoder_create: dropout probabilities must be in [0,1)");
+  if (cfg->n_tensors <= 0 || !cfg->names || !cfg->dims) return fail(SB_ERR_ARG, "sb_encoder_create: no layouts given");
+
+  std::unique_ptr<sb_encoder> e(new sb_encoder);
+  e->B = cfg->batch; e->S = cfg->seq; e->H = cfg->heads; e->I = cfg->embed;
+  e->P = cfg->embed / cfg->heads; e->U = 4 * cfg->embed;
+  e->activation = cfg->activation;
+  e->p_softmax = cfg->p_softmax; e->p_resid1 = cfg->p_resid1;
+  e->p_act = cfg->p_activation; e->p_resid2 = cfg->p_resid2;
+  const auto& logical = logical_dims();
+  auto in_list = [](const char* const* list, int n, const std::string& name) {
+    for (int i = 0; i < n; ++i)
+      if (name == list[i]) return true;
+    return false;
+  };
+  for (int i = 0; i < cfg->n_tensors; ++i) {
+    if (!cfg->names[i] || !cfg->dims[i]) return fail(SB_ERR_ARG, "sb_encoder_create: null layout entry");
+    const std::string name = cfg->names[i], dims = cfg->dims[i];
+    auto it = logical.find(name);
+    if (it == logical.end()) return fail(SB_ERR_LAYOUT, "sb_encoder_create: unknown tensor '" + name + "'");
+    if (!is_permutation(dims, it->second))
+      return fail(SB_ERR_LAYOUT, "sb_encoder_create: layout '" + dims + "' of " + name +
+                                     " is not a permutation of its dims '" + it->second + "'");
+    if (e->layout.count(name)) return fail(SB_ERR_LAYOUT, "sb_encoder_create: tensor '" + name + "' listed twice");
+    e->layout[name] = dims;
+    if (in_list(kParamNames, SB_NUM_PARAMS, name)) e->param_order.push_back(name);
+    else if (in_list(kFwdNames, SB_NUM_FWD_INTERM, name)) e->fwd_order.push_back(name);
+    else if (in_list(kBwdNames, SB_NUM_BWD_INTERM, name)) e->bwd_order.push_back(name);
+  }
+  for (const auto& kv : logical)
+    if (!e->layout.count(kv.first)) return fail(SB_ERR_LAYOUT, "sb_encoder_create: no layout given for '" + kv.first + "'");
+  // Stacked tensors are sliced by pointer offset, so the stacking dim must be outermost.
+  for (const char* n : {"KKQQVV", "DKKQQVV", "WKKWQQWVV", "BKQV", "WKQV"})
+    if (e->layout[n][0] != 'Q')
+      return fail(SB_ERR_LAYOUT, std::string("sb_encoder_create: stacked tensor ") + n + " must have Q outermost");
+  if (e->layout["X"] != e->layout["SB2"])
+    return fail(SB_ERR_LAYOUT, "sb_encoder_create: input and output layouts must be equal so that layers chain");
+  SB_CUDA_OK(cudaGetDevice(&e->device));
+  SB_CUDA_OK(cudaMalloc(&e->workspace, kWsBytes));
+  SB_CUDA_OK(cudaMemset(e->workspace, 0, kWsBytes));
+  *out = e.release();
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_destroy(sb_encoder* e) {
+  if (!e) return SB_OK;
+  for (auto& m : e->marks) cudaEventDestroy(m.second);
+  for (auto ev : e->event_pool) cudaEventDestroy(ev);
+  if (e->workspace) cudaFree(e->workspace);
+  delete e;
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_set_timing(sb_encoder* e, int enabled) {
+  if (!e) return fail(SB_ERR_ARG, "null handle");
+  e->timing = enabled != 0;
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_launch_count(sb_encoder* e) { return e ? e->launches : 0; }
+
+extern "C" int sb_encoder_get_timing(sb_encoder* e, int max, const char** names, float* ms) {
+  if (!e) return 0;
+  if (!e->marks.empty()) {
+    // marks: begin-of-op events plus one closing event named "" per pass
+    cudaEventSynchronize(e->marks.back().second);
+    e->last_times.clear();
+    for (size_t i = 0; i + 1 < e->marks.size(); ++i) {
+      if (e->marks[i].first.empty()) continue;
+      float t = 0.f;
+      cudaEventElapsedTime(&t, e->marks[i].second, e->marks[i + 1].second);
+      e->last_times.emplace_back(e->marks[i].first, t);
+    }
+    for (auto& m : e->marks) e->event_pool.push_back(m.second);
+    e->marks.clear();
+  }
+  int n = 0;
+  for (auto& kv : e->last_times) {
+    if (n >= max) break;
+    names[n] = kv.first.c_str();
+    ms[n] = kv.second;
+    ++n;
+  }
+  return n;
+}
+
+namespace {
+
+int gather(sb_encoder* e, const void* x, const void* const* params, void* const* fwd, Ptrs* P) {
+  if (!x || !params || !fwd) return fail(SB_ERR_ARG, "encoder: null pointer table");
+  P->p["X"] = const_cast<void*>(x);
+  for (size_t i = 0; i < e->param_order.size(); ++i) {
+    if (!params[i]) return fail(SB_ERR_ARG, "encoder: null parameter pointer (" + e->param_order[i] + ")");
+    P->p[e->param_order[i]] = const_cast<void*>(params[i]);
+  }
+  for (size_t i = 0; i < e->fwd_order.size(); ++i) {
+    if (!fwd[i]) return fail(SB_ERR_ARG, "encoder: null forward-intermediate pointer (" + e->fwd_order[i] + ")");
+    P->p[e->fwd_order[i]] = fwd[i];
+  }
+  return SB_OK;
+}
+
+sb_dropout drop(float p, int mode, uint64_t seed, uint64_t offset) {
+  sb_dropout d;
+  d.p = p; d.mode = mode; d.seed = seed; d.offset = offset;
+  return d;
+}
+
+}  // namespace
+
+extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, const void* const* params,
+                                  void* const* fwd, void* y, int mask_mode, uint64_t seed, uint64_t offset) {
+  if (!e || !y) return fail(SB_ERR_ARG, "sb_encoder_forward: null argument");
+  if (mask_mode != SB_MASK_EXPLICIT && mask_mode != SB_MASK_PHILOX)
+    return fail(SB_ERR_ARG, "sb_encoder_forward: unknown mask mode");
+  cudaStream_t s = (cudaStream_t)stream;
+  Ptrs T;
+  SB_TRY(gather(e, x, params, fwd, &T));
+  T.p["SB2"] = y;
+  e->launches = 0;
+  const auto& L = e->layout;
+  const long long slice = (long long)e->P * e->H * e->B * e->S;  // elements per stacked projection
+  auto q_slice = [&](const char* name, int q) { return (void*)((__half*)T[name] + q * slice); };
+  const std::string lKK = L.at("KKQQVV").substr(1);
+
+  // F1: stacked K,Q,V projections
+  SB_TRY(einsum(e, s, "QKV-fused", L.at("X"), T["X"], L.at("WKQV"), T["WKQV"], L.at("WKKWQQWVV"),
+                T["WKKWQQWVV"], 1.f));
+  {
+    e->mark(s, "aib");
+    sb_tensor in = e->view(T["WKKWQQWVV"], "WKKWQQWVV"), out = e->view(T["KKQQVV"], "KKQQVV");
+    sb_tensor bias = e->view(T["BKQV"], "BKQV");
+    SB_TRY(sb_attention_input_biases(stream, &in, &bias, &out));
+  }
+  // F2: scaled scores.  K and V views are the J-indexed projections relabelled with K.
+  SB_TRY(einsum(e, s, "QKT", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 0), lKK, q_slice("KKQQVV", 1),
+                L.at("BETA"), T["BETA"], 1.f / std::sqrt((float)e->P)));
+  {
+    e->mark(s, "softmax");
+    sb_tensor beta = e->view(T["BETA"], "BETA"), alpha = e->view(T["ALPHA"], "ALPHA");
+    sb_tensor mask = e->view(T["ATTN_DROP_MASK"], "ATTN_DROP_MASK"), dr = e->view(T["ATTN_DROP"], "ATTN_DROP");
+    sb_dropout d = drop(e->p_softmax, mask_mode, seed, offset + 0);
+    SB_TRY(sb_softmax_dropout(stream, &beta, &alpha, &mask, &dr, 1.f, &d));
+  }
+  SB_TRY(einsum(e, s, "gamma", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 2), L.at("ATTN_DROP"), T["ATTN_DROP"],
+                L.at("GAMMA"), T["GAMMA"], 1.f));
+  SB_TRY(einsum(e, s, "out", L.at("WO"), T["WO"], L.at("GAMMA"), T["GAMMA"], L.at("ATT"), T["ATT"], 1.f));
+  {
+    e->mark(s, "bdrln1");
+    sb_tensor in = e->view(T["ATT"], "ATT"), resid = e->view(T["X"], "X");
+    sb_tensor bias = e->view(T["BO"], "BO"), gamma = e->view(T["S1"], "S1"), beta = e->view(T["B1"], "B1");
+    sb_tensor mask = e->view(T["DROP1MASK"], "DROP1MASK"), diff = e->view(T["LN1DIFF"], "LN1DIFF");
+    sb_tensor istd = e->view(T["LN1STD"], "LN1STD"), ln = e->view(T["LN1"], "LN1"), out = e->view(T["SB1"], "SB1");
+    sb_dropout d = drop(e->p_resid1, mask_mode, seed, offset + 1);
+    // the biased projection is written back over ATT
+    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask, &in, &diff,
+                                              &istd, &ln, &out, &d));
+  }
+  SB_TRY(einsum(e, s, "lin1", L.at("SB1"), T["SB1"], L.at("LINW1"), T["LINW1"], L.at("SB1_LINW1"),
+                T["SB1_LINW1"], 1.f));
+  {
+    e->mark(s, "bad");
+    sb_tensor in = e->view(T["SB1_LINW1"], "SB1_LINW1"), bias = e->view(T["LINB1"], "LINB1");
+    sb_tensor mask = e->view(T["DROP2MASK"], "DROP2MASK"), lin1 = e->view(T["LIN1"], "LIN1");
+    sb_tensor d2 = e->view(T["DROP2"], "DROP2");
+    sb_dropout d = drop(e->p_act, mask_mode, seed, offset + 2);
+    SB_TRY(sb_bias_activation_dropout(stream, &in, &bias, &mask, &lin1, &d2, e->activation, &d));
+  }
+  SB_TRY(einsum(e, s, "lin2", L.at("DROP2"), T["DROP2"], L.at("LINW2"), T["LINW2"], L.at("DROP2_LINW2"),
+                T["DROP2_LINW2"], 1.f));
+  {
+    e->mark(s, "bdrln2");
+    sb_tensor in = e->view(T["DROP2_LINW2"], "DROP2_LINW2"), resid = e->view(T["SB1"], "SB1");
+    sb_tensor bias = e->view(T["LINB2"], "LINB2"), gamma = e->view(T["S2"], "S2"), beta = e->view(T["B2"], "B2");
+    sb_tensor mask = e->view(T["DROP3MASK"], "DROP3MASK"), lin = e->view(T["LIN2"], "LIN2");
+    sb_tensor diff = e->view(T["LN2DIFF"], "LN2DIFF"), istd = e->view(T["LN2STD"], "LN2STD");
+    sb_tensor ln = e->view(T["LN2"], "LN2"), out = e->view(T["SB2"], "SB2");
+    sb_dropout d = drop(e->p_resid2, mask_mode, seed, offset + 3);
+    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask, &lin, &diff,
+                                              &istd, &ln, &out, &d));
+  }
+  if (e->timing) { e->mark(s, ""); --e->launches; }
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, void* const* dparams,
+                                   void* const* bwd, const void* const* params, void* const* fwd,
+                                   const void* x, void* dx) {
+  if (!e || !dy || !dparams || !bwd || !dx) return fail(SB_ERR_ARG, "sb_encoder_backward: null argument");
+  cudaStream_t s = (cudaStream_t)stream;
+  Ptrs T;
+  SB_TRY(gather(e, x, params, fwd, &T));
+  for (size_t i = 0; i < e->bwd_order.size(); ++i) {
+    if (!bwd[i]) return fail(SB_ERR_ARG, "encoder: null backward-intermediate pointer (" + e->bwd_order[i] + ")");
+    T.p[e->bwd_order[i]] = bwd[i];
+  }
+  std::map<std::string, void*> D;  // parameter gradients
+  for (size_t i = 0; i < e->param_order.size(); ++i) {
+    if (!dparams[i]) return fail(SB_ERR_ARG, "encoder: null gradient pointer (" + e->param_order[i] + ")");
+    D[e->param_order[i]] = dparams[i];
+  }
+  e->launches = 0;
+  const auto& L = e->layout;
+  const long long slice = (long long)e->P * e->H * e->B * e->S;
+  auto q_slice = [&](void* base, int q) { return (void*)((__half*)base + q * slice); };
+  const std::string lKK = L.at("KKQQVV").substr(1), lDKK = L.at("DKKQQVV").substr(1);
+  void* ws = e->workspace;
+  auto v = [&](const char* name) { return e->view(T[name], name); };
+  auto pv = [&](const char* name) { return e->view(T[name], name); };
+  auto dv = [&](const char* name) { return e->view(D.at(name), L.at(name), logical_dims().at(name)); };
+  const sb_tensor tDY = e->view(dy, L.at("SB2"), "BJI");
+  const sb_tensor tDX = e->view(dx, L.at("X"), "BJI");
+
+  {
+    e->mark(s, "bsb");
+    sb_tensor ln = v("LN2"), gamma = pv("S2"), dln = v("DLN2"), dg = dv("S2"), db = dv("B2");
+    SB_TRY(sb_backward_scale_bias(stream, ws, &tDY, &ln, &gamma, &dln, &dg, &db));
+  }
+  {
+    e->mark(s, "blnrd1");
+    sb_tensor dln = v("DLN2"), istd = v("LN2STD"), diff = v("LN2DIFF"), mask = v("DROP3MASK");
+    sb_tensor dres = v("DRESID2"), dlin = v("DLIN2");
+    SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln, &istd, &diff, &mask, &dres, &dlin));
+  }
+  SB_TRY(einsum(e, s, "dXlin2", L.at("DLIN2"), T["DLIN2"], L.at("LINW2"), T["LINW2"], L.at("DDROP2"),
+                T["DDROP2"], 1.f));
+  SB_TRY(einsum(e, s, "dWlin2", L.at("DLIN2"), T["DLIN2"], L.at("DROP2"), T["DROP2"], L.at("LINW2"),
+                D.at("LINW2"), 1.f));
+  {
+    e->mark(s, "bdrlb");
+    sb_tensor g = v("DDROP2"), mask = v("DROP2MASK"), lin1 = v("LIN1"), o = v("DLIN1"), db = dv("LINB1");
+    SB_TRY(sb_backward_dropout_activation_bias(stream, ws, &g, &mask, &lin1, &o, &db, e->activation));
+  }
+  SB_TRY(einsum(e, s, "dXlin1", L.at("DLIN1"), T["DLIN1"], L.at("LINW1"), T["LINW1"], L.at("DLIN1_LINW1"),
+                T["DLIN1_LINW1"], 1.f));
+  SB_TRY(einsum(e, s, "dWlin1", L.at("DLIN1"), T["DLIN1"], L.at("SB1"), T["SB1"], L.at("LINW1"),
+                D.at("LINW1"), 1.f));
+  {
+    e->mark(s, "ebsb");
+    sb_tensor ln1 = v("LN1"), gamma = pv("S1"), dres2 = v("DRESID2"), dlw = v("DLIN1_LINW1"), dlin2 = v("DLIN2");
+    sb_tensor dln1 = v("DLN1"), dg = dv("S1"), db = dv("B1"), dlb2 = dv("LINB2");
+    SB_TRY(sb_extended_backward_scale_bias(stream, ws, &ln1, &gamma, &dres2, &dlw, &dlin2, &dln1, &dg, &db, &dlb2));
+  }
+  {
+    e->mark(s, "blnrd2");
+    sb_tensor dln = v("DLN1"), istd = v("LN1STD"), diff = v("LN1DIFF"), mask = v("DROP1MASK");
+    sb_tensor dres = v("DRESID1"), datt = v("DATT");
+    SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln, &istd, &diff, &mask, &dres, &datt));
+  }
+  {
+    e->mark(s, "baob");
+    sb_tensor datt = v("DATT"), dbo = dv("BO");
+    SB_TRY(sb_backward_attn_out_bias(stream, ws, &datt, &dbo));
+  }
+  SB_TRY(einsum(e, s, "dWout", L.at("GAMMA"), T["GAMMA"], L.at("DATT"), T["DATT"], L.at("WO"), D.at("WO"), 1.f));
+  SB_TRY(einsum(e, s, "dXout", L.at("WO"), T["WO"], L.at("DATT"), T["DATT"], L.at("DGAMMA"), T["DGAMMA"], 1.f));
+  const float scale = 1.f / std::sqrt((float)e->P);
+  void *KK = q_slice(T["KKQQVV"], 0), *QQ = q_slice(T["KKQQVV"], 1), *VV = q_slice(T["KKQQVV"], 2);
+  void *DKK = q_slice(T["DKKQQVV"], 0), *DQQ = q_slice(T["DKKQQVV"], 1), *DVV = q_slice(T["DKKQQVV"], 2);
+  SB_TRY(einsum(e, s, "dX1gamma", rename(lKK, 'J', 'K'), VV, L.at("DGAMMA"), T["DGAMMA"], L.at("DATTN_DROP"),
+                T["DATTN_DROP"], 1.f));
+  SB_TRY(einsum(e, s, "dX2gamma", L.at("DGAMMA"), T["DGAMMA"], L.at("ATTN_DROP"), T["ATTN_DROP"],
+                rename(lDKK, 'J', 'K'), DVV, 1.f));
+  {
+    e->mark(s, "bs");
+    sb_tensor alpha = v("ALPHA"), mask = v("ATTN_DROP_MASK"), g = v("DATTN_DROP"), o = v("DBETA");
+    SB_TRY(sb_backward_softmax(stream, &alpha, &mask, &g, &o));
+  }
+  SB_TRY(einsum(e, s, "dX1QKT", rename(lKK, 'J', 'K'), KK, L.at("DBETA"), T["DBETA"], lDKK, DQQ, scale));
+  SB_TRY(einsum(e, s, "dX2QKT", lKK, QQ, L.at("DBETA"), T["DBETA"], rename(lDKK, 'J', 'K'), DKK, scale));
+  SB_TRY(einsum(e, s, "dXQKV-fused", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
+                T["DXATT"], 1.f));
+  SB_TRY(einsum(e, s, "dWQKV-fused", L.at("X"), T["X"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("WKQV"),
+                D.at("WKQV"), 1.f));
+  {
+    e->mark(s, "baib");
+    sb_tensor d = v("DKKQQVV"), db = dv("BKQV");
+    SB_TRY(sb_backward_attention_input_biases(stream, &d, &db));
+  }
+  {
+    e->mark(s, "bei");
+    sb_tensor a = v("DXATT"), b = v("DRESID1");
+    SB_TRY(sb_backward_encoder_input(stream, &a, &b, &tDX));
+  }
+  if (e->timing) { e->mark(s, ""); --e->launches; }
+  return SB_OK;
+}

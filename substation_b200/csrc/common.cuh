@@ -1,0 +1,202 @@
+// Shared device/host helpers for the fused operators: strided tensor views,
+// 128-bit vector access with a scalar fallback, warp reductions and the
+// counter-based dropout generator.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/substation_b200.h"
+
+namespace sb {
+
+// ---------------------------------------------------------------------------
+// Error plumbing (host)
+// ---------------------------------------------------------------------------
+void set_error(const std::string& msg);
+int fail(int status, const std::string& msg);
+
+#define SB_CUDA_OK(expr)                                                                  \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess)                                                                \
+      return ::sb::fail(SB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+  } while (0)
+
+#define SB_TRY(expr)             \
+  do {                           \
+    int _s = (expr);             \
+    if (_s != SB_OK) return _s;  \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// Views.  "vec" means: innermost logical dim has unit stride, its extent is a
+// multiple of 8, every other stride is a multiple of 8 elements and the base
+// is 16-byte aligned (8-byte for uint8 masks), so each aligned group of eight
+// elements along that dim is one 128-bit (64-bit) access.
+// ---------------------------------------------------------------------------
+struct View3 {  // [B, J, F]
+  void* p;
+  long long sB, sJ, sF;
+  int vec;
+};
+struct View2 {  // [B, J]
+  void* p;
+  long long sB, sJ;
+};
+struct View4 {  // [H, B, J, K]
+  void* p;
+  long long sH, sB, sJ, sK;
+  int vec;
+};
+struct View5 {  // [N, P, H, B, J]
+  void* p;
+  long long sN, sP, sH, sB, sJ;
+  int vec;
+};
+
+struct Rng {
+  uint32_t seed_lo, seed_hi, off_lo, off_hi;
+  uint32_t thr;  // drop when 16 random bits < thr
+  int philox;    // 0: masks are inputs; 1: masks are generated and written
+};
+
+#ifdef __CUDACC__
+
+constexpr int kWarp = 32;
+constexpr float kLnEps = 1e-5f;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <int LANES>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <int LANES>
+__device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- 8-element accessors -------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float v[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float v[8]) {
+  uint4 u;
+  __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
+// Load eight fp16 values base[(f..f+7)*sF] as float; elements at or beyond F read as `fill`.
+__device__ __forceinline__ void load8h(const void* base, long long off, long long sF, int vec,
+                                       int f, int F, float v[8], float fill = 0.f) {
+  const __half* p = reinterpret_cast<const __half*>(base) + off;
+  if (vec) {
+    uint4 u = *reinterpret_cast<const uint4*>(p + f);
+    unpack8(u, v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (f + e < F) ? __half2float(p[(long long)(f + e) * sF]) : fill;
+  }
+}
+__device__ __forceinline__ void store8h(void* base, long long off, long long sF, int vec, int f,
+                                        int F, const float v[8]) {
+  __half* p = reinterpret_cast<__half*>(base) + off;
+  if (vec) {
+    *reinterpret_cast<uint4*>(p + f) = pack8(v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f + e < F) p[(long long)(f + e) * sF] = __float2half_rn(v[e]);
+  }
+}
+__device__ __forceinline__ void load8m(const void* base, long long off, long long sF, int vec,
+                                       int f, int F, uint32_t m[8]) {
+  const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + off;
+  if (vec) {
+    uint2 u = *reinterpret_cast<const uint2*>(p + f);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      m[e] = (u.x >> (8 * e)) & 0xffu;
+      m[4 + e] = (u.y >> (8 * e)) & 0xffu;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m[e] = (f + e < F) ? p[(long long)(f + e) * sF] : 0u;
+  }
+}
+__device__ __forceinline__ void store8m(void* base, long long off, long long sF, int vec, int f,
+                                        int F, const uint32_t m[8]) {
+  uint8_t* p = reinterpret_cast<uint8_t*>(base) + off;
+  if (vec) {
+    uint2 u;
+    u.x = m[0] | (m[1] << 8) | (m[2] << 16) | (m[3] << 24);
+    u.y = m[4] | (m[5] << 8) | (m[6] << 16) | (m[7] << 24);
+    *reinterpret_cast<uint2*>(p + f) = u;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f + e < F) p[(long long)(f + e) * sF] = (uint8_t)m[e];
+  }
+}
+// Contiguous per-feature vectors (bias, gamma, beta): [F], unit stride.
+__device__ __forceinline__ void load8p(const void* base, int f, int F, int vec, float v[8]) {
+  load8h(base, 0, 1, vec, f, F, v, 0.f);
+}
+
+// ---- Philox4x32-10 ---------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c;
+}
+// Keep flags (0/1) of the eight elements of logical group g (= linear index >> 3).
+__device__ __forceinline__ void philox_keep8(const Rng& r, unsigned long long g, uint32_t m[8]) {
+  uint4 w = philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), r.off_lo, r.off_hi),
+                          r.seed_lo, r.seed_hi);
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int t = 0; t < 8; ++t) m[t] = (((ww[t >> 1] >> (16 * (t & 1))) & 0xffffu) >= r.thr) ? 1u : 0u;
+}
+// Keep flags for eight consecutive logical indices e0..e0+7 that need not be group aligned.
+__device__ __forceinline__ void philox_keep8_unaligned(const Rng& r, unsigned long long e0,
+                                                       uint32_t m[8]) {
+  if ((e0 & 7ull) == 0) {
+    philox_keep8(r, e0 >> 3, m);
+    return;
+  }
+  uint32_t a[8], b[8];
+  philox_keep8(r, e0 >> 3, a);
+  philox_keep8(r, (e0 >> 3) + 1, b);
+  const int s = (int)(e0 & 7ull);
+#pragma unroll
+  for (int t = 0; t < 8; ++t) m[t] = (t + s < 8) ? a[(t + s) & 7] : b[(t + s) & 7];
+}
+
+#endif  // __CUDACC__
+
+}  // namespace sb

@@ -1,0 +1,767 @@
+// Memory-bound fused operators of the encoder layer, written for sm_100a.
+//
+// Common structure: a warp owns one row (token, or attention row) at a time and
+// its lanes walk the row's innermost logical dim in 128-bit groups, so a row is
+// read once into registers, reduced with warp shuffles and written once.  Every
+// tensor is addressed through its own strides; a tensor whose innermost dim is
+// not contiguous falls back to scalar accesses inside the same kernel.
+// Reductions over tokens (parameter gradients) use per-CTA fp32 partial sums in
+// a workspace and a ticket counter: the last CTA of a feature slice adds the
+// partials in a fixed order, so results are deterministic and need one launch.
+
+#include <math.h>
+
+#include "ops.h"
+
+namespace sb {
+
+namespace {
+
+constexpr int kRowThreads = 128;  // 4 warps per CTA for the row kernels
+constexpr int kColThreads = 256;  // 8 warps per CTA for the token-reduction kernels
+
+__device__ __forceinline__ float act_fwd(float x, int activation) {
+  if (activation == SB_ACT_RELU) return fmaxf(x, 0.f);
+  // tanh-form GELU
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float act_bwd(float x, float dy, int activation) {
+  if (activation == SB_ACT_RELU) return x > 0.f ? dy : 0.f;
+  const float x3 = x * x * x;
+  const float inner = 0.0356774f * x3 + 0.797885f * x;
+  const float th = tanhf(inner);
+  const float sech2 = 1.f - th * th;
+  return (0.5f * th + (0.0535161f * x3 + 0.398942f * x) * sech2 + 0.5f) * dy;
+}
+
+// ---------------------------------------------------------------------------
+// Softmax (+scale, +dropout) forward and backward over [H,B,J,K]
+// LPR lanes cooperate on one row, each holding NV groups of eight elements.
+// ---------------------------------------------------------------------------
+template <int LPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, float scale, Rng rng) {
+  constexpr int RPW = kWarp / LPR;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPR, sl = lane % LPR;
+  const long long R = (long long)d.H * d.B * d.J;
+  long long row = ((long long)blockIdx.x * (kRowThreads / kWarp) + warp) * RPW + sub;
+  const bool valid = row < R;
+  if (!valid) row = R - 1;
+  const int j = (int)(row % d.J);
+  const long long hb = row / d.J;
+  const int b = (int)(hb % d.B), h = (int)(hb / d.B);
+  const long long o_beta = h * beta.sH + b * beta.sB + j * beta.sJ;
+  const long long o_alpha = h * alpha.sH + b * alpha.sB + j * alpha.sJ;
+  const long long o_mask = h * mask.sH + b * mask.sB + j * mask.sJ;
+  const long long o_drop = h * drop.sH + b * drop.sB + j * drop.sJ;
+
+  float x[NV][8];
+  uint32_t m[NV][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (sl + LPR * i) * 8;
+    if (k < d.K) {
+      load8h(beta.p, o_beta, beta.sK, beta.vec, k, d.K, x[i]);
+      if (!rng.philox) load8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (sl + LPR * i) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[i][e] = (k + e < d.K) ? x[i][e] * scale : -INFINITY;
+      mx = fmaxf(mx, x[i][e]);
+    }
+  }
+  mx = group_max<LPR>(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[i][e] = __expf(x[i][e] - mx);
+      sum += x[i][e];
+    }
+  sum = group_sum<LPR>(sum);
+  const float inv = 1.f / sum;
+  if (!valid) return;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (sl + LPR * i) * 8;
+    if (k >= d.K) continue;
+    float a[8], dr[8];
+    if (rng.philox) {
+      philox_keep8_unaligned(rng, (unsigned long long)row * d.K + k, m[i]);
+      store8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      a[e] = x[i][e] * inv;
+      dr[e] = m[i][e] ? a[e] : 0.f;
+    }
+    store8h(alpha.p, o_alpha, alpha.sK, alpha.vec, k, d.K, a);
+    store8h(drop.p, o_drop, drop.sK, drop.vec, k, d.K, dr);
+  }
+}
+
+template <int LPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta) {
+  constexpr int RPW = kWarp / LPR;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPR, sl = lane % LPR;
+  const long long R = (long long)d.H * d.B * d.J;
+  long long row = ((long long)blockIdx.x * (kRowThreads / kWarp) + warp) * RPW + sub;
+  const bool valid = row < R;
+  if (!valid) row = R - 1;
+  const int j = (int)(row % d.J);
+  const long long hb = row / d.J;
+  const int b = (int)(hb % d.B), h = (int)(hb / d.B);
+  const long long o_alpha = h * alpha.sH + b * alpha.sB + j * alpha.sJ;
+  const long long o_mask = h * mask.sH + b * mask.sB + j * mask.sJ;
+  const long long o_dad = h * dad.sH + b * dad.sB + j * dad.sJ;
+  const long long o_dbeta = h * dbeta.sH + b * dbeta.sB + j * dbeta.sJ;
+
+  float a[NV][8], g[NV][8];
+  uint32_t m[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (sl + LPR * i) * 8;
+    if (k < d.K) {
+      load8h(alpha.p, o_alpha, alpha.sK, alpha.vec, k, d.K, a[i]);
+      load8h(dad.p, o_dad, dad.sK, dad.vec, k, d.K, g[i]);
+      load8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[i][e] = 0.f; g[i][e] = 0.f; m[i][e] = 0u; }
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      g[i][e] = m[i][e] ? g[i][e] : 0.f;
+      s += g[i][e] * a[i][e];
+    }
+  s = group_sum<LPR>(s);
+  if (!valid) return;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (sl + LPR * i) * 8;
+    if (k >= d.K) continue;
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = a[i][e] * (g[i][e] - s);
+    store8h(dbeta.p, o_dbeta, dbeta.sK, dbeta.vec, k, d.K, o);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// bias + dropout + residual + LayerNorm over [B,J,F]; one warp per token.
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads)
+bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma, const void* beta,
+             View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng, int pvec) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long R = (long long)d.B * d.J;
+  const long long row = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
+  if (row >= R) return;
+  const int b = (int)(row / d.J), j = (int)(row % d.J);
+  const long long o_in = b * in.sB + j * in.sJ, o_res = b * resid.sB + j * resid.sJ;
+  const long long o_mask = b * mask.sB + j * mask.sJ, o_lin = b * lin.sB + j * lin.sJ;
+
+  float r[NV][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int f = (lane + kWarp * i) * 8;
+    if (f < d.F) {
+      float x[8], rs[8], bs[8];
+      uint32_t m[8];
+      load8h(in.p, o_in, in.sF, in.vec, f, d.F, x);
+      load8h(resid.p, o_res, resid.sF, resid.vec, f, d.F, rs);
+      load8p(bias, f, d.F, pvec, bs);
+      if (rng.philox) {
+        philox_keep8_unaligned(rng, (unsigned long long)row * d.F + f, m);
+        store8m(mask.p, o_mask, mask.sF, mask.vec, f, d.F, m);
+      } else {
+        load8m(mask.p, o_mask, mask.sF, mask.vec, f, d.F, m);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] += bs[e];
+      store8h(lin.p, o_lin, lin.sF, lin.vec, f, d.F, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        r[i][e] = (f + e < d.F) ? (m[e] ? x[e] : 0.f) + rs[e] : 0.f;
+        sum += r[i][e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[i][e] = 0.f;
+    }
+  }
+  const float mean = warp_sum(sum) / (float)d.F;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int f = (lane + kWarp * i) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      r[i][e] = (f + e < d.F) ? r[i][e] - mean : 0.f;
+      sq += r[i][e] * r[i][e];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / (float)d.F + kLnEps);
+  if (lane == 0) reinterpret_cast<__half*>(istd.p)[b * istd.sB + j * istd.sJ] = __float2half_rn(rstd);
+  const long long o_diff = b * diff.sB + j * diff.sJ, o_ln = b * ln.sB + j * ln.sJ;
+  const long long o_out = b * out.sB + j * out.sJ;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int f = (lane + kWarp * i) * 8;
+    if (f >= d.F) continue;
+    float gm[8], bt[8], n[8], o[8];
+    load8p(gamma, f, d.F, pvec, gm);
+    load8p(beta, f, d.F, pvec, bt);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      n[e] = r[i][e] * rstd;
+      o[e] = n[e] * gm[e] + bt[e];
+    }
+    store8h(diff.p, o_diff, diff.sF, diff.vec, f, d.F, r[i]);
+    store8h(ln.p, o_ln, ln.sF, ln.vec, f, d.F, n);
+    store8h(out.p, o_out, out.sF, out.vec, f, d.F, o);
+  }
+}
+
+// LayerNorm backward-data + dropout backward; one warp per token.
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads)
+blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresid, View3 dlin) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long R = (long long)d.B * d.J;
+  const long long row = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
+  if (row >= R) return;
+  const int b = (int)(row / d.J), j = (int)(row % d.J);
+  const long long o_g = b * dln.sB + j * dln.sJ, o_d = b * diff.sB + j * diff.sJ;
+  const long long o_m = b * mask.sB + j * mask.sJ;
+  float g[NV][8], df[NV][8];
+  uint32_t m[NV][8];
+  float sg = 0.f, sgd = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int f = (lane + kWarp * i) * 8;
+    if (f < d.F) {
+      load8h(dln.p, o_g, dln.sF, dln.vec, f, d.F, g[i]);
+      load8h(diff.p, o_d, diff.sF, diff.vec, f, d.F, df[i]);
+      load8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { g[i][e] = 0.f; df[i][e] = 0.f; m[i][e] = 0u; }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      sg += g[i][e];
+      sgd += g[i][e] * df[i][e];
+    }
+  sg = warp_sum(sg);
+  sgd = warp_sum(sgd);
+  const float s = __half2float(reinterpret_cast<const __half*>(istd.p)[b * istd.sB + j * istd.sJ]);
+  const float invn = 1.f / (float)d.F;
+  const float c1 = sg * s * invn, c2 = sgd * s * s * s * invn;
+  const long long o_r = b * dresid.sB + j * dresid.sJ, o_l = b * dlin.sB + j * dlin.sJ;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int f = (lane + kWarp * i) * 8;
+    if (f >= d.F) continue;
+    float dr[8], dl[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dr[e] = g[i][e] * s - c1 - df[i][e] * c2;
+      dl[e] = m[i][e] ? dr[e] : 0.f;
+    }
+    store8h(dresid.p, o_r, dresid.sF, dresid.vec, f, d.F, dr);
+    store8h(dlin.p, o_l, dlin.sF, dlin.vec, f, d.F, dl);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Elementwise kernels over [B,J,F]: a warp takes one token and a span of
+// 4 * 256 features.
+// ---------------------------------------------------------------------------
+constexpr int kEwNV = 4;
+
+__global__ void __launch_bounds__(kRowThreads)
+bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin1, View3 drop2,
+           int activation, Rng rng, int pvec) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long R = (long long)d.B * d.J;
+  const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
+  if (item >= R * spans) return;
+  const long long row = item / spans;
+  const int span = (int)(item % spans);
+  const int b = (int)(row / d.J), j = (int)(row % d.J);
+  const long long o_in = b * in.sB + j * in.sJ, o_m = b * mask.sB + j * mask.sJ;
+  const long long o_l = b * lin1.sB + j * lin1.sJ, o_d = b * drop2.sB + j * drop2.sJ;
+  float x[kEwNV][8];
+  uint32_t m[kEwNV][8];
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f < d.F) {
+      load8h(in.p, o_in, in.sF, in.vec, f, d.F, x[i]);
+      if (!rng.philox) load8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f >= d.F) continue;
+    float bs[8], o[8];
+    load8p(bias, f, d.F, pvec, bs);
+    if (rng.philox) {
+      philox_keep8_unaligned(rng, (unsigned long long)row * d.F + f, m[i]);
+      store8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[i][e] += bs[e];
+      o[e] = m[i][e] ? act_fwd(x[i][e], activation) : 0.f;
+    }
+    store8h(lin1.p, o_l, lin1.sF, lin1.vec, f, d.F, x[i]);
+    store8h(drop2.p, o_d, drop2.sF, drop2.vec, f, d.F, o);
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+bei_kernel(Dims3 d, int spans, View3 a, View3 b_, View3 out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long R = (long long)d.B * d.J;
+  const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
+  if (item >= R * spans) return;
+  const long long row = item / spans;
+  const int span = (int)(item % spans);
+  const int b = (int)(row / d.J), j = (int)(row % d.J);
+  const long long o_a = b * a.sB + j * a.sJ, o_b = b * b_.sB + j * b_.sJ;
+  const long long o_o = b * out.sB + j * out.sJ;
+  float x[kEwNV][8], y[kEwNV][8];
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f < d.F) {
+      load8h(a.p, o_a, a.sF, a.vec, f, d.F, x[i]);
+      load8h(b_.p, o_b, b_.sF, b_.vec, f, d.F, y[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f >= d.F) continue;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[i][e] += y[i][e];
+    store8h(out.p, o_o, out.sF, out.vec, f, d.F, x[i]);
+  }
+}
+
+// out[n,p,h,b,j] = in[n,p,h,b,j] + bias[n,p,h]; a warp takes one (n,p,h,b) row and a span of J.
+__global__ void __launch_bounds__(kRowThreads)
+aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long long bsP,
+           long long bsH, View5 out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long R = (long long)d.N * d.P * d.H * d.B;
+  const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
+  if (item >= R * spans) return;
+  long long row = item / spans;
+  const int span = (int)(item % spans);
+  const int b = (int)(row % d.B); row /= d.B;
+  const int h = (int)(row % d.H); row /= d.H;
+  const int p = (int)(row % d.P);
+  const int n = (int)(row / d.P);
+  const long long o_in = n * in.sN + p * in.sP + h * in.sH + b * in.sB;
+  const long long o_out = n * out.sN + p * out.sP + h * out.sH + b * out.sB;
+  const float bv = __half2float(reinterpret_cast<const __half*>(bias)[n * bsN + p * bsP + h * bsH]);
+  float x[kEwNV][8];
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f < d.J) load8h(in.p, o_in, in.sJ, in.vec, f, d.J, x[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < kEwNV; ++i) {
+    const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
+    if (f >= d.J) continue;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[i][e] += bv;
+    store8h(out.p, o_out, out.sJ, out.vec, f, d.J, x[i]);
+  }
+}
+
+// dbias[n,p,h] = sum_{b,j} in[n,p,h,b,j]; one CTA per output element.
+__global__ void __launch_bounds__(kColThreads)
+baib_kernel(Dims5 d, View5 in, void* dbias, long long bsN, long long bsP, long long bsH) {
+  long long row = blockIdx.x;
+  const int h = (int)(row % d.H); row /= d.H;
+  const int p = (int)(row % d.P);
+  const int n = (int)(row / d.P);
+  const long long base = n * in.sN + p * in.sP + h * in.sH;
+  const int groups = (d.J + 7) / 8;
+  float acc = 0.f;
+  for (long long idx = threadIdx.x; idx < (long long)d.B * groups; idx += kColThreads) {
+    const int b = (int)(idx / groups);
+    const int f = (int)(idx % groups) * 8;
+    float x[8];
+    load8h(in.p, base + b * in.sB, in.sJ, in.vec, f, d.J, x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += x[e];
+  }
+  acc = warp_sum(acc);
+  __shared__ float sm[kColThreads / kWarp];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kColThreads / kWarp; ++w) s += sm[w];
+    reinterpret_cast<__half*>(dbias)[n * bsN + p * bsP + h * bsH] = __float2half_rn(s);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Token reductions fused with elementwise work.
+// grid = (feature slices of 256, row chunks); see file header for the scheme.
+// ---------------------------------------------------------------------------
+template <int NQ>
+struct ColOut {
+  void* out[NQ];  // fp16 [F], unit stride
+};
+
+struct BsbOp {
+  static constexpr int NQ = 2;
+  View3 dy, ln, dln;
+  const void* gamma;
+  int pvec;
+  __device__ __forceinline__ void row(int b, int j, int f, int F, const float gm[8],
+                                      float acc[NQ][8]) const {
+    float y[8], n[8], o[8];
+    load8h(dy.p, b * dy.sB + j * dy.sJ, dy.sF, dy.vec, f, F, y);
+    load8h(ln.p, b * ln.sB + j * ln.sJ, ln.sF, ln.vec, f, F, n);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      o[e] = y[e] * gm[e];
+      acc[0][e] += y[e] * n[e];
+      acc[1][e] += y[e];
+    }
+    store8h(dln.p, b * dln.sB + j * dln.sJ, dln.sF, dln.vec, f, F, o);
+  }
+  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, pvec, gm); }
+};
+
+struct EbsbOp {
+  static constexpr int NQ = 3;
+  View3 ln1, dresid2, dlw, dlin2, dln1;
+  const void* gamma;
+  int pvec;
+  __device__ __forceinline__ void row(int b, int j, int f, int F, const float gm[8],
+                                      float acc[NQ][8]) const {
+    float n[8], r[8], w[8], l2[8], o[8];
+    load8h(ln1.p, b * ln1.sB + j * ln1.sJ, ln1.sF, ln1.vec, f, F, n);
+    load8h(dresid2.p, b * dresid2.sB + j * dresid2.sJ, dresid2.sF, dresid2.vec, f, F, r);
+    load8h(dlw.p, b * dlw.sB + j * dlw.sJ, dlw.sF, dlw.vec, f, F, w);
+    load8h(dlin2.p, b * dlin2.sB + j * dlin2.sJ, dlin2.sF, dlin2.vec, f, F, l2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float g = r[e] + w[e];
+      o[e] = g * gm[e];
+      acc[0][e] += g * n[e];
+      acc[1][e] += g;
+      acc[2][e] += l2[e];
+    }
+    store8h(dln1.p, b * dln1.sB + j * dln1.sJ, dln1.sF, dln1.vec, f, F, o);
+  }
+  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, pvec, gm); }
+};
+
+struct BdrlbOp {
+  static constexpr int NQ = 1;
+  View3 ddrop2, mask, lin1, dlin1;
+  int activation;
+  __device__ __forceinline__ void row(int b, int j, int f, int F, const float[8],
+                                      float acc[NQ][8]) const {
+    float g[8], x[8], o[8];
+    uint32_t m[8];
+    load8h(ddrop2.p, b * ddrop2.sB + j * ddrop2.sJ, ddrop2.sF, ddrop2.vec, f, F, g);
+    load8h(lin1.p, b * lin1.sB + j * lin1.sJ, lin1.sF, lin1.vec, f, F, x);
+    load8m(mask.p, b * mask.sB + j * mask.sJ, mask.sF, mask.vec, f, F, m);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      o[e] = (f + e < F) ? act_bwd(x[e], m[e] ? g[e] : 0.f, activation) : 0.f;
+      acc[0][e] += o[e];
+    }
+    store8h(dlin1.p, b * dlin1.sB + j * dlin1.sJ, dlin1.sF, dlin1.vec, f, F, o);
+  }
+  __device__ __forceinline__ void scale(int, int, float[8]) const {}
+};
+
+struct BaobOp {
+  static constexpr int NQ = 1;
+  View3 datt;
+  __device__ __forceinline__ void row(int b, int j, int f, int F, const float[8],
+                                      float acc[NQ][8]) const {
+    float x[8];
+    load8h(datt.p, b * datt.sB + j * datt.sJ, datt.sF, datt.vec, f, F, x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[0][e] += x[e];
+  }
+  __device__ __forceinline__ void scale(int, int, float[8]) const {}
+};
+
+template <class Op>
+__global__ void __launch_bounds__(kColThreads)
+colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* counters,
+                 ColOut<Op::NQ> outs) {
+  constexpr int NQ = Op::NQ;
+  constexpr int NW = kColThreads / kWarp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slice = blockIdx.x, chunk = blockIdx.y, P = gridDim.y;
+  const int Fp = gridDim.x * 256;
+  const int f = slice * 256 + lane * 8;
+  const long long R = (long long)d.B * d.J;
+  const long long r0 = (long long)chunk * rows_per_chunk;
+  const long long r1 = (r0 + rows_per_chunk < R) ? r0 + rows_per_chunk : R;
+
+  float acc[NQ][8];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+  if (f < d.F) {
+    float gm[8];
+    op.scale(f, d.F, gm);
+    for (long long r = r0 + warp; r < r1; r += NW) {
+      const int b = (int)(r / d.J), j = (int)(r % d.J);
+      op.row(b, j, f, d.F, gm, acc);
+    }
+  }
+  __shared__ float sm[NW][NQ][256];
+  __shared__ int is_last;
+#pragma unroll
+  for (int q = 0; q < NQ; ++q)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sm[warp][q][lane * 8 + e] = acc[q][e];
+  __syncthreads();
+  const int t = threadIdx.x;
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) s += sm[w][q][t];
+    partial[((long long)q * P + chunk) * Fp + slice * 256 + t] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  if (t == 0) is_last = (atomicAdd(&counters[slice], 1u) == (unsigned)(P - 1));
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // Last CTA of this slice: add the P partial rows, warp w taking chunks w, w+NW, ...
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.f;
+    for (int c = warp; c < P; c += NW) {
+      const float4* src =
+          reinterpret_cast<const float4*>(partial + ((long long)q * P + c) * Fp + slice * 256 + lane * 8);
+      const float4 u = __ldcg(src), v = __ldcg(src + 1);
+      a[0] += u.x; a[1] += u.y; a[2] += u.z; a[3] += u.w;
+      a[4] += v.x; a[5] += v.y; a[6] += v.z; a[7] += v.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sm[warp][q][lane * 8 + e] = a[e];
+  }
+  __syncthreads();
+  if (slice * 256 + t < d.F) {
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += sm[w][q][t];
+      reinterpret_cast<__half*>(outs.out[q])[slice * 256 + t] = __float2half_rn(s);
+    }
+  }
+  if (t == 0) counters[slice] = 0u;
+}
+
+template <class Op>
+int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op::NQ> outs) {
+  if (!ws) return fail(SB_ERR_ARG, "token-reduction operator called without a workspace");
+  const int slices = (d.F + 255) / 256;
+  if (slices > (int)(kWsCounterBytes / sizeof(unsigned)))
+    return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace counters");
+  const long long R = (long long)d.B * d.J;
+  const long long Fp = (long long)slices * 256;
+  // about four 8-warp CTAs per SM; bounded by rows and by the workspace
+  long long P = (148 * 4 + slices - 1) / slices;
+  const long long cap = (long long)((kWsBytes - kWsCounterBytes) / (Op::NQ * Fp * sizeof(float)));
+  if (cap < 1) return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace");
+  if (P > cap) P = cap;
+  if (P > (R + 7) / 8) P = (R + 7) / 8;
+  if (P < 1) P = 1;
+  const int rpc = (int)((R + P - 1) / P);
+  P = (R + rpc - 1) / rpc;
+  unsigned* counters = reinterpret_cast<unsigned*>(ws);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
+  dim3 grid(slices, (unsigned)P);
+  colreduce_kernel<Op><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int param_vec(std::initializer_list<const void*> ptrs, int F) {
+  if (F % 8) return 0;
+  for (const void* p : ptrs)
+    if (reinterpret_cast<uintptr_t>(p) & 15u) return 0;
+  return 1;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+#define SB_SOFTMAX_CASES(KERNEL, ...)                                                        \
+  do {                                                                                       \
+    const long long R = (long long)d.H * d.B * d.J;                                          \
+    if (R == 0 || d.K == 0) return SB_OK;                                                    \
+    auto blocks = [&](int lpr) { return (unsigned)((R + 4 * (32 / lpr) - 1) / (4 * (32 / lpr))); }; \
+    if (d.K <= 64) KERNEL<8, 1><<<blocks(8), kRowThreads, 0, s>>>(__VA_ARGS__);              \
+    else if (d.K <= 128) KERNEL<16, 1><<<blocks(16), kRowThreads, 0, s>>>(__VA_ARGS__);      \
+    else if (d.K <= 256) KERNEL<32, 1><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);      \
+    else if (d.K <= 512) KERNEL<32, 2><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);      \
+    else if (d.K <= 1024) KERNEL<32, 4><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);     \
+    else if (d.K <= 2048) KERNEL<32, 8><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);     \
+    else                                                                                     \
+      return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");    \
+    SB_CUDA_OK(cudaGetLastError());                                                          \
+  } while (0)
+
+int launch_softmax_fwd(cudaStream_t s, Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop,
+                       float scale, Rng rng) {
+  SB_SOFTMAX_CASES(softmax_fwd_kernel, d, beta, alpha, mask, drop, scale, rng);
+  return SB_OK;
+}
+
+int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 dattn_drop,
+                       View4 dbeta) {
+  SB_SOFTMAX_CASES(softmax_bwd_kernel, d, alpha, mask, dattn_drop, dbeta);
+  return SB_OK;
+}
+
+#define SB_ROW_CASES(KERNEL, F, ...)                                                      \
+  do {                                                                                    \
+    const long long R = (long long)d.B * d.J;                                             \
+    if (R == 0 || (F) == 0) return SB_OK;                                                 \
+    const unsigned blocks = (unsigned)((R + 3) / 4);                                      \
+    if ((F) <= 256) KERNEL<1><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);                \
+    else if ((F) <= 512) KERNEL<2><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);           \
+    else if ((F) <= 1024) KERNEL<4><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);          \
+    else if ((F) <= 2048) KERNEL<8><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);          \
+    else                                                                                  \
+      return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported"); \
+    SB_CUDA_OK(cudaGetLastError());                                                       \
+  } while (0)
+
+int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid,
+                 const void* gamma, const void* beta, View3 mask, View3 lin, View3 diff,
+                 View2 istd, View3 ln, View3 out, Rng rng) {
+  const int pvec = param_vec({bias, gamma, beta}, d.F);
+  SB_ROW_CASES(bdrln_kernel, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out,
+               rng, pvec);
+  return SB_OK;
+}
+
+int launch_blnrd(cudaStream_t s, Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask,
+                 View3 dresid, View3 dlin) {
+  SB_ROW_CASES(blnrd_kernel, d.F, d, dln, istd, diff, mask, dresid, dlin);
+  return SB_OK;
+}
+
+int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, View3 lin1,
+               View3 drop2, int activation, Rng rng) {
+  const long long R = (long long)d.B * d.J;
+  if (R == 0 || d.F == 0) return SB_OK;
+  const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
+  const unsigned blocks = (unsigned)((R * spans + 3) / 4);
+  bad_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng,
+                                            param_vec({bias}, d.F));
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int launch_bei(cudaStream_t s, Dims3 d, View3 a, View3 b, View3 out) {
+  const long long R = (long long)d.B * d.J;
+  if (R == 0 || d.F == 0) return SB_OK;
+  const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
+  const unsigned blocks = (unsigned)((R * spans + 3) / 4);
+  bei_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bsN, long long bsP,
+               long long bsH, View5 out) {
+  const long long R = (long long)d.N * d.P * d.H * d.B;
+  if (R == 0 || d.J == 0) return SB_OK;
+  const int spans = (d.J + kEwNV * 256 - 1) / (kEwNV * 256);
+  const unsigned blocks = (unsigned)((R * spans + 3) / 4);
+  aib_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int launch_baib(cudaStream_t s, Dims5 d, View5 in, void* dbias, long long bsN, long long bsP,
+                long long bsH) {
+  const long long R = (long long)d.N * d.P * d.H;
+  if (R == 0) return SB_OK;
+  baib_kernel<<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int launch_bsb(cudaStream_t s, void* ws, Dims3 d, View3 dy, View3 ln, const void* gamma,
+               View3 dln, void* dgamma, void* dbeta) {
+  BsbOp op{dy, ln, dln, gamma, param_vec({gamma}, d.F)};
+  ColOut<2> outs{{dgamma, dbeta}};
+  return launch_colreduce(s, ws, d, op, outs);
+}
+
+int launch_ebsb(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gamma1, View3 dresid2,
+                View3 dlin1_linw1, View3 dlin2, View3 dln1, void* dgamma1, void* dbeta1,
+                void* dlinb2) {
+  EbsbOp op{ln1, dresid2, dlin1_linw1, dlin2, dln1, gamma1, param_vec({gamma1}, d.F)};
+  ColOut<3> outs{{dgamma1, dbeta1, dlinb2}};
+  return launch_colreduce(s, ws, d, op, outs);
+}
+
+int launch_bdrlb(cudaStream_t s, void* ws, Dims3 d, View3 ddrop2, View3 mask, View3 lin1,
+                 View3 dlin1, void* dbias, int activation) {
+  BdrlbOp op{ddrop2, mask, lin1, dlin1, activation};
+  ColOut<1> outs{{dbias}};
+  return launch_colreduce(s, ws, d, op, outs);
+}
+
+int launch_baob(cudaStream_t s, void* ws, Dims3 d, View3 datt, void* dbo) {
+  BaobOp op{datt};
+  ColOut<1> outs{{dbo}};
+  return launch_colreduce(s, ws, d, op, outs);
+}
+
+}  // namespace sb

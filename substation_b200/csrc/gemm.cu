@@ -1,0 +1,653 @@
+// Tensor contractions of the encoder layer.
+//
+// plan_einsum() collapses an einsum over strided operands into one batched GEMM
+//   C[b,m,n] = alpha * sum_k A[b,m,k] * B[b,n,k]
+// with independent strides for every index of every operand.
+//
+// gemm_tc_kernel: the sm_100a path.  One CTA computes a 128 x BN tile:
+//   warp 0   : TMA producer, cp.async.bulk.tensor into a ring of 128-byte-swizzled
+//              shared-memory stages (every CTA fetches its own tiles), completion on
+//              mbarriers;
+//   warp 1   : allocates tensor memory and issues tcgen05.mma (fp16 x fp16 -> fp32
+//              accumulator in TMEM) from shared-memory descriptors, one thread;
+//   warps 2-5: epilogue, tcgen05.ld of the accumulator, alpha, fp16 stores.
+// Either operand may be K-major or MN-major in global memory (the eight layout
+// cases a BLAS expresses with op flags and operand swapping); that choice only
+// changes the TMA box shape and the shared-memory descriptor.
+// Every mbarrier wait is bounded: after ~2 s it records an error code, the CTA
+// drains, frees its tensor memory and returns.
+//
+// gemm_simt_kernel: plain FMA fallback for operands TMA cannot address
+// (strides that are not multiples of 16 bytes, or no unit-stride index).
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "ops.h"
+
+namespace sb {
+
+thread_local int g_last_gemm_impl = 0;
+
+// ---------------------------------------------------------------------------
+// Einsum -> GEMM
+// ---------------------------------------------------------------------------
+namespace {
+
+struct Operand {
+  const char* dims;
+  const sb_tensor* t;
+  int find(char c) const {
+    const char* p = strchr(dims, c);
+    return p ? (int)(p - dims) : -1;
+  }
+};
+
+// Collapse the letters of `group`, taken in the order `order`, to (size, stride) in operand o.
+bool collapse_in(const Operand& o, const std::string& order, long long* stride) {
+  long long st = 0;
+  bool first = true;
+  long long expect = 0;
+  for (int i = (int)order.size() - 1; i >= 0; --i) {
+    const int d = o.find(order[i]);
+    const long long sz = o.t->size[d];
+    if (sz == 1) continue;
+    if (first) {
+      st = o.t->stride[d];
+      expect = st * sz;
+      first = false;
+    } else {
+      if (o.t->stride[d] != expect) return false;
+      expect *= sz;
+    }
+  }
+  *stride = first ? 0 : st;
+  return true;
+}
+
+std::string order_in(const Operand& o, const std::string& group) {
+  std::string r;
+  for (const char* p = o.dims; *p; ++p)
+    if (group.find(*p) != std::string::npos) r.push_back(*p);
+  return r;
+}
+
+}  // namespace
+
+int plan_einsum(const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
+                const char* c_dims, const sb_tensor* c, float alpha, GemmProblem* g) {
+  if (!a_dims || !b_dims || !c_dims || !a || !b || !c || !g)
+    return fail(SB_ERR_ARG, "einsum: null argument");
+  Operand A{a_dims, a}, B{b_dims, b}, C{c_dims, c};
+  for (const Operand* o : {&A, &B, &C}) {
+    const int n = (int)strlen(o->dims);
+    if (n != o->t->ndim || n > SB_MAX_DIMS)
+      return fail(SB_ERR_LAYOUT, std::string("einsum: dims string '") + o->dims +
+                                     "' does not match the operand's rank");
+    for (int i = 0; i < n; ++i) {
+      if (strchr(o->dims + i + 1, o->dims[i]))
+        return fail(SB_ERR_LAYOUT, std::string("einsum: repeated index in '") + o->dims + "'");
+      if (o->t->size[i] <= 0) return fail(SB_ERR_ARG, "einsum: non-positive extent");
+    }
+    if (!o->t->ptr) return fail(SB_ERR_ARG, "einsum: null data pointer");
+  }
+  std::string batch, sum, aonly, bonly;
+  long long nb = 1, nm = 1, nn = 1, nk = 1;
+  auto size_of = [&](char ch, long long* out) -> bool {
+    long long s = -1;
+    for (const Operand* o : {&A, &B, &C}) {
+      const int d = o->find(ch);
+      if (d < 0) continue;
+      if (s < 0) s = o->t->size[d];
+      else if (s != o->t->size[d]) return false;
+    }
+    *out = s;
+    return true;
+  };
+  std::string all = std::string(a_dims) + b_dims + c_dims, seen;
+  for (char ch : all) {
+    if (seen.find(ch) != std::string::npos) continue;
+    seen.push_back(ch);
+    const bool ia = A.find(ch) >= 0, ib = B.find(ch) >= 0, ic = C.find(ch) >= 0;
+    long long s;
+    if (!size_of(ch, &s))
+      return fail(SB_ERR_ARG, std::string("einsum: extent of index '") + ch + "' differs between operands");
+    if (ia && ib && ic) { batch.push_back(ch); nb *= s; }
+    else if (ia && ib) { sum.push_back(ch); nk *= s; }
+    else if (ia && ic) { aonly.push_back(ch); nm *= s; }
+    else if (ib && ic) { bonly.push_back(ch); nn *= s; }
+    else return fail(SB_ERR_UNSUPPORTED, std::string("einsum: index '") + ch + "' appears in only one operand");
+  }
+  // Find one index order per group under which the group collapses in every operand holding it.
+  auto solve = [&](const std::string& group, std::initializer_list<const Operand*> ops,
+                   long long* strides) -> bool {
+    if (group.empty()) {
+      int i = 0;
+      for (const Operand* o : ops) { (void)o; strides[i++] = 0; }
+      return true;
+    }
+    for (const Operand* cand : ops) {
+      const std::string order = order_in(*cand, group);
+      bool ok = true;
+      int i = 0;
+      for (const Operand* o : ops) ok = ok && collapse_in(*o, order, &strides[i++]);
+      if (ok) return true;
+    }
+    return false;
+  };
+  long long sb3[3], sm2[2], sn2[2], sk2[2];
+  if (!solve(batch, {&A, &B, &C}, sb3))
+    return fail(SB_ERR_UNSUPPORTED, "einsum: batch indices do not collapse to one stride in every operand");
+  if (!solve(aonly, {&A, &C}, sm2))
+    return fail(SB_ERR_UNSUPPORTED, "einsum: A-only indices do not collapse to one stride");
+  if (!solve(bonly, {&B, &C}, sn2))
+    return fail(SB_ERR_UNSUPPORTED, "einsum: B-only indices do not collapse to one stride");
+  if (!solve(sum, {&A, &B}, sk2))
+    return fail(SB_ERR_UNSUPPORTED, "einsum: summed indices do not collapse to one stride");
+  g->batch = nb; g->M = nm; g->N = nn; g->K = nk;
+  g->sAb = sb3[0]; g->sBb = sb3[1]; g->sCb = sb3[2];
+  g->sAm = sm2[0]; g->sCm = sm2[1];
+  g->sBn = sn2[0]; g->sCn = sn2[1];
+  g->sAk = sk2[0]; g->sBk = sk2[1];
+  g->A = a->ptr; g->B = b->ptr; g->C = c->ptr;
+  g->alpha = alpha;
+  return SB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SIMT fallback
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kSt = 64, kSk = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(GemmProblem g) {
+  __shared__ float As[kSk][kSt + 4];
+  __shared__ float Bs[kSk][kSt + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid % 16, ty = tid / 16;
+  const long long m0 = (long long)blockIdx.y * kSt, n0 = (long long)blockIdx.x * kSt;
+  const __half* A = reinterpret_cast<const __half*>(g.A);
+  const __half* B = reinterpret_cast<const __half*>(g.B);
+  __half* C = reinterpret_cast<__half*>(g.C);
+  for (long long bt = blockIdx.z; bt < g.batch; bt += gridDim.z) {
+    float acc[4][4] = {};
+    for (long long k0 = 0; k0 < g.K; k0 += kSk) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = tid + 256 * i;
+        // consecutive threads follow the unit-stride index of each operand
+        int am, ak, bn, bk;
+        if (g.sAk == 1) { ak = idx % kSk; am = idx / kSk; } else { am = idx % kSt; ak = idx / kSt; }
+        if (g.sBk == 1) { bk = idx % kSk; bn = idx / kSk; } else { bn = idx % kSt; bk = idx / kSt; }
+        const long long m = m0 + am, ka = k0 + ak, n = n0 + bn, kb = k0 + bk;
+        As[ak][am] = (m < g.M && ka < g.K) ? __half2float(A[bt * g.sAb + m * g.sAm + ka * g.sAk]) : 0.f;
+        Bs[bk][bn] = (n < g.N && kb < g.K) ? __half2float(B[bt * g.sBb + n * g.sBn + kb * g.sBk]) : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < kSk; ++k) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { a[i] = As[k][ty * 4 + i]; b[i] = Bs[k][tx * 4 + i]; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+        if (m < g.M && n < g.N) C[bt * g.sCb + m * g.sCm + n * g.sCn] = __float2half_rn(acc[i][j] * g.alpha);
+      }
+  }
+}
+
+}  // namespace
+
+int launch_gemm_simt(cudaStream_t s, const GemmProblem& g) {
+  if (g.batch == 0 || g.M == 0 || g.N == 0) return SB_OK;
+  dim3 grid((unsigned)((g.N + kSt - 1) / kSt), (unsigned)((g.M + kSt - 1) / kSt),
+            (unsigned)std::min<long long>(g.batch, 65535));
+  gemm_simt_kernel<<<grid, 256, 0, s>>>(g);
+  SB_CUDA_OK(cudaGetLastError());
+  g_last_gemm_impl = SB_GEMM_SIMT;
+  return SB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// tcgen05 path
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kBM = 128;                 // UMMA M
+constexpr int kBK = 64;                  // one 128-byte swizzle span of fp16
+constexpr int kTcThreads = 192;          // 6 warps
+constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
+constexpr unsigned long long kWaitNs = 2000000000ull;
+
+__device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel in this process
+
+struct TcParams {
+  long long M, N, K;
+  long long sCb, sCm, sCn;
+  __half* C;
+  float alpha;
+  int a_mn, b_mn;      // operand is MN-major in global memory
+  int a_swap, b_swap;  // tensor-map dims 1 and 2 are exchanged (kept in increasing-stride order)
+  int c_vec;           // sCn == 1 and rows are 16-byte aligned
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kWaitNs, or earlier when another CTA already failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 0x3ffu) == 0) {
+      if (*reinterpret_cast<volatile int*>(&g_tc_error) != 0) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitNs) { atomicCAS(&g_tc_error, 0, code); return false; }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  lbo/sbo in bytes.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+struct TcCfg {
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const TcParams p) {
+  using Cfg = TcCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles + Cfg::kTileBytes;       // full[S], empty[S], tmem_full
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * S, bar_acc = bars + 16 * S;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (tiles - raw) + Cfg::kTileBytes + 16 * S + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kBM, bt = blockIdx.z;
+  const int KT = (int)((p.K + kBK - 1) / kBK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ---------------- TMA producer (whole warp walks the loop, lane 0 issues) ----------------
+    for (int kt = 0; kt < KT; ++kt) {
+      const int s = kt % S;
+      const uint32_t ph = (uint32_t)(kt / S) & 1u;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
+      if (!ok) break;
+      if (lane == 0) {
+        const uint32_t full = bar_full + 8 * s;
+        mbar_expect_tx(full, (uint32_t)Cfg::kStageBytes);
+        const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
+        const int k0 = kt * kBK;
+        if (!p.a_mn) {
+          // dims (k, m, batch), box 64 x 128
+          if (p.a_swap) tma_load_3d(sa, &tmA, full, k0, bt, m0);
+          else tma_load_3d(sa, &tmA, full, k0, m0, bt);
+        } else {
+          // dims (m, k, batch), two boxes of 64 (m) x 64 (k)
+#pragma unroll
+          for (int h = 0; h < kBM / 64; ++h) {
+            if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
+            else tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+          }
+        }
+        if (!p.b_mn) {
+          if (p.b_swap) tma_load_3d(sb_, &tmB, full, k0, bt, n0);
+          else tma_load_3d(sb_, &tmB, full, k0, n0, bt);
+        } else {
+#pragma unroll
+          for (int h = 0; h < BN / 64; ++h) {
+            if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
+            else tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (whole warp walks the loop, lane 0 issues) ----------------
+    // instruction descriptor: fp32 accumulate, fp16 A and B, operand majors, N, M
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+                           ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                           ((uint32_t)(kBM >> 4) << 24);
+    // K-major: 8-row groups 1024 B apart, 32 B per K step of 16.
+    // MN-major: 64-wide MN blocks 8192 B apart (LBO), 8-row K groups 1024 B apart, 2048 B per K step.
+    const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+    const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
+    bool ok = true;
+    for (int kt = 0; kt < KT; ++kt) {
+      const int s = kt % S;
+      const uint32_t ph = (uint32_t)(kt / S) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) {
+          const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
+          const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
+          umma_f16(tmem_base, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+      }
+      __syncwarp();
+    }
+    if (ok && lane == 0) umma_commit(bar_acc);
+    __syncwarp();
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool ok = mbar_wait(bar_acc, 0u, 3);
+    tc_fence_after();
+    if (ok) {
+      const long long m = (long long)m0 + q * 32 + lane;
+      __half* crow = p.C + (long long)bt * p.sCb + m * p.sCm;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        if (m < p.M) {
+          const long long nb = (long long)n0 + c * 32;
+          if (p.c_vec) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (nb + v * 8 < p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+                *reinterpret_cast<uint4*>(crow + nb + v * 8) = pack8(f);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+          }
+        }
+      }
+    }
+  }
+  if (*reinterpret_cast<volatile int*>(&g_tc_error) != 0) {
+    // failure path: give bulk copies already in flight time to land before the CTA's memory is reused
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::once_flag g_encode_once;
+
+void load_encode() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+}
+
+struct OperandMap {
+  CUtensorMap map;
+  int mn;    // MN-major
+  int swap;  // dims 1 and 2 exchanged
+};
+
+// Operand X[batch][r][k] (r = m or n) with strides (sb, sr, sk); tile = rows x 64 (k).
+bool make_operand_map(const void* ptr, long long R, long long K, long long batch, long long sr,
+                      long long sk, long long sb, int rows, OperandMap* out, std::string* why) {
+  if (reinterpret_cast<uintptr_t>(ptr) & 15u) { *why = "operand base is not 16-byte aligned"; return false; }
+  cuuint64_t dim[3];
+  long long str[3];
+  cuuint32_t box[3];
+  if (sk == 1 || K == 1) {  // K-major (a single K column is K-major with any stride)
+    out->mn = 0;
+    dim[0] = (cuuint64_t)K; dim[1] = (cuuint64_t)R; dim[2] = (cuuint64_t)batch;
+    str[0] = 1; str[1] = sr; str[2] = sb;
+    box[0] = kBK; box[1] = (cuuint32_t)rows; box[2] = 1;
+    if (K == 1 && sk != 1) { /* dim0 has extent 1; its stride is irrelevant */ }
+  } else if (sr == 1) {
+    out->mn = 1;
+    dim[0] = (cuuint64_t)R; dim[1] = (cuuint64_t)K; dim[2] = (cuuint64_t)batch;
+    str[0] = 1; str[1] = sk; str[2] = sb;
+    box[0] = 64; box[1] = kBK; box[2] = 1;
+  } else {
+    *why = "operand has no unit-stride index";
+    return false;
+  }
+  // extent-1 dims: any legal stride (a multiple of 8 elements)
+  if (dim[1] == 1) str[1] = ((long long)dim[0] + 7) / 8 * 8;
+  if (dim[2] == 1) str[2] = std::max(str[1] * (long long)dim[1], ((long long)dim[0] + 7) / 8 * 8);
+  out->swap = 0;
+  if (str[2] < str[1]) {  // keep strides increasing
+    std::swap(dim[1], dim[2]);
+    std::swap(str[1], str[2]);
+    std::swap(box[1], box[2]);
+    out->swap = 1;
+  }
+  for (int i = 1; i < 3; ++i)
+    if (str[i] <= 0 || (str[i] * 2) % 16 != 0) { *why = "operand stride is not a positive multiple of 16 bytes"; return false; }
+  for (int i = 0; i < 3; ++i)
+    if (dim[i] == 0 || dim[i] > 0xffffffffull) { *why = "operand extent out of range"; return false; }
+  cuuint64_t gstr[2] = {(cuuint64_t)str[1] * 2, (cuuint64_t)str[2] * 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = g_encode(&out->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dim,
+                              gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled rejected the operand (code " + std::to_string((int)r) + ")"; return false; }
+  return true;
+}
+
+template <int BN>
+int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b) {
+  using Cfg = TcCfg<BN>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  // the attribute is per device; set it again when the current device differs (cheap, idempotent)
+  SB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  (void)attr_err;
+  TcParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
+  p.C = reinterpret_cast<__half*>(g.C);
+  p.alpha = g.alpha;
+  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
+  p.c_vec = (g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && g.sCb % 8 == 0 &&
+             (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0) ? 1 : 0;
+  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + kBM - 1) / kBM), (unsigned)g.batch);
+  gemm_tc_kernel<BN><<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(a.map, b.map, p);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int pick_bn(long long M, long long N, long long batch) {
+  // Largest tile that still yields at least one CTA per SM; otherwise the one with most CTAs
+  // that does not pad N by more than it has to.
+  const long long mt = (M + kBM - 1) / kBM;
+  for (int bn : {256, 128, 64}) {
+    if (N <= bn / 2 && bn > 64) continue;
+    const long long ctas = mt * ((N + bn - 1) / bn) * batch;
+    if (ctas >= 148) return bn;
+  }
+  if (N <= 64) return 64;
+  if (N <= 128) return 128;
+  return 64;
+}
+
+long long padded_work(long long M, long long N) {
+  const long long mp = (M + kBM - 1) / kBM * kBM;
+  const long long np = (N + 63) / 64 * 64;
+  return mp * np;
+}
+
+}  // namespace
+
+bool tcgen05_supported(const GemmProblem& g, std::string* why) {
+  if (g.batch > 65535) { *why = "more than 65535 batches"; return false; }
+  if (g.K < 1 || g.M < 1 || g.N < 1) { *why = "empty problem"; return false; }
+  if (!(g.sAk == 1 || g.sAm == 1 || g.K == 1)) { *why = "A has no unit-stride index"; return false; }
+  if (!(g.sBk == 1 || g.sBn == 1 || g.K == 1)) { *why = "B has no unit-stride index"; return false; }
+  return true;
+}
+
+int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0) {
+  std::string why;
+  if (!tcgen05_supported(g0, &why)) return fail(SB_ERR_UNSUPPORTED, "tcgen05 contraction: " + why);
+  std::call_once(g_encode_once, load_encode);
+  if (!g_encode) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  // C^T = B^T A^T: use the orientation that wastes fewer padded tile elements
+  // (ties: keep N as the unit-stride index of C so rows are stored as 128-bit vectors).
+  GemmProblem g = g0;
+  const long long w0 = padded_work(g.M, g.N), w1 = padded_work(g.N, g.M);
+  const bool swap = (w1 < w0) || (w1 == w0 && g.sCn != 1 && g.sCm == 1);
+  if (swap) {
+    std::swap(g.M, g.N);
+    std::swap(g.A, g.B);
+    std::swap(g.sAb, g.sBb);
+    std::swap(g.sAm, g.sBn);
+    std::swap(g.sAk, g.sBk);
+    std::swap(g.sCm, g.sCn);
+  }
+  const int bn = pick_bn(g.M, g.N, g.batch);
+  OperandMap a, b;
+  if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
+    return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
+  if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))
+    return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand B: " + why);
+  int st;
+  if (bn == 256) st = launch_tc<256>(s, g, a, b);
+  else if (bn == 128) st = launch_tc<128>(s, g, a, b);
+  else st = launch_tc<64>(s, g, a, b);
+  if (st == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
+  return st;
+}
+
+int run_gemm(cudaStream_t s, const GemmProblem& g, int impl) {
+  if (impl == SB_GEMM_SIMT) return launch_gemm_simt(s, g);
+  if (impl == SB_GEMM_TCGEN05) return launch_gemm_tcgen05(s, g);
+  if (impl != SB_GEMM_AUTO) return fail(SB_ERR_ARG, "einsum: unknown implementation selector");
+  const int st = launch_gemm_tcgen05(s, g);
+  if (st == SB_ERR_UNSUPPORTED || st == SB_ERR_ALIGNMENT) return launch_gemm_simt(s, g);
+  return st;
+}
+
+int gemm_device_error(cudaStream_t s, int* code) {
+  int v = 0;
+  SB_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_tc_error, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+  SB_CUDA_OK(cudaStreamSynchronize(s));
+  *code = v;
+  return SB_OK;
+}
+
+}  // namespace sb

@@ -1,0 +1,64 @@
+// Internal launch interface of the fused operators (views already validated).
+#pragma once
+
+#include "common.cuh"
+
+namespace sb {
+
+struct Dims3 { int B, J, F; };
+struct Dims4 { int H, B, J, K; };
+struct Dims5 { int N, P, H, B, J; };
+
+// Workspace layout: [0, kWsCounterBytes) ticket counters (must start at zero; every
+// kernel that uses them leaves them at zero), then fp32 partial sums.
+constexpr size_t kWsCounterBytes = 4096;
+constexpr size_t kWsBytes = 8u << 20;
+
+int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bsN, long long bsP,
+               long long bsH, View5 out);
+int launch_softmax_fwd(cudaStream_t s, Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop,
+                       float scale, Rng rng);
+int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 dattn_drop,
+                       View4 dbeta);
+int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid,
+                 const void* gamma, const void* beta, View3 mask, View3 lin, View3 diff,
+                 View2 istd, View3 ln, View3 out, Rng rng);
+int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, View3 lin1,
+               View3 drop2, int activation, Rng rng);
+int launch_blnrd(cudaStream_t s, Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask,
+                 View3 dresid, View3 dlin);
+int launch_bei(cudaStream_t s, Dims3 d, View3 a, View3 b, View3 out);
+int launch_baib(cudaStream_t s, Dims5 d, View5 in, void* dbias, long long bsN, long long bsP,
+                long long bsH);
+int launch_bsb(cudaStream_t s, void* ws, Dims3 d, View3 dy, View3 ln, const void* gamma,
+               View3 dln, void* dgamma, void* dbeta);
+int launch_ebsb(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gamma1, View3 dresid2,
+                View3 dlin1_linw1, View3 dlin2, View3 dln1, void* dgamma1, void* dbeta1,
+                void* dlinb2);
+int launch_bdrlb(cudaStream_t s, void* ws, Dims3 d, View3 ddrop2, View3 mask, View3 lin1,
+                 View3 dlin1, void* dbias, int activation);
+int launch_baob(cudaStream_t s, void* ws, Dims3 d, View3 datt, void* dbo);
+
+// Contractions -----------------------------------------------------------------
+struct GemmProblem {
+  long long batch, M, N, K;
+  long long sAb, sAm, sAk;
+  long long sBb, sBn, sBk;
+  long long sCb, sCm, sCn;
+  const void* A;
+  const void* B;
+  void* C;
+  float alpha;
+};
+// Collapse an einsum over strided operands into one batched GEMM (error if it is not one).
+int plan_einsum(const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
+                const char* c_dims, const sb_tensor* c, float alpha, GemmProblem* out);
+bool tcgen05_supported(const GemmProblem& g, std::string* why);
+int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g);
+int launch_gemm_simt(cudaStream_t s, const GemmProblem& g);
+int run_gemm(cudaStream_t s, const GemmProblem& g, int impl);
+extern thread_local int g_last_gemm_impl;
+// Non-zero once a tcgen05 kernel on this process reported a bounded wait running out.
+int gemm_device_error(cudaStream_t s, int* code);
+
+}  // namespace sb

@@ -1,0 +1,306 @@
+"""PyTorch interface to the B200 encoder layer: a drop-in for the reference's
+``pytorch_module/encoder.py``.
+
+Same class name, positional signature, parameter names/shapes, ``.params``,
+``.layouts``, ``.debug`` and autograd behaviour (``backward`` returns
+``(DX, *parameter gradients)`` in the configuration's order); underneath, one
+ctypes call per pass into the hand-written sm_100a library instead of a
+per-configuration nvcc build (pytorch_module/encoder.py:165-405).
+
+What differs, on purpose:
+  * only ``torch.float16`` is implemented (fp16 storage, fp32 accumulation);
+  * dropout masks are ``uint8``; with ``mask_mode='explicit'`` the four masks
+    are caller-supplied inputs (``set_masks``), with ``'philox'`` (default, the
+    reference's behaviour) the kernels generate them from ``(seed, offset)``;
+  * all intermediates of a pass live in ONE allocation (the reference makes
+    23 + 27 ``torch.empty`` calls per iteration, pytorch_module/encoder.py:80-85,
+    :110-121), and work is enqueued on the current torch stream;
+  * ``activation='gelu'`` is available (the reference CUDA path is ReLU only).
+There is no CPU path: tensors must be on a CUDA device.
+"""
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from . import layouts as L
+
+_ALIGN = 256
+
+
+def _round_up(n, a=_ALIGN):
+    return (n + a - 1) // a * a
+
+
+class Encoder(torch.nn.Module):
+    """Optimized BERT encoder layer (API of pytorch_module/encoder.py:19-25)."""
+
+    def __init__(self, compilation_dir, batch_size, max_seq_len, num_heads, embedding_size,
+                 layouts, torch_dtype,
+                 softmax_dropout_probability, residual1_dropout_probability,
+                 activation_dropout_probability, residual2_dropout_probability,
+                 enable_debug=False, profiling=False, *,
+                 activation='relu', mask_mode='philox', seed=0):
+        super().__init__()
+        if torch_dtype != torch.float16:
+            raise NotImplementedError(
+                f'substation_b200.Encoder computes in float16 storage with float32 accumulation; '
+                f'{torch_dtype} is not implemented')
+        if activation not in ('relu', 'gelu'):
+            raise ValueError('Unknown activation ' + str(activation))
+        if mask_mode not in ('philox', 'explicit'):
+            raise ValueError("mask_mode must be 'philox' or 'explicit'")
+        if embedding_size % num_heads:
+            raise ValueError('embedding_size must be a multiple of num_heads')
+
+        self.compilation_dir = compilation_dir  # accepted for compatibility; nothing is compiled per configuration
+        self.batch_size = batch_size
+        self.max_seq_len = max_seq_len
+        self.num_heads = num_heads
+        self.embedding_size = embedding_size
+        self.proj_size = self.embedding_size // self.num_heads
+        self.intermediate_size = self.embedding_size * 4
+        self.softmax_dropout_probability = softmax_dropout_probability
+        self.residual1_dropout_probability = residual1_dropout_probability
+        self.activation_dropout_probability = activation_dropout_probability
+        self.residual2_dropout_probability = residual2_dropout_probability
+        self.torch_dtype = torch_dtype
+        self.debug = {}  # intermediate tensors as numpy arrays when enable_debug
+        self.layouts = layouts
+        self.enable_debug = enable_debug
+        self.profiling = profiling
+        self.activation = activation
+        self.mask_mode = mask_mode
+        self.seed = int(seed)
+        self.philox_offset = 0          # advanced by 4 per forward, one per dropout site
+        self._masks = None
+        self._handle = None
+        self._handle_device = None
+
+        self._table = L.validate(layouts)
+        self.sizes = L.sizes_map(batch_size, max_seq_len, num_heads, embedding_size)
+
+        # Parameters: one per entry of layouts['params'], shaped by its dim letters
+        # (pytorch_module/encoder.py:56-60).
+        for param, layout in layouts['params']:
+            sz = L.shape_of(layout, self.sizes)
+            setattr(self, param, torch.nn.Parameter(torch.empty(*sz, dtype=self.torch_dtype)))
+        self.params = tuple(getattr(self, k) for k, _ in layouts['params'])
+        self.reset_parameters()
+
+        self._fwd_names = [n for n, _ in layouts['forward_interm']]
+        self._bwd_names = [n for n, _ in layouts['backward_interm']]
+        self._param_names = [n for n, _ in layouts['params']]
+        self._fwd_plan = self._plan(layouts['forward_interm'])
+        self._bwd_plan = self._plan(layouts['backward_interm'])
+        self._grad_plan = self._plan(layouts['params'])
+
+        outer = self
+
+        class EncoderFunction(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, X, *weights):
+                Y = torch.empty_like(X)
+                fwd = outer._alloc(outer._fwd_plan, X.device)
+                if outer.mask_mode == 'explicit':
+                    fwd.update(outer._explicit_masks(X.device))
+                outer.forward_raw(X, weights, fwd, Y)
+                ctx.save_for_backward(*weights, *(fwd[n] for n in outer._fwd_names), X)
+                if outer.enable_debug:
+                    torch.cuda.synchronize()
+                    for name in outer._fwd_names:
+                        outer.debug[name] = fwd[name].detach().cpu().numpy()
+                    for name, w in zip(outer._param_names, weights):
+                        outer.debug[name] = w.detach().cpu().numpy()
+                return Y
+
+            @staticmethod
+            def backward(ctx, DY):
+                saved = ctx.saved_tensors
+                np_, nf = len(outer._param_names), len(outer._fwd_names)
+                weights, fwd_list, X = saved[:np_], saved[np_:np_ + nf], saved[-1]
+                fwd = dict(zip(outer._fwd_names, fwd_list))
+                DY = DY.contiguous()
+                DX = torch.empty_like(DY)
+                bwd = outer._alloc(outer._bwd_plan, DY.device)
+                grads = outer._alloc(outer._grad_plan, DY.device)
+                outer.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
+                if outer.enable_debug:
+                    torch.cuda.synchronize()
+                    for name in outer._bwd_names:
+                        outer.debug[name] = bwd[name].detach().cpu().numpy()
+                    for name in outer._param_names:
+                        outer.debug['D' + name] = grads[name].detach().cpu().numpy()
+                return (DX, *(grads[n] for n in outer._param_names))
+
+        self.encoder_func = EncoderFunction
+
+    # ------------------------------------------------------------------ parameters
+    def reset_parameters(self):
+        """uniform(-1/sqrt(2), 1/sqrt(2)) as in pytorch_module/encoder.py:144-158."""
+        stdev = 1.0 / math.sqrt(2)
+        for weight in self.parameters():
+            t = torch.empty_like(weight, dtype=torch.float32)
+            torch.nn.init.uniform_(t, -stdev, stdev)
+            with torch.no_grad():
+                weight[:] = t
+
+    # ------------------------------------------------------------------ buffers
+    def _plan(self, entries):
+        """(name, shape, dtype, byte offset) for one arena holding all listed tensors."""
+        plan, off = [], 0
+        for name, layout in entries:
+            shape = L.shape_of(layout, self.sizes)
+            dtype = torch.uint8 if name in L.MASKS else self.torch_dtype
+            nbytes = math.prod(shape) * (1 if dtype == torch.uint8 else 2)
+            plan.append((name, shape, dtype, off, nbytes))
+            off += _round_up(nbytes)
+        return plan, off
+
+    @staticmethod
+    def _alloc(plan_total, device):
+        plan, total = plan_total
+        arena = torch.empty(max(total, 1), dtype=torch.uint8, device=device)
+        out = {}
+        for name, shape, dtype, off, nbytes in plan:
+            out[name] = arena[off:off + nbytes].view(dtype).view(shape)
+        out['__arena__'] = arena
+        return out
+
+    def intermediate_bytes(self):
+        """Bytes of the forward and backward arenas (what one layer keeps alive)."""
+        return self._fwd_plan[1], self._bwd_plan[1]
+
+    def set_masks(self, masks):
+        """Dropout masks for ``mask_mode='explicit'``: dict with ATTN_DROP_MASK,
+        DROP1MASK, DROP2MASK, DROP3MASK -> uint8 {0,1} tensors stored in the layout
+        the configuration gives each mask.  They are used in place (no copy)."""
+        if masks is not None:
+            for name in L.MASKS:
+                if name not in masks:
+                    raise KeyError(f'missing mask {name}')
+                t = masks[name]
+                want = L.shape_of(self._table[name], self.sizes)
+                if t.dtype != torch.uint8 or tuple(t.shape) != want or not t.is_contiguous():
+                    raise ValueError(f'mask {name} must be a contiguous uint8 tensor of shape {want}')
+        self._masks = masks
+
+    def _explicit_masks(self, device):
+        if self._masks is None:
+            raise RuntimeError("mask_mode='explicit' needs set_masks(...) before forward")
+        for t in self._masks.values():
+            if t.device != device:
+                raise ValueError('masks must live on the same device as the input')
+        return {n: self._masks[n] for n in L.MASKS}
+
+    # ------------------------------------------------------------------ native handle
+    def _native(self, device):
+        if self._handle is not None and self._handle_device == device:
+            return self._handle
+        if self._handle is not None:
+            self._destroy()
+        lib = _lib.load()
+        names = list(self._table.keys())
+        cfg = _lib.SbEncoderConfig()
+        cfg.batch, cfg.seq = self.batch_size, self.max_seq_len
+        cfg.heads, cfg.embed = self.num_heads, self.embedding_size
+        cfg.activation = _lib.SB_ACT_RELU if self.activation == 'relu' else _lib.SB_ACT_GELU
+        cfg.p_softmax = self.softmax_dropout_probability
+        cfg.p_resid1 = self.residual1_dropout_probability
+        cfg.p_activation = self.activation_dropout_probability
+        cfg.p_resid2 = self.residual2_dropout_probability
+        # pointer-table order = order of the configuration's lists (pytorch_module/encoder.py:229-299)
+        ordered = (['X', 'SB2'] + self._param_names + self._fwd_names + self._bwd_names)
+        assert sorted(ordered) == sorted(names)
+        cfg.n_tensors = len(ordered)
+        name_arr = (ctypes.c_char_p * len(ordered))(*[n.encode() for n in ordered])
+        dims_arr = (ctypes.c_char_p * len(ordered))(*[self._table[n].encode() for n in ordered])
+        cfg.names, cfg.dims = name_arr, dims_arr
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(lib.sb_encoder_create(ctypes.byref(cfg), ctypes.byref(handle)))
+            if self.profiling:
+                _lib.check(lib.sb_encoder_set_timing(handle, 1))
+        self._handle, self._handle_device = handle, device
+        return handle
+
+    def _destroy(self):
+        if self.__dict__.get('_handle') is not None:
+            try:
+                _lib.load().sb_encoder_destroy(self._handle)
+            except Exception:  # interpreter shutdown
+                pass
+            self._handle = None
+
+    def __del__(self):
+        self._destroy()
+
+    @staticmethod
+    def _ptrs(tensors):
+        arr = (ctypes.c_void_p * len(tensors))()
+        for i, t in enumerate(tensors):
+            arr[i] = t.data_ptr()
+        return arr
+
+    def _check_input(self, X, what):
+        want = L.shape_of(self._table['X'], self.sizes)
+        if not X.is_cuda:
+            raise ValueError(f'{what} must be a CUDA tensor (there is no CPU path)')
+        if X.dtype != self.torch_dtype or tuple(X.shape) != want:
+            raise ValueError(f'{what} must be {self.torch_dtype} of shape {want} '
+                             f'(layout {self._table["X"]}), got {X.dtype} {tuple(X.shape)}')
+
+    # ------------------------------------------------------------------ raw passes (no autograd)
+    def forward_raw(self, X, weights, fwd, Y):
+        """One forward pass into caller-provided buffers.  ``fwd``: name -> tensor for
+        the 23 forward intermediates (see ``_alloc``)."""
+        self._check_input(X, 'X')
+        X = X.contiguous()
+        lib = _lib.load()
+        h = self._native(X.device)
+        mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
+        stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
+        wl = [w.contiguous() for w in weights]
+        _lib.check(lib.sb_encoder_forward(
+            h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(wl),
+            self._ptrs([fwd[n] for n in self._fwd_names]), ctypes.c_void_p(Y.data_ptr()),
+            mode, self.seed, self.philox_offset))
+        self.philox_offset += 4
+        return Y
+
+    def backward_raw(self, DY, grads, bwd, weights, fwd, X, DX):
+        """One backward pass; ``grads``/``bwd``: name -> preallocated tensor."""
+        self._check_input(DY, 'DY')
+        lib = _lib.load()
+        h = self._native(DY.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
+        wl = [w.contiguous() for w in weights]
+        _lib.check(lib.sb_encoder_backward(
+            h, stream, ctypes.c_void_p(DY.data_ptr()),
+            self._ptrs([grads[n] for n in self._param_names]),
+            self._ptrs([bwd[n] for n in self._bwd_names]),
+            self._ptrs(wl), self._ptrs([fwd[n] for n in self._fwd_names]),
+            ctypes.c_void_p(X.data_ptr()), ctypes.c_void_p(DX.data_ptr())))
+        return DX
+
+    def op_times(self):
+        """[(operator name, ms)] of the passes since the last call (needs profiling=True).
+        Names follow the NVTX ranges of pytorch_module/encoder.cu:89-296."""
+        if self._handle is None:
+            return []
+        lib = _lib.load()
+        n = 64
+        names = (ctypes.c_char_p * n)()
+        ms = (ctypes.c_float * n)()
+        k = lib.sb_encoder_get_timing(self._handle, n, names, ms)
+        return [(names[i].decode(), ms[i]) for i in range(k)]
+
+    def launch_count(self):
+        """Kernels launched by the most recent raw pass."""
+        return 0 if self._handle is None else _lib.load().sb_encoder_launch_count(self._handle)
+
+    def forward(self, X):
+        """Run the encoder."""
+        return self.encoder_func.apply(X, *self.params)

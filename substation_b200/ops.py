@@ -1,0 +1,166 @@
+"""Per-operator Python entry points over the C ABI (one per fused kernel, one
+for contractions).  They take torch CUDA tensors *viewed in logical index
+order* (any permuted view of the stored tensor is fine: strides carry the
+layout) and run on the current torch stream.  This is the interface the
+reference's kernel harness drives one generated launcher at a time
+(pytorch_module/benchmark.py); it is also what the kernel-level parity tests call.
+"""
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import (SB_ACT_GELU, SB_ACT_RELU, SB_GEMM_AUTO, SB_GEMM_SIMT, SB_GEMM_TCGEN05,
+                   SB_MASK_EXPLICIT, SB_MASK_PHILOX, SbDropout, check, tensor_desc)
+
+_ACT = {'relu': SB_ACT_RELU, 'gelu': SB_ACT_GELU}
+_MODE = {'explicit': SB_MASK_EXPLICIT, 'philox': SB_MASK_PHILOX}
+_IMPL = {'auto': SB_GEMM_AUTO, 'tcgen05': SB_GEMM_TCGEN05, 'simt': SB_GEMM_SIMT}
+_workspaces = {}
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def workspace(device=None):
+    """Zero-initialised scratch for the token-reduction operators, one per
+    (device, stream)."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(_lib.load().sb_workspace_bytes(), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError('substation_b200 operators need CUDA tensors (there is no CPU path)')
+
+
+def _half(*tensors):
+    for t in tensors:
+        if t.dtype != torch.float16:
+            raise TypeError(f'expected float16, got {t.dtype}')
+
+
+def _mask(t):
+    if t.dtype != torch.uint8:
+        raise TypeError(f'dropout masks are uint8, got {t.dtype}')
+
+
+def _dropout(p, mode, seed, offset):
+    d = SbDropout()
+    d.p, d.mode, d.seed, d.offset = float(p), _MODE[mode], int(seed), int(offset)
+    return d
+
+
+def _d(t):
+    return ctypes.byref(tensor_desc(t))
+
+
+def attention_input_biases(inp, bias, out):
+    """out[n,p,h,b,j] = inp[n,p,h,b,j] + bias[n,p,h]."""
+    _check_cuda(inp, bias, out); _half(inp, bias, out)
+    check(_lib.load().sb_attention_input_biases(_stream(), _d(inp), _d(bias), _d(out)))
+
+
+def softmax_dropout(beta, alpha, mask, drop, scale=1.0, p=0.0, mode='explicit', seed=0, offset=0):
+    """alpha = softmax_k(scale*beta), drop = mask*alpha; all [H,B,J,K]."""
+    _check_cuda(beta, alpha, mask, drop); _half(beta, alpha, drop); _mask(mask)
+    d = _dropout(p, mode, seed, offset)
+    check(_lib.load().sb_softmax_dropout(_stream(), _d(beta), _d(alpha), _d(mask), _d(drop),
+                                         float(scale), ctypes.byref(d)))
+
+
+def backward_softmax(alpha, mask, dattn_drop, dbeta):
+    _check_cuda(alpha, mask, dattn_drop, dbeta); _half(alpha, dattn_drop, dbeta); _mask(mask)
+    check(_lib.load().sb_backward_softmax(_stream(), _d(alpha), _d(mask), _d(dattn_drop), _d(dbeta)))
+
+
+def bias_dropout_residual_layernorm(inp, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out,
+                                    p=0.0, mode='explicit', seed=0, offset=0):
+    _check_cuda(inp, out); _half(inp, bias, resid, gamma, beta, lin, diff, istd, ln, out); _mask(mask)
+    d = _dropout(p, mode, seed, offset)
+    check(_lib.load().sb_bias_dropout_residual_layernorm(
+        _stream(), _d(inp), _d(bias), _d(resid), _d(gamma), _d(beta), _d(mask), _d(lin), _d(diff),
+        _d(istd), _d(ln), _d(out), ctypes.byref(d)))
+
+
+def bias_activation_dropout(inp, bias, mask, lin1, drop2, activation='relu', p=0.0,
+                            mode='explicit', seed=0, offset=0):
+    _check_cuda(inp, drop2); _half(inp, bias, lin1, drop2); _mask(mask)
+    d = _dropout(p, mode, seed, offset)
+    check(_lib.load().sb_bias_activation_dropout(_stream(), _d(inp), _d(bias), _d(mask), _d(lin1),
+                                                 _d(drop2), _ACT[activation], ctypes.byref(d)))
+
+
+def backward_scale_bias(dy, ln, gamma, dln, dgamma, dbeta):
+    _check_cuda(dy); _half(dy, ln, gamma, dln, dgamma, dbeta)
+    ws = workspace(dy.device)
+    check(_lib.load().sb_backward_scale_bias(_stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy),
+                                             _d(ln), _d(gamma), _d(dln), _d(dgamma), _d(dbeta)))
+
+
+def backward_layernorm_residual_dropout(dln, istd, diff, mask, dresid, dlin):
+    _check_cuda(dln); _half(dln, istd, diff, dresid, dlin); _mask(mask)
+    check(_lib.load().sb_backward_layernorm_residual_dropout(
+        _stream(), _d(dln), _d(istd), _d(diff), _d(mask), _d(dresid), _d(dlin)))
+
+
+def backward_dropout_activation_bias(ddrop2, mask, lin1, dlin1, dbias, activation='relu'):
+    _check_cuda(ddrop2); _half(ddrop2, lin1, dlin1, dbias); _mask(mask)
+    ws = workspace(ddrop2.device)
+    check(_lib.load().sb_backward_dropout_activation_bias(
+        _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ddrop2), _d(mask), _d(lin1), _d(dlin1),
+        _d(dbias), _ACT[activation]))
+
+
+def extended_backward_scale_bias(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1, dgamma1, dbeta1,
+                                 dlinb2):
+    _check_cuda(ln1); _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1, dgamma1, dbeta1, dlinb2)
+    ws = workspace(ln1.device)
+    check(_lib.load().sb_extended_backward_scale_bias(
+        _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ln1), _d(gamma1), _d(dresid2),
+        _d(dlin1_linw1), _d(dlin2), _d(dln1), _d(dgamma1), _d(dbeta1), _d(dlinb2)))
+
+
+def backward_attn_out_bias(datt, dbo):
+    _check_cuda(datt); _half(datt, dbo)
+    ws = workspace(datt.device)
+    check(_lib.load().sb_backward_attn_out_bias(_stream(), ctypes.c_void_p(ws.data_ptr()),
+                                                _d(datt), _d(dbo)))
+
+
+def backward_attention_input_biases(d, dbias):
+    _check_cuda(d); _half(d, dbias)
+    check(_lib.load().sb_backward_attention_input_biases(_stream(), _d(d), _d(dbias)))
+
+
+def backward_encoder_input(dxatt, dresid1, dx):
+    _check_cuda(dxatt); _half(dxatt, dresid1, dx)
+    check(_lib.load().sb_backward_encoder_input(_stream(), _d(dxatt), _d(dresid1), _d(dx)))
+
+
+def einsum(spec, a, b, c, alpha=1.0, impl='auto'):
+    """c = alpha * einsum(spec, a, b) with spec like 'phbk,phbj->hbjk'; the dims of
+    each operand are named in the order of its own (size, stride) lists.  Returns
+    'tcgen05' or 'simt' (the kernel that ran)."""
+    _check_cuda(a, b, c); _half(a, b, c)
+    lhs, cd = spec.replace(' ', '').split('->')
+    ad, bd = lhs.split(',')
+    lib = _lib.load()
+    check(lib.sb_einsum(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
+                        float(alpha), _IMPL[impl]))
+    return {SB_GEMM_TCGEN05: 'tcgen05', SB_GEMM_SIMT: 'simt'}.get(lib.sb_einsum_last_impl(), '?')
+
+
+def device_error():
+    """Sticky code set when a bounded wait inside the tcgen05 kernel ran out (0 = never)."""
+    code = ctypes.c_int(0)
+    check(_lib.load().sb_device_error(_stream(), ctypes.byref(code)))
+    return code.value

@@ -1,0 +1,144 @@
+"""Contraction parity on the GPU: the tcgen05 kernel and the SIMT fallback against
+numpy float64 matmul, over the eight operand-major combinations the reference maps to
+cuBLAS op flags (pytorch_module/gemm.cuh:71-89), ragged extents, batching, and the
+layer's own einsums under both shipped layout configurations."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import encoder_oracle as orc
+from tests.gpu_util import DEV, assert_close, get, h16
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from substation_b200 import ops
+    return ops
+
+
+def _operand(rng, batch, rows, k, rows_major, pad=0):
+    """fp16 operand [batch, rows, k] stored k-innermost (rows_major False) or
+    rows-innermost (True); returns (float64 values, logical-order device view)."""
+    a = h16(rng.normal(0, 1, (batch, rows, k)) / np.sqrt(k))
+    if rows_major:
+        st = torch.zeros(batch, k, rows + pad, dtype=torch.float16, device=DEV)
+        st[..., :rows] = torch.from_numpy(a.transpose(0, 2, 1).copy()).to(DEV, torch.float16)
+        view = st[..., :rows].permute(0, 2, 1)
+    else:
+        st = torch.zeros(batch, rows, k + pad, dtype=torch.float16, device=DEV)
+        st[..., :k] = torch.from_numpy(a).to(DEV, torch.float16)
+        view = st[..., :k]
+    return a, view
+
+
+SHAPES = [  # batch, M, N, K
+    (1, 128, 256, 64), (1, 256, 512, 256), (3, 200, 136, 72), (2, 64, 512, 512), (4, 512, 64, 64),
+    (1, 128, 128, 64 * 21), (2, 384, 320, 200), (1, 1024, 1024, 1024),
+]
+
+
+@pytest.mark.parametrize('batch,M,N,K', SHAPES)
+@pytest.mark.parametrize('a_mn,b_mn,c_mn', [(a, b, c) for a in (0, 1) for b in (0, 1) for c in (0, 1)])
+def test_tcgen05_all_operand_majors(batch, M, N, K, a_mn, b_mn, c_mn):
+    ops = _ops()
+    rng = np.random.default_rng(M * 7 + N * 3 + K + a_mn * 4 + b_mn * 2 + c_mn)
+    pad = 8  # rows are not dense: strides differ from extents
+    A, dA = _operand(rng, batch, M, K, bool(a_mn), pad)
+    B, dB = _operand(rng, batch, N, K, bool(b_mn), pad)
+    if c_mn:
+        st = torch.full((batch, N, M + pad), float('nan'), dtype=torch.float16, device=DEV)
+        dC = st[..., :M].permute(0, 2, 1)
+    else:
+        st = torch.full((batch, M, N + pad), float('nan'), dtype=torch.float16, device=DEV)
+        dC = st[..., :N]
+    used = ops.einsum('bmk,bnk->bmn', dA, dB, dC, alpha=0.5, impl='tcgen05')
+    assert used == 'tcgen05'
+    assert ops.device_error() == 0
+    want = 0.5 * np.einsum('bmk,bnk->bmn', A, B)
+    assert_close(dC, want, tol=2e-3, what=f'C a_mn={a_mn} b_mn={b_mn} c_mn={c_mn}')
+    # the padding columns must be untouched
+    assert torch.isnan(st[..., -pad:]).all()
+
+
+@pytest.mark.parametrize('batch,M,N,K', [(1, 70, 50, 33), (3, 128, 64, 100), (2, 5, 7, 3)])
+def test_simt_fallback_and_auto_dispatch(batch, M, N, K):
+    ops = _ops()
+    rng = np.random.default_rng(K)
+    A, dA = _operand(rng, batch, M, K, False)
+    B, dB = _operand(rng, batch, N, K, True)
+    dC = torch.full((batch, M, N), float('nan'), dtype=torch.float16, device=DEV)
+    assert ops.einsum('bmk,bnk->bmn', dA, dB, dC, impl='simt') == 'simt'
+    want = np.einsum('bmk,bnk->bmn', A, B)
+    assert_close(dC, want, tol=2e-3, what='simt')
+    dC.fill_(float('nan'))
+    used = ops.einsum('bmk,bnk->bmn', dA, dB, dC, impl='auto')
+    assert used in ('tcgen05', 'simt')
+    assert_close(dC, want, tol=2e-3, what='auto')
+
+
+def test_tcgen05_rejects_what_tma_cannot_address():
+    ops = _ops()
+    from substation_b200._lib import SubstationError
+    a = torch.zeros(1, 16, 33, dtype=torch.float16, device=DEV)   # row stride 66 bytes
+    b = torch.zeros(1, 16, 33, dtype=torch.float16, device=DEV)
+    c = torch.zeros(1, 16, 16, dtype=torch.float16, device=DEV)
+    with pytest.raises(SubstationError) as e:
+        ops.einsum('bmk,bnk->bmn', a, b, c, impl='tcgen05')
+    assert e.value.status in (3, 5)
+    assert ops.einsum('bmk,bnk->bmn', a, b, c, impl='auto') == 'simt'
+
+
+def _layer_einsums(lay):
+    """(name, spec in memory-order letters) for the 18 contractions of
+    pytorch_module/encoder.cu:87-299 under layout table ``lay``."""
+    kk = lay['KKQQVV'][1:]
+    dkk = lay['DKKQQVV'][1:]
+    r = lambda s: s.replace('J', 'K')
+    return [
+        ('QKV-fused', lay['X'], lay['WKQV'], lay['WKKWQQWVV']),
+        ('QKT', r(kk), kk, lay['BETA']),
+        ('gamma', r(kk), lay['ATTN_DROP'], lay['GAMMA']),
+        ('out', lay['WO'], lay['GAMMA'], lay['ATT']),
+        ('lin1', lay['SB1'], lay['LINW1'], lay['SB1_LINW1']),
+        ('lin2', lay['DROP2'], lay['LINW2'], lay['DROP2_LINW2']),
+        ('dXlin2', lay['DLIN2'], lay['LINW2'], lay['DDROP2']),
+        ('dWlin2', lay['DLIN2'], lay['DROP2'], lay['LINW2']),
+        ('dXlin1', lay['DLIN1'], lay['LINW1'], lay['DLIN1_LINW1']),
+        ('dWlin1', lay['DLIN1'], lay['SB1'], lay['LINW1']),
+        ('dWout', lay['GAMMA'], lay['DATT'], lay['WO']),
+        ('dXout', lay['WO'], lay['DATT'], lay['DGAMMA']),
+        ('dX1gamma', r(kk), lay['DGAMMA'], lay['DATTN_DROP']),
+        ('dX2gamma', lay['DGAMMA'], lay['ATTN_DROP'], r(dkk)),
+        ('dX1QKT', r(kk), lay['DBETA'], dkk),
+        ('dX2QKT', kk, lay['DBETA'], r(dkk)),
+        ('dXQKV-fused', lay['WKQV'], lay['DKKQQVV'], lay['DXATT']),
+        ('dWQKV-fused', lay['X'], lay['DKKQQVV'], lay['WKQV']),
+    ]
+
+
+@pytest.mark.parametrize('which', ['uniform', 'b8_l512', 'b96_l128'])
+def test_layer_einsums_run_on_tensor_cores(which):
+    """Every contraction of the layer, with the operand layouts of each configuration,
+    must qualify for the tcgen05 kernel and match numpy."""
+    ops = _ops()
+    from substation_b200 import layouts as L
+    from tests.layer_harness import get_layouts
+    lay = L.validate(get_layouts(which))
+    sizes = L.sizes_map(2, 128, 2, 128)   # B=2, L=128, H=2, P=64
+    rng = np.random.default_rng(1)
+    for name, ad, bd, cd in _layer_einsums(lay):
+        shp = lambda d: tuple(sizes[c] for c in d)
+        ksz = np.prod([sizes[c] for c in ad if c in bd and c not in cd])
+        A = h16(rng.normal(0, 1, shp(ad)) / np.sqrt(ksz))
+        B = h16(rng.normal(0, 1, shp(bd)))
+        dA = torch.from_numpy(A).to(DEV, torch.float16)
+        dB = torch.from_numpy(B).to(DEV, torch.float16)
+        dC = torch.full(shp(cd), float('nan'), dtype=torch.float16, device=DEV)
+        spec = f'{ad.lower()},{bd.lower()}->{cd.lower()}'
+        used = ops.einsum(spec, dA, dB, dC, impl='auto')
+        assert used == 'tcgen05', f'{name} ({spec}) fell back to {used}'
+        want = np.einsum(spec, A, B)
+        assert_close(dC, want, tol=2e-3, what=f'{which}:{name} {spec}')
+    assert ops.device_error() == 0
