@@ -20,6 +20,17 @@ namespace {
 constexpr int kRowThreads = 128;  // 4 warps per CTA for the row kernels
 constexpr int kColThreads = 256;  // 8 warps per CTA for the token-reduction kernels
 
+// AV ("all vector") is a compile-time promise that every view of the launch takes the 128-bit
+// path, which removes the per-access branch so that a row's loads issue back to back.
+#define SB_VEC(view) (AV || (view).vec)
+
+// Keep flags of logical elements e0..e0+7; under AV the extent is a multiple of 8, so e0 is group aligned.
+template <bool AV>
+__device__ __forceinline__ void philox8(const Rng& r, unsigned long long e0, uint32_t m[8]) {
+  if (AV) philox_keep8(r, e0 >> 3, m);
+  else philox_keep8_unaligned(r, e0, m);
+}
+
 __device__ __forceinline__ float act_fwd(float x, int activation) {
   if (activation == SB_ACT_RELU) return fmaxf(x, 0.f);
   // tanh-form GELU
@@ -39,7 +50,7 @@ __device__ __forceinline__ float act_bwd(float x, float dy, int activation) {
 // Softmax (+scale, +dropout) forward and backward over [H,B,J,K]
 // LPR lanes cooperate on one row, each holding NV groups of eight elements.
 // ---------------------------------------------------------------------------
-template <int LPR, int NV>
+template <int LPR, int NV, bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, float scale, Rng rng) {
   constexpr int RPW = kWarp / LPR;
@@ -64,8 +75,8 @@ softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, flo
   for (int i = 0; i < NV; ++i) {
     const int k = (sl + LPR * i) * 8;
     if (k < d.K) {
-      load8h(beta.p, o_beta, beta.sK, beta.vec, k, d.K, x[i]);
-      if (!rng.philox) load8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+      load8h(beta.p, o_beta, beta.sK, SB_VEC(beta), k, d.K, x[i]);
+      if (!rng.philox) load8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
     }
   }
 #pragma unroll
@@ -95,20 +106,20 @@ softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, flo
     if (k >= d.K) continue;
     float a[8], dr[8];
     if (rng.philox) {
-      philox_keep8_unaligned(rng, (unsigned long long)row * d.K + k, m[i]);
-      store8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+      philox8<AV>(rng, (unsigned long long)row * d.K + k, m[i]);
+      store8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       a[e] = x[i][e] * inv;
       dr[e] = m[i][e] ? a[e] : 0.f;
     }
-    store8h(alpha.p, o_alpha, alpha.sK, alpha.vec, k, d.K, a);
-    store8h(drop.p, o_drop, drop.sK, drop.vec, k, d.K, dr);
+    store8h(alpha.p, o_alpha, alpha.sK, SB_VEC(alpha), k, d.K, a);
+    store8h(drop.p, o_drop, drop.sK, SB_VEC(drop), k, d.K, dr);
   }
 }
 
-template <int LPR, int NV>
+template <int LPR, int NV, bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta) {
   constexpr int RPW = kWarp / LPR;
@@ -132,9 +143,9 @@ softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta) {
   for (int i = 0; i < NV; ++i) {
     const int k = (sl + LPR * i) * 8;
     if (k < d.K) {
-      load8h(alpha.p, o_alpha, alpha.sK, alpha.vec, k, d.K, a[i]);
-      load8h(dad.p, o_dad, dad.sK, dad.vec, k, d.K, g[i]);
-      load8m(mask.p, o_mask, mask.sK, mask.vec, k, d.K, m[i]);
+      load8h(alpha.p, o_alpha, alpha.sK, SB_VEC(alpha), k, d.K, a[i]);
+      load8h(dad.p, o_dad, dad.sK, SB_VEC(dad), k, d.K, g[i]);
+      load8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) { a[i][e] = 0.f; g[i][e] = 0.f; m[i][e] = 0u; }
@@ -157,14 +168,14 @@ softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta) {
     float o[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = a[i][e] * (g[i][e] - s);
-    store8h(dbeta.p, o_dbeta, dbeta.sK, dbeta.vec, k, d.K, o);
+    store8h(dbeta.p, o_dbeta, dbeta.sK, SB_VEC(dbeta), k, d.K, o);
   }
 }
 
 // ---------------------------------------------------------------------------
 // bias + dropout + residual + LayerNorm over [B,J,F]; one warp per token.
 // ---------------------------------------------------------------------------
-template <int NV>
+template <int NV, bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma, const void* beta,
              View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng, int pvec) {
@@ -184,18 +195,18 @@ bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma
     if (f < d.F) {
       float x[8], rs[8], bs[8];
       uint32_t m[8];
-      load8h(in.p, o_in, in.sF, in.vec, f, d.F, x);
-      load8h(resid.p, o_res, resid.sF, resid.vec, f, d.F, rs);
-      load8p(bias, f, d.F, pvec, bs);
+      load8h(in.p, o_in, in.sF, SB_VEC(in), f, d.F, x);
+      load8h(resid.p, o_res, resid.sF, SB_VEC(resid), f, d.F, rs);
+      load8p(bias, f, d.F, AV || pvec, bs);
       if (rng.philox) {
-        philox_keep8_unaligned(rng, (unsigned long long)row * d.F + f, m);
-        store8m(mask.p, o_mask, mask.sF, mask.vec, f, d.F, m);
+        philox8<AV>(rng, (unsigned long long)row * d.F + f, m);
+        store8m(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F, m);
       } else {
-        load8m(mask.p, o_mask, mask.sF, mask.vec, f, d.F, m);
+        load8m(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F, m);
       }
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[e] += bs[e];
-      store8h(lin.p, o_lin, lin.sF, lin.vec, f, d.F, x);
+      store8h(lin.p, o_lin, lin.sF, SB_VEC(lin), f, d.F, x);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         r[i][e] = (f + e < d.F) ? (m[e] ? x[e] : 0.f) + rs[e] : 0.f;
@@ -226,21 +237,21 @@ bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma
     const int f = (lane + kWarp * i) * 8;
     if (f >= d.F) continue;
     float gm[8], bt[8], n[8], o[8];
-    load8p(gamma, f, d.F, pvec, gm);
-    load8p(beta, f, d.F, pvec, bt);
+    load8p(gamma, f, d.F, AV || pvec, gm);
+    load8p(beta, f, d.F, AV || pvec, bt);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       n[e] = r[i][e] * rstd;
       o[e] = n[e] * gm[e] + bt[e];
     }
-    store8h(diff.p, o_diff, diff.sF, diff.vec, f, d.F, r[i]);
-    store8h(ln.p, o_ln, ln.sF, ln.vec, f, d.F, n);
-    store8h(out.p, o_out, out.sF, out.vec, f, d.F, o);
+    store8h(diff.p, o_diff, diff.sF, SB_VEC(diff), f, d.F, r[i]);
+    store8h(ln.p, o_ln, ln.sF, SB_VEC(ln), f, d.F, n);
+    store8h(out.p, o_out, out.sF, SB_VEC(out), f, d.F, o);
   }
 }
 
 // LayerNorm backward-data + dropout backward; one warp per token.
-template <int NV>
+template <int NV, bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresid, View3 dlin) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -257,9 +268,9 @@ blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresi
   for (int i = 0; i < NV; ++i) {
     const int f = (lane + kWarp * i) * 8;
     if (f < d.F) {
-      load8h(dln.p, o_g, dln.sF, dln.vec, f, d.F, g[i]);
-      load8h(diff.p, o_d, diff.sF, diff.vec, f, d.F, df[i]);
-      load8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+      load8h(dln.p, o_g, dln.sF, SB_VEC(dln), f, d.F, g[i]);
+      load8h(diff.p, o_d, diff.sF, SB_VEC(diff), f, d.F, df[i]);
+      load8m(mask.p, o_m, mask.sF, SB_VEC(mask), f, d.F, m[i]);
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) { g[i][e] = 0.f; df[i][e] = 0.f; m[i][e] = 0u; }
@@ -288,8 +299,8 @@ blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresi
       dr[e] = g[i][e] * s - c1 - df[i][e] * c2;
       dl[e] = m[i][e] ? dr[e] : 0.f;
     }
-    store8h(dresid.p, o_r, dresid.sF, dresid.vec, f, d.F, dr);
-    store8h(dlin.p, o_l, dlin.sF, dlin.vec, f, d.F, dl);
+    store8h(dresid.p, o_r, dresid.sF, SB_VEC(dresid), f, d.F, dr);
+    store8h(dlin.p, o_l, dlin.sF, SB_VEC(dlin), f, d.F, dl);
   }
 }
 
@@ -299,6 +310,7 @@ blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresi
 // ---------------------------------------------------------------------------
 constexpr int kEwNV = 4;
 
+template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin1, View3 drop2,
            int activation, Rng rng, int pvec) {
@@ -317,8 +329,8 @@ bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin
   for (int i = 0; i < kEwNV; ++i) {
     const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
     if (f < d.F) {
-      load8h(in.p, o_in, in.sF, in.vec, f, d.F, x[i]);
-      if (!rng.philox) load8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+      load8h(in.p, o_in, in.sF, SB_VEC(in), f, d.F, x[i]);
+      if (!rng.philox) load8m(mask.p, o_m, mask.sF, SB_VEC(mask), f, d.F, m[i]);
     }
   }
 #pragma unroll
@@ -326,21 +338,22 @@ bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin
     const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
     if (f >= d.F) continue;
     float bs[8], o[8];
-    load8p(bias, f, d.F, pvec, bs);
+    load8p(bias, f, d.F, AV || pvec, bs);
     if (rng.philox) {
-      philox_keep8_unaligned(rng, (unsigned long long)row * d.F + f, m[i]);
-      store8m(mask.p, o_m, mask.sF, mask.vec, f, d.F, m[i]);
+      philox8<AV>(rng, (unsigned long long)row * d.F + f, m[i]);
+      store8m(mask.p, o_m, mask.sF, SB_VEC(mask), f, d.F, m[i]);
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       x[i][e] += bs[e];
       o[e] = m[i][e] ? act_fwd(x[i][e], activation) : 0.f;
     }
-    store8h(lin1.p, o_l, lin1.sF, lin1.vec, f, d.F, x[i]);
-    store8h(drop2.p, o_d, drop2.sF, drop2.vec, f, d.F, o);
+    store8h(lin1.p, o_l, lin1.sF, SB_VEC(lin1), f, d.F, x[i]);
+    store8h(drop2.p, o_d, drop2.sF, SB_VEC(drop2), f, d.F, o);
   }
 }
 
+template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 bei_kernel(Dims3 d, int spans, View3 a, View3 b_, View3 out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -357,8 +370,8 @@ bei_kernel(Dims3 d, int spans, View3 a, View3 b_, View3 out) {
   for (int i = 0; i < kEwNV; ++i) {
     const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
     if (f < d.F) {
-      load8h(a.p, o_a, a.sF, a.vec, f, d.F, x[i]);
-      load8h(b_.p, o_b, b_.sF, b_.vec, f, d.F, y[i]);
+      load8h(a.p, o_a, a.sF, SB_VEC(a), f, d.F, x[i]);
+      load8h(b_.p, o_b, b_.sF, SB_VEC(b_), f, d.F, y[i]);
     }
   }
 #pragma unroll
@@ -367,11 +380,12 @@ bei_kernel(Dims3 d, int spans, View3 a, View3 b_, View3 out) {
     if (f >= d.F) continue;
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[i][e] += y[i][e];
-    store8h(out.p, o_o, out.sF, out.vec, f, d.F, x[i]);
+    store8h(out.p, o_o, out.sF, SB_VEC(out), f, d.F, x[i]);
   }
 }
 
 // out[n,p,h,b,j] = in[n,p,h,b,j] + bias[n,p,h]; a warp takes one (n,p,h,b) row and a span of J.
+template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long long bsP,
            long long bsH, View5 out) {
@@ -392,7 +406,7 @@ aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long l
 #pragma unroll
   for (int i = 0; i < kEwNV; ++i) {
     const int f = span * (kEwNV * 256) + (lane + kWarp * i) * 8;
-    if (f < d.J) load8h(in.p, o_in, in.sJ, in.vec, f, d.J, x[i]);
+    if (f < d.J) load8h(in.p, o_in, in.sJ, SB_VEC(in), f, d.J, x[i]);
   }
 #pragma unroll
   for (int i = 0; i < kEwNV; ++i) {
@@ -400,11 +414,12 @@ aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long l
     if (f >= d.J) continue;
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[i][e] += bv;
-    store8h(out.p, o_out, out.sJ, out.vec, f, d.J, x[i]);
+    store8h(out.p, o_out, out.sJ, SB_VEC(out), f, d.J, x[i]);
   }
 }
 
 // dbias[n,p,h] = sum_{b,j} in[n,p,h,b,j]; one CTA per output element.
+template <bool AV>
 __global__ void __launch_bounds__(kColThreads)
 baib_kernel(Dims5 d, View5 in, void* dbias, long long bsN, long long bsP, long long bsH) {
   long long row = blockIdx.x;
@@ -418,7 +433,7 @@ baib_kernel(Dims5 d, View5 in, void* dbias, long long bsN, long long bsP, long l
     const int b = (int)(idx / groups);
     const int f = (int)(idx % groups) * 8;
     float x[8];
-    load8h(in.p, base + b * in.sB, in.sJ, in.vec, f, d.J, x);
+    load8h(in.p, base + b * in.sB, in.sJ, SB_VEC(in), f, d.J, x);
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc += x[e];
   }
@@ -443,92 +458,119 @@ struct ColOut {
   void* out[NQ];  // fp16 [F], unit stride
 };
 
+// Each operator supplies: NQ reduced quantities, NIN fp16 inputs per row, whether it reads a
+// mask, load<AV>() of one row's eight features and finish<AV>() = elementwise output + accumulate.
+template <int NIN>
+struct RowRegs {
+  float v[NIN][8];
+  uint32_t m[8];
+};
+
 struct BsbOp {
-  static constexpr int NQ = 2;
+  static constexpr int NQ = 2, NIN = 2;
   View3 dy, ln, dln;
   const void* gamma;
   int pvec;
-  __device__ __forceinline__ void row(int b, int j, int f, int F, const float gm[8],
-                                      float acc[NQ][8]) const {
-    float y[8], n[8], o[8];
-    load8h(dy.p, b * dy.sB + j * dy.sJ, dy.sF, dy.vec, f, F, y);
-    load8h(ln.p, b * ln.sB + j * ln.sJ, ln.sF, ln.vec, f, F, n);
+  template <bool AV>
+  __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
+    load8h(dy.p, b * dy.sB + j * dy.sJ, dy.sF, SB_VEC(dy), f, F, r.v[0]);
+    load8h(ln.p, b * ln.sB + j * ln.sJ, ln.sF, SB_VEC(ln), f, F, r.v[1]);
+  }
+  template <bool AV>
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float gm[8],
+                                         const RowRegs<NIN>& r, float acc[NQ][8]) const {
+    float o[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      o[e] = y[e] * gm[e];
-      acc[0][e] += y[e] * n[e];
-      acc[1][e] += y[e];
+      o[e] = r.v[0][e] * gm[e];
+      acc[0][e] += r.v[0][e] * r.v[1][e];
+      acc[1][e] += r.v[0][e];
     }
-    store8h(dln.p, b * dln.sB + j * dln.sJ, dln.sF, dln.vec, f, F, o);
+    store8h(dln.p, b * dln.sB + j * dln.sJ, dln.sF, SB_VEC(dln), f, F, o);
   }
-  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, pvec, gm); }
+  template <bool AV>
+  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, AV || pvec, gm); }
 };
 
 struct EbsbOp {
-  static constexpr int NQ = 3;
+  static constexpr int NQ = 3, NIN = 4;
   View3 ln1, dresid2, dlw, dlin2, dln1;
   const void* gamma;
   int pvec;
-  __device__ __forceinline__ void row(int b, int j, int f, int F, const float gm[8],
-                                      float acc[NQ][8]) const {
-    float n[8], r[8], w[8], l2[8], o[8];
-    load8h(ln1.p, b * ln1.sB + j * ln1.sJ, ln1.sF, ln1.vec, f, F, n);
-    load8h(dresid2.p, b * dresid2.sB + j * dresid2.sJ, dresid2.sF, dresid2.vec, f, F, r);
-    load8h(dlw.p, b * dlw.sB + j * dlw.sJ, dlw.sF, dlw.vec, f, F, w);
-    load8h(dlin2.p, b * dlin2.sB + j * dlin2.sJ, dlin2.sF, dlin2.vec, f, F, l2);
+  template <bool AV>
+  __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
+    load8h(ln1.p, b * ln1.sB + j * ln1.sJ, ln1.sF, SB_VEC(ln1), f, F, r.v[0]);
+    load8h(dresid2.p, b * dresid2.sB + j * dresid2.sJ, dresid2.sF, SB_VEC(dresid2), f, F, r.v[1]);
+    load8h(dlw.p, b * dlw.sB + j * dlw.sJ, dlw.sF, SB_VEC(dlw), f, F, r.v[2]);
+    load8h(dlin2.p, b * dlin2.sB + j * dlin2.sJ, dlin2.sF, SB_VEC(dlin2), f, F, r.v[3]);
+  }
+  template <bool AV>
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float gm[8],
+                                         const RowRegs<NIN>& r, float acc[NQ][8]) const {
+    float o[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float g = r[e] + w[e];
+      const float g = r.v[1][e] + r.v[2][e];
       o[e] = g * gm[e];
-      acc[0][e] += g * n[e];
+      acc[0][e] += g * r.v[0][e];
       acc[1][e] += g;
-      acc[2][e] += l2[e];
+      acc[2][e] += r.v[3][e];
     }
-    store8h(dln1.p, b * dln1.sB + j * dln1.sJ, dln1.sF, dln1.vec, f, F, o);
+    store8h(dln1.p, b * dln1.sB + j * dln1.sJ, dln1.sF, SB_VEC(dln1), f, F, o);
   }
-  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, pvec, gm); }
+  template <bool AV>
+  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, AV || pvec, gm); }
 };
 
 struct BdrlbOp {
-  static constexpr int NQ = 1;
+  static constexpr int NQ = 1, NIN = 2;
   View3 ddrop2, mask, lin1, dlin1;
   int activation;
-  __device__ __forceinline__ void row(int b, int j, int f, int F, const float[8],
-                                      float acc[NQ][8]) const {
-    float g[8], x[8], o[8];
-    uint32_t m[8];
-    load8h(ddrop2.p, b * ddrop2.sB + j * ddrop2.sJ, ddrop2.sF, ddrop2.vec, f, F, g);
-    load8h(lin1.p, b * lin1.sB + j * lin1.sJ, lin1.sF, lin1.vec, f, F, x);
-    load8m(mask.p, b * mask.sB + j * mask.sJ, mask.sF, mask.vec, f, F, m);
+  template <bool AV>
+  __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
+    load8h(ddrop2.p, b * ddrop2.sB + j * ddrop2.sJ, ddrop2.sF, SB_VEC(ddrop2), f, F, r.v[0]);
+    load8h(lin1.p, b * lin1.sB + j * lin1.sJ, lin1.sF, SB_VEC(lin1), f, F, r.v[1]);
+    load8m(mask.p, b * mask.sB + j * mask.sJ, mask.sF, SB_VEC(mask), f, F, r.m);
+  }
+  template <bool AV>
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float[8],
+                                         const RowRegs<NIN>& r, float acc[NQ][8]) const {
+    float o[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      o[e] = (f + e < F) ? act_bwd(x[e], m[e] ? g[e] : 0.f, activation) : 0.f;
+      o[e] = (f + e < F) ? act_bwd(r.v[1][e], r.m[e] ? r.v[0][e] : 0.f, activation) : 0.f;
       acc[0][e] += o[e];
     }
-    store8h(dlin1.p, b * dlin1.sB + j * dlin1.sJ, dlin1.sF, dlin1.vec, f, F, o);
+    store8h(dlin1.p, b * dlin1.sB + j * dlin1.sJ, dlin1.sF, SB_VEC(dlin1), f, F, o);
   }
+  template <bool AV>
   __device__ __forceinline__ void scale(int, int, float[8]) const {}
 };
 
 struct BaobOp {
-  static constexpr int NQ = 1;
+  static constexpr int NQ = 1, NIN = 1;
   View3 datt;
-  __device__ __forceinline__ void row(int b, int j, int f, int F, const float[8],
-                                      float acc[NQ][8]) const {
-    float x[8];
-    load8h(datt.p, b * datt.sB + j * datt.sJ, datt.sF, datt.vec, f, F, x);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[0][e] += x[e];
+  template <bool AV>
+  __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
+    load8h(datt.p, b * datt.sB + j * datt.sJ, datt.sF, SB_VEC(datt), f, F, r.v[0]);
   }
+  template <bool AV>
+  __device__ __forceinline__ void finish(int, int, int, int, const float[8], const RowRegs<NIN>& r,
+                                         float acc[NQ][8]) const {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[0][e] += r.v[0][e];
+  }
+  template <bool AV>
   __device__ __forceinline__ void scale(int, int, float[8]) const {}
 };
 
-template <class Op>
+template <class Op, bool AV>
 __global__ void __launch_bounds__(kColThreads)
 colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* counters,
                  ColOut<Op::NQ> outs) {
   constexpr int NQ = Op::NQ;
   constexpr int NW = kColThreads / kWarp;
+  constexpr int UNR = 4;  // rows in flight per warp
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slice = blockIdx.x, chunk = blockIdx.y, P = gridDim.y;
   const int Fp = gridDim.x * 256;
@@ -544,10 +586,19 @@ colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* c
     for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
   if (f < d.F) {
     float gm[8];
-    op.scale(f, d.F, gm);
-    for (long long r = r0 + warp; r < r1; r += NW) {
-      const int b = (int)(r / d.J), j = (int)(r % d.J);
-      op.row(b, j, f, d.F, gm, acc);
+    op.template scale<AV>(f, d.F, gm);
+    for (long long r = r0 + warp; r < r1; r += NW * UNR) {
+      RowRegs<Op::NIN> regs[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long rr = r + (long long)u * NW;
+        if (rr < r1) op.template load<AV>((int)(rr / d.J), (int)(rr % d.J), f, d.F, regs[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long rr = r + (long long)u * NW;
+        if (rr < r1) op.template finish<AV>((int)(rr / d.J), (int)(rr % d.J), f, d.F, gm, regs[u], acc);
+      }
     }
   }
   __shared__ float sm[NW][NQ][256];
@@ -601,7 +652,7 @@ colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* c
 }
 
 template <class Op>
-int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op::NQ> outs) {
+int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op::NQ> outs, bool all_vec) {
   if (!ws) return fail(SB_ERR_ARG, "token-reduction operator called without a workspace");
   const int slices = (d.F + 255) / 256;
   if (slices > (int)(kWsCounterBytes / sizeof(unsigned)))
@@ -620,7 +671,8 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
   unsigned* counters = reinterpret_cast<unsigned*>(ws);
   float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
   dim3 grid(slices, (unsigned)P);
-  colreduce_kernel<Op><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  if (all_vec) colreduce_kernel<Op, true><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  else colreduce_kernel<Op, false><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -637,60 +689,82 @@ int param_vec(std::initializer_list<const void*> ptrs, int F) {
 // ---------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------
-#define SB_SOFTMAX_CASES(KERNEL, ...)                                                        \
-  do {                                                                                       \
-    const long long R = (long long)d.H * d.B * d.J;                                          \
-    if (R == 0 || d.K == 0) return SB_OK;                                                    \
+template <class... V>
+bool all_vec(const V&... v) {
+  return ((v.vec != 0) && ...);
+}
+
+#define SB_SOFTMAX_LAUNCH(KERNEL, AVFLAG, ...)                                                     \
+  do {                                                                                             \
     auto blocks = [&](int lpr) { return (unsigned)((R + 4 * (32 / lpr) - 1) / (4 * (32 / lpr))); }; \
-    if (d.K <= 64) KERNEL<8, 1><<<blocks(8), kRowThreads, 0, s>>>(__VA_ARGS__);              \
-    else if (d.K <= 128) KERNEL<16, 1><<<blocks(16), kRowThreads, 0, s>>>(__VA_ARGS__);      \
-    else if (d.K <= 256) KERNEL<32, 1><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);      \
-    else if (d.K <= 512) KERNEL<32, 2><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);      \
-    else if (d.K <= 1024) KERNEL<32, 4><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);     \
-    else if (d.K <= 2048) KERNEL<32, 8><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);     \
-    else                                                                                     \
-      return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");    \
-    SB_CUDA_OK(cudaGetLastError());                                                          \
+    if (d.K <= 64) KERNEL<8, 1, AVFLAG><<<blocks(8), kRowThreads, 0, s>>>(__VA_ARGS__);            \
+    else if (d.K <= 128) KERNEL<16, 1, AVFLAG><<<blocks(16), kRowThreads, 0, s>>>(__VA_ARGS__);    \
+    else if (d.K <= 256) KERNEL<32, 1, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);    \
+    else if (d.K <= 512) KERNEL<32, 2, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);    \
+    else if (d.K <= 1024) KERNEL<32, 4, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);   \
+    else KERNEL<32, 8, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);                    \
   } while (0)
 
 int launch_softmax_fwd(cudaStream_t s, Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop,
                        float scale, Rng rng) {
-  SB_SOFTMAX_CASES(softmax_fwd_kernel, d, beta, alpha, mask, drop, scale, rng);
+  const long long R = (long long)d.H * d.B * d.J;
+  if (R == 0 || d.K == 0) return SB_OK;
+  if (d.K > 2048) return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");
+  if (all_vec(beta, alpha, mask, drop))
+    SB_SOFTMAX_LAUNCH(softmax_fwd_kernel, true, d, beta, alpha, mask, drop, scale, rng);
+  else
+    SB_SOFTMAX_LAUNCH(softmax_fwd_kernel, false, d, beta, alpha, mask, drop, scale, rng);
+  SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
 
 int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 dattn_drop,
                        View4 dbeta) {
-  SB_SOFTMAX_CASES(softmax_bwd_kernel, d, alpha, mask, dattn_drop, dbeta);
+  const long long R = (long long)d.H * d.B * d.J;
+  if (R == 0 || d.K == 0) return SB_OK;
+  if (d.K > 2048) return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");
+  if (all_vec(alpha, mask, dattn_drop, dbeta))
+    SB_SOFTMAX_LAUNCH(softmax_bwd_kernel, true, d, alpha, mask, dattn_drop, dbeta);
+  else
+    SB_SOFTMAX_LAUNCH(softmax_bwd_kernel, false, d, alpha, mask, dattn_drop, dbeta);
+  SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
 
-#define SB_ROW_CASES(KERNEL, F, ...)                                                      \
-  do {                                                                                    \
-    const long long R = (long long)d.B * d.J;                                             \
-    if (R == 0 || (F) == 0) return SB_OK;                                                 \
-    const unsigned blocks = (unsigned)((R + 3) / 4);                                      \
-    if ((F) <= 256) KERNEL<1><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);                \
-    else if ((F) <= 512) KERNEL<2><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);           \
-    else if ((F) <= 1024) KERNEL<4><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);          \
-    else if ((F) <= 2048) KERNEL<8><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);          \
-    else                                                                                  \
-      return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported"); \
-    SB_CUDA_OK(cudaGetLastError());                                                       \
+#define SB_ROW_LAUNCH(KERNEL, AVFLAG, F, ...)                                    \
+  do {                                                                           \
+    const unsigned blocks = (unsigned)((R + 3) / 4);                             \
+    if ((F) <= 256) KERNEL<1, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);       \
+    else if ((F) <= 512) KERNEL<2, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);  \
+    else if ((F) <= 1024) KERNEL<4, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__); \
+    else KERNEL<8, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);                  \
   } while (0)
 
 int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid,
                  const void* gamma, const void* beta, View3 mask, View3 lin, View3 diff,
                  View2 istd, View3 ln, View3 out, Rng rng) {
+  const long long R = (long long)d.B * d.J;
+  if (R == 0 || d.F == 0) return SB_OK;
+  if (d.F > 2048) return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported");
   const int pvec = param_vec({bias, gamma, beta}, d.F);
-  SB_ROW_CASES(bdrln_kernel, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out,
-               rng, pvec);
+  if (pvec && all_vec(in, resid, mask, lin, diff, ln, out))
+    SB_ROW_LAUNCH(bdrln_kernel, true, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out, rng, pvec);
+  else
+    SB_ROW_LAUNCH(bdrln_kernel, false, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out, rng, pvec);
+  SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
 
 int launch_blnrd(cudaStream_t s, Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask,
                  View3 dresid, View3 dlin) {
-  SB_ROW_CASES(blnrd_kernel, d.F, d, dln, istd, diff, mask, dresid, dlin);
+  const long long R = (long long)d.B * d.J;
+  if (R == 0 || d.F == 0) return SB_OK;
+  if (d.F > 2048) return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported");
+  if (all_vec(dln, diff, mask, dresid, dlin))
+    SB_ROW_LAUNCH(blnrd_kernel, true, d.F, d, dln, istd, diff, mask, dresid, dlin);
+  else
+    SB_ROW_LAUNCH(blnrd_kernel, false, d.F, d, dln, istd, diff, mask, dresid, dlin);
+  SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
 
@@ -700,8 +774,11 @@ int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, 
   if (R == 0 || d.F == 0) return SB_OK;
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  bad_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng,
-                                            param_vec({bias}, d.F));
+  const int pvec = param_vec({bias}, d.F);
+  if (pvec && all_vec(in, mask, lin1, drop2))
+    bad_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec);
+  else
+    bad_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -711,7 +788,8 @@ int launch_bei(cudaStream_t s, Dims3 d, View3 a, View3 b, View3 out) {
   if (R == 0 || d.F == 0) return SB_OK;
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  bei_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
+  if (all_vec(a, b, out)) bei_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
+  else bei_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -722,7 +800,8 @@ int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bs
   if (R == 0 || d.J == 0) return SB_OK;
   const int spans = (d.J + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  aib_kernel<<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
+  if (all_vec(in, out)) aib_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
+  else aib_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -731,7 +810,8 @@ int launch_baib(cudaStream_t s, Dims5 d, View5 in, void* dbias, long long bsN, l
                 long long bsH) {
   const long long R = (long long)d.N * d.P * d.H;
   if (R == 0) return SB_OK;
-  baib_kernel<<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
+  if (all_vec(in)) baib_kernel<true><<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
+  else baib_kernel<false><<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -740,7 +820,7 @@ int launch_bsb(cudaStream_t s, void* ws, Dims3 d, View3 dy, View3 ln, const void
                View3 dln, void* dgamma, void* dbeta) {
   BsbOp op{dy, ln, dln, gamma, param_vec({gamma}, d.F)};
   ColOut<2> outs{{dgamma, dbeta}};
-  return launch_colreduce(s, ws, d, op, outs);
+  return launch_colreduce(s, ws, d, op, outs, op.pvec && all_vec(dy, ln, dln));
 }
 
 int launch_ebsb(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gamma1, View3 dresid2,
@@ -748,20 +828,20 @@ int launch_ebsb(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gamma1
                 void* dlinb2) {
   EbsbOp op{ln1, dresid2, dlin1_linw1, dlin2, dln1, gamma1, param_vec({gamma1}, d.F)};
   ColOut<3> outs{{dgamma1, dbeta1, dlinb2}};
-  return launch_colreduce(s, ws, d, op, outs);
+  return launch_colreduce(s, ws, d, op, outs, op.pvec && all_vec(ln1, dresid2, dlin1_linw1, dlin2, dln1));
 }
 
 int launch_bdrlb(cudaStream_t s, void* ws, Dims3 d, View3 ddrop2, View3 mask, View3 lin1,
                  View3 dlin1, void* dbias, int activation) {
   BdrlbOp op{ddrop2, mask, lin1, dlin1, activation};
   ColOut<1> outs{{dbias}};
-  return launch_colreduce(s, ws, d, op, outs);
+  return launch_colreduce(s, ws, d, op, outs, all_vec(ddrop2, mask, lin1, dlin1));
 }
 
 int launch_baob(cudaStream_t s, void* ws, Dims3 d, View3 datt, void* dbo) {
   BaobOp op{datt};
   ColOut<1> outs{{dbo}};
-  return launch_colreduce(s, ws, d, op, outs);
+  return launch_colreduce(s, ws, d, op, outs, all_vec(datt));
 }
 
 }  // namespace sb

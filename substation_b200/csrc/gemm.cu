@@ -4,7 +4,8 @@
 //   C[b,m,n] = alpha * sum_k A[b,m,k] * B[b,n,k]
 // with independent strides for every index of every operand.
 //
-// gemm_tc_kernel: the sm_100a path.  One CTA computes a 128 x BN tile:
+// gemm_tc_kernel: the sm_100a path.  Persistent CTAs (one per SM) walk 128 x BN output tiles;
+// two TMEM accumulators let the epilogue of one tile overlap the MMAs of the next:
 //   warp 0   : TMA producer, cp.async.bulk.tensor into a ring of 128-byte-swizzled
 //              shared-memory stages (every CTA fetches its own tiles), completion on
 //              mbarriers;
@@ -246,6 +247,8 @@ struct TcParams {
   int a_mn, b_mn;      // operand is MN-major in global memory
   int a_swap, b_swap;  // tensor-map dims 1 and 2 are exchanged (kept in increasing-stride order)
   int c_vec;           // sCn == 1 and rows are 16-byte aligned
+  int tiles_m, tiles_n;
+  long long tiles;     // tiles_m * tiles_n * batch
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -328,9 +331,15 @@ struct TcCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators: the epilogue of one tile overlaps the next tile's MMAs
   static constexpr int kSmemBytes = kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent: CTA c works on tiles c, c + gridDim.x, ... (n fastest, then m, then batch).
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -340,12 +349,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const uint32_t bars = tiles + Cfg::kTileBytes;       // full[S], empty[S], tmem_full
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * S, bar_acc = bars + 16 * S;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (tiles - raw) + Cfg::kTileBytes + 16 * S + 8);
+  const uint32_t bars = tiles + Cfg::kTileBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * S;
+  const uint32_t bar_accf = bars + 16 * S, bar_acce = bars + 16 * S + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (tiles - raw) + Cfg::kTileBytes + 16 * S + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kBM, bt = blockIdx.z;
   const int KT = (int)((p.K + kBK - 1) / kBK);
 
   if (threadIdx.x == 0) {
@@ -353,7 +362,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_accf + 8 * b, 1);
+      mbar_init(bar_acce + 8 * b, 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
@@ -361,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -371,40 +383,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // ---------------- TMA producer (whole warp walks the loop, lane 0 issues) ----------------
-    for (int kt = 0; kt < KT; ++kt) {
-      const int s = kt % S;
-      const uint32_t ph = (uint32_t)(kt / S) & 1u;
-      const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
-      if (!ok) break;
-      if (lane == 0) {
-        const uint32_t full = bar_full + 8 * s;
-        mbar_expect_tx(full, (uint32_t)Cfg::kStageBytes);
-        const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
-        const int k0 = kt * kBK;
-        if (!p.a_mn) {
-          // dims (k, m, batch), box 64 x 128
-          if (p.a_swap) tma_load_3d(sa, &tmA, full, k0, bt, m0);
-          else tma_load_3d(sa, &tmA, full, k0, m0, bt);
-        } else {
-          // dims (m, k, batch), two boxes of 64 (m) x 64 (k)
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+      const int n0 = (int)(t % p.tiles_n) * BN;
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * kBM;
+      const int bt = (int)(t / ((long long)p.tiles_n * p.tiles_m));
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = bar_full + 8 * s;
+          mbar_expect_tx(full, (uint32_t)Cfg::kStageBytes);
+          const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
+          const int k0 = kt * kBK;
+          if (!p.a_mn) {
+            // dims (k, m, batch), box 64 x 128
+            if (p.a_swap) tma_load_3d(sa, &tmA, full, k0, bt, m0);
+            else tma_load_3d(sa, &tmA, full, k0, m0, bt);
+          } else {
+            // dims (m, k, batch), two boxes of 64 (m) x 64 (k)
 #pragma unroll
-          for (int h = 0; h < kBM / 64; ++h) {
-            if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
-            else tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+            for (int h = 0; h < kBM / 64; ++h) {
+              if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
+              else tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+            }
+          }
+          if (!p.b_mn) {
+            if (p.b_swap) tma_load_3d(sb_, &tmB, full, k0, bt, n0);
+            else tma_load_3d(sb_, &tmB, full, k0, n0, bt);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h) {
+              if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
+              else tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
+            }
           }
         }
-        if (!p.b_mn) {
-          if (p.b_swap) tma_load_3d(sb_, &tmB, full, k0, bt, n0);
-          else tma_load_3d(sb_, &tmB, full, k0, n0, bt);
-        } else {
-#pragma unroll
-          for (int h = 0; h < BN / 64; ++h) {
-            if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
-            else tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
-          }
-        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (whole warp walks the loop, lane 0 issues) ----------------
@@ -416,39 +435,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // MN-major: 64-wide MN blocks 8192 B apart (LBO), 8-row K groups 1024 B apart, 2048 B per K step.
     const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
     const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
+    uint32_t it = 0, lt = 0;
     bool ok = true;
-    for (int kt = 0; kt < KT; ++kt) {
-      const int s = kt % S;
-      const uint32_t ph = (uint32_t)(kt / S) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
+      // the epilogue must have drained this accumulator (passes at once for its first use)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_acce + 8 * buf, aph ^ 1u, 4));
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0) {
-        const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
 #pragma unroll
-        for (int k = 0; k < kBK / 16; ++k) {
-          const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
-          const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
-          umma_f16(tmem_base, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
+            const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
+            umma_f16(tmem_d, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
         }
-        umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+        __syncwarp();
       }
+      if (ok && lane == 0) umma_commit(bar_accf + 8 * buf);
       __syncwarp();
     }
-    if (ok && lane == 0) umma_commit(bar_acc);
-    __syncwarp();
   } else {
-    // ---------------- epilogue ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const bool ok = mbar_wait(bar_acc, 0u, 3);
-    tc_fence_after();
-    if (ok) {
+    // ---------------- epilogue (4 warps; warp w reads TMEM lanes 32*(w%4)..+31) ----------------
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++lt) {
+      const int n0 = (int)(t % p.tiles_n) * BN;
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * kBM;
+      const long long bt = t / ((long long)p.tiles_n * p.tiles_m);
+      const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_accf + 8 * buf, aph, 3));
+      if (!ok) break;
+      tc_fence_after();
       const long long m = (long long)m0 + q * 32 + lane;
-      __half* crow = p.C + (long long)bt * p.sCb + m * p.sCm;
+      __half* crow = p.C + bt * p.sCb + m * p.sCm;
+      const uint32_t tsrc = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld32(tsrc + (uint32_t)(c * 32), r);
+        if (c == BN / 32 - 1) {
+          // accumulator fully read into registers: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acce + 8 * buf);
+        }
         if (m < p.M) {
           const long long nb = (long long)n0 + c * 32;
           if (p.c_vec) {
@@ -479,7 +521,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
   }
 }
 
@@ -546,17 +588,22 @@ bool make_operand_map(const void* ptr, long long R, long long K, long long batch
   return true;
 }
 
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    cached_dev = dev;
+  }
+  return cached > 0 ? cached : 148;
+}
+
 template <int BN>
 int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b) {
   using Cfg = TcCfg<BN>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-  });
-  // the attribute is per device; set it again when the current device differs (cheap, idempotent)
+  // per-device attribute; setting it is cheap and idempotent
   SB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  (void)attr_err;
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
@@ -565,7 +612,10 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
   p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
   p.c_vec = (g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && g.sCb % 8 == 0 &&
              (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0) ? 1 : 0;
-  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + kBM - 1) / kBM), (unsigned)g.batch);
+  p.tiles_n = (int)((g.N + BN - 1) / BN);
+  p.tiles_m = (int)((g.M + kBM - 1) / kBM);
+  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
+  const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
   gemm_tc_kernel<BN><<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(a.map, b.map, p);
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
@@ -594,7 +644,6 @@ long long padded_work(long long M, long long N) {
 }  // namespace
 
 bool tcgen05_supported(const GemmProblem& g, std::string* why) {
-  if (g.batch > 65535) { *why = "more than 65535 batches"; return false; }
   if (g.K < 1 || g.M < 1 || g.N < 1) { *why = "empty problem"; return false; }
   if (!(g.sAk == 1 || g.sAm == 1 || g.K == 1)) { *why = "A has no unit-stride index"; return false; }
   if (!(g.sBk == 1 || g.sBn == 1 || g.K == 1)) { *why = "B has no unit-stride index"; return false; }
