@@ -622,16 +622,16 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
 }
 
 int pick_bn(long long M, long long N, long long batch) {
-  // Largest tile that still yields at least one CTA per SM; otherwise the one with most CTAs
-  // that does not pad N by more than it has to.
+  // 128 x 256 moves the fewest operand bytes per flop (each CTA fetches its own tiles), so it is
+  // used whenever N fills most of it and the persistent grid still covers about half the SMs.
   const long long mt = (M + kBM - 1) / kBM;
-  for (int bn : {256, 128, 64}) {
-    if (N <= bn / 2 && bn > 64) continue;
-    const long long ctas = mt * ((N + bn - 1) / bn) * batch;
-    if (ctas >= 148) return bn;
-  }
   if (N <= 64) return 64;
   if (N <= 128) return 128;
+  const long long t256 = mt * ((N + 255) / 256) * batch;
+  const bool fills = (N % 256 == 0) || (N % 256 > 128) || N >= 1024;
+  if (fills && t256 >= 64) return 256;
+  const long long t128 = mt * ((N + 127) / 128) * batch;
+  if (t128 >= 64 || N % 128 == 0 || N % 128 > 64) return 128;
   return 64;
 }
 
