@@ -163,6 +163,22 @@ int sb_extended_backward_scale_bias(void* stream, void* workspace, const sb_tens
 int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* datt,
                               const sb_tensor* dbo);
 
+/* The same sum as sb_backward_attn_out_bias for callers that cannot provide a
+ * workspace or reach the CUDA allocator (a plugin handed only inputs and outputs,
+ * a process whose device heap is sealed after start-up).  This entry point has
+ * no counterpart in the reference.  It makes no allocation of any kind: the
+ * fp32 partial sums live in a 1 MiB + 4 KiB device array built into the library
+ * (every GPU that loads the library holds it until the process exits).
+ * Limits and rules:
+ *   - the feature extent (last dim of datt) may be at most 16384, larger ones are
+ *     refused with SB_ERR_UNSUPPORTED; any number of tokens is fine;
+ *   - the first call on each device looks up that device's copy of the array
+ *     (the stream's device must be current); make that first call outside of any
+ *     stream capture;
+ *   - all calls on a device share the one array, so two calls that may overlap
+ *     on the GPU (different streams) race; serialise them. */
+int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* datt, const sb_tensor* dbo);
+
 /* dbeta = alpha*(da - sum_k da*alpha), da = mask*dattn_drop.  All [H,B,J,K].
  * Replaces BackwardSoftmax::run, pytorch_module/block_bs.cuh:100-156. */
 int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,

@@ -66,6 +66,7 @@ SIGNATURES = {
     'sb_backward_dropout_activation_bias': (c_int, [c_void_p, c_void_p] + [_T] * 5 + [c_int]),
     'sb_extended_backward_scale_bias': (c_int, [c_void_p, c_void_p] + [_T] * 9),
     'sb_backward_attn_out_bias': (c_int, [c_void_p, c_void_p, _T, _T]),
+    'sb_backward_attn_out_bias_noalloc': (c_int, [c_void_p, _T, _T]),
     'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
     'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
     'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),

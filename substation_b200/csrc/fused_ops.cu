@@ -11,6 +11,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 #include "ops.h"
 
 namespace sb {
@@ -844,4 +846,92 @@ int launch_baob(cudaStream_t s, void* ws, Dims3 d, View3 datt, void* dbo) {
   return launch_colreduce(s, ws, d, op, outs, all_vec(datt));
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the attention-output-bias gradient.
+//
+// Some hosts cannot hand this library a workspace: a plugin that is only ever given
+// its inputs and outputs, a runtime whose device heap is owned by another component
+// and locked after start-up, a caller that is not allowed to touch the CUDA
+// allocator from the thread it runs on.  For them the fp32 partial sums and the
+// ticket counters live in a fixed device array that is part of the library image:
+// every GPU that loads the library carries these bytes until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticPartialBytes = 1u << 20;                              // 1 MiB of partial sums
+constexpr size_t kStaticScratchBytes = kWsCounterBytes + kStaticPartialBytes;  // + 4 KiB of counters
+constexpr int kStaticMaxFeatures = 16384;
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char sb_static_scratch[kStaticScratchBytes];
+
+// In host code `sb_static_scratch` is only a handle for the runtime, never a device pointer;
+// the address each device sees is asked for once, with that device current, and remembered.
+void* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  SB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SB_ERR_UNSUPPORTED, "device ordinal beyond the per-device scratch table");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    SB_CUDA_OK(cudaGetSymbolAddress(&ptr, sb_static_scratch));
+    if (!ptr) return fail(SB_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SB_OK;
+}
+
+}  // namespace
 }  // namespace sb
+
+extern "C" int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* datt, const sb_tensor* dbo) {
+  using namespace sb;
+  if (!datt || !dbo) return fail(SB_ERR_ARG, "baob (no-alloc): null tensor");
+  if (datt->ndim != 3 || dbo->ndim != 1) return fail(SB_ERR_ARG, "baob (no-alloc): datt must have rank 3 and dbo rank 1");
+  for (int i = 0; i < 3; ++i)
+    if (datt->size[i] < 0 || datt->size[i] > 0x7fffffffLL) return fail(SB_ERR_ARG, "baob (no-alloc): extent out of range");
+  const long long B = datt->size[0], J = datt->size[1], F = datt->size[2];
+  if (dbo->size[0] != F) return fail(SB_ERR_ARG, "baob (no-alloc): extent mismatch between operands");
+  if (F > kStaticMaxFeatures)
+    return fail(SB_ERR_UNSUPPORTED, "baob (no-alloc): feature extent " + std::to_string(F) +
+                                        " exceeds the built-in scratch limit of " + std::to_string(kStaticMaxFeatures) +
+                                        "; use sb_backward_attn_out_bias with a caller workspace");
+  if (F > 1 && dbo->stride[0] != 1) return fail(SB_ERR_UNSUPPORTED, "baob (no-alloc): dbo must be contiguous");
+  if (B * J * F == 0) return SB_OK;
+  if (!datt->ptr || !dbo->ptr) return fail(SB_ERR_ARG, "baob (no-alloc): null data pointer");
+
+  void* scratch = nullptr;
+  SB_TRY(static_scratch_for_current_device(&scratch));
+  cudaStream_t s = (cudaStream_t)stream;
+
+  View3 v;
+  v.p = datt->ptr; v.sB = datt->stride[0]; v.sJ = datt->stride[1]; v.sF = datt->stride[2];
+  v.vec = (v.sF == 1 && F % 8 == 0 && (reinterpret_cast<uintptr_t>(v.p) & 15u) == 0 &&
+           (B <= 1 || v.sB % 8 == 0) && (J <= 1 || v.sJ % 8 == 0)) ? 1 : 0;
+  const Dims3 d{(int)B, (int)J, (int)F};
+  const int slices = (int)((F + 255) / 256);
+  const long long R = B * J, Fp = (long long)slices * 256;
+  long long P = (148 * 4 + slices - 1) / slices;
+  const long long cap = (long long)(kStaticPartialBytes / (Fp * sizeof(float)));  // >= 16 for F <= 16384
+  if (P > cap) P = cap;
+  if (P > (R + 7) / 8) P = (R + 7) / 8;
+  if (P < 1) P = 1;
+  const int rpc = (int)((R + P - 1) / P);
+  P = (R + rpc - 1) / rpc;
+  // The array keeps whatever the previous call left in it.  Partial sums are fully rewritten
+  // before they are read; the ticket counters must start at zero, so clear them on the stream.
+  SB_CUDA_OK(cudaMemsetAsync(scratch, 0, kWsCounterBytes, s));
+  unsigned* counters = reinterpret_cast<unsigned*>(scratch);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kWsCounterBytes);
+  BaobOp op{v};
+  ColOut<1> outs{{dbo->ptr}};
+  dim3 grid(slices, (unsigned)P);
+  if (v.vec) colreduce_kernel<BaobOp, true><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  else colreduce_kernel<BaobOp, false><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
