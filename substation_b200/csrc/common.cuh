@@ -157,6 +157,78 @@ __device__ __forceinline__ void store8m(void* base, long long off, long long sF,
       if (f + e < F) p[(long long)(f + e) * sF] = (uint8_t)m[e];
   }
 }
+// ---- raw forms: eight fp16 values stay packed in one uint4 and eight mask bytes in one
+// uint2 until they are used, so data in flight costs 4 (2) registers per access ------------
+__device__ __forceinline__ uint4 load8h_raw(const void* base, long long off, long long sF, int vec,
+                                            int f, int F) {
+  const __half* p = reinterpret_cast<const __half*>(base) + off;
+  if (vec) return *reinterpret_cast<const uint4*>(p + f);
+  uint4 u;
+  __half* h = reinterpret_cast<__half*>(&u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) h[e] = (f + e < F) ? p[(long long)(f + e) * sF] : __float2half_rn(0.f);
+  return u;
+}
+__device__ __forceinline__ void store8h_raw(void* base, long long off, long long sF, int vec, int f,
+                                            int F, const uint4& u) {
+  __half* p = reinterpret_cast<__half*>(base) + off;
+  if (vec) {
+    *reinterpret_cast<uint4*>(p + f) = u;
+  } else {
+    const __half* h = reinterpret_cast<const __half*>(&u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f + e < F) p[(long long)(f + e) * sF] = h[e];
+  }
+}
+__device__ __forceinline__ uint2 load8m_raw(const void* base, long long off, long long sF, int vec,
+                                            int f, int F) {
+  const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + off;
+  if (vec) return *reinterpret_cast<const uint2*>(p + f);
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (f + e < F) w[e >> 2] |= (uint32_t)p[(long long)(f + e) * sF] << (8 * (e & 3));
+  return make_uint2(w[0], w[1]);
+}
+__device__ __forceinline__ void store8m_raw(void* base, long long off, long long sF, int vec, int f,
+                                            int F, const uint2& u) {
+  uint8_t* p = reinterpret_cast<uint8_t*>(base) + off;
+  if (vec) {
+    *reinterpret_cast<uint2*>(p + f) = u;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f + e < F) p[(long long)(f + e) * sF] = (uint8_t)(((e < 4 ? u.x : u.y) >> (8 * (e & 3))) & 0xffu);
+  }
+}
+// keep flag of element e (0..7) of a packed mask
+__device__ __forceinline__ bool mask_keep(const uint2& m, int e) {
+  return (((e < 4 ? m.x : m.y) >> (8 * (e & 3))) & 0xffu) != 0u;
+}
+__device__ __forceinline__ uint2 mask_pack(const uint32_t m[8]) {
+  return make_uint2(m[0] | (m[1] << 8) | (m[2] << 16) | (m[3] << 24),
+                    m[4] | (m[5] << 8) | (m[6] << 16) | (m[7] << 24));
+}
+
+// Two mask bytes (0/1) -> half2 of 0.0/1.0: spread the bytes to 16-bit lanes, multiply by 0x3C00.
+__device__ __forceinline__ __half2 mask_half2(uint32_t word, int pair) {
+  const uint32_t spread = __byte_perm(word, 0u, pair ? 0x4342 : 0x4140);  // (b_lo, 0, b_hi, 0)
+  const uint32_t bits = spread * 0x3C00u;
+  return *reinterpret_cast<const __half2*>(&bits);
+}
+// out = v (8 packed halves) times the 0/1 mask, lane for lane
+__device__ __forceinline__ uint4 mask_apply(const uint4& v, const uint2& m) {
+  uint4 o;
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+  __half2* q = reinterpret_cast<__half2*>(&o);
+  q[0] = __hmul2(h[0], mask_half2(m.x, 0));
+  q[1] = __hmul2(h[1], mask_half2(m.x, 1));
+  q[2] = __hmul2(h[2], mask_half2(m.y, 0));
+  q[3] = __hmul2(h[3], mask_half2(m.y, 1));
+  return o;
+}
+
 // Contiguous per-feature vectors (bias, gamma, beta): [F], unit stride.
 __device__ __forceinline__ void load8p(const void* base, int f, int F, int vec, float v[8]) {
   load8h(base, 0, 1, vec, f, F, v, 0.f);

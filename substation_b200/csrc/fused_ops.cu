@@ -11,6 +11,7 @@
 
 #include <math.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "ops.h"
@@ -48,269 +49,440 @@ __device__ __forceinline__ float act_bwd(float x, float dy, int activation) {
   return (0.5f * th + (0.0535161f * x3 + 0.398942f * x) * sech2 + 0.5f) * dy;
 }
 
+__device__ __forceinline__ uint4 hmul8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&a);
+  const __half2* y = reinterpret_cast<const __half2*>(&b);
+  __half2* q = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = __hmul2(x[i], y[i]);
+  return o;
+}
+__device__ __forceinline__ uint4 hadd8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&a);
+  const __half2* y = reinterpret_cast<const __half2*>(&b);
+  __half2* q = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = __hadd2(x[i], y[i]);
+  return o;
+}
+
 // ---------------------------------------------------------------------------
-// Softmax (+scale, +dropout) forward and backward over [H,B,J,K]
+// Softmax (+scale, +dropout) forward and backward over [H,B,J,K].
 // LPR lanes cooperate on one row, each holding NV groups of eight elements.
+// Persistent: a warp walks row groups with a grid stride and keeps ROWS rows in
+// flight (all of their loads are issued before the first is consumed); loaded
+// data stays packed (uint4 / uint2) until it is used.
 // ---------------------------------------------------------------------------
-template <int LPR, int NV, bool AV>
-__global__ void __launch_bounds__(kRowThreads)
-softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, float scale, Rng rng) {
+constexpr int kSmThreads = 256;
+
+struct RowPos4 {
+  long long o_a, o_b, o_c, o_d;  // element offsets of the row in up to four views
+  unsigned row;
+  bool valid;
+};
+__device__ __forceinline__ RowPos4 row_pos4(const Dims4& d, unsigned row, unsigned R, const View4& a,
+                                            const View4& b, const View4& c, const View4& e) {
+  RowPos4 p;
+  p.valid = row < R;
+  p.row = p.valid ? row : R - 1;
+  const unsigned j = p.row % (unsigned)d.J, hb = p.row / (unsigned)d.J;
+  const unsigned bb = hb % (unsigned)d.B, h = hb / (unsigned)d.B;
+  p.o_a = h * a.sH + bb * a.sB + j * a.sJ;
+  p.o_b = h * b.sH + bb * b.sB + j * b.sJ;
+  p.o_c = h * c.sH + bb * c.sB + j * c.sJ;
+  p.o_d = h * e.sH + bb * e.sB + j * e.sJ;
+  return p;
+}
+
+template <int LPR, int NV, int ROWS, bool AV>
+__global__ void __launch_bounds__(kSmThreads, (NV * ROWS <= 4) ? 4 : 1)
+softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, float scale, Rng rng,
+                   unsigned R, unsigned ngroups) {
   constexpr int RPW = kWarp / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPR, sl = lane % LPR;
-  const long long R = (long long)d.H * d.B * d.J;
-  long long row = ((long long)blockIdx.x * (kRowThreads / kWarp) + warp) * RPW + sub;
-  const bool valid = row < R;
-  if (!valid) row = R - 1;
-  const int j = (int)(row % d.J);
-  const long long hb = row / d.J;
-  const int b = (int)(hb % d.B), h = (int)(hb / d.B);
-  const long long o_beta = h * beta.sH + b * beta.sB + j * beta.sJ;
-  const long long o_alpha = h * alpha.sH + b * alpha.sB + j * alpha.sJ;
-  const long long o_mask = h * mask.sH + b * mask.sB + j * mask.sJ;
-  const long long o_drop = h * drop.sH + b * drop.sB + j * drop.sJ;
-
-  float x[NV][8];
-  uint32_t m[NV][8];
-  float mx = -INFINITY;
+  const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
+  const float c2 = scale * 1.4426950408889634f;
+  for (unsigned g = blockIdx.x * (kSmThreads / kWarp) + warp; g < ngroups; g += nwarps) {
+    RowPos4 pos[ROWS];
+    uint4 xr[ROWS][NV];
+    uint2 mr[ROWS][NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int k = (sl + LPR * i) * 8;
-    if (k < d.K) {
-      load8h(beta.p, o_beta, beta.sK, SB_VEC(beta), k, d.K, x[i]);
-      if (!rng.philox) load8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
-    }
-  }
+    for (int rr = 0; rr < ROWS; ++rr) {
+      pos[rr] = row_pos4(d, (g * ROWS + rr) * RPW + sub, R, beta, alpha, mask, drop);
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int k = (sl + LPR * i) * 8;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      x[i][e] = (k + e < d.K) ? x[i][e] * scale : -INFINITY;
-      mx = fmaxf(mx, x[i][e]);
-    }
-  }
-  mx = group_max<LPR>(mx);
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      x[i][e] = __expf(x[i][e] - mx);
-      sum += x[i][e];
-    }
-  sum = group_sum<LPR>(sum);
-  const float inv = 1.f / sum;
-  if (!valid) return;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int k = (sl + LPR * i) * 8;
-    if (k >= d.K) continue;
-    float a[8], dr[8];
-    if (rng.philox) {
-      philox8<AV>(rng, (unsigned long long)row * d.K + k, m[i]);
-      store8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
+      for (int i = 0; i < NV; ++i) {
+        const int k = (sl + LPR * i) * 8;
+        if (k < d.K) {
+          xr[rr][i] = load8h_raw(beta.p, pos[rr].o_a, beta.sK, SB_VEC(beta), k, d.K);
+          if (!rng.philox) mr[rr][i] = load8m_raw(mask.p, pos[rr].o_c, mask.sK, SB_VEC(mask), k, d.K);
+        }
+      }
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      a[e] = x[i][e] * inv;
-      dr[e] = m[i][e] ? a[e] : 0.f;
+    for (int rr = 0; rr < ROWS; ++rr) {
+      // t = x * (scale * log2 e); softmax = 2^(t - max t) / sum
+      float x[NV][8];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int k = (sl + LPR * i) * 8;
+        unpack8(xr[rr][i], x[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const bool in = AV ? (k < d.K) : (k + e < d.K);
+          x[i][e] = in ? x[i][e] * c2 : -INFINITY;
+          mx = fmaxf(mx, x[i][e]);
+        }
+      }
+      mx = group_max<LPR>(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          x[i][e] = exp2f(x[i][e] - mx);
+          sum += x[i][e];
+        }
+      sum = group_sum<LPR>(sum);
+      const float inv = 1.f / sum;
+      if (!pos[rr].valid) continue;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int k = (sl + LPR * i) * 8;
+        if (k >= d.K) continue;
+        uint2 m = mr[rr][i];
+        if (rng.philox) {
+          uint32_t mm[8];
+          philox8<AV>(rng, (unsigned long long)pos[rr].row * d.K + k, mm);
+          m = mask_pack(mm);
+          store8m_raw(mask.p, pos[rr].o_c, mask.sK, SB_VEC(mask), k, d.K, m);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[i][e] *= inv;
+        const uint4 a = pack8(x[i]);
+        store8h_raw(alpha.p, pos[rr].o_b, alpha.sK, SB_VEC(alpha), k, d.K, a);
+        store8h_raw(drop.p, pos[rr].o_d, drop.sK, SB_VEC(drop), k, d.K, mask_apply(a, m));
+      }
     }
-    store8h(alpha.p, o_alpha, alpha.sK, SB_VEC(alpha), k, d.K, a);
-    store8h(drop.p, o_drop, drop.sK, SB_VEC(drop), k, d.K, dr);
   }
 }
 
-template <int LPR, int NV, bool AV>
-__global__ void __launch_bounds__(kRowThreads)
-softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta) {
+template <int LPR, int NV, int ROWS, bool AV>
+__global__ void __launch_bounds__(kSmThreads, (NV * ROWS <= 4) ? 4 : 1)
+softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta, unsigned R, unsigned ngroups) {
   constexpr int RPW = kWarp / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPR, sl = lane % LPR;
-  const long long R = (long long)d.H * d.B * d.J;
-  long long row = ((long long)blockIdx.x * (kRowThreads / kWarp) + warp) * RPW + sub;
-  const bool valid = row < R;
-  if (!valid) row = R - 1;
-  const int j = (int)(row % d.J);
-  const long long hb = row / d.J;
-  const int b = (int)(hb % d.B), h = (int)(hb / d.B);
-  const long long o_alpha = h * alpha.sH + b * alpha.sB + j * alpha.sJ;
-  const long long o_mask = h * mask.sH + b * mask.sB + j * mask.sJ;
-  const long long o_dad = h * dad.sH + b * dad.sB + j * dad.sJ;
-  const long long o_dbeta = h * dbeta.sH + b * dbeta.sB + j * dbeta.sJ;
-
-  float a[NV][8], g[NV][8];
-  uint32_t m[NV][8];
+  const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
+  for (unsigned g = blockIdx.x * (kSmThreads / kWarp) + warp; g < ngroups; g += nwarps) {
+    RowPos4 pos[ROWS];
+    uint4 ar[ROWS][NV], gr[ROWS][NV];
+    uint2 mr[ROWS][NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int k = (sl + LPR * i) * 8;
-    if (k < d.K) {
-      load8h(alpha.p, o_alpha, alpha.sK, SB_VEC(alpha), k, d.K, a[i]);
-      load8h(dad.p, o_dad, dad.sK, SB_VEC(dad), k, d.K, g[i]);
-      load8m(mask.p, o_mask, mask.sK, SB_VEC(mask), k, d.K, m[i]);
-    } else {
+    for (int rr = 0; rr < ROWS; ++rr) {
+      pos[rr] = row_pos4(d, (g * ROWS + rr) * RPW + sub, R, alpha, mask, dad, dbeta);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { a[i][e] = 0.f; g[i][e] = 0.f; m[i][e] = 0u; }
+      for (int i = 0; i < NV; ++i) {
+        const int k = (sl + LPR * i) * 8;
+        if (k < d.K) {
+          ar[rr][i] = load8h_raw(alpha.p, pos[rr].o_a, alpha.sK, SB_VEC(alpha), k, d.K);
+          gr[rr][i] = load8h_raw(dad.p, pos[rr].o_c, dad.sK, SB_VEC(dad), k, d.K);
+          mr[rr][i] = load8m_raw(mask.p, pos[rr].o_b, mask.sK, SB_VEC(mask), k, d.K);
+        } else {
+          ar[rr][i] = make_uint4(0, 0, 0, 0);
+          gr[rr][i] = make_uint4(0, 0, 0, 0);
+          mr[rr][i] = make_uint2(0, 0);
+        }
+      }
     }
-  }
-  float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
+    for (int rr = 0; rr < ROWS; ++rr) {
+      float a[NV][8], gg[NV][8];
+      float s = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      g[i][e] = m[i][e] ? g[i][e] : 0.f;
-      s += g[i][e] * a[i][e];
+      for (int i = 0; i < NV; ++i) {
+        unpack8(ar[rr][i], a[i]);
+        unpack8(gr[rr][i], gg[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          gg[i][e] = mask_keep(mr[rr][i], e) ? gg[i][e] : 0.f;
+          s += gg[i][e] * a[i][e];
+        }
+      }
+      s = group_sum<LPR>(s);
+      if (!pos[rr].valid) continue;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int k = (sl + LPR * i) * 8;
+        if (k >= d.K) continue;
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = a[i][e] * (gg[i][e] - s);
+        store8h_raw(dbeta.p, pos[rr].o_d, dbeta.sK, SB_VEC(dbeta), k, d.K, pack8(o));
+      }
     }
-  s = group_sum<LPR>(s);
-  if (!valid) return;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int k = (sl + LPR * i) * 8;
-    if (k >= d.K) continue;
-    float o[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = a[i][e] * (g[i][e] - s);
-    store8h(dbeta.p, o_dbeta, dbeta.sK, SB_VEC(dbeta), k, d.K, o);
   }
 }
 
 // ---------------------------------------------------------------------------
-// bias + dropout + residual + LayerNorm over [B,J,F]; one warp per token.
+// bias + dropout + residual + LayerNorm over [B,J,F]; one warp per token, persistent
+// grid-stride over tokens, a token's inputs stay packed until they are consumed.
 // ---------------------------------------------------------------------------
 template <int NV, bool AV>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kSmThreads, NV <= 2 ? 3 : (NV <= 4 ? 2 : 1))
 bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma, const void* beta,
              View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng, int pvec) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long R = (long long)d.B * d.J;
-  const long long row = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
-  if (row >= R) return;
-  const int b = (int)(row / d.J), j = (int)(row % d.J);
-  const long long o_in = b * in.sB + j * in.sJ, o_res = b * resid.sB + j * resid.sJ;
-  const long long o_mask = b * mask.sB + j * mask.sJ, o_lin = b * lin.sB + j * lin.sJ;
-
-  float r[NV][8];
-  float sum = 0.f;
+  const unsigned R = (unsigned)d.B * (unsigned)d.J;
+  const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
+  const float invF = 1.f / (float)d.F;
+  for (unsigned row = blockIdx.x * (kSmThreads / kWarp) + warp; row < R; row += nwarps) {
+    const int b = (int)(row / (unsigned)d.J), j = (int)(row % (unsigned)d.J);
+    const long long o_in = b * in.sB + j * in.sJ, o_res = b * resid.sB + j * resid.sJ;
+    const long long o_mask = b * mask.sB + j * mask.sJ, o_lin = b * lin.sB + j * lin.sJ;
+    uint4 xr[NV], rr[NV];
+    uint2 mr[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int f = (lane + kWarp * i) * 8;
-    if (f < d.F) {
-      float x[8], rs[8], bs[8];
-      uint32_t m[8];
-      load8h(in.p, o_in, in.sF, SB_VEC(in), f, d.F, x);
-      load8h(resid.p, o_res, resid.sF, SB_VEC(resid), f, d.F, rs);
-      load8p(bias, f, d.F, AV || pvec, bs);
-      if (rng.philox) {
-        philox8<AV>(rng, (unsigned long long)row * d.F + f, m);
-        store8m(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F, m);
-      } else {
-        load8m(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F, m);
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
+      if (f < d.F) {
+        xr[i] = load8h_raw(in.p, o_in, in.sF, SB_VEC(in), f, d.F);
+        rr[i] = load8h_raw(resid.p, o_res, resid.sF, SB_VEC(resid), f, d.F);
+        if (!rng.philox) mr[i] = load8m_raw(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F);
       }
+    }
+    float r[NV][8];
+    float sum = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] += bs[e];
-      store8h(lin.p, o_lin, lin.sF, SB_VEC(lin), f, d.F, x);
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
+      if (f < d.F) {
+        if (rng.philox) {
+          uint32_t mm[8];
+          philox8<AV>(rng, (unsigned long long)row * d.F + f, mm);
+          mr[i] = mask_pack(mm);
+          store8m_raw(mask.p, o_mask, mask.sF, SB_VEC(mask), f, d.F, mr[i]);
+        }
+        const uint4 bs = load8h_raw(bias, 0, 1, AV || pvec, f, d.F);
+        float x[8], bb[8], rs[8];
+        unpack8(xr[i], x);
+        unpack8(bs, bb);
+        unpack8(rr[i], rs);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] += bb[e];
+        store8h_raw(lin.p, o_lin, lin.sF, SB_VEC(lin), f, d.F, pack8(x));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          r[i][e] = (AV || f + e < d.F) ? (mask_keep(mr[i], e) ? x[e] : 0.f) + rs[e] : 0.f;
+          sum += r[i][e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[i][e] = 0.f;
+      }
+    }
+    const float mean = warp_sum(sum) * invF;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        r[i][e] = (f + e < d.F) ? (m[e] ? x[e] : 0.f) + rs[e] : 0.f;
-        sum += r[i][e];
+        r[i][e] = (f + e < d.F) ? r[i][e] - mean : 0.f;
+        sq = fmaf(r[i][e], r[i][e], sq);
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) r[i][e] = 0.f;
     }
-  }
-  const float mean = warp_sum(sum) / (float)d.F;
-  float sq = 0.f;
+    const float rstd = rsqrtf(warp_sum(sq) * invF + kLnEps);
+    if (lane == 0) reinterpret_cast<__half*>(istd.p)[b * istd.sB + j * istd.sJ] = __float2half_rn(rstd);
+    const long long o_diff = b * diff.sB + j * diff.sJ, o_ln = b * ln.sB + j * ln.sJ;
+    const long long o_out = b * out.sB + j * out.sJ;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int f = (lane + kWarp * i) * 8;
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
+      if (f >= d.F) continue;
+      float gm[8], bt[8], n[8], o[8];
+      unpack8(load8h_raw(gamma, 0, 1, AV || pvec, f, d.F), gm);
+      unpack8(load8h_raw(beta, 0, 1, AV || pvec, f, d.F), bt);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      r[i][e] = (f + e < d.F) ? r[i][e] - mean : 0.f;
-      sq += r[i][e] * r[i][e];
+      for (int e = 0; e < 8; ++e) {
+        n[e] = r[i][e] * rstd;
+        o[e] = fmaf(n[e], gm[e], bt[e]);
+      }
+      store8h_raw(diff.p, o_diff, diff.sF, SB_VEC(diff), f, d.F, pack8(r[i]));
+      store8h_raw(ln.p, o_ln, ln.sF, SB_VEC(ln), f, d.F, pack8(n));
+      store8h_raw(out.p, o_out, out.sF, SB_VEC(out), f, d.F, pack8(o));
     }
-  }
-  const float rstd = rsqrtf(warp_sum(sq) / (float)d.F + kLnEps);
-  if (lane == 0) reinterpret_cast<__half*>(istd.p)[b * istd.sB + j * istd.sJ] = __float2half_rn(rstd);
-  const long long o_diff = b * diff.sB + j * diff.sJ, o_ln = b * ln.sB + j * ln.sJ;
-  const long long o_out = b * out.sB + j * out.sJ;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int f = (lane + kWarp * i) * 8;
-    if (f >= d.F) continue;
-    float gm[8], bt[8], n[8], o[8];
-    load8p(gamma, f, d.F, AV || pvec, gm);
-    load8p(beta, f, d.F, AV || pvec, bt);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      n[e] = r[i][e] * rstd;
-      o[e] = n[e] * gm[e] + bt[e];
-    }
-    store8h(diff.p, o_diff, diff.sF, SB_VEC(diff), f, d.F, r[i]);
-    store8h(ln.p, o_ln, ln.sF, SB_VEC(ln), f, d.F, n);
-    store8h(out.p, o_out, out.sF, SB_VEC(out), f, d.F, o);
   }
 }
 
-// LayerNorm backward-data + dropout backward; one warp per token.
+// LayerNorm backward-data + dropout backward; one warp per token, persistent.
 template <int NV, bool AV>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kSmThreads, NV <= 2 ? 3 : (NV <= 4 ? 2 : 1))
 blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresid, View3 dlin) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long R = (long long)d.B * d.J;
-  const long long row = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
-  if (row >= R) return;
-  const int b = (int)(row / d.J), j = (int)(row % d.J);
-  const long long o_g = b * dln.sB + j * dln.sJ, o_d = b * diff.sB + j * diff.sJ;
-  const long long o_m = b * mask.sB + j * mask.sJ;
-  float g[NV][8], df[NV][8];
-  uint32_t m[NV][8];
-  float sg = 0.f, sgd = 0.f;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int f = (lane + kWarp * i) * 8;
-    if (f < d.F) {
-      load8h(dln.p, o_g, dln.sF, SB_VEC(dln), f, d.F, g[i]);
-      load8h(diff.p, o_d, diff.sF, SB_VEC(diff), f, d.F, df[i]);
-      load8m(mask.p, o_m, mask.sF, SB_VEC(mask), f, d.F, m[i]);
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) { g[i][e] = 0.f; df[i][e] = 0.f; m[i][e] = 0u; }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      sg += g[i][e];
-      sgd += g[i][e] * df[i][e];
-    }
-  sg = warp_sum(sg);
-  sgd = warp_sum(sgd);
-  const float s = __half2float(reinterpret_cast<const __half*>(istd.p)[b * istd.sB + j * istd.sJ]);
+  const unsigned R = (unsigned)d.B * (unsigned)d.J;
+  const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
   const float invn = 1.f / (float)d.F;
-  const float c1 = sg * s * invn, c2 = sgd * s * s * s * invn;
-  const long long o_r = b * dresid.sB + j * dresid.sJ, o_l = b * dlin.sB + j * dlin.sJ;
+  for (unsigned row = blockIdx.x * (kSmThreads / kWarp) + warp; row < R; row += nwarps) {
+    const int b = (int)(row / (unsigned)d.J), j = (int)(row % (unsigned)d.J);
+    const long long o_g = b * dln.sB + j * dln.sJ, o_d = b * diff.sB + j * diff.sJ;
+    const long long o_m = b * mask.sB + j * mask.sJ;
+    uint4 gr[NV], dr_[NV];
+    uint2 mr[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int f = (lane + kWarp * i) * 8;
-    if (f >= d.F) continue;
-    float dr[8], dl[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      dr[e] = g[i][e] * s - c1 - df[i][e] * c2;
-      dl[e] = m[i][e] ? dr[e] : 0.f;
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
+      if (f < d.F) {
+        gr[i] = load8h_raw(dln.p, o_g, dln.sF, SB_VEC(dln), f, d.F);
+        dr_[i] = load8h_raw(diff.p, o_d, diff.sF, SB_VEC(diff), f, d.F);
+        mr[i] = load8m_raw(mask.p, o_m, mask.sF, SB_VEC(mask), f, d.F);
+      } else {
+        gr[i] = make_uint4(0, 0, 0, 0);
+        dr_[i] = make_uint4(0, 0, 0, 0);
+        mr[i] = make_uint2(0, 0);
+      }
     }
-    store8h(dresid.p, o_r, dresid.sF, SB_VEC(dresid), f, d.F, dr);
-    store8h(dlin.p, o_l, dlin.sF, SB_VEC(dlin), f, d.F, dl);
+    const float s = __half2float(reinterpret_cast<const __half*>(istd.p)[b * istd.sB + j * istd.sJ]);
+    float sg = 0.f, sgd = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float g[8], df[8];
+      unpack8(gr[i], g);
+      unpack8(dr_[i], df);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sg += g[e];
+        sgd = fmaf(g[e], df[e], sgd);
+      }
+    }
+    sg = warp_sum(sg);
+    sgd = warp_sum(sgd);
+    const float c1 = sg * s * invn, c2 = sgd * s * s * s * invn;
+    const long long o_r = b * dresid.sB + j * dresid.sJ, o_l = b * dlin.sB + j * dlin.sJ;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int f = (lane + kWarp * i) * 8;
+      if (f >= d.F) continue;
+      float g[8], df[8], o[8];
+      unpack8(gr[i], g);
+      unpack8(dr_[i], df);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = fmaf(g[e], s, -c1) - df[e] * c2;
+      const uint4 packed = pack8(o);
+      store8h_raw(dresid.p, o_r, dresid.sF, SB_VEC(dresid), f, d.F, packed);
+      store8h_raw(dlin.p, o_l, dlin.sF, SB_VEC(dlin), f, d.F, mask_apply(packed, mr[i]));
+    }
   }
 }
 
 // ---------------------------------------------------------------------------
-// Elementwise kernels over [B,J,F]: a warp takes one token and a span of
-// 4 * 256 features.
+// Elementwise kernels.  Flat form: every tensor is dense in logical order, so element i of one
+// is element i of all; a thread takes UNR groups of eight, a grid stride apart (persistent).
+// Row form: strided views, a warp takes one token and a span of 4 * 256 features.
 // ---------------------------------------------------------------------------
 constexpr int kEwNV = 4;
+constexpr int kFlatUnr = 4;
+
+template <int ACT>
+__global__ void __launch_bounds__(kSmThreads, 4)
+bad_flat_kernel(unsigned long long ngroups, int groups_per_row, const uint4* __restrict__ in,
+                const uint4* __restrict__ bias, uint2* mask, uint4* __restrict__ lin1,
+                uint4* __restrict__ drop2, Rng rng) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
+  for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
+       g0 += stride * kFlatUnr) {
+    uint4 x[kFlatUnr];
+    uint2 m[kFlatUnr];
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g < ngroups) {
+        x[u] = in[g];
+        if (!rng.philox) m[u] = mask[g];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g >= ngroups) continue;
+      if (rng.philox) {
+        uint32_t mm[8];
+        philox_keep8(rng, g, mm);
+        m[u] = mask_pack(mm);
+        mask[g] = m[u];
+      }
+      const uint4 l = hadd8(x[u], bias[g % (unsigned)groups_per_row]);
+      lin1[g] = l;
+      uint4 a;
+      if (ACT == SB_ACT_RELU) {
+        const __half2* h = reinterpret_cast<const __half2*>(&l);
+        __half2* q = reinterpret_cast<__half2*>(&a);
+        const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = __hmax2(h[i], zero);
+      } else {
+        float v[8];
+        unpack8(l, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = act_fwd(v[e], SB_ACT_GELU);
+        a = pack8(v);
+      }
+      drop2[g] = mask_apply(a, m[u]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kSmThreads, 4)
+add_flat_kernel(unsigned long long ngroups, const uint4* __restrict__ a, const uint4* __restrict__ b,
+                uint4* __restrict__ out) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
+  for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
+       g0 += stride * kFlatUnr) {
+    uint4 x[kFlatUnr], y[kFlatUnr];
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g < ngroups) { x[u] = a[g]; y[u] = b[g]; }
+    }
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g < ngroups) out[g] = hadd8(x[u], y[u]);
+    }
+  }
+}
+
+// out[r, :] = in[r, :] + bias[r] over dense rows of `groups_per_row` groups of eight
+__global__ void __launch_bounds__(kSmThreads, 4)
+rowbias_flat_kernel(unsigned long long ngroups, unsigned groups_per_row, const uint4* __restrict__ in,
+                    const __half* __restrict__ bias, uint4* __restrict__ out) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
+  for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
+       g0 += stride * kFlatUnr) {
+    uint4 x[kFlatUnr];
+    __half bv[kFlatUnr];
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g < ngroups) { x[u] = in[g]; bv[u] = bias[g / groups_per_row]; }
+    }
+#pragma unroll
+    for (int u = 0; u < kFlatUnr; ++u) {
+      const unsigned long long g = g0 + u * stride;
+      if (g >= ngroups) continue;
+      const __half2 b2 = __half2half2(bv[u]);
+      uint4 o;
+      const __half2* h = reinterpret_cast<const __half2*>(&x[u]);
+      __half2* q = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = __hadd2(h[i], b2);
+      out[g] = o;
+    }
+  }
+}
 
 template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
@@ -460,126 +632,152 @@ struct ColOut {
   void* out[NQ];  // fp16 [F], unit stride
 };
 
-// Each operator supplies: NQ reduced quantities, NIN fp16 inputs per row, whether it reads a
-// mask, load<AV>() of one row's eight features and finish<AV>() = elementwise output + accumulate.
+// Each operator supplies: NQ reduced quantities, NIN fp16 inputs per row, UNR rows kept in
+// flight per warp, load<AV>() of one row's eight features (kept packed) and finish<AV>() =
+// elementwise output + accumulation.
 template <int NIN>
 struct RowRegs {
-  float v[NIN][8];
-  uint32_t m[8];
+  uint4 v[NIN];
+  uint2 m;
 };
 
 struct BsbOp {
-  static constexpr int NQ = 2, NIN = 2;
+  static constexpr int NQ = 2, NIN = 2, UNR = 4;
   View3 dy, ln, dln;
   const void* gamma;
   int pvec;
   template <bool AV>
   __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
-    load8h(dy.p, b * dy.sB + j * dy.sJ, dy.sF, SB_VEC(dy), f, F, r.v[0]);
-    load8h(ln.p, b * ln.sB + j * ln.sJ, ln.sF, SB_VEC(ln), f, F, r.v[1]);
+    r.v[0] = load8h_raw(dy.p, b * dy.sB + j * dy.sJ, dy.sF, SB_VEC(dy), f, F);
+    r.v[1] = load8h_raw(ln.p, b * ln.sB + j * ln.sJ, ln.sF, SB_VEC(ln), f, F);
   }
   template <bool AV>
-  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float gm[8],
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const uint4& gm,
                                          const RowRegs<NIN>& r, float acc[NQ][8]) const {
-    float o[8];
+    float y[8], n[8];
+    unpack8(r.v[0], y);
+    unpack8(r.v[1], n);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      o[e] = r.v[0][e] * gm[e];
-      acc[0][e] += r.v[0][e] * r.v[1][e];
-      acc[1][e] += r.v[0][e];
+      acc[0][e] = fmaf(y[e], n[e], acc[0][e]);
+      acc[1][e] += y[e];
     }
-    store8h(dln.p, b * dln.sB + j * dln.sJ, dln.sF, SB_VEC(dln), f, F, o);
+    // a product of two fp16 values is exact in fp32, so one half-precision multiply rounds the same
+    store8h_raw(dln.p, b * dln.sB + j * dln.sJ, dln.sF, SB_VEC(dln), f, F, hmul8(r.v[0], gm));
   }
   template <bool AV>
-  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, AV || pvec, gm); }
+  __device__ __forceinline__ uint4 scale(int f, int F) const { return load8h_raw(gamma, 0, 1, AV || pvec, f, F); }
 };
 
 struct EbsbOp {
-  static constexpr int NQ = 3, NIN = 4;
+  static constexpr int NQ = 3, NIN = 4, UNR = 2;
   View3 ln1, dresid2, dlw, dlin2, dln1;
   const void* gamma;
   int pvec;
   template <bool AV>
   __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
-    load8h(ln1.p, b * ln1.sB + j * ln1.sJ, ln1.sF, SB_VEC(ln1), f, F, r.v[0]);
-    load8h(dresid2.p, b * dresid2.sB + j * dresid2.sJ, dresid2.sF, SB_VEC(dresid2), f, F, r.v[1]);
-    load8h(dlw.p, b * dlw.sB + j * dlw.sJ, dlw.sF, SB_VEC(dlw), f, F, r.v[2]);
-    load8h(dlin2.p, b * dlin2.sB + j * dlin2.sJ, dlin2.sF, SB_VEC(dlin2), f, F, r.v[3]);
+    r.v[0] = load8h_raw(ln1.p, b * ln1.sB + j * ln1.sJ, ln1.sF, SB_VEC(ln1), f, F);
+    r.v[1] = load8h_raw(dresid2.p, b * dresid2.sB + j * dresid2.sJ, dresid2.sF, SB_VEC(dresid2), f, F);
+    r.v[2] = load8h_raw(dlw.p, b * dlw.sB + j * dlw.sJ, dlw.sF, SB_VEC(dlw), f, F);
+    r.v[3] = load8h_raw(dlin2.p, b * dlin2.sB + j * dlin2.sJ, dlin2.sF, SB_VEC(dlin2), f, F);
   }
   template <bool AV>
-  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float gm[8],
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const uint4& gm,
                                          const RowRegs<NIN>& r, float acc[NQ][8]) const {
-    float o[8];
+    float n[8], rr[8], w[8], l2[8], g8[8], o[8];
+    unpack8(r.v[0], n);
+    unpack8(r.v[1], rr);
+    unpack8(r.v[2], w);
+    unpack8(r.v[3], l2);
+    unpack8(gm, g8);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float g = r.v[1][e] + r.v[2][e];
-      o[e] = g * gm[e];
-      acc[0][e] += g * r.v[0][e];
+      const float g = rr[e] + w[e];
+      o[e] = g * g8[e];
+      acc[0][e] = fmaf(g, n[e], acc[0][e]);
       acc[1][e] += g;
-      acc[2][e] += r.v[3][e];
+      acc[2][e] += l2[e];
     }
-    store8h(dln1.p, b * dln1.sB + j * dln1.sJ, dln1.sF, SB_VEC(dln1), f, F, o);
+    store8h_raw(dln1.p, b * dln1.sB + j * dln1.sJ, dln1.sF, SB_VEC(dln1), f, F, pack8(o));
   }
   template <bool AV>
-  __device__ __forceinline__ void scale(int f, int F, float gm[8]) const { load8p(gamma, f, F, AV || pvec, gm); }
+  __device__ __forceinline__ uint4 scale(int f, int F) const { return load8h_raw(gamma, 0, 1, AV || pvec, f, F); }
 };
 
 struct BdrlbOp {
-  static constexpr int NQ = 1, NIN = 2;
+  static constexpr int NQ = 1, NIN = 2, UNR = 4;
   View3 ddrop2, mask, lin1, dlin1;
   int activation;
   template <bool AV>
   __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
-    load8h(ddrop2.p, b * ddrop2.sB + j * ddrop2.sJ, ddrop2.sF, SB_VEC(ddrop2), f, F, r.v[0]);
-    load8h(lin1.p, b * lin1.sB + j * lin1.sJ, lin1.sF, SB_VEC(lin1), f, F, r.v[1]);
-    load8m(mask.p, b * mask.sB + j * mask.sJ, mask.sF, SB_VEC(mask), f, F, r.m);
+    r.v[0] = load8h_raw(ddrop2.p, b * ddrop2.sB + j * ddrop2.sJ, ddrop2.sF, SB_VEC(ddrop2), f, F);
+    r.v[1] = load8h_raw(lin1.p, b * lin1.sB + j * lin1.sJ, lin1.sF, SB_VEC(lin1), f, F);
+    r.m = load8m_raw(mask.p, b * mask.sB + j * mask.sJ, mask.sF, SB_VEC(mask), f, F);
   }
   template <bool AV>
-  __device__ __forceinline__ void finish(int b, int j, int f, int F, const float[8],
+  __device__ __forceinline__ void finish(int b, int j, int f, int F, const uint4&,
                                          const RowRegs<NIN>& r, float acc[NQ][8]) const {
+    uint4 out;
     float o[8];
+    if (activation == SB_ACT_RELU) {
+      // dlin1 = [lin1 > 0] * mask * ddrop2, all exact selections of fp16 values
+      const uint4 g = mask_apply(r.v[0], r.m);
+      const __half2* x = reinterpret_cast<const __half2*>(&r.v[1]);
+      const __half2* gg = reinterpret_cast<const __half2*>(&g);
+      __half2* q = reinterpret_cast<__half2*>(&out);
+      const __half2 zero = __float2half2_rn(0.f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      o[e] = (f + e < F) ? act_bwd(r.v[1][e], r.m[e] ? r.v[0][e] : 0.f, activation) : 0.f;
-      acc[0][e] += o[e];
+      for (int i = 0; i < 4; ++i) q[i] = __hmul2(gg[i], __hgt2(x[i], zero));
+      unpack8(out, o);
+    } else {
+      float g[8], x[8];
+      unpack8(r.v[0], g);
+      unpack8(r.v[1], x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = act_bwd(x[e], mask_keep(r.m, e) ? g[e] : 0.f, activation);
+      out = pack8(o);
     }
-    store8h(dlin1.p, b * dlin1.sB + j * dlin1.sJ, dlin1.sF, SB_VEC(dlin1), f, F, o);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[0][e] += (AV || f + e < F) ? o[e] : 0.f;
+    store8h_raw(dlin1.p, b * dlin1.sB + j * dlin1.sJ, dlin1.sF, SB_VEC(dlin1), f, F, out);
   }
   template <bool AV>
-  __device__ __forceinline__ void scale(int, int, float[8]) const {}
+  __device__ __forceinline__ uint4 scale(int, int) const { return make_uint4(0, 0, 0, 0); }
 };
 
 struct BaobOp {
-  static constexpr int NQ = 1, NIN = 1;
+  static constexpr int NQ = 1, NIN = 1, UNR = 8;
   View3 datt;
   template <bool AV>
   __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
-    load8h(datt.p, b * datt.sB + j * datt.sJ, datt.sF, SB_VEC(datt), f, F, r.v[0]);
+    r.v[0] = load8h_raw(datt.p, b * datt.sB + j * datt.sJ, datt.sF, SB_VEC(datt), f, F);
   }
   template <bool AV>
-  __device__ __forceinline__ void finish(int, int, int, int, const float[8], const RowRegs<NIN>& r,
+  __device__ __forceinline__ void finish(int, int, int, int, const uint4&, const RowRegs<NIN>& r,
                                          float acc[NQ][8]) const {
+    float x[8];
+    unpack8(r.v[0], x);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[0][e] += r.v[0][e];
+    for (int e = 0; e < 8; ++e) acc[0][e] += x[e];
   }
   template <bool AV>
-  __device__ __forceinline__ void scale(int, int, float[8]) const {}
+  __device__ __forceinline__ uint4 scale(int, int) const { return make_uint4(0, 0, 0, 0); }
 };
 
 template <class Op, bool AV>
-__global__ void __launch_bounds__(kColThreads)
+__global__ void __launch_bounds__(kColThreads, 2)
 colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* counters,
                  ColOut<Op::NQ> outs) {
   constexpr int NQ = Op::NQ;
   constexpr int NW = kColThreads / kWarp;
-  constexpr int UNR = 4;  // rows in flight per warp
+  constexpr int UNR = Op::UNR;  // rows in flight per warp
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slice = blockIdx.x, chunk = blockIdx.y, P = gridDim.y;
   const int Fp = gridDim.x * 256;
   const int f = slice * 256 + lane * 8;
-  const long long R = (long long)d.B * d.J;
-  const long long r0 = (long long)chunk * rows_per_chunk;
-  const long long r1 = (r0 + rows_per_chunk < R) ? r0 + rows_per_chunk : R;
+  const unsigned R = (unsigned)d.B * (unsigned)d.J;
+  const unsigned r0 = (unsigned)chunk * (unsigned)rows_per_chunk;
+  const unsigned r1 = (r0 + rows_per_chunk < R) ? r0 + rows_per_chunk : R;
 
   float acc[NQ][8];
 #pragma unroll
@@ -587,19 +785,18 @@ colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* c
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
   if (f < d.F) {
-    float gm[8];
-    op.template scale<AV>(f, d.F, gm);
-    for (long long r = r0 + warp; r < r1; r += NW * UNR) {
+    const uint4 gm = op.template scale<AV>(f, d.F);
+    for (unsigned r = r0 + warp; r < r1; r += NW * UNR) {
       RowRegs<Op::NIN> regs[UNR];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        const long long rr = r + (long long)u * NW;
-        if (rr < r1) op.template load<AV>((int)(rr / d.J), (int)(rr % d.J), f, d.F, regs[u]);
+        const unsigned rr = r + u * NW;
+        if (rr < r1) op.template load<AV>((int)(rr / (unsigned)d.J), (int)(rr % (unsigned)d.J), f, d.F, regs[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        const long long rr = r + (long long)u * NW;
-        if (rr < r1) op.template finish<AV>((int)(rr / d.J), (int)(rr % d.J), f, d.F, gm, regs[u], acc);
+        const unsigned rr = r + u * NW;
+        if (rr < r1) op.template finish<AV>((int)(rr / (unsigned)d.J), (int)(rr % (unsigned)d.J), f, d.F, gm, regs[u], acc);
       }
     }
   }
@@ -624,18 +821,33 @@ colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* c
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // Last CTA of this slice: add the P partial rows, warp w taking chunks w, w+NW, ...
+  // Last CTA of this slice adds the P partial rows in a fixed order: warp w takes chunks
+  // w, w+NW, ... (eight independent loads in flight per lane), then the warps are summed in order.
 #pragma unroll
   for (int q = 0; q < NQ; ++q) {
     float a[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = 0.f;
-    for (int c = warp; c < P; c += NW) {
-      const float4* src =
-          reinterpret_cast<const float4*>(partial + ((long long)q * P + c) * Fp + slice * 256 + lane * 8);
-      const float4 u = __ldcg(src), v = __ldcg(src + 1);
-      a[0] += u.x; a[1] += u.y; a[2] += u.z; a[3] += u.w;
-      a[4] += v.x; a[5] += v.y; a[6] += v.z; a[7] += v.w;
+    const float* base = partial + (long long)q * P * Fp + slice * 256 + lane * 8;
+    for (int c0 = warp; c0 < P; c0 += NW * 4) {
+      float4 u[4], v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + i * NW;
+        if (c < P) {
+          const float4* src = reinterpret_cast<const float4*>(base + (long long)c * Fp);
+          u[i] = __ldcg(src);
+          v[i] = __ldcg(src + 1);
+        } else {
+          u[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          v[i] = u[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[0] += u[i].x; a[1] += u[i].y; a[2] += u[i].z; a[3] += u[i].w;
+        a[4] += v[i].x; a[5] += v[i].y; a[6] += v[i].z; a[7] += v[i].w;
+      }
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) sm[warp][q][lane * 8 + e] = a[e];
@@ -661,8 +873,8 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
     return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace counters");
   const long long R = (long long)d.B * d.J;
   const long long Fp = (long long)slices * 256;
-  // about four 8-warp CTAs per SM; bounded by rows and by the workspace
-  long long P = (148 * 4 + slices - 1) / slices;
+  // about two 8-warp CTAs per SM; bounded by rows and by the workspace
+  long long P = (148 * 2 + slices - 1) / slices;
   const long long cap = (long long)((kWsBytes - kWsCounterBytes) / (Op::NQ * Fp * sizeof(float)));
   if (cap < 1) return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace");
   if (P > cap) P = cap;
@@ -696,15 +908,34 @@ bool all_vec(const V&... v) {
   return ((v.vec != 0) && ...);
 }
 
-#define SB_SOFTMAX_LAUNCH(KERNEL, AVFLAG, ...)                                                     \
-  do {                                                                                             \
-    auto blocks = [&](int lpr) { return (unsigned)((R + 4 * (32 / lpr) - 1) / (4 * (32 / lpr))); }; \
-    if (d.K <= 64) KERNEL<8, 1, AVFLAG><<<blocks(8), kRowThreads, 0, s>>>(__VA_ARGS__);            \
-    else if (d.K <= 128) KERNEL<16, 1, AVFLAG><<<blocks(16), kRowThreads, 0, s>>>(__VA_ARGS__);    \
-    else if (d.K <= 256) KERNEL<32, 1, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);    \
-    else if (d.K <= 512) KERNEL<32, 2, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);    \
-    else if (d.K <= 1024) KERNEL<32, 4, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);   \
-    else KERNEL<32, 8, AVFLAG><<<blocks(32), kRowThreads, 0, s>>>(__VA_ARGS__);                    \
+// Persistent grid: enough CTAs to fill every SM at the kernel's occupancy, no more than the work needs.
+template <class K>
+unsigned persistent_blocks(K kernel, int threads, unsigned long long work_blocks) {
+  int dev = 0, sms = 148, per_sm = 1;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const unsigned long long cap = (unsigned long long)sms * per_sm;
+  return (unsigned)std::max<unsigned long long>(1, std::min(work_blocks, cap));
+}
+
+#define SB_SOFTMAX_ONE(KERNEL, LPR, NV, ROWS, AVFLAG, ...)                                          \
+  do {                                                                                              \
+    const unsigned ngroups = (unsigned)((R + (32 / (LPR)) * (ROWS) - 1) / ((32 / (LPR)) * (ROWS))); \
+    auto k = KERNEL<LPR, NV, ROWS, AVFLAG>;                                                         \
+    const unsigned blocks = persistent_blocks(k, kSmThreads, (ngroups + 7) / 8);                    \
+    k<<<blocks, kSmThreads, 0, s>>>(__VA_ARGS__, (unsigned)R, ngroups);                             \
+  } while (0)
+
+#define SB_SOFTMAX_LAUNCH(KERNEL, AVFLAG, ...)                                    \
+  do {                                                                            \
+    if (d.K <= 64) SB_SOFTMAX_ONE(KERNEL, 8, 1, 2, AVFLAG, __VA_ARGS__);          \
+    else if (d.K <= 128) SB_SOFTMAX_ONE(KERNEL, 16, 1, 2, AVFLAG, __VA_ARGS__);   \
+    else if (d.K <= 256) SB_SOFTMAX_ONE(KERNEL, 32, 1, 2, AVFLAG, __VA_ARGS__);   \
+    else if (d.K <= 512) SB_SOFTMAX_ONE(KERNEL, 32, 2, 2, AVFLAG, __VA_ARGS__);   \
+    else if (d.K <= 1024) SB_SOFTMAX_ONE(KERNEL, 32, 4, 1, AVFLAG, __VA_ARGS__);  \
+    else SB_SOFTMAX_ONE(KERNEL, 32, 8, 1, AVFLAG, __VA_ARGS__);                   \
   } while (0)
 
 int launch_softmax_fwd(cudaStream_t s, Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop,
@@ -712,6 +943,7 @@ int launch_softmax_fwd(cudaStream_t s, Dims4 d, View4 beta, View4 alpha, View4 m
   const long long R = (long long)d.H * d.B * d.J;
   if (R == 0 || d.K == 0) return SB_OK;
   if (d.K > 2048) return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");
+  if (R > 0x3fffffffLL) return fail(SB_ERR_UNSUPPORTED, "softmax over more than 2^30 rows is not supported");
   if (all_vec(beta, alpha, mask, drop))
     SB_SOFTMAX_LAUNCH(softmax_fwd_kernel, true, d, beta, alpha, mask, drop, scale, rng);
   else
@@ -725,6 +957,7 @@ int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 d
   const long long R = (long long)d.H * d.B * d.J;
   if (R == 0 || d.K == 0) return SB_OK;
   if (d.K > 2048) return fail(SB_ERR_UNSUPPORTED, "softmax rows longer than 2048 are not supported");
+  if (R > 0x3fffffffLL) return fail(SB_ERR_UNSUPPORTED, "softmax over more than 2^30 rows is not supported");
   if (all_vec(alpha, mask, dattn_drop, dbeta))
     SB_SOFTMAX_LAUNCH(softmax_bwd_kernel, true, d, alpha, mask, dattn_drop, dbeta);
   else
@@ -733,14 +966,29 @@ int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 d
   return SB_OK;
 }
 
-#define SB_ROW_LAUNCH(KERNEL, AVFLAG, F, ...)                                    \
-  do {                                                                           \
-    const unsigned blocks = (unsigned)((R + 3) / 4);                             \
-    if ((F) <= 256) KERNEL<1, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);       \
-    else if ((F) <= 512) KERNEL<2, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);  \
-    else if ((F) <= 1024) KERNEL<4, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__); \
-    else KERNEL<8, AVFLAG><<<blocks, kRowThreads, 0, s>>>(__VA_ARGS__);                  \
+#define SB_ROW_ONE(KERNEL, NV, AVFLAG, ...)                                                  \
+  do {                                                                                       \
+    auto k = KERNEL<NV, AVFLAG>;                                                             \
+    const unsigned blocks = persistent_blocks(k, kSmThreads, (unsigned long long)((R + 7) / 8)); \
+    k<<<blocks, kSmThreads, 0, s>>>(__VA_ARGS__);                                            \
   } while (0)
+
+#define SB_ROW_LAUNCH(KERNEL, AVFLAG, F, ...)                            \
+  do {                                                                   \
+    if ((F) <= 256) SB_ROW_ONE(KERNEL, 1, AVFLAG, __VA_ARGS__);          \
+    else if ((F) <= 512) SB_ROW_ONE(KERNEL, 2, AVFLAG, __VA_ARGS__);     \
+    else if ((F) <= 1024) SB_ROW_ONE(KERNEL, 4, AVFLAG, __VA_ARGS__);    \
+    else SB_ROW_ONE(KERNEL, 8, AVFLAG, __VA_ARGS__);                     \
+  } while (0)
+
+// dense, logical-order [B,J,F] (so that flat element i is the same element in every tensor)
+bool dense3(const Dims3& d, const View3& v) {
+  return v.vec && v.sF == 1 && (d.J <= 1 || v.sJ == d.F) && (d.B <= 1 || v.sB == (long long)d.J * d.F);
+}
+template <class... V>
+bool all_dense3(const Dims3& d, const V&... v) {
+  return (dense3(d, v) && ...);
+}
 
 int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid,
                  const void* gamma, const void* beta, View3 mask, View3 lin, View3 diff,
@@ -748,6 +996,7 @@ int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resi
   const long long R = (long long)d.B * d.J;
   if (R == 0 || d.F == 0) return SB_OK;
   if (d.F > 2048) return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported");
+  if (R > 0x3fffffffLL) return fail(SB_ERR_UNSUPPORTED, "more than 2^30 tokens are not supported");
   const int pvec = param_vec({bias, gamma, beta}, d.F);
   if (pvec && all_vec(in, resid, mask, lin, diff, ln, out))
     SB_ROW_LAUNCH(bdrln_kernel, true, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out, rng, pvec);
@@ -762,6 +1011,7 @@ int launch_blnrd(cudaStream_t s, Dims3 d, View3 dln, View2 istd, View3 diff, Vie
   const long long R = (long long)d.B * d.J;
   if (R == 0 || d.F == 0) return SB_OK;
   if (d.F > 2048) return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported");
+  if (R > 0x3fffffffLL) return fail(SB_ERR_UNSUPPORTED, "more than 2^30 tokens are not supported");
   if (all_vec(dln, diff, mask, dresid, dlin))
     SB_ROW_LAUNCH(blnrd_kernel, true, d.F, d, dln, istd, diff, mask, dresid, dlin);
   else
@@ -774,9 +1024,24 @@ int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, 
                View3 drop2, int activation, Rng rng) {
   const long long R = (long long)d.B * d.J;
   if (R == 0 || d.F == 0) return SB_OK;
+  const int pvec = param_vec({bias}, d.F);
+  if (pvec && all_dense3(d, in, mask, lin1, drop2)) {
+    const unsigned long long ngroups = (unsigned long long)R * (d.F / 8);
+    const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
+    if (activation == SB_ACT_RELU) {
+      auto k = bad_flat_kernel<SB_ACT_RELU>;
+      k<<<persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s>>>(
+          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng);
+    } else {
+      auto k = bad_flat_kernel<SB_ACT_GELU>;
+      k<<<persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s>>>(
+          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng);
+    }
+    SB_CUDA_OK(cudaGetLastError());
+    return SB_OK;
+  }
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  const int pvec = param_vec({bias}, d.F);
   if (pvec && all_vec(in, mask, lin1, drop2))
     bad_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec);
   else
@@ -788,6 +1053,18 @@ int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, 
 int launch_bei(cudaStream_t s, Dims3 d, View3 a, View3 b, View3 out) {
   const long long R = (long long)d.B * d.J;
   if (R == 0 || d.F == 0) return SB_OK;
+  // same dense memory order in all three (any order): flat add
+  const bool same = a.vec && b.vec && out.vec && a.sB == b.sB && a.sB == out.sB && a.sJ == b.sJ && a.sJ == out.sJ &&
+                    ((a.sJ == d.F && a.sB == (long long)d.J * d.F) || (a.sB == d.F && a.sJ == (long long)d.B * d.F) ||
+                     d.B == 1 || d.J == 1);
+  if (same && dense3(d, a) ) {
+    const unsigned long long ngroups = (unsigned long long)R * (d.F / 8);
+    const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
+    add_flat_kernel<<<persistent_blocks(add_flat_kernel, kSmThreads, work), kSmThreads, 0, s>>>(
+        ngroups, (const uint4*)a.p, (const uint4*)b.p, (uint4*)out.p);
+    SB_CUDA_OK(cudaGetLastError());
+    return SB_OK;
+  }
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
   if (all_vec(a, b, out)) bei_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
@@ -800,6 +1077,20 @@ int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bs
                long long bsH, View5 out) {
   const long long R = (long long)d.N * d.P * d.H * d.B;
   if (R == 0 || d.J == 0) return SB_OK;
+  // dense [N,P,H,B,J] in logical order on both sides and a dense bias: rows of B*J elements plus one scalar
+  const long long BJ = (long long)d.B * d.J;
+  const bool dense = in.vec && out.vec && d.J % 8 == 0 && in.sJ == 1 && out.sJ == 1 && in.sB == d.J && out.sB == d.J &&
+                     in.sH == BJ && out.sH == BJ && in.sP == BJ * d.H && out.sP == BJ * d.H &&
+                     in.sN == BJ * d.H * d.P && out.sN == BJ * d.H * d.P && bsH == 1 && bsP == d.H &&
+                     bsN == (long long)d.H * d.P;
+  if (dense) {
+    const unsigned long long ngroups = (unsigned long long)R * (d.J / 8);
+    const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
+    rowbias_flat_kernel<<<persistent_blocks(rowbias_flat_kernel, kSmThreads, work), kSmThreads, 0, s>>>(
+        ngroups, (unsigned)(BJ / 8), (const uint4*)in.p, (const __half*)bias, (uint4*)out.p);
+    SB_CUDA_OK(cudaGetLastError());
+    return SB_OK;
+  }
   const int spans = (d.J + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
   if (all_vec(in, out)) aib_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
