@@ -198,10 +198,13 @@ int sb_backward_encoder_input(void* stream, const sb_tensor* dxatt, const sb_ten
  * Letters in all three are batch dims, letters in A and B only are summed.
  * Each of the four letter groups must collapse to one stride in every operand,
  * as in the reference (pytorch_module/einsumparser.h:29-37).
- * Replaces Einsum::run / Gemm::run, pytorch_module/gemm.cuh:52-147. */
+ * Replaces Einsum::run / Gemm::run, pytorch_module/gemm.cuh:52-147.
+ * workspace (optional, may be NULL): device scratch for fp32 partial sums; with it a
+ * contraction that has few output tiles and a long summed extent (the weight gradients)
+ * is split along K over more SMs and reduced in a fixed order.  It need not be cleared. */
 int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims,
               const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha,
-              int impl);
+              int impl, void* workspace, size_t workspace_bytes);
 /* Which kernel the last sb_einsum on this thread ran: SB_GEMM_TCGEN05 or SB_GEMM_SIMT. */
 int sb_einsum_last_impl(void);
 /* Every wait inside the tcgen05 kernel is bounded; when one runs out the kernel
@@ -233,8 +236,8 @@ typedef struct sb_encoder_config {
 } sb_encoder_config;
 
 /* Replaces init() (pytorch_module/encoder.cu:304-306) and the code generation of
- * pytorch_module/encoder.py:165-405.  Allocates the handle's workspace (the only
- * device allocation the library ever makes for a layer). */
+ * pytorch_module/encoder.py:165-405.  Allocates the handle's workspaces (token-reduction partials and
+ * split-K partials: the only device allocations the library makes for a layer). */
 int sb_encoder_create(const sb_encoder_config* cfg, sb_encoder** out);
 /* Replaces destroy() (pytorch_module/encoder.cu:316-318). */
 int sb_encoder_destroy(sb_encoder* enc);

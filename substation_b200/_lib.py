@@ -70,7 +70,8 @@ SIGNATURES = {
     'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
     'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
     'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),
-    'sb_einsum': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, c_int]),
+    'sb_einsum': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, c_int, c_void_p,
+                        ctypes.c_size_t]),
     'sb_einsum_last_impl': (c_int, []),
     'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
     'sb_encoder_create': (c_int, [ctypes.POINTER(SbEncoderConfig), ctypes.POINTER(c_void_p)]),

@@ -325,10 +325,13 @@ extern "C" int sb_backward_encoder_input(void* stream, const sb_tensor* dxatt, c
 }
 
 extern "C" int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims,
-                         const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha, int impl) {
+                         const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha, int impl,
+                         void* workspace, size_t workspace_bytes) {
   GemmProblem g;
   SB_TRY(plan_einsum(a_dims, a, b_dims, b, c_dims, c, alpha, &g));
-  return run_gemm((cudaStream_t)stream, g, impl);
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
+    return fail(SB_ERR_ALIGNMENT, "einsum: workspace must be 16-byte aligned");
+  return run_gemm((cudaStream_t)stream, g, impl, workspace, workspace ? workspace_bytes : 0);
 }
 extern "C" int sb_einsum_last_impl(void) { return g_last_gemm_impl; }
 extern "C" int sb_device_error(void* stream, int* code) {
@@ -384,6 +387,8 @@ struct sb_encoder {
   std::map<std::string, std::string> layout;  // name -> dim order in memory
   std::vector<std::string> param_order, fwd_order, bwd_order;
   void* workspace = nullptr;
+  void* gemm_ws = nullptr;     // fp32 split-K partials of the weight-gradient contractions
+  size_t gemm_ws_bytes = 0;
   int device = 0;
   int launches = 0;
   bool timing = false;
@@ -468,7 +473,7 @@ int einsum(sb_encoder* e, cudaStream_t s, const char* name, const std::string& a
   const sb_tensor ta = e->mem(a, ad), tb = e->mem(b, bd), tc = e->mem(c, cd);
   GemmProblem g;
   SB_TRY(plan_einsum(ad.c_str(), &ta, bd.c_str(), &tb, cd.c_str(), &tc, alpha, &g));
-  return run_gemm(s, g, SB_GEMM_AUTO);
+  return run_gemm(s, g, SB_GEMM_AUTO, e->gemm_ws, e->gemm_ws_bytes);
 }
 
 }  // namespace
@@ -522,6 +527,13 @@ extern "C" int sb_encoder_create(const sb_encoder_config* cfg, sb_encoder** out)
   SB_CUDA_OK(cudaGetDevice(&e->device));
   SB_CUDA_OK(cudaMalloc(&e->workspace, kWsBytes));
   SB_CUDA_OK(cudaMemset(e->workspace, 0, kWsBytes));
+  // up to four fp32 partial copies of the largest weight gradient (the stacked [3E, E] projection)
+  e->gemm_ws_bytes = std::min<size_t>((size_t)4 * 3 * e->I * e->I * sizeof(float), (size_t)512 << 20);
+  if (cudaMalloc(&e->gemm_ws, e->gemm_ws_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    e->gemm_ws = nullptr;       // split-K is an optimisation; run without it
+    e->gemm_ws_bytes = 0;
+  }
   *out = e.release();
   return SB_OK;
 }
@@ -531,6 +543,7 @@ extern "C" int sb_encoder_destroy(sb_encoder* e) {
   for (auto& m : e->marks) cudaEventDestroy(m.second);
   for (auto ev : e->event_pool) cudaEventDestroy(ev);
   if (e->workspace) cudaFree(e->workspace);
+  if (e->gemm_ws) cudaFree(e->gemm_ws);
   delete e;
   return SB_OK;
 }

@@ -234,7 +234,8 @@ namespace {
 constexpr int kBM = 128;                 // UMMA M
 constexpr int kBK = 64;                  // one 128-byte swizzle span of fp16
 constexpr int kTcThreads = 192;          // 6 warps
-constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
+constexpr int kABytes = kBM * kBK * 2;   // 16 KiB per 64-wide K block
+constexpr int kStageOutBytes = 4 * 2 * 4096;  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B)
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
 __device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel in this process
@@ -242,13 +243,15 @@ __device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel in t
 struct TcParams {
   long long M, N, K;
   long long sCb, sCm, sCn;
-  __half* C;
+  void* C;             // fp16 output, or fp32 split-K partials [split][batch][M][N]
   float alpha;
   int a_mn, b_mn;      // operand is MN-major in global memory
   int a_swap, b_swap;  // tensor-map dims 1 and 2 are exchanged (kept in increasing-stride order)
-  int c_vec;           // sCn == 1 and rows are 16-byte aligned
-  int tiles_m, tiles_n;
-  long long tiles;     // tiles_m * tiles_n * batch
+  int c_swap;
+  int c_mode;          // 0: scalar fp16 stores, 1: 128-bit fp16 stores, 2: TMA stores, 3: fp32 partials
+  int tiles_m, tiles_n, batch;
+  int splits, kt_per_split;  // split-K: K stages per split
+  long long tiles;     // tiles_m * tiles_n * batch * splits
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -262,6 +265,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -289,6 +295,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -312,7 +323,8 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+// 32 consecutive accumulator columns of this thread's TMEM lane (no wait)
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -322,40 +334,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int BN>
+// KS: 64-wide K blocks per pipeline stage (2 halves the number of passes over a K-major
+// operand's rows, which matters when the operand streams from HBM).
+template <int BN, int KS>
 struct TcCfg {
-  static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kBBytes = BN * kBK * 2;                 // per K block
+  static constexpr int kStageBytes = KS * (kABytes + kBBytes);
+  static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   static constexpr int kTileBytes = kStages * kStageBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators: the epilogue of one tile overlaps the next tile's MMAs
-  static constexpr int kSmemBytes = kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kTileBytes + kStageOutBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// Persistent: CTA c works on tiles c, c + gridDim.x, ... (n fastest, then m, then batch).
-template <int BN>
+// Persistent: CTA c works on items c, c + gridDim.x, ...; item = (split, batch, m tile, n tile), n fastest.
+template <int BN, int KS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const TcParams p) {
-  using Cfg = TcCfg<BN>;
+               const __grid_constant__ CUtensorMap tmC, const TcParams p) {
+  using Cfg = TcCfg<BN, KS>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const uint32_t bars = tiles + Cfg::kTileBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t stage_out = tiles + Cfg::kTileBytes;  // 1024-aligned
+  const uint32_t bars = stage_out + kStageOutBytes;    // full[S], empty[S], acc_full[2], acc_empty[2]
   const uint32_t bar_full = bars, bar_empty = bars + 8 * S;
   const uint32_t bar_accf = bars + 16 * S, bar_acce = bars + 16 * S + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (tiles - raw) + Cfg::kTileBytes + 16 * S + 32);
+  uint8_t* gen_base = smem_raw + (tiles - raw);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + Cfg::kTileBytes + kStageOutBytes + 16 * S + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KT = (int)((p.K + kBK - 1) / kBK);
+  const int KT = (int)((p.K + kBK - 1) / kBK);        // 64-wide K blocks in total
+  const long long per_split = (long long)p.tiles_n * p.tiles_m * p.batch;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -370,6 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    if (p.c_mode == 2) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -386,10 +400,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
-      const int n0 = (int)(t % p.tiles_n) * BN;
-      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * kBM;
-      const int bt = (int)(t / ((long long)p.tiles_n * p.tiles_m));
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      const long long tt = t % per_split;
+      const int split = (int)(t / per_split);
+      const int n0 = (int)(tt % p.tiles_n) * BN;
+      const int m0 = (int)((tt / p.tiles_n) % p.tiles_m) * kBM;
+      const int bt = (int)(tt / ((long long)p.tiles_n * p.tiles_m));
+      const int kb_begin = split * p.kt_per_split;
+      const int kb_end = min(KT, kb_begin + p.kt_per_split);
+      for (int kb = kb_begin; kb < kb_end; kb += KS, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
@@ -397,28 +415,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
           const uint32_t full = bar_full + 8 * s;
           mbar_expect_tx(full, (uint32_t)Cfg::kStageBytes);
-          const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
-          const int k0 = kt * kBK;
-          if (!p.a_mn) {
-            // dims (k, m, batch), box 64 x 128
-            if (p.a_swap) tma_load_3d(sa, &tmA, full, k0, bt, m0);
-            else tma_load_3d(sa, &tmA, full, k0, m0, bt);
-          } else {
-            // dims (m, k, batch), two boxes of 64 (m) x 64 (k)
+          const uint32_t sa0 = tiles + s * Cfg::kStageBytes;
+          const uint32_t sb0 = sa0 + KS * kABytes;
 #pragma unroll
-            for (int h = 0; h < kBM / 64; ++h) {
-              if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
-              else tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+          for (int ks = 0; ks < KS; ++ks) {
+            // blocks past the end of K are fetched out of range: zero filled, no memory traffic
+            const int k0 = (kb + ks) * kBK;
+            const uint32_t sa = sa0 + ks * kABytes, sb_ = sb0 + ks * Cfg::kBBytes;
+            if (!p.a_mn) {
+              // dims (k, m, batch), box 64 x 128
+              if (p.a_swap) tma_load_3d(sa, &tmA, full, k0, bt, m0);
+              else tma_load_3d(sa, &tmA, full, k0, m0, bt);
+            } else {
+              // dims (m, k, batch), two boxes of 64 (m) x 64 (k)
+#pragma unroll
+              for (int h = 0; h < kBM / 64; ++h) {
+                if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
+                else tma_load_3d(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+              }
             }
-          }
-          if (!p.b_mn) {
-            if (p.b_swap) tma_load_3d(sb_, &tmB, full, k0, bt, n0);
-            else tma_load_3d(sb_, &tmB, full, k0, n0, bt);
-          } else {
+            if (!p.b_mn) {
+              if (p.b_swap) tma_load_3d(sb_, &tmB, full, k0, bt, n0);
+              else tma_load_3d(sb_, &tmB, full, k0, n0, bt);
+            } else {
 #pragma unroll
-            for (int h = 0; h < BN / 64; ++h) {
-              if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
-              else tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
+              for (int h = 0; h < BN / 64; ++h) {
+                if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
+                else tma_load_3d(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
+              }
             }
           }
         }
@@ -438,25 +462,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t it = 0, lt = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++lt) {
+      const int split = (int)(t / per_split);
+      const int kb_begin = split * p.kt_per_split;
+      const int kb_end = min(KT, kb_begin + p.kt_per_split);
       const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
       // the epilogue must have drained this accumulator (passes at once for its first use)
       ok = __all_sync(0xffffffffu, mbar_wait(bar_acce + 8 * buf, aph ^ 1u, 4));
       if (!ok) break;
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      for (int kb = kb_begin; kb < kb_end; kb += KS, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t sa = tiles + s * Cfg::kStageBytes, sb_ = sa + kABytes;
+          const uint32_t sa0 = tiles + s * Cfg::kStageBytes;
+          const uint32_t sb0 = sa0 + KS * kABytes;
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
-            const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
-            umma_f16(tmem_d, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint64_t da = make_desc(sa0 + ks * kABytes + k * a_step, a_lbo, 1024u);
+              const uint64_t db = make_desc(sb0 + ks * Cfg::kBBytes + k * b_step, b_lbo, 1024u);
+              umma_f16(tmem_d, da, db, idesc, (kb > kb_begin || ks > 0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
         }
@@ -468,49 +499,114 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ---------------- epilogue (4 warps; warp w reads TMEM lanes 32*(w%4)..+31) ----------------
     const int q = warp & 3;
-    uint32_t lt = 0;
+    const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;  // two 4 KiB buffers
+    uint8_t* my_stage_gen = gen_base + Cfg::kTileBytes + (warp - 2) * 8192;
+    uint32_t lt = 0, nstore = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++lt) {
-      const int n0 = (int)(t % p.tiles_n) * BN;
-      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * kBM;
-      const long long bt = t / ((long long)p.tiles_n * p.tiles_m);
+      const long long tt = t % per_split;
+      const int split = (int)(t / per_split);
+      const int n0 = (int)(tt % p.tiles_n) * BN;
+      const int m0 = (int)((tt / p.tiles_n) % p.tiles_m) * kBM;
+      const long long bt = tt / ((long long)p.tiles_n * p.tiles_m);
       const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_accf + 8 * buf, aph, 3));
       if (!ok) break;
       tc_fence_after();
       const long long m = (long long)m0 + q * 32 + lane;
-      __half* crow = p.C + bt * p.sCb + m * p.sCm;
       const uint32_t tsrc = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+      if (p.c_mode == 2) {
+        // 64 columns at a time: TMEM -> registers -> fp16 -> swizzled staging row -> TMA store
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tsrc + (uint32_t)(c * 32), r);
-        if (c == BN / 32 - 1) {
-          // accumulator fully read into registers: hand it back to the MMA warp
-          tc_fence_before();
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 64), r);
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 64 + 32), r + 32);
+          tmem_ld_wait();
+          if (c == BN / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acce + 8 * buf);
+          }
+          const uint32_t sbuf = nstore & 1u;
+          // the store issued two chunks ago must have finished reading this buffer
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acce + 8 * buf);
+          uint8_t* row = my_stage_gen + sbuf * 4096 + lane * 128;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+            *reinterpret_cast<uint4*>(row + ((v ^ (lane & 7)) << 4)) = pack8(f);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          const int nc = n0 + c * 64, mc = m0 + q * 32;
+          if (lane == 0 && nc < p.N && mc < p.M) {
+            if (p.c_swap) tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, (int)bt, mc);
+            else tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, mc, (int)bt);
+          }
+          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          ++nstore;
         }
-        if (m < p.M) {
-          const long long nb = (long long)n0 + c * 32;
-          if (p.c_vec) {
+      } else if (p.c_mode == 3) {
+        float* crow = reinterpret_cast<float*>(p.C) + ((long long)split * p.batch + bt) * p.M * p.N + m * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          if (c == BN / 32 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acce + 8 * buf);
+          }
+          if (m < p.M) {
+            const long long nb = (long long)n0 + c * 32;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (nb + v * 8 < p.N) {
-                float f[8];
+            for (int v = 0; v < 8; ++v)
+              if (nb + v * 4 < p.N)  // N % 4 == 0 in this mode
+                *reinterpret_cast<uint4*>(crow + nb + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+          }
+        }
+      } else {
+        __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          if (c == BN / 32 - 1) {
+            // accumulator fully read into registers: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acce + 8 * buf);
+          }
+          if (m < p.M) {
+            const long long nb = (long long)n0 + c * 32;
+            if (p.c_mode == 1) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
-                *reinterpret_cast<uint4*>(crow + nb + v * 8) = pack8(f);
+              for (int v = 0; v < 4; ++v) {
+                if (nb + v * 8 < p.N) {
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+                  *reinterpret_cast<uint4*>(crow + nb + v * 8) = pack8(f);
+                }
               }
-            }
-          } else {
+            } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+              for (int e = 0; e < 32; ++e)
+                if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+            }
           }
         }
       }
     }
+    // all bulk stores of this thread must be complete before the CTA's shared memory goes away
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
   }
   if (*reinterpret_cast<volatile int*>(&g_tc_error) != 0) {
     // failure path: give bulk copies already in flight time to land before the CTA's memory is reused
@@ -522,6 +618,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+  }
+}
+
+// out = alpha * sum over splits of the fp32 partials [split][batch][M][N] (fixed order)
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, long long M, long long N,
+                     __half* out, long long sCb, long long sCm, long long sCn, float alpha) {
+  const long long total4 = batch * M * N / 4;  // N % 4 == 0
+  const long long plane = batch * M * N;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total4; i += (long long)gridDim.x * 256) {
+    float4 acc = __ldcs(reinterpret_cast<const float4*>(ws) + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(ws + s * plane) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long e = i * 4;
+    const long long n = e % N, m = (e / N) % M, b = e / (N * M);
+    __half* o = out + b * sCb + m * sCm + n * sCn;
+    if (sCn == 1 && ((reinterpret_cast<uintptr_t>(o) & 7u) == 0)) {
+      __half2 lo = __floats2half2_rn(acc.x * alpha, acc.y * alpha), hi = __floats2half2_rn(acc.z * alpha, acc.w * alpha);
+      uint2 u;
+      u.x = *reinterpret_cast<uint32_t*>(&lo);
+      u.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o) = u;
+    } else {
+      o[0] = __float2half_rn(acc.x * alpha);
+      o[sCn] = __float2half_rn(acc.y * alpha);
+      o[2 * sCn] = __float2half_rn(acc.z * alpha);
+      o[3 * sCn] = __float2half_rn(acc.w * alpha);
+    }
   }
 }
 
@@ -543,49 +669,52 @@ struct OperandMap {
   int swap;  // dims 1 and 2 exchanged
 };
 
-// Operand X[batch][r][k] (r = m or n) with strides (sb, sr, sk); tile = rows x 64 (k).
-bool make_operand_map(const void* ptr, long long R, long long K, long long batch, long long sr,
-                      long long sk, long long sb, int rows, OperandMap* out, std::string* why) {
-  if (reinterpret_cast<uintptr_t>(ptr) & 15u) { *why = "operand base is not 16-byte aligned"; return false; }
-  cuuint64_t dim[3];
-  long long str[3];
-  cuuint32_t box[3];
-  if (sk == 1 || K == 1) {  // K-major (a single K column is K-major with any stride)
-    out->mn = 0;
-    dim[0] = (cuuint64_t)K; dim[1] = (cuuint64_t)R; dim[2] = (cuuint64_t)batch;
-    str[0] = 1; str[1] = sr; str[2] = sb;
-    box[0] = kBK; box[1] = (cuuint32_t)rows; box[2] = 1;
-    if (K == 1 && sk != 1) { /* dim0 has extent 1; its stride is irrelevant */ }
-  } else if (sr == 1) {
-    out->mn = 1;
-    dim[0] = (cuuint64_t)R; dim[1] = (cuuint64_t)K; dim[2] = (cuuint64_t)batch;
-    str[0] = 1; str[1] = sk; str[2] = sb;
-    box[0] = 64; box[1] = kBK; box[2] = 1;
-  } else {
-    *why = "operand has no unit-stride index";
-    return false;
-  }
+// 3-D fp16 tensor map with 128-byte swizzle over dims (inner, d1, d2) with element strides
+// (1, s1, s2) and box (b0, b1, 1); dims 1 and 2 are exchanged when needed to keep strides increasing.
+bool encode_map(const void* ptr, cuuint64_t n0, cuuint64_t n1, cuuint64_t n2, long long s1, long long s2,
+                cuuint32_t b0, cuuint32_t b1, CUtensorMap* map, int* swapped, std::string* why) {
+  if (reinterpret_cast<uintptr_t>(ptr) & 15u) { *why = "base is not 16-byte aligned"; return false; }
+  cuuint64_t dim[3] = {n0, n1, n2};
+  long long str[3] = {1, s1, s2};
+  cuuint32_t box[3] = {b0, b1, 1};
   // extent-1 dims: any legal stride (a multiple of 8 elements)
   if (dim[1] == 1) str[1] = ((long long)dim[0] + 7) / 8 * 8;
   if (dim[2] == 1) str[2] = std::max(str[1] * (long long)dim[1], ((long long)dim[0] + 7) / 8 * 8);
-  out->swap = 0;
-  if (str[2] < str[1]) {  // keep strides increasing
+  *swapped = 0;
+  if (str[2] < str[1]) {
     std::swap(dim[1], dim[2]);
     std::swap(str[1], str[2]);
     std::swap(box[1], box[2]);
-    out->swap = 1;
+    *swapped = 1;
   }
   for (int i = 1; i < 3; ++i)
-    if (str[i] <= 0 || (str[i] * 2) % 16 != 0) { *why = "operand stride is not a positive multiple of 16 bytes"; return false; }
+    if (str[i] <= 0 || (str[i] * 2) % 16 != 0) { *why = "stride is not a positive multiple of 16 bytes"; return false; }
   for (int i = 0; i < 3; ++i)
-    if (dim[i] == 0 || dim[i] > 0xffffffffull) { *why = "operand extent out of range"; return false; }
+    if (dim[i] == 0 || dim[i] > 0xffffffffull) { *why = "extent out of range"; return false; }
   cuuint64_t gstr[2] = {(cuuint64_t)str[1] * 2, (cuuint64_t)str[2] * 2};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = g_encode(&out->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dim,
-                              gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dim, gstr, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled rejected the operand (code " + std::to_string((int)r) + ")"; return false; }
+  if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled rejected it (code " + std::to_string((int)r) + ")"; return false; }
   return true;
+}
+
+// Operand X[batch][r][k] (r = m or n) with strides (sb, sr, sk); tile = rows x 64 (k).
+bool make_operand_map(const void* ptr, long long R, long long K, long long batch, long long sr,
+                      long long sk, long long sb, int rows, OperandMap* out, std::string* why) {
+  if (sk == 1 || K == 1) {  // K-major (a single K column is K-major with any stride)
+    out->mn = 0;
+    return encode_map(ptr, (cuuint64_t)K, (cuuint64_t)R, (cuuint64_t)batch, sr, sb, kBK, (cuuint32_t)rows,
+                      &out->map, &out->swap, why);
+  }
+  if (sr == 1) {
+    out->mn = 1;
+    return encode_map(ptr, (cuuint64_t)R, (cuuint64_t)K, (cuuint64_t)batch, sk, sb, 64, kBK, &out->map,
+                      &out->swap, why);
+  }
+  *why = "operand has no unit-stride index";
+  return false;
 }
 
 int sm_count() {
@@ -599,37 +728,84 @@ int sm_count() {
   return cached > 0 ? cached : 148;
 }
 
-template <int BN>
-int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b) {
-  using Cfg = TcCfg<BN>;
+// Split K only when the output tiles cover less than a third of the SMs: the fp32 partials cost
+// 2 * splits * M * N * 4 bytes of extra traffic, which a fuller grid does not win back.
+int pick_splits(long long tiles, int KT, int ks, long long out_elems, size_t ws_bytes) {
+  const int sms = sm_count();
+  if (tiles * 3 > sms) return 1;
+  int best = 1;
+  for (int s : {2, 3, 4}) {
+    if (KT / s < 8 * ks) break;  // keep at least 8 stages per item
+    if ((size_t)s * out_elems * sizeof(float) > ws_bytes) break;
+    if (tiles * s > sms) break;
+    best = s;
+  }
+  return best;
+}
+
+template <int BN, int KS>
+int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b, void* ws,
+              size_t ws_bytes) {
+  using Cfg = TcCfg<BN, KS>;
   // per-device attribute; setting it is cheap and idempotent
-  SB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  SB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<BN, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
-  p.C = reinterpret_cast<__half*>(g.C);
+  p.C = g.C;
   p.alpha = g.alpha;
-  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
-  p.c_vec = (g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && g.sCb % 8 == 0 &&
-             (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0) ? 1 : 0;
+  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap; p.c_swap = 0;
   p.tiles_n = (int)((g.N + BN - 1) / BN);
   p.tiles_m = (int)((g.M + kBM - 1) / kBM);
-  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
+  p.batch = (int)g.batch;
+  const int KT = (int)((g.K + kBK - 1) / kBK);
+  const long long base_tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
+  p.splits = 1;
+  if (ws && g.N % 4 == 0) p.splits = pick_splits(base_tiles, KT, KS, g.batch * g.M * g.N, ws_bytes);
+  p.kt_per_split = ((KT + p.splits - 1) / p.splits + KS - 1) / KS * KS;
+  p.splits = (KT + p.kt_per_split - 1) / p.kt_per_split;  // no split may be left without work
+  p.tiles = base_tiles * p.splits;
+  CUtensorMap cmap;
+  memset(&cmap, 0, sizeof(cmap));
+  const bool c_vec = g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && (g.batch == 1 || g.sCb % 8 == 0) &&
+                     (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0;
+  if (p.splits > 1) {
+    p.c_mode = 3;
+    p.C = ws;
+  } else {
+    p.c_mode = c_vec ? 1 : 0;
+    if (c_vec) {
+      std::string why;
+      int swapped = 0;
+      if (encode_map(g.C, (cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch, g.sCm, g.sCb, 64, 32, &cmap, &swapped, &why)) {
+        p.c_mode = 2;
+        p.c_swap = swapped;
+      }
+    }
+  }
   const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
-  gemm_tc_kernel<BN><<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(a.map, b.map, p);
+  gemm_tc_kernel<BN, KS><<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(a.map, b.map, cmap, p);
   SB_CUDA_OK(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long total4 = g.batch * g.M * g.N / 4;
+    const unsigned blocks = (unsigned)std::min<long long>((total4 + 255) / 256, (long long)sm_count() * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float*>(ws), p.splits, g.batch, g.M, g.N,
+                                                reinterpret_cast<__half*>(g.C), g.sCb, g.sCm, g.sCn, g.alpha);
+    SB_CUDA_OK(cudaGetLastError());
+  }
   return SB_OK;
 }
 
 int pick_bn(long long M, long long N, long long batch) {
   // 128 x 256 moves the fewest operand bytes per flop (each CTA fetches its own tiles), so it is
-  // used whenever N fills most of it and the persistent grid still covers about half the SMs.
+  // used whenever N fills most of it and the persistent grid still covers about half the SMs
+  // (split-K can recover the rest when K is long).
   const long long mt = (M + kBM - 1) / kBM;
   if (N <= 64) return 64;
   if (N <= 128) return 128;
   const long long t256 = mt * ((N + 255) / 256) * batch;
   const bool fills = (N % 256 == 0) || (N % 256 > 128) || N >= 1024;
-  if (fills && t256 >= 64) return 256;
+  if (fills && t256 >= 24) return 256;
   const long long t128 = mt * ((N + 127) / 128) * batch;
   if (t128 >= 64 || N % 128 == 0 || N % 128 > 64) return 128;
   return 64;
@@ -645,18 +821,19 @@ long long padded_work(long long M, long long N) {
 
 bool tcgen05_supported(const GemmProblem& g, std::string* why) {
   if (g.K < 1 || g.M < 1 || g.N < 1) { *why = "empty problem"; return false; }
+  if (g.batch > 0x7fffffffLL) { *why = "too many batches"; return false; }
   if (!(g.sAk == 1 || g.sAm == 1 || g.K == 1)) { *why = "A has no unit-stride index"; return false; }
   if (!(g.sBk == 1 || g.sBn == 1 || g.K == 1)) { *why = "B has no unit-stride index"; return false; }
   return true;
 }
 
-int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0) {
+int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0, void* ws, size_t ws_bytes) {
   std::string why;
   if (!tcgen05_supported(g0, &why)) return fail(SB_ERR_UNSUPPORTED, "tcgen05 contraction: " + why);
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   // C^T = B^T A^T: use the orientation that wastes fewer padded tile elements
-  // (ties: keep N as the unit-stride index of C so rows are stored as 128-bit vectors).
+  // (ties: keep N as the unit-stride index of C so rows are stored as full lines).
   GemmProblem g = g0;
   const long long w0 = padded_work(g.M, g.N), w1 = padded_work(g.N, g.M);
   const bool swap = (w1 < w0) || (w1 == w0 && g.sCn != 1 && g.sCm == 1);
@@ -675,18 +852,18 @@ int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0) {
   if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))
     return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand B: " + why);
   int st;
-  if (bn == 256) st = launch_tc<256>(s, g, a, b);
-  else if (bn == 128) st = launch_tc<128>(s, g, a, b);
-  else st = launch_tc<64>(s, g, a, b);
+  if (bn == 256) st = launch_tc<256, 1>(s, g, a, b, ws, ws_bytes);
+  else if (bn == 128) st = launch_tc<128, 2>(s, g, a, b, ws, ws_bytes);
+  else st = launch_tc<64, 2>(s, g, a, b, ws, ws_bytes);
   if (st == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
   return st;
 }
 
-int run_gemm(cudaStream_t s, const GemmProblem& g, int impl) {
+int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws, size_t ws_bytes) {
   if (impl == SB_GEMM_SIMT) return launch_gemm_simt(s, g);
-  if (impl == SB_GEMM_TCGEN05) return launch_gemm_tcgen05(s, g);
+  if (impl == SB_GEMM_TCGEN05) return launch_gemm_tcgen05(s, g, ws, ws_bytes);
   if (impl != SB_GEMM_AUTO) return fail(SB_ERR_ARG, "einsum: unknown implementation selector");
-  const int st = launch_gemm_tcgen05(s, g);
+  const int st = launch_gemm_tcgen05(s, g, ws, ws_bytes);
   if (st == SB_ERR_UNSUPPORTED || st == SB_ERR_ALIGNMENT) return launch_gemm_simt(s, g);
   return st;
 }

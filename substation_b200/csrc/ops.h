@@ -54,9 +54,10 @@ struct GemmProblem {
 int plan_einsum(const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
                 const char* c_dims, const sb_tensor* c, float alpha, GemmProblem* out);
 bool tcgen05_supported(const GemmProblem& g, std::string* why);
-int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g);
+int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g, void* ws, size_t ws_bytes);
 int launch_gemm_simt(cudaStream_t s, const GemmProblem& g);
-int run_gemm(cudaStream_t s, const GemmProblem& g, int impl);
+// ws (optional): scratch for fp32 split-K partials; without it few-tile problems are not split.
+int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws = nullptr, size_t ws_bytes = 0);
 extern thread_local int g_last_gemm_impl;
 // Non-zero once a tcgen05 kernel on this process reported a bounded wait running out.
 int gemm_device_error(cudaStream_t s, int* code);

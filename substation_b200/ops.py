@@ -146,16 +146,19 @@ def backward_encoder_input(dxatt, dresid1, dx):
     check(_lib.load().sb_backward_encoder_input(_stream(), _d(dxatt), _d(dresid1), _d(dx)))
 
 
-def einsum(spec, a, b, c, alpha=1.0, impl='auto'):
+def einsum(spec, a, b, c, alpha=1.0, impl='auto', workspace=None):
     """c = alpha * einsum(spec, a, b) with spec like 'phbk,phbj->hbjk'; the dims of
     each operand are named in the order of its own (size, stride) lists.  Returns
-    'tcgen05' or 'simt' (the kernel that ran)."""
+    'tcgen05' or 'simt' (the kernel that ran).  ``workspace``: optional uint8 CUDA
+    tensor for split-K partial sums."""
     _check_cuda(a, b, c); _half(a, b, c)
     lhs, cd = spec.replace(' ', '').split('->')
     ad, bd = lhs.split(',')
     lib = _lib.load()
+    ws_ptr = ctypes.c_void_p(workspace.data_ptr()) if workspace is not None else None
+    ws_len = workspace.numel() * workspace.element_size() if workspace is not None else 0
     check(lib.sb_einsum(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
-                        float(alpha), _IMPL[impl]))
+                        float(alpha), _IMPL[impl], ws_ptr, ws_len))
     return {SB_GEMM_TCGEN05: 'tcgen05', SB_GEMM_SIMT: 'simt'}.get(lib.sb_einsum_last_impl(), '?')
 
 

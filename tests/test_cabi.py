@@ -101,7 +101,7 @@ def test_einsum_planner_rejects_non_gemm_requests_before_any_launch():
     b = _tensor([4, 6, 8], [48, 8, 1])
     c = _tensor([4, 4], [4, 1])
     call = lambda ad, bd, cd, aa=a, bb=b, cc=c: lib.sb_einsum(None, ad, ctypes.byref(aa), bd, ctypes.byref(bb), cd,
-                                                             ctypes.byref(cc), 1.0, 0)
+                                                             ctypes.byref(cc), 1.0, 0, None, 0)
     assert call(b'bmk', b'bnk', b'mnx') == 2            # rank mismatch
     assert b'rank' in lib.sb_last_error()
     assert call(b'bmm', b'bnk', b'mn') == 2             # repeated index
@@ -114,7 +114,7 @@ def test_einsum_planner_rejects_non_gemm_requests_before_any_launch():
     a4 = _tensor([2, 3, 4, 8], [96, 32, 8, 1])
     b4 = _tensor([2, 3, 5, 8], [120, 40, 8, 1])
     c4 = _tensor([2, 4, 3, 5], [60, 15, 5, 1])          # h m b n
-    st = lib.sb_einsum(None, b'hbmk', ctypes.byref(a4), b'hbnk', ctypes.byref(b4), b'hmbn', ctypes.byref(c4), 1.0, 0)
+    st = lib.sb_einsum(None, b'hbmk', ctypes.byref(a4), b'hbnk', ctypes.byref(b4), b'hmbn', ctypes.byref(c4), 1.0, 0, None, 0)
     assert st == 3 and b'collapse' in lib.sb_last_error()
 
 

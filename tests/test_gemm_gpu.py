@@ -142,3 +142,27 @@ def test_layer_einsums_run_on_tensor_cores(which):
         want = np.einsum(spec, A, B)
         assert_close(dC, want, tol=2e-3, what=f'{which}:{name} {spec}')
     assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize('M,N,K,c_mn', [(1024, 1024, 4096, 0), (3072, 1024, 4096, 0), (256, 512, 2048, 1),
+                                        (384, 1000, 8192, 0)])
+def test_split_k_with_workspace_matches_unsplit(M, N, K, c_mn):
+    """Few output tiles and a long summed extent: with a workspace the kernel splits K over
+    more SMs and reduces fp32 partials in a fixed order; results must match numpy and be
+    reproducible bit for bit."""
+    ops = _ops()
+    rng = np.random.default_rng(M + N + K)
+    A, dA = _operand(rng, 1, M, K, True)       # both operands token-major, as in the weight gradients
+    B, dB = _operand(rng, 1, N, K, True)
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=DEV)
+    shape = (1, N, M) if c_mn else (1, M, N)
+    outs = []
+    for _ in range(2):
+        st = torch.full(shape, float('nan'), dtype=torch.float16, device=DEV)
+        dC = st.permute(0, 2, 1) if c_mn else st
+        assert ops.einsum('bmk,bnk->bmn', dA, dB, dC, alpha=0.25, impl='tcgen05', workspace=ws) == 'tcgen05'
+        outs.append(st.clone())
+        want = 0.25 * np.einsum('bmk,bnk->bmn', A, B)
+        assert_close(dC, want, tol=2e-3, what='split-K C')
+    assert torch.equal(outs[0], outs[1])
+    assert ops.device_error() == 0
