@@ -173,7 +173,7 @@ def workload_config(args, layouts_name):
     return {'workload': f'BERT-large encoder layer fwd+bwd, B={args.batch} per GPU, L={args.seq}, H={H}, P={P}, '
                         f'E={E}, U={U}, ReLU, dropout p={P_DROP} (seeded explicit masks)',
             'batch_per_gpu': args.batch, 'seq_len': args.seq, 'layouts': layouts_name,
-            'parallelism': f'dp{args.gpus}',
+            'parallelism': f'dp{args.gpus}', 'comm_ctas': args.comm_ctas if args.gpus > 1 else 0,
             'l2': 'per-step working set (~0.9 GB of intermediates) is larger than the 126 MB L2; no flush needed'}
 
 
@@ -185,6 +185,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from substation_b200 import Encoder, layouts as L
+    from substation_b200.data_parallel import GradientBucketReducer
     from tests.layer_harness import get_layouts
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -196,8 +197,22 @@ def run_ours(args):
         raise SystemExit('bench.py needs a CUDA device: the product path has no CPU fallback')
     torch.cuda.set_device(local_rank)
     dev = torch.device('cuda', local_rank)
+    comm_ctas = 0
     if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
+        # Few NCCL CTAs are enough for a 25 MB bucket over NVLink; the persistent contraction
+        # kernels leave exactly those SMs free so that the allreduce runs beside them.
+        comm_ctas = args.comm_ctas
+        opts = None
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = comm_ctas
+            opts.config.min_ctas = min(4, comm_ctas)
+        except Exception:
+            opts = None
+        dist.init_process_group('nccl', device_id=dev, pg_options=opts)
+        from substation_b200 import ops as _ops
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        _ops.set_sm_budget(sms - comm_ctas)
 
     B, S = args.batch, args.seq
     lay = get_layouts(args.layouts)
@@ -227,26 +242,17 @@ def run_ours(args):
     fwd = enc._alloc(enc._fwd_plan, dev)
     fwd.update(masks)
     bwd = enc._alloc(enc._bwd_plan, dev)
-    grads = [enc._alloc(enc._grad_plan, dev) for _ in range(2)]   # double-buffered gradient buckets
+    # double-buffered gradient buckets: the allreduce of step i overlaps step i+1
+    reducer = GradientBucketReducer(enc.arena_bytes('grads'), dev, buffers=2)
     Y, DX = torch.empty_like(X), torch.empty_like(X)
-    pending = [None, None]
 
     def step(i):
-        buf = i & 1
-        if pending[buf] is not None:          # bucket still being reduced two steps ago
-            pending[buf].wait()
-            pending[buf] = None
+        grads = enc.views('grads', reducer.arena(i))     # waits if this bucket is still being reduced
         enc.forward_raw(X, weights, fwd, Y)
-        enc.backward_raw(DY, grads[buf], bwd, weights, fwd, X, DX)
-        if world > 1:
-            bucket = grads[buf]['__arena__'].view(torch.float16)
-            pending[buf] = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, async_op=True)
+        enc.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
+        reducer.reduce_async(i)
 
-    def drain():
-        for b in (0, 1):
-            if pending[b] is not None:
-                pending[b].wait()
-                pending[b] = None
+    drain = reducer.drain
 
     def barrier():
         if world > 1:
@@ -405,6 +411,7 @@ def main():
     ap.add_argument('--layouts', default='uniform')
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
+    ap.add_argument('--comm-ctas', type=int, default=8, help='SMs left to NCCL when N > 1')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')
     args = ap.parse_args()

@@ -213,6 +213,12 @@ int sb_einsum_last_impl(void);
  * (0 = no wait ever ran out).  The reference has no counterpart: its CHECK
  * macro aborts the process (pytorch_module/all.cuh:7-13). */
 int sb_device_error(void* stream, int* code);
+/* The contraction kernels are persistent: one CTA per SM walks the output tiles.  When
+ * another kernel must run next to them (the NCCL gradient allreduce of the data-parallel
+ * path), tell the library to occupy only n_sms SMs so that no CTA of a contraction waits
+ * behind it (0 = use every SM, the default).  Process-wide.  No counterpart in the
+ * reference, which has no multi-GPU path. */
+int sb_set_sm_budget(int n_sms);
 
 /* ------------------------------------------------------------------------- */
 /* Whole layer                                                               */

@@ -74,6 +74,7 @@ SIGNATURES = {
                         ctypes.c_size_t]),
     'sb_einsum_last_impl': (c_int, []),
     'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    'sb_set_sm_budget': (c_int, [c_int]),
     'sb_encoder_create': (c_int, [ctypes.POINTER(SbEncoderConfig), ctypes.POINTER(c_void_p)]),
     'sb_encoder_destroy': (c_int, [c_void_p]),
     'sb_encoder_forward': (c_int, [c_void_p, c_void_p, c_void_p, _PP, _PP, c_void_p, c_int,

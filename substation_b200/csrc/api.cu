@@ -334,6 +334,11 @@ extern "C" int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, c
   return run_gemm((cudaStream_t)stream, g, impl, workspace, workspace ? workspace_bytes : 0);
 }
 extern "C" int sb_einsum_last_impl(void) { return g_last_gemm_impl; }
+extern "C" int sb_set_sm_budget(int n_sms) {
+  if (n_sms < 0) return fail(SB_ERR_ARG, "sb_set_sm_budget: negative SM count");
+  set_gemm_sm_budget(n_sms);
+  return SB_OK;
+}
 extern "C" int sb_device_error(void* stream, int* code) {
   if (!code) return fail(SB_ERR_ARG, "sb_device_error: null argument");
   return gemm_device_error((cudaStream_t)stream, code);

@@ -717,6 +717,8 @@ bool make_operand_map(const void* ptr, long long R, long long K, long long batch
   return false;
 }
 
+int g_sm_budget = 0;  // 0: all SMs; otherwise the persistent grid leaves the rest to concurrent kernels
+
 int sm_count() {
   static thread_local int cached_dev = -1, cached = 0;
   int dev = 0;
@@ -725,7 +727,8 @@ int sm_count() {
     cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
     cached_dev = dev;
   }
-  return cached > 0 ? cached : 148;
+  const int n = cached > 0 ? cached : 148;
+  return (g_sm_budget > 0 && g_sm_budget < n) ? g_sm_budget : n;
 }
 
 // Split K only when the output tiles cover less than a third of the SMs: the fp32 partials cost
@@ -867,6 +870,8 @@ int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws, size_t ws
   if (st == SB_ERR_UNSUPPORTED || st == SB_ERR_ALIGNMENT) return launch_gemm_simt(s, g);
   return st;
 }
+
+void set_gemm_sm_budget(int n) { g_sm_budget = n; }
 
 int gemm_device_error(cudaStream_t s, int* code) {
   int v = 0;

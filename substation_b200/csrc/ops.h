@@ -59,6 +59,8 @@ int launch_gemm_simt(cudaStream_t s, const GemmProblem& g);
 // ws (optional): scratch for fp32 split-K partials; without it few-tile problems are not split.
 int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws = nullptr, size_t ws_bytes = 0);
 extern thread_local int g_last_gemm_impl;
+// Number of SMs the persistent contraction kernels may occupy (0 = all).
+void set_gemm_sm_budget(int n);
 // Non-zero once a tcgen05 kernel on this process reported a bounded wait running out.
 int gemm_device_error(cudaStream_t s, int* code);
 

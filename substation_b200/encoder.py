@@ -169,6 +169,22 @@ class Encoder(torch.nn.Module):
         out['__arena__'] = arena
         return out
 
+    def views(self, which, arena):
+        """Named tensor views over a caller-provided uint8 arena; ``which`` is 'forward',
+        'backward' or 'grads'.  Lets a caller keep buffers alive across steps (or place the
+        gradients inside a communication bucket) instead of allocating per pass."""
+        plan, total = {'forward': self._fwd_plan, 'backward': self._bwd_plan, 'grads': self._grad_plan}[which]
+        if arena.dtype != torch.uint8 or arena.numel() < total or not arena.is_contiguous():
+            raise ValueError(f'arena must be a contiguous uint8 tensor of at least {total} bytes')
+        out = {}
+        for name, shape, dtype, off, nbytes in plan:
+            out[name] = arena[off:off + nbytes].view(dtype).view(shape)
+        out['__arena__'] = arena
+        return out
+
+    def arena_bytes(self, which):
+        return {'forward': self._fwd_plan, 'backward': self._bwd_plan, 'grads': self._grad_plan}[which][1]
+
     def intermediate_bytes(self):
         """Bytes of the forward and backward arenas (what one layer keeps alive)."""
         return self._fwd_plan[1], self._bwd_plan[1]

@@ -167,3 +167,9 @@ def device_error():
     code = ctypes.c_int(0)
     check(_lib.load().sb_device_error(_stream(), ctypes.byref(code)))
     return code.value
+
+
+def set_sm_budget(n_sms):
+    """Let the persistent contraction kernels occupy only ``n_sms`` SMs (0 = all), leaving the
+    rest to a kernel that runs beside them, e.g. the NCCL allreduce of the data-parallel path."""
+    check(_lib.load().sb_set_sm_budget(int(n_sms)))
