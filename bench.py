@@ -1,7 +1,7 @@
 """Benchmark of the encoder-layer hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--layouts uniform|b8_l512|b96_l128] [--batch B] [--seq L]
+                    [--layouts b200_b8_l512|uniform|b8_l512|b96_l128] [--batch B] [--seq L]
 
 One "step" = one BERT-large encoder layer forward+backward (B=8, L=512, H=16,
 E=1024, fp16 storage / fp32 accumulation, dropout p=0.1 with seeded explicit
@@ -408,7 +408,9 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--layouts', default='uniform')
+    ap.add_argument('--layouts', default='b200_b8_l512',
+                    help='b200_b8_l512 (chosen by the layout search for these kernels), uniform, '
+                         'b8_l512 / b96_l128 (the reference\'s shipped configurations) or a .json path')
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
     ap.add_argument('--comm-ctas', type=int, default=8, help='SMs left to NCCL when N > 1')

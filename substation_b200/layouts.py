@@ -109,3 +109,19 @@ def uniform_layouts(feature_inner=True):
         'backward_interm': [(n, bwd[n]) for n in BACKWARD_INTERM],
         'special_dims': {}, 'algorithms': {},
     }
+
+
+def selected_layouts(tag='b8_l512'):
+    """The configuration the layout search chose for these kernels on B200
+    (``layout_selection/results_<tag>/layouts_b200_<tag>.json``; regenerate with
+    ``python -m substation_b200.layout_selection.sweep`` then ``.optimize``)."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'layout_selection', f'results_{tag}',
+                        f'layouts_b200_{tag}.json')
+    with open(path) as f:
+        d = json.load(f)
+    for k in ('params', 'forward_interm', 'backward_interm'):
+        d[k] = [tuple(x) for x in d[k]]
+    d['input'], d['output'] = tuple(d['input']), tuple(d['output'])
+    return d

@@ -11,6 +11,7 @@ import ctypes
 import torch
 
 from . import _lib
+from ._lib import SubstationError  # noqa: F401
 from ._lib import (SB_ACT_GELU, SB_ACT_RELU, SB_GEMM_AUTO, SB_GEMM_SIMT, SB_GEMM_TCGEN05,
                    SB_MASK_EXPLICIT, SB_MASK_PHILOX, SbDropout, check, tensor_desc)
 

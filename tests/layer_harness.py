@@ -25,7 +25,10 @@ def get_layouts(which):
         return which
     if which == 'uniform':
         return L.uniform_layouts()
-    with open(os.path.join(GOLDEN_DIR, f'layouts_{which}.json')) as f:
+    if which.startswith('b200_'):
+        return L.selected_layouts(which[5:])
+    path = which if which.endswith('.json') else os.path.join(GOLDEN_DIR, f'layouts_{which}.json')
+    with open(path) as f:
         d = json.load(f)
     for k in ('params', 'forward_interm', 'backward_interm'):
         d[k] = [tuple(x) for x in d[k]]
