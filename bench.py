@@ -402,6 +402,77 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_stack(args):
+    """--layers N > 1: a stack of N layers with independent weights (BASELINE.json config 5 at N=24);
+    one step = forward through all layers + backward through all layers, each layer's gradient
+    bucket allreduced while the next layer's backward runs."""
+    import torch
+    import torch.distributed as dist
+    from substation_b200 import ops as _ops
+    from substation_b200.stack import EncoderStack
+    from tests.layer_harness import get_layouts
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus:
+        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run')
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.config.max_ctas = args.comm_ctas
+        opts.config.min_ctas = min(4, args.comm_ctas)
+        dist.init_process_group('nccl', device_id=dev, pg_options=opts)
+        _ops.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - args.comm_ctas)
+    lay = get_layouts(args.layouts)
+    st = EncoderStack(args.layers, args.batch, args.seq, H, E, lay, dropout_p=P_DROP, device=dev, seed=1234)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    X = torch.randn(st.acts[0].shape, device=dev, generator=gen).half()
+    DY = torch.randn(st.acts[0].shape, device=dev, generator=gen).half()
+
+    def step():
+        st.forward(X)
+        st.backward(DY)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    st.wait_gradients()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    st.wait_gradients()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        cfg = workload_config(args, args.layouts)
+        cfg['workload'] = f'{args.layers}-layer stack of: ' + cfg['workload'] + ' (Philox masks)'
+        cfg['layers'] = args.layers
+        print(json.dumps({
+            'metric': METRIC, 'value': world * args.batch * args.steps / (ms / 1e3), 'unit': UNIT, 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms / args.steps,
+            'ms_per_layer': ms / args.steps / args.layers, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic', 'config': cfg, 'clocks': clocks,
+            'gpu_launches': 32 * args.layers * args.steps, 'stack_memory_gb': round(st.memory_bytes() / 2 ** 30, 2)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -414,6 +485,7 @@ def main():
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
     ap.add_argument('--comm-ctas', type=int, default=8, help='SMs left to NCCL when N > 1')
+    ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (config 5 uses 24)')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')
     args = ap.parse_args()
@@ -421,6 +493,8 @@ def main():
         args.warmup = 3
     if args.impl == 'reference':
         run_reference_arm(args)
+    elif args.layers > 1:
+        run_stack(args)
     else:
         run_ours(args)
 

@@ -25,6 +25,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -651,6 +652,8 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
   }
 }
 
+#include "gemm_pair.cuh"
+
 // ---- host side ------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 std::once_flag g_encode_once;
@@ -799,6 +802,77 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
   return SB_OK;
 }
 
+// Paired-CTA launch: 256 x 256 tiles, one cluster of two CTAs per tile.
+int pair_clusters() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cached_dev = dev;
+    cached = 0;
+    if (cudaFuncSetAttribute(pair::gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             pair::kSmemBytes) == cudaSuccess) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2 * 74);
+      cfg.blockDim = dim3(kTcThreads);
+      cfg.dynamicSmemBytes = pair::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, pair::gemm_tc_pair_kernel, &cfg) == cudaSuccess) cached = n;
+      else cudaGetLastError();
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return cached;
+}
+
+bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SUBSTATION_B200_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b, int clusters) {
+  TcParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
+  p.C = g.C;
+  p.alpha = g.alpha;
+  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap; p.c_swap = 0;
+  p.tiles_n = (int)((g.N + 255) / 256);
+  p.tiles_m = (int)((g.M + 255) / 256);
+  p.batch = (int)g.batch;
+  p.splits = 1;
+  p.kt_per_split = (int)((g.K + kBK - 1) / kBK);
+  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
+  CUtensorMap cmap;
+  memset(&cmap, 0, sizeof(cmap));
+  const bool c_vec = g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && (g.batch == 1 || g.sCb % 8 == 0) &&
+                     (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0;
+  p.c_mode = c_vec ? 1 : 0;
+  if (c_vec) {
+    std::string why;
+    int swapped = 0;
+    if (encode_map(g.C, (cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch, g.sCm, g.sCb, 64, 32, &cmap, &swapped, &why)) {
+      p.c_mode = 2;
+      p.c_swap = swapped;
+    }
+  }
+  const int budget = sm_count() / 2;
+  const unsigned nclusters = (unsigned)std::max<long long>(1, std::min<long long>(p.tiles, std::min(clusters, budget)));
+  pair::gemm_tc_pair_kernel<<<2 * nclusters, kTcThreads, pair::kSmemBytes, s>>>(a.map, b.map, cmap, p);
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
 int pick_bn(long long M, long long N, long long batch) {
   // 128 x 256 moves the fewest operand bytes per flop (each CTA fetches its own tiles), so it is
   // used whenever N fills most of it and the persistent grid still covers about half the SMs
@@ -850,6 +924,21 @@ int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0, void* ws, size_t 
   }
   const int bn = pick_bn(g.M, g.N, g.batch);
   OperandMap a, b;
+  // Large single-batch problems go to the paired-CTA kernel (256 x 256 tiles) when enough of its
+  // clusters fit on the device and there are enough tiles to keep them busy.
+  if (bn == 256 && g.batch == 1 && g.M >= 256 && g.N >= 256 && g.K >= 256 && pair_enabled()) {
+    const int clusters = pair_clusters();
+    const long long tiles2 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+    if (clusters >= 32 && tiles2 * 2 >= clusters) {
+      if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
+        return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
+      if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, 128, &b, &why))
+        return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand B: " + why);
+      const int st2 = launch_tc_pair(s, g, a, b, clusters);
+      if (st2 == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
+      return st2;
+    }
+  }
   if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
     return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
   if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))

@@ -1,0 +1,302 @@
+// Paired-CTA variant of the tcgen05 contraction kernel (included by gemm.cu).
+//
+// Two CTAs on neighbouring SMs form a cluster and compute one 256 x 256 output
+// tile with tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and
+// its own 128 rows (= half) of B, the tensor cores of both SMs read both halves
+// of B, and each CTA's tensor memory receives its 128 x 256 part of the
+// accumulator.  Per CTA and 64-wide K block that is 32 KiB of operands for
+// 128 x 256 x 64 multiply-adds, against 48 KiB for the single-CTA kernel, with
+// every CTA still fetching only its own tiles.
+//
+// Roles per CTA: warp 0 TMA producer, warp 1 tensor-memory allocation (+ MMA
+// issue in the leader CTA, rank 0), warps 2-5 epilogue.  Barriers:
+//   full[s]      leader only; the leader's producer arms it with the bytes of BOTH
+//                CTAs, the peer's bulk loads complete on it too;
+//   empty[s]     one per CTA; the leader's MMA thread commits to its own and to
+//                the peer's when the stage has been read;
+//   acc_full[b]  one per CTA (leader commits to both); acc_empty[b] leader only,
+//                8 arrivals (4 epilogue warps of each CTA).
+// Remote barrier addresses come from mapa.  Waits are bounded like in the
+// single-CTA kernel.
+
+#pragma once
+
+namespace pair {
+
+constexpr int kBN = 256;
+constexpr int kHalfBBytes = 128 * kBK * 2;                 // this CTA's half of B per K block
+constexpr int kStageBytes = kABytes + kHalfBBytes;         // 32 KiB
+constexpr int kStages = 6;
+constexpr int kTileBytes = kStages * kStageBytes;          // 192 KiB
+constexpr int kTmemCols = 512;                             // two 256-column accumulators
+constexpr int kSmemBytes = kTileBytes + kStageOutBytes + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// bulk tensor load of this CTA's tile whose completion bytes are counted on a barrier of the leader
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                              uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+// Persistent: cluster c works on pair tiles c, c + (#clusters), ...; n fastest, then m (256 rows), then batch.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const TcParams p) {
+  constexpr int S = kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t stage_out = tiles + kTileBytes;
+  const uint32_t bars = stage_out + kStageOutBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * S;
+  const uint32_t bar_accf = bars + 16 * S, bar_acce = bars + 16 * S + 16;
+  uint8_t* gen_base = smem_raw + (tiles - raw);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kTileBytes + kStageOutBytes + 16 * S + 32);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();          // 0 = leader
+  const unsigned cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+  const int KT = (int)((p.K + kBK - 1) / kBK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_accf + 8 * b, 1);
+      mbar_init(bar_acce + 8 * b, 8);  // four epilogue warps of each CTA
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    if (p.c_mode == 2) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    const uint32_t leader_full = map_to_rank(bar_full, 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long t = cluster_id; t < p.tiles && ok; t += nclusters) {
+      const int n0 = (int)(t % p.tiles_n) * kBN + (int)rank * 128;       // this CTA's half of B
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
+      const int bt = (int)(t / ((long long)p.tiles_n * p.tiles_m));
+      for (int kb = 0; kb < KT; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = leader_full + 8 * s;
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2u * (uint32_t)kStageBytes);
+          const uint32_t sa = tiles + s * kStageBytes, sb_ = sa + kABytes;
+          const int k0 = kb * kBK;
+          if (!p.a_mn) {
+            if (p.a_swap) tma_load_3d_pair(sa, &tmA, full, k0, bt, m0);
+            else tma_load_3d_pair(sa, &tmA, full, k0, m0, bt);
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (p.a_swap) tma_load_3d_pair(sa + h * 8192, &tmA, full, m0 + 64 * h, bt, k0);
+              else tma_load_3d_pair(sa + h * 8192, &tmA, full, m0 + 64 * h, k0, bt);
+            }
+          }
+          if (!p.b_mn) {
+            if (p.b_swap) tma_load_3d_pair(sb_, &tmB, full, k0, bt, n0);
+            else tma_load_3d_pair(sb_, &tmB, full, k0, n0, bt);
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (p.b_swap) tma_load_3d_pair(sb_ + h * 8192, &tmB, full, n0 + 64 * h, bt, k0);
+              else tma_load_3d_pair(sb_ + h * 8192, &tmB, full, n0 + 64 * h, k0, bt);
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0) {
+      // ---------------- MMA issuer (leader CTA only; lane 0 issues) ----------------
+      // instruction descriptor: fp32 accumulate, fp16 operands, majors, N = 256, M = 256 across the pair
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+                             ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                             ((uint32_t)(256 >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
+      const uint32_t peer_empty = map_to_rank(bar_empty, 1), peer_accf = map_to_rank(bar_accf, 1);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (long long t = cluster_id; t < p.tiles && ok; t += nclusters, ++lt) {
+        const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_acce + 8 * buf, aph ^ 1u, 4));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * kBN;
+        for (int kb = 0; kb < KT; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = tiles + s * kStageBytes, sb_ = sa + kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
+              const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
+              umma_f16_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            // the stage is free in both CTAs once these MMAs have read it
+            umma_commit_pair(bar_empty + 8 * s);
+            umma_commit_pair(peer_empty + 8 * s);
+          }
+          __syncwarp();
+        }
+        if (ok && lane == 0) {
+          umma_commit_pair(bar_accf + 8 * buf);
+          umma_commit_pair(peer_accf + 8 * buf);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs; each stores its own 128 rows) ----------------
+    const int q = warp & 3;
+    const uint32_t leader_acce = map_to_rank(bar_acce, 0);
+    const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
+    uint8_t* my_stage_gen = gen_base + kTileBytes + (warp - 2) * 8192;
+    uint32_t lt = 0, nstore = 0;
+    bool ok = true;
+    for (long long t = cluster_id; t < p.tiles && ok; t += nclusters, ++lt) {
+      const int n0 = (int)(t % p.tiles_n) * kBN;
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
+      const long long bt = t / ((long long)p.tiles_n * p.tiles_m);
+      const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_accf + 8 * buf, aph, 3));
+      if (!ok) break;
+      tc_fence_after();
+      const long long m = (long long)m0 + q * 32 + lane;
+      const uint32_t tsrc = tmem_base + buf * kBN + ((uint32_t)(q * 32) << 16);
+      if (p.c_mode == 2) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 64), r);
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 64 + 32), r + 32);
+          tmem_ld_wait();
+          if (c == kBN / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);
+          }
+          const uint32_t sbuf = nstore & 1u;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          uint8_t* row = my_stage_gen + sbuf * 4096 + lane * 128;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+            *reinterpret_cast<uint4*>(row + ((v ^ (lane & 7)) << 4)) = pack8(f);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          const int nc = n0 + c * 64, mc = m0 + q * 32;
+          if (lane == 0 && nc < p.N && mc < p.M) {
+            if (p.c_swap) tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, (int)bt, mc);
+            else tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, mc, (int)bt);
+          }
+          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          ++nstore;
+        }
+      } else {
+        __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32_nowait(tsrc + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          if (c == kBN / 32 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);
+          }
+          if (m < p.M) {
+            const long long nb = (long long)n0 + c * 32;
+            if (p.c_mode == 1) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (nb + v * 8 < p.N) {
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+                  *reinterpret_cast<uint4*>(crow + nb + v * 8) = pack8(f);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+  }
+  if (*reinterpret_cast<volatile int*>(&g_tc_error) != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();   // neither CTA may leave (or free tensor memory) while its peer can still reach it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+  }
+}
+
+}  // namespace pair

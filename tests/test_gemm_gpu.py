@@ -166,3 +166,23 @@ def test_split_k_with_workspace_matches_unsplit(M, N, K, c_mn):
         assert_close(dC, want, tol=2e-3, what='split-K C')
     assert torch.equal(outs[0], outs[1])
     assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize('M,N,K', [(4096, 4096, 1024), (2000, 1544, 520), (4096, 1024, 4096)])
+@pytest.mark.parametrize('a_mn,b_mn,c_mn', [(0, 0, 0), (1, 0, 0), (0, 1, 0), (1, 1, 1)])
+def test_paired_cta_kernel_on_large_problems(M, N, K, a_mn, b_mn, c_mn):
+    """Problems with enough 256 x 256 tiles run on the two-CTA kernel (tcgen05.mma.cta_group::2);
+    checked against an fp32 torch matmul (too large for the float64 oracle), ragged edges included."""
+    ops = _ops()
+    g = torch.Generator(device=DEV).manual_seed(M + K)
+    A = (torch.randn(1, M, K, device=DEV, generator=g) / K ** 0.5).half()
+    B = torch.randn(1, N, K, device=DEV, generator=g).half()
+    dA = A.transpose(1, 2).contiguous().transpose(1, 2) if a_mn else A
+    dB = B.transpose(1, 2).contiguous().transpose(1, 2) if b_mn else B
+    st = torch.full((1, N, M) if c_mn else (1, M, N), float('nan'), dtype=torch.float16, device=DEV)
+    dC = st.transpose(1, 2) if c_mn else st
+    assert ops.einsum('bmk,bnk->bmn', dA, dB, dC, alpha=2.0, impl='tcgen05') == 'tcgen05'
+    assert ops.device_error() == 0
+    ref = 2.0 * torch.einsum('bmk,bnk->bmn', A.float(), B.float())
+    assert torch.isfinite(dC).all()
+    assert ((dC.float() - ref).norm() / ref.norm()).item() < 1e-3
