@@ -66,6 +66,8 @@ SIGNATURES = {
     'sb_backward_dropout_activation_bias': (c_int, [c_void_p, c_void_p] + [_T] * 5 + [c_int]),
     'sb_extended_backward_scale_bias': (c_int, [c_void_p, c_void_p] + [_T] * 9),
     'sb_backward_attn_out_bias': (c_int, [c_void_p, c_void_p, _T, _T]),
+    'sb_backward_scale_bias_layernorm': (c_int, [c_void_p, c_void_p] + [_T] * 11),
+    'sb_extended_backward_scale_bias_layernorm': (c_int, [c_void_p, c_void_p] + [_T] * 15),
     'sb_backward_attn_out_bias_noalloc': (c_int, [c_void_p, _T, _T]),
     'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
     'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
@@ -85,6 +87,7 @@ SIGNATURES = {
     'sb_encoder_get_timing': (c_int, [c_void_p, c_int, ctypes.POINTER(c_char_p),
                                       ctypes.POINTER(c_float)]),
     'sb_encoder_launch_count': (c_int, [c_void_p]),
+    'sb_encoder_set_fusion': (c_int, [c_void_p, c_int]),
 }
 
 _lib = None

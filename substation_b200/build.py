@@ -17,7 +17,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, 'csrc')
 LIB_NAME = 'libsubstation_b200.so'
 LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
-SOURCES = ('api.cu', 'fused_ops.cu', 'gemm.cu')
+SOURCES = ('api.cu', 'fused_ops.cu', 'fused_lnbwd.cu', 'gemm.cu')
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
               '-Xcompiler', '-fPIC', '-shared']
 

@@ -296,6 +296,55 @@ extern "C" int sb_extended_backward_scale_bias(void* stream, void* workspace, co
   return launch_ebsb((cudaStream_t)stream, workspace, dims3(ln1), vn, pg, vr, vw, vl2, vo, pdg, pdb, pdl);
 }
 
+extern "C" int sb_backward_scale_bias_layernorm(void* stream, void* workspace, const sb_tensor* dy,
+                                                const sb_tensor* ln, const sb_tensor* gamma, const sb_tensor* istd,
+                                                const sb_tensor* diff, const sb_tensor* mask, const sb_tensor* dln,
+                                                const sb_tensor* dresid, const sb_tensor* dlin,
+                                                const sb_tensor* dgamma, const sb_tensor* dbeta) {
+  View3 vy, vn, vd, vm, vg, vr, vl;
+  View2 vs;
+  void *pg, *pdg, *pdb;
+  SB_TRY(to_view3(dy, nullptr, false, "bsb+blnrd.dy", &vy));
+  SB_TRY(to_view3(ln, dy, false, "bsb+blnrd.ln", &vn));
+  SB_TRY(to_view3(diff, dy, false, "bsb+blnrd.diff", &vd));
+  SB_TRY(to_view3(mask, dy, true, "bsb+blnrd.mask", &vm));
+  SB_TRY(to_view3(dln, dy, false, "bsb+blnrd.dln", &vg));
+  SB_TRY(to_view3(dresid, dy, false, "bsb+blnrd.dresid", &vr));
+  SB_TRY(to_view3(dlin, dy, false, "bsb+blnrd.dlin", &vl));
+  SB_TRY(to_view2(istd, dy, "bsb+blnrd.istd", &vs));
+  SB_TRY(to_param(gamma, dy->size[2], "bsb+blnrd.gamma", &pg));
+  SB_TRY(to_param(dgamma, dy->size[2], "bsb+blnrd.dgamma", &pdg));
+  SB_TRY(to_param(dbeta, dy->size[2], "bsb+blnrd.dbeta", &pdb));
+  return launch_lnbwd_a((cudaStream_t)stream, workspace, dims3(dy), vy, vn, pg, vs, vd, vm, vg, vr, vl, pdg, pdb);
+}
+
+extern "C" int sb_extended_backward_scale_bias_layernorm(
+    void* stream, void* workspace, const sb_tensor* ln1, const sb_tensor* gamma1, const sb_tensor* dresid2,
+    const sb_tensor* dlin1_linw1, const sb_tensor* dlin2, const sb_tensor* istd, const sb_tensor* diff,
+    const sb_tensor* mask, const sb_tensor* dln1, const sb_tensor* dresid1, const sb_tensor* datt,
+    const sb_tensor* dgamma1, const sb_tensor* dbeta1, const sb_tensor* dlinb2, const sb_tensor* dbo) {
+  View3 vn, vr2, vw, vl2, vd, vm, vg, vr, va;
+  View2 vs;
+  void *pg, *p0, *p1, *p2, *p3;
+  SB_TRY(to_view3(ln1, nullptr, false, "ebsb+blnrd.ln1", &vn));
+  SB_TRY(to_view3(dresid2, ln1, false, "ebsb+blnrd.dresid2", &vr2));
+  SB_TRY(to_view3(dlin1_linw1, ln1, false, "ebsb+blnrd.dlin1_linw1", &vw));
+  SB_TRY(to_view3(dlin2, ln1, false, "ebsb+blnrd.dlin2", &vl2));
+  SB_TRY(to_view3(diff, ln1, false, "ebsb+blnrd.diff", &vd));
+  SB_TRY(to_view3(mask, ln1, true, "ebsb+blnrd.mask", &vm));
+  SB_TRY(to_view3(dln1, ln1, false, "ebsb+blnrd.dln1", &vg));
+  SB_TRY(to_view3(dresid1, ln1, false, "ebsb+blnrd.dresid1", &vr));
+  SB_TRY(to_view3(datt, ln1, false, "ebsb+blnrd.datt", &va));
+  SB_TRY(to_view2(istd, ln1, "ebsb+blnrd.istd", &vs));
+  SB_TRY(to_param(gamma1, ln1->size[2], "ebsb+blnrd.gamma1", &pg));
+  SB_TRY(to_param(dgamma1, ln1->size[2], "ebsb+blnrd.dgamma1", &p0));
+  SB_TRY(to_param(dbeta1, ln1->size[2], "ebsb+blnrd.dbeta1", &p1));
+  SB_TRY(to_param(dlinb2, ln1->size[2], "ebsb+blnrd.dlinb2", &p2));
+  SB_TRY(to_param(dbo, ln1->size[2], "ebsb+blnrd.dbo", &p3));
+  return launch_lnbwd_b((cudaStream_t)stream, workspace, dims3(ln1), vn, pg, vr2, vw, vl2, vs, vd, vm, vg, vr, va,
+                        p0, p1, p2, p3);
+}
+
 extern "C" int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* datt,
                                          const sb_tensor* dbo) {
   View3 v;
@@ -397,6 +446,7 @@ struct sb_encoder {
   int device = 0;
   int launches = 0;
   bool timing = false;
+  bool fuse = true;            // use the fused multi-operator kernels where the layouts allow
   std::vector<std::pair<std::string, cudaEvent_t>> marks;
   std::vector<cudaEvent_t> event_pool;
   std::vector<std::pair<std::string, float>> last_times;
@@ -448,6 +498,10 @@ struct sb_encoder {
     return view(ptr, layout.at(name), logical_dims().at(name));
   }
 
+  // rename the operator just marked (a fused attempt fell back to its first separate operator)
+  void relabel(const char* name) {
+    if (timing && !marks.empty()) marks.back().first = name;
+  }
   void mark(cudaStream_t s, const char* name) {
     ++launches;
     if (!timing) return;
@@ -560,6 +614,11 @@ extern "C" int sb_encoder_set_timing(sb_encoder* e, int enabled) {
 }
 
 extern "C" int sb_encoder_launch_count(sb_encoder* e) { return e ? e->launches : 0; }
+extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
+  if (!e) return fail(SB_ERR_ARG, "null handle");
+  e->fuse = enabled != 0;
+  return SB_OK;
+}
 
 extern "C" int sb_encoder_get_timing(sb_encoder* e, int max, const char** names, float* ms) {
   if (!e) return 0;
@@ -714,15 +773,21 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
   const sb_tensor tDX = e->view(dx, L.at("X"), "BJI");
 
   {
-    e->mark(s, "bsb");
+    // LayerNorm-2 backward: one fused pass when every view is feature-innermost, else the two separate operators
     sb_tensor ln = v("LN2"), gamma = pv("S2"), dln = v("DLN2"), dg = dv("S2"), db = dv("B2");
-    SB_TRY(sb_backward_scale_bias(stream, ws, &tDY, &ln, &gamma, &dln, &dg, &db));
-  }
-  {
-    e->mark(s, "blnrd1");
-    sb_tensor dln = v("DLN2"), istd = v("LN2STD"), diff = v("LN2DIFF"), mask = v("DROP3MASK");
-    sb_tensor dres = v("DRESID2"), dlin = v("DLIN2");
-    SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln, &istd, &diff, &mask, &dres, &dlin));
+    sb_tensor istd = v("LN2STD"), diff = v("LN2DIFF"), mask = v("DROP3MASK"), dres = v("DRESID2"), dlin = v("DLIN2");
+    e->mark(s, "bsb+blnrd1");
+    int st = e->fuse ? sb_backward_scale_bias_layernorm(stream, ws, &tDY, &ln, &gamma, &istd, &diff, &mask, &dln, &dres,
+                                                         &dlin, &dg, &db)
+                     : SB_ERR_UNSUPPORTED;
+    if (st == SB_ERR_UNSUPPORTED) {
+      e->relabel("bsb");
+      SB_TRY(sb_backward_scale_bias(stream, ws, &tDY, &ln, &gamma, &dln, &dg, &db));
+      e->mark(s, "blnrd1");
+      SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln, &istd, &diff, &mask, &dres, &dlin));
+    } else if (st != SB_OK) {
+      return st;
+    }
   }
   SB_TRY(einsum(e, s, "dXlin2", L.at("DLIN2"), T["DLIN2"], L.at("LINW2"), T["LINW2"], L.at("DDROP2"),
                 T["DDROP2"], 1.f));
@@ -738,21 +803,23 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
   SB_TRY(einsum(e, s, "dWlin1", L.at("DLIN1"), T["DLIN1"], L.at("SB1"), T["SB1"], L.at("LINW1"),
                 D.at("LINW1"), 1.f));
   {
-    e->mark(s, "ebsb");
     sb_tensor ln1 = v("LN1"), gamma = pv("S1"), dres2 = v("DRESID2"), dlw = v("DLIN1_LINW1"), dlin2 = v("DLIN2");
-    sb_tensor dln1 = v("DLN1"), dg = dv("S1"), db = dv("B1"), dlb2 = dv("LINB2");
-    SB_TRY(sb_extended_backward_scale_bias(stream, ws, &ln1, &gamma, &dres2, &dlw, &dlin2, &dln1, &dg, &db, &dlb2));
-  }
-  {
-    e->mark(s, "blnrd2");
-    sb_tensor dln = v("DLN1"), istd = v("LN1STD"), diff = v("LN1DIFF"), mask = v("DROP1MASK");
-    sb_tensor dres = v("DRESID1"), datt = v("DATT");
-    SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln, &istd, &diff, &mask, &dres, &datt));
-  }
-  {
-    e->mark(s, "baob");
-    sb_tensor datt = v("DATT"), dbo = dv("BO");
-    SB_TRY(sb_backward_attn_out_bias(stream, ws, &datt, &dbo));
+    sb_tensor dln1 = v("DLN1"), dg = dv("S1"), db = dv("B1"), dlb2 = dv("LINB2"), dbo = dv("BO");
+    sb_tensor istd = v("LN1STD"), diff = v("LN1DIFF"), mask = v("DROP1MASK"), dres1 = v("DRESID1"), datt = v("DATT");
+    e->mark(s, "ebsb+blnrd2+baob");
+    int st = e->fuse ? sb_extended_backward_scale_bias_layernorm(stream, ws, &ln1, &gamma, &dres2, &dlw, &dlin2, &istd,
+                                                                  &diff, &mask, &dln1, &dres1, &datt, &dg, &db, &dlb2, &dbo)
+                     : SB_ERR_UNSUPPORTED;
+    if (st == SB_ERR_UNSUPPORTED) {
+      e->relabel("ebsb");
+      SB_TRY(sb_extended_backward_scale_bias(stream, ws, &ln1, &gamma, &dres2, &dlw, &dlin2, &dln1, &dg, &db, &dlb2));
+      e->mark(s, "blnrd2");
+      SB_TRY(sb_backward_layernorm_residual_dropout(stream, &dln1, &istd, &diff, &mask, &dres1, &datt));
+      e->mark(s, "baob");
+      SB_TRY(sb_backward_attn_out_bias(stream, ws, &datt, &dbo));
+    } else if (st != SB_OK) {
+      return st;
+    }
   }
   SB_TRY(einsum(e, s, "dWout", L.at("GAMMA"), T["GAMMA"], L.at("DATT"), T["DATT"], L.at("WO"), D.at("WO"), 1.f));
   SB_TRY(einsum(e, s, "dXout", L.at("WO"), T["WO"], L.at("DATT"), T["DATT"], L.at("DGAMMA"), T["DGAMMA"], 1.f));

@@ -642,7 +642,7 @@ struct RowRegs {
 };
 
 struct BsbOp {
-  static constexpr int NQ = 2, NIN = 2, UNR = 4;
+  static constexpr int NQ = 2, NIN = 2, UNR = 4, MINB = 3;
   View3 dy, ln, dln;
   const void* gamma;
   int pvec;
@@ -670,7 +670,7 @@ struct BsbOp {
 };
 
 struct EbsbOp {
-  static constexpr int NQ = 3, NIN = 4, UNR = 2;
+  static constexpr int NQ = 3, NIN = 4, UNR = 2, MINB = 3;
   View3 ln1, dresid2, dlw, dlin2, dln1;
   const void* gamma;
   int pvec;
@@ -705,7 +705,7 @@ struct EbsbOp {
 };
 
 struct BdrlbOp {
-  static constexpr int NQ = 1, NIN = 2, UNR = 4;
+  static constexpr int NQ = 1, NIN = 2, UNR = 4, MINB = 4;
   View3 ddrop2, mask, lin1, dlin1;
   int activation;
   template <bool AV>
@@ -746,7 +746,7 @@ struct BdrlbOp {
 };
 
 struct BaobOp {
-  static constexpr int NQ = 1, NIN = 1, UNR = 8;
+  static constexpr int NQ = 1, NIN = 1, UNR = 8, MINB = 4;
   View3 datt;
   template <bool AV>
   __device__ __forceinline__ void load(int b, int j, int f, int F, RowRegs<NIN>& r) const {
@@ -765,7 +765,7 @@ struct BaobOp {
 };
 
 template <class Op, bool AV>
-__global__ void __launch_bounds__(kColThreads, 2)
+__global__ void __launch_bounds__(kColThreads, Op::MINB)
 colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* counters,
                  ColOut<Op::NQ> outs) {
   constexpr int NQ = Op::NQ;
@@ -873,8 +873,8 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
     return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace counters");
   const long long R = (long long)d.B * d.J;
   const long long Fp = (long long)slices * 256;
-  // about two 8-warp CTAs per SM; bounded by rows and by the workspace
-  long long P = (148 * 2 + slices - 1) / slices;
+  // as many 8-warp CTAs per SM as the kernel's register budget allows; bounded by rows and by the workspace
+  long long P = (148 * Op::MINB + slices - 1) / slices;
   const long long cap = (long long)((kWsBytes - kWsCounterBytes) / (Op::NQ * Fp * sizeof(float)));
   if (cap < 1) return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace");
   if (P > cap) P = cap;

@@ -39,6 +39,14 @@ int launch_bdrlb(cudaStream_t s, void* ws, Dims3 d, View3 ddrop2, View3 mask, Vi
                  View3 dlin1, void* dbias, int activation);
 int launch_baob(cudaStream_t s, void* ws, Dims3 d, View3 datt, void* dbo);
 
+// Fused LayerNorm backward (scale/bias gradients + backward-data + dropout [+ bias gradients]);
+// SB_ERR_UNSUPPORTED when a view is not feature-innermost or has more than 1024 features.
+int launch_lnbwd_a(cudaStream_t s, void* ws, Dims3 d, View3 dy, View3 ln, const void* gamma, View2 istd, View3 diff,
+                   View3 mask, View3 dln, View3 dresid, View3 dlin, void* dgamma, void* dbeta);
+int launch_lnbwd_b(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gamma1, View3 dresid2, View3 dlw,
+                   View3 dlin2, View2 istd, View3 diff, View3 mask, View3 dln1, View3 dresid1, View3 datt,
+                   void* dgamma1, void* dbeta1, void* dlinb2, void* dbo);
+
 // Contractions -----------------------------------------------------------------
 struct GemmProblem {
   long long batch, M, N, K;

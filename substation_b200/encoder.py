@@ -42,7 +42,7 @@ class Encoder(torch.nn.Module):
                  softmax_dropout_probability, residual1_dropout_probability,
                  activation_dropout_probability, residual2_dropout_probability,
                  enable_debug=False, profiling=False, *,
-                 activation='relu', mask_mode='philox', seed=0):
+                 activation='relu', mask_mode='philox', seed=0, fuse=True):
         super().__init__()
         if torch_dtype != torch.float16:
             raise NotImplementedError(
@@ -74,6 +74,7 @@ class Encoder(torch.nn.Module):
         self.activation = activation
         self.mask_mode = mask_mode
         self.seed = int(seed)
+        self.fuse = bool(fuse)          # fused multi-operator kernels where layouts allow (False: one kernel per reference operator)
         self.philox_offset = 0          # advanced by 4 per forward, one per dropout site
         self._masks = None
         self._handle = None
@@ -239,6 +240,7 @@ class Encoder(torch.nn.Module):
             _lib.check(lib.sb_encoder_create(ctypes.byref(cfg), ctypes.byref(handle)))
             if self.profiling:
                 _lib.check(lib.sb_encoder_set_timing(handle, 1))
+            _lib.check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
         self._handle, self._handle_device = handle, device
         return handle
 

@@ -130,6 +130,26 @@ def extended_backward_scale_bias(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1,
         _d(dlin1_linw1), _d(dlin2), _d(dln1), _d(dgamma1), _d(dbeta1), _d(dlinb2)))
 
 
+def backward_scale_bias_layernorm(dy, ln, gamma, istd, diff, mask, dln, dresid, dlin, dgamma, dbeta):
+    """backward_scale_bias + backward_layernorm_residual_dropout in one pass."""
+    _check_cuda(dy); _half(dy, ln, gamma, istd, diff, dln, dresid, dlin, dgamma, dbeta); _mask(mask)
+    ws = workspace(dy.device)
+    check(_lib.load().sb_backward_scale_bias_layernorm(
+        _stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy), _d(ln), _d(gamma), _d(istd), _d(diff), _d(mask),
+        _d(dln), _d(dresid), _d(dlin), _d(dgamma), _d(dbeta)))
+
+
+def extended_backward_scale_bias_layernorm(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, mask, dln1,
+                                           dresid1, datt, dgamma1, dbeta1, dlinb2, dbo):
+    """extended_backward_scale_bias + backward_layernorm_residual_dropout + backward_attn_out_bias in one pass."""
+    _check_cuda(ln1); _mask(mask)
+    _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, dln1, dresid1, datt, dgamma1, dbeta1, dlinb2, dbo)
+    ws = workspace(ln1.device)
+    check(_lib.load().sb_extended_backward_scale_bias_layernorm(
+        _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ln1), _d(gamma1), _d(dresid2), _d(dlin1_linw1), _d(dlin2),
+        _d(istd), _d(diff), _d(mask), _d(dln1), _d(dresid1), _d(datt), _d(dgamma1), _d(dbeta1), _d(dlinb2), _d(dbo)))
+
+
 def backward_attn_out_bias(datt, dbo):
     _check_cuda(datt); _half(datt, dbo)
     ws = workspace(datt.device)

@@ -259,3 +259,54 @@ def test_full_size_sweep_shapes_structural_properties():
     assert torch.equal(dlin1, refd.half())
     refb = refd.sum((0, 1))
     assert (db.float() - refb).norm() / refb.norm() < 2e-3
+
+
+@pytest.mark.parametrize('B,J,F,lay', [(4, 64, 1024, 'BJI'), (2, 9, 200, 'BJI'), (3, 8, 520, 'JBI'), (16, 128, 64, 'BJI'),
+                                       (8, 512, 1024, 'BJI')])
+def test_fused_layernorm_backward_operators(B, J, F, lay):
+    """bsb+blnrd and ebsb+blnrd+baob in one pass each, against the oracle's separate operators."""
+    ops = _ops()
+    rng = np.random.default_rng(B * F + J)
+    vec = lambda: torch.full((F,), float('nan'), dtype=torch.float16, device=DEV)
+    dy, ln, diff = (h16(rng.normal(0, 1, (B, J, F))) for _ in range(3))
+    istd = h16(rng.uniform(0.5, 2.0, (B, J)))
+    gamma = h16(rng.normal(1, 0.1, F))
+    mask = (rng.random((B, J, F)) >= 0.1).astype(np.uint8)
+    tg = torch.tensor(gamma, dtype=torch.float16, device=DEV)
+    d_mask = place(mask, 'BJI', lay, torch.uint8)
+    d_dln, d_dres, d_dlin = (empty((B, J, F), 'BJI', lay) for _ in range(3))
+    d_dg, d_db = vec(), vec()
+    for _ in range(2):
+        ops.backward_scale_bias_layernorm(place(dy, 'BJI', lay), place(ln, 'BJI', lay), tg, place(istd, 'BJ', 'BJ'),
+                                          place(diff, 'BJI', lay), d_mask, d_dln, d_dres, d_dlin, d_dg, d_db)
+    dln, dg, db = orc.backward_scale_bias(dy, ln, gamma)
+    dres, dlin = orc.backward_layernorm_residual_dropout(dln, diff, istd, mask)
+    for got, want, what in ((d_dln, dln, 'DLN'), (d_dres, dres, 'DRESID'), (d_dlin, dlin, 'DLIN'), (d_dg, dg, 'dgamma'),
+                            (d_db, db, 'dbeta')):
+        assert_close(got, want, what=what)
+
+    r2, lw, l2 = (h16(rng.normal(0, 1, (B, J, F))) for _ in range(3))
+    d_dln1, d_dres1, d_datt = (empty((B, J, F), 'BJI', lay) for _ in range(3))
+    o = [vec() for _ in range(4)]
+    ops.extended_backward_scale_bias_layernorm(place(ln, 'BJI', lay), tg, place(r2, 'BJI', lay), place(lw, 'BJI', lay),
+                                               place(l2, 'BJI', lay), place(istd, 'BJ', 'BJ'), place(diff, 'BJI', lay),
+                                               d_mask, d_dln1, d_dres1, d_datt, *o)
+    dln1, dg1, db1, dl2 = orc.extended_backward_scale_bias(ln, gamma, r2, lw, l2)
+    dres1, datt = orc.backward_layernorm_residual_dropout(dln1, diff, istd, mask)
+    for got, want, what in ((d_dln1, dln1, 'DLN1'), (d_dres1, dres1, 'DRESID1'), (d_datt, datt, 'DATT'),
+                            (o[0], dg1, 'dgamma1'), (o[1], db1, 'dbeta1'), (o[2], dl2, 'dlinb2'),
+                            (o[3], orc.backward_attn_out_bias(datt), 'dbo')):
+        assert_close(got, want, what=what)
+
+
+def test_fused_layernorm_backward_declines_strided_views():
+    ops = _ops()
+    from substation_b200._lib import SubstationError
+    B, J, F = 2, 8, 64
+    x = torch.zeros(F, B, J, dtype=torch.float16, device=DEV).permute(1, 2, 0)     # feature-outermost
+    m = torch.zeros(B, J, F, dtype=torch.uint8, device=DEV)
+    v = torch.zeros(F, dtype=torch.float16, device=DEV)
+    s2 = torch.zeros(B, J, dtype=torch.float16, device=DEV)
+    with pytest.raises(SubstationError) as e:
+        ops.backward_scale_bias_layernorm(x, x, v, s2, x, m, x, x, x, v, v)
+    assert e.value.status == 3
