@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -15,6 +16,14 @@ namespace sb {
 
 namespace {
 thread_local std::string g_error;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SUBSTATION_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 void set_error(const std::string& msg) { g_error = msg; }

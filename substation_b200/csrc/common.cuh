@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
 #include <string>
 
 #include "../../include/substation_b200.h"
@@ -65,6 +66,44 @@ struct Rng {
 };
 
 #ifdef __CUDACC__
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the library is launched with
+// the programmatic-stream-serialization attribute and begins with
+// grid_dependency_sync(): the next kernel's CTAs may be scheduled, and run
+// whatever set-up precedes that call, while the previous kernel drains; nothing
+// touches global memory before the previous grid has completed and flushed.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+bool pdl_enabled();  // false when the environment sets SUBSTATION_B200_PDL=0
+
+template <class... KArgs, class... Args>
+cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                     Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define SB_LAUNCH_OK(expr)                                                              \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return ::sb::fail(SB_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(_e)); \
+  } while (0)
 
 constexpr int kWarp = 32;
 constexpr float kLnEps = 1e-5f;

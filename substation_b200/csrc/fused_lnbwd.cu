@@ -50,6 +50,7 @@ __device__ __forceinline__ void group_barrier(int group) {
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 lnbwd_kernel(LnBwdParams p) {
+  grid_dependency_sync();
   constexpr int NQ = MODE == 0 ? 2 : 4;
   constexpr int NIN = MODE == 0 ? 2 : 4;
   __shared__ float red[kGroups][2][4][2 * kRows];
@@ -199,6 +200,7 @@ lnbwd_kernel(LnBwdParams p) {
 // added by 4 thread groups and combined through shared memory.
 __global__ void __launch_bounds__(256)
 colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, void* o0, void* o1, void* o2, void* o3) {
+  grid_dependency_sync();
   __shared__ float sm[4][64];
   const int q = blockIdx.y;
   const int fl = threadIdx.x & 63, part = threadIdx.x >> 6;
@@ -240,10 +242,10 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
   const size_t smem = (size_t)kGroups * NQ * kMaxF * sizeof(float);
   SB_CUDA_OK(cudaFuncSetAttribute(lnbwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  lnbwd_kernel<MODE><<<P, kThreads, smem, s>>>(p);
+  SB_LAUNCH_OK(launch_k(lnbwd_kernel<MODE>, P, kThreads, smem, s, p));
   SB_CUDA_OK(cudaGetLastError());
   dim3 grid((p.d.F + 63) / 64, NQ);
-  colsum_finish_kernel<<<grid, 256, 0, s>>>(p.partial, P, p.d.F, NQ, outs[0], outs[1], outs[2], outs[3]);
+  SB_LAUNCH_OK(launch_k(colsum_finish_kernel, grid, 256, 0, s, p.partial, P, p.d.F, NQ, outs[0], outs[1], outs[2], outs[3]));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }

@@ -100,6 +100,7 @@ template <int LPR, int NV, int ROWS, bool AV>
 __global__ void __launch_bounds__(kSmThreads, (NV * ROWS <= 4) ? 4 : 1)
 softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, float scale, Rng rng,
                    unsigned R, unsigned ngroups) {
+  grid_dependency_sync();
   constexpr int RPW = kWarp / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPR, sl = lane % LPR;
@@ -173,6 +174,7 @@ softmax_fwd_kernel(Dims4 d, View4 beta, View4 alpha, View4 mask, View4 drop, flo
 template <int LPR, int NV, int ROWS, bool AV>
 __global__ void __launch_bounds__(kSmThreads, (NV * ROWS <= 4) ? 4 : 1)
 softmax_bwd_kernel(Dims4 d, View4 alpha, View4 mask, View4 dad, View4 dbeta, unsigned R, unsigned ngroups) {
+  grid_dependency_sync();
   constexpr int RPW = kWarp / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPR, sl = lane % LPR;
@@ -235,6 +237,7 @@ template <int NV, bool AV>
 __global__ void __launch_bounds__(kSmThreads, NV <= 2 ? 3 : (NV <= 4 ? 2 : 1))
 bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma, const void* beta,
              View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng, int pvec) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned R = (unsigned)d.B * (unsigned)d.J;
   const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
@@ -322,6 +325,7 @@ bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma
 template <int NV, bool AV>
 __global__ void __launch_bounds__(kSmThreads, NV <= 2 ? 3 : (NV <= 4 ? 2 : 1))
 blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresid, View3 dlin) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned R = (unsigned)d.B * (unsigned)d.J;
   const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
@@ -391,6 +395,7 @@ __global__ void __launch_bounds__(kSmThreads, 4)
 bad_flat_kernel(unsigned long long ngroups, int groups_per_row, const uint4* __restrict__ in,
                 const uint4* __restrict__ bias, uint2* mask, uint4* __restrict__ lin1,
                 uint4* __restrict__ drop2, Rng rng) {
+  grid_dependency_sync();
   const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
   for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
        g0 += stride * kFlatUnr) {
@@ -438,6 +443,7 @@ bad_flat_kernel(unsigned long long ngroups, int groups_per_row, const uint4* __r
 __global__ void __launch_bounds__(kSmThreads, 4)
 add_flat_kernel(unsigned long long ngroups, const uint4* __restrict__ a, const uint4* __restrict__ b,
                 uint4* __restrict__ out) {
+  grid_dependency_sync();
   const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
   for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
        g0 += stride * kFlatUnr) {
@@ -459,6 +465,7 @@ add_flat_kernel(unsigned long long ngroups, const uint4* __restrict__ a, const u
 __global__ void __launch_bounds__(kSmThreads, 4)
 rowbias_flat_kernel(unsigned long long ngroups, unsigned groups_per_row, const uint4* __restrict__ in,
                     const __half* __restrict__ bias, uint4* __restrict__ out) {
+  grid_dependency_sync();
   const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
   for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
        g0 += stride * kFlatUnr) {
@@ -488,6 +495,7 @@ template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin1, View3 drop2,
            int activation, Rng rng, int pvec) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long R = (long long)d.B * d.J;
   const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
@@ -530,6 +538,7 @@ bad_kernel(Dims3 d, int spans, View3 in, const void* bias, View3 mask, View3 lin
 template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 bei_kernel(Dims3 d, int spans, View3 a, View3 b_, View3 out) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long R = (long long)d.B * d.J;
   const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
@@ -563,6 +572,7 @@ template <bool AV>
 __global__ void __launch_bounds__(kRowThreads)
 aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long long bsP,
            long long bsH, View5 out) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long R = (long long)d.N * d.P * d.H * d.B;
   const long long item = (long long)blockIdx.x * (kRowThreads / kWarp) + warp;
@@ -592,10 +602,41 @@ aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long l
   }
 }
 
+// Dense rows: out[r] = sum of the `groups` groups of eight of row r; one warp per row, eight
+// 128-bit loads in flight per lane.
+__global__ void __launch_bounds__(kSmThreads)
+rowsum_flat_kernel(unsigned rows, unsigned groups, const uint4* __restrict__ in, __half* __restrict__ out) {
+  grid_dependency_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
+  for (unsigned r = blockIdx.x * (kSmThreads / kWarp) + warp; r < rows; r += nwarps) {
+    const uint4* p = in + (unsigned long long)r * groups;
+    float acc = 0.f;
+    for (unsigned g0 = lane; g0 < groups; g0 += kWarp * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const unsigned g = g0 + u * kWarp;
+        v[u] = g < groups ? p[g] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float x[8];
+        unpack8(v[u], x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += x[e];
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[r] = __float2half_rn(acc);
+  }
+}
+
 // dbias[n,p,h] = sum_{b,j} in[n,p,h,b,j]; one CTA per output element.
 template <bool AV>
 __global__ void __launch_bounds__(kColThreads)
 baib_kernel(Dims5 d, View5 in, void* dbias, long long bsN, long long bsP, long long bsH) {
+  grid_dependency_sync();
   long long row = blockIdx.x;
   const int h = (int)(row % d.H); row /= d.H;
   const int p = (int)(row % d.P);
@@ -768,6 +809,7 @@ template <class Op, bool AV>
 __global__ void __launch_bounds__(kColThreads, Op::MINB)
 colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* counters,
                  ColOut<Op::NQ> outs) {
+  grid_dependency_sync();
   constexpr int NQ = Op::NQ;
   constexpr int NW = kColThreads / kWarp;
   constexpr int UNR = Op::UNR;  // rows in flight per warp
@@ -885,8 +927,8 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
   unsigned* counters = reinterpret_cast<unsigned*>(ws);
   float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
   dim3 grid(slices, (unsigned)P);
-  if (all_vec) colreduce_kernel<Op, true><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
-  else colreduce_kernel<Op, false><<<grid, kColThreads, 0, s>>>(op, d, rpc, partial, counters, outs);
+  if (all_vec) SB_LAUNCH_OK(launch_k(colreduce_kernel<Op, true>, grid, kColThreads, 0, s, op, d, rpc, partial, counters, outs));
+  else SB_LAUNCH_OK(launch_k(colreduce_kernel<Op, false>, grid, kColThreads, 0, s, op, d, rpc, partial, counters, outs));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -925,7 +967,7 @@ unsigned persistent_blocks(K kernel, int threads, unsigned long long work_blocks
     const unsigned ngroups = (unsigned)((R + (32 / (LPR)) * (ROWS) - 1) / ((32 / (LPR)) * (ROWS))); \
     auto k = KERNEL<LPR, NV, ROWS, AVFLAG>;                                                         \
     const unsigned blocks = persistent_blocks(k, kSmThreads, (ngroups + 7) / 8);                    \
-    k<<<blocks, kSmThreads, 0, s>>>(__VA_ARGS__, (unsigned)R, ngroups);                             \
+    SB_LAUNCH_OK(launch_k(k, blocks, kSmThreads, 0, s, __VA_ARGS__, (unsigned)R, ngroups));                             \
   } while (0)
 
 #define SB_SOFTMAX_LAUNCH(KERNEL, AVFLAG, ...)                                    \
@@ -970,7 +1012,7 @@ int launch_softmax_bwd(cudaStream_t s, Dims4 d, View4 alpha, View4 mask, View4 d
   do {                                                                                       \
     auto k = KERNEL<NV, AVFLAG>;                                                             \
     const unsigned blocks = persistent_blocks(k, kSmThreads, (unsigned long long)((R + 7) / 8)); \
-    k<<<blocks, kSmThreads, 0, s>>>(__VA_ARGS__);                                            \
+    SB_LAUNCH_OK(launch_k(k, blocks, kSmThreads, 0, s, __VA_ARGS__));                                            \
   } while (0)
 
 #define SB_ROW_LAUNCH(KERNEL, AVFLAG, F, ...)                            \
@@ -1030,12 +1072,12 @@ int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, 
     const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
     if (activation == SB_ACT_RELU) {
       auto k = bad_flat_kernel<SB_ACT_RELU>;
-      k<<<persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s>>>(
-          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng);
+      SB_LAUNCH_OK(launch_k(k, persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s, 
+          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng));
     } else {
       auto k = bad_flat_kernel<SB_ACT_GELU>;
-      k<<<persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s>>>(
-          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng);
+      SB_LAUNCH_OK(launch_k(k, persistent_blocks(k, kSmThreads, work), kSmThreads, 0, s, 
+          ngroups, d.F / 8, (const uint4*)in.p, (const uint4*)bias, (uint2*)mask.p, (uint4*)lin1.p, (uint4*)drop2.p, rng));
     }
     SB_CUDA_OK(cudaGetLastError());
     return SB_OK;
@@ -1043,9 +1085,9 @@ int launch_bad(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 mask, 
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
   if (pvec && all_vec(in, mask, lin1, drop2))
-    bad_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec);
+    SB_LAUNCH_OK(launch_k(bad_kernel<true>, blocks, kRowThreads, 0, s, d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec));
   else
-    bad_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec);
+    SB_LAUNCH_OK(launch_k(bad_kernel<false>, blocks, kRowThreads, 0, s, d, spans, in, bias, mask, lin1, drop2, activation, rng, pvec));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -1060,15 +1102,15 @@ int launch_bei(cudaStream_t s, Dims3 d, View3 a, View3 b, View3 out) {
   if (same && dense3(d, a) ) {
     const unsigned long long ngroups = (unsigned long long)R * (d.F / 8);
     const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
-    add_flat_kernel<<<persistent_blocks(add_flat_kernel, kSmThreads, work), kSmThreads, 0, s>>>(
-        ngroups, (const uint4*)a.p, (const uint4*)b.p, (uint4*)out.p);
+    SB_LAUNCH_OK(launch_k(add_flat_kernel, persistent_blocks(add_flat_kernel, kSmThreads, work), kSmThreads, 0, s, 
+        ngroups, (const uint4*)a.p, (const uint4*)b.p, (uint4*)out.p));
     SB_CUDA_OK(cudaGetLastError());
     return SB_OK;
   }
   const int spans = (d.F + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  if (all_vec(a, b, out)) bei_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
-  else bei_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, a, b, out);
+  if (all_vec(a, b, out)) SB_LAUNCH_OK(launch_k(bei_kernel<true>, blocks, kRowThreads, 0, s, d, spans, a, b, out));
+  else SB_LAUNCH_OK(launch_k(bei_kernel<false>, blocks, kRowThreads, 0, s, d, spans, a, b, out));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -1086,15 +1128,15 @@ int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bs
   if (dense) {
     const unsigned long long ngroups = (unsigned long long)R * (d.J / 8);
     const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
-    rowbias_flat_kernel<<<persistent_blocks(rowbias_flat_kernel, kSmThreads, work), kSmThreads, 0, s>>>(
-        ngroups, (unsigned)(BJ / 8), (const uint4*)in.p, (const __half*)bias, (uint4*)out.p);
+    SB_LAUNCH_OK(launch_k(rowbias_flat_kernel, persistent_blocks(rowbias_flat_kernel, kSmThreads, work), kSmThreads, 0, s, 
+        ngroups, (unsigned)(BJ / 8), (const uint4*)in.p, (const __half*)bias, (uint4*)out.p));
     SB_CUDA_OK(cudaGetLastError());
     return SB_OK;
   }
   const int spans = (d.J + kEwNV * 256 - 1) / (kEwNV * 256);
   const unsigned blocks = (unsigned)((R * spans + 3) / 4);
-  if (all_vec(in, out)) aib_kernel<true><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
-  else aib_kernel<false><<<blocks, kRowThreads, 0, s>>>(d, spans, in, bias, bsN, bsP, bsH, out);
+  if (all_vec(in, out)) SB_LAUNCH_OK(launch_k(aib_kernel<true>, blocks, kRowThreads, 0, s, d, spans, in, bias, bsN, bsP, bsH, out));
+  else SB_LAUNCH_OK(launch_k(aib_kernel<false>, blocks, kRowThreads, 0, s, d, spans, in, bias, bsN, bsP, bsH, out));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -1103,8 +1145,16 @@ int launch_baib(cudaStream_t s, Dims5 d, View5 in, void* dbias, long long bsN, l
                 long long bsH) {
   const long long R = (long long)d.N * d.P * d.H;
   if (R == 0) return SB_OK;
-  if (all_vec(in)) baib_kernel<true><<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
-  else baib_kernel<false><<<(unsigned)R, kColThreads, 0, s>>>(d, in, dbias, bsN, bsP, bsH);
+  const long long BJ = (long long)d.B * d.J;
+  if (in.vec && in.sJ == 1 && in.sB == d.J && in.sH == BJ && in.sP == BJ * d.H && in.sN == BJ * d.H * d.P &&
+      bsH == 1 && bsP == d.H && bsN == (long long)d.H * d.P && R < 0x7fffffffLL && BJ / 8 < 0x7fffffffLL) {
+    const unsigned blocks = persistent_blocks(rowsum_flat_kernel, kSmThreads, (unsigned long long)((R + 7) / 8));
+    SB_LAUNCH_OK(launch_k(rowsum_flat_kernel, blocks, kSmThreads, 0, s, (unsigned)R, (unsigned)(BJ / 8), (const uint4*)in.p, (__half*)dbias));
+    SB_CUDA_OK(cudaGetLastError());
+    return SB_OK;
+  }
+  if (all_vec(in)) SB_LAUNCH_OK(launch_k(baib_kernel<true>, (unsigned)R, kColThreads, 0, s, d, in, dbias, bsN, bsP, bsH));
+  else SB_LAUNCH_OK(launch_k(baib_kernel<false>, (unsigned)R, kColThreads, 0, s, d, in, dbias, bsN, bsP, bsH));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }

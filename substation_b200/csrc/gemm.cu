@@ -170,6 +170,7 @@ constexpr int kSt = 64, kSk = 16;
 
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(GemmProblem g) {
+  grid_dependency_sync();
   __shared__ float As[kSk][kSt + 4];
   __shared__ float Bs[kSk][kSt + 4];
   const int tid = threadIdx.x;
@@ -221,7 +222,7 @@ int launch_gemm_simt(cudaStream_t s, const GemmProblem& g) {
   if (g.batch == 0 || g.M == 0 || g.N == 0) return SB_OK;
   dim3 grid((unsigned)((g.N + kSt - 1) / kSt), (unsigned)((g.M + kSt - 1) / kSt),
             (unsigned)std::min<long long>(g.batch, 65535));
-  gemm_simt_kernel<<<grid, 256, 0, s>>>(g);
+  SB_LAUNCH_OK(launch_k(gemm_simt_kernel, grid, 256, 0, s, g));
   SB_CUDA_OK(cudaGetLastError());
   g_last_gemm_impl = SB_GEMM_SIMT;
   return SB_OK;
@@ -395,6 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  grid_dependency_sync();  // barriers, tensor memory and tensor maps were set up while the previous kernel drained
 
   if (warp == 0) {
     // ---------------- TMA producer (whole warp walks the loop, lane 0 issues) ----------------
@@ -626,6 +628,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, long long M, long long N,
                      __half* out, long long sCb, long long sCm, long long sCn, float alpha) {
+  grid_dependency_sync();
   const long long total4 = batch * M * N / 4;  // N % 4 == 0
   const long long plane = batch * M * N;
   for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total4; i += (long long)gridDim.x * 256) {
@@ -790,13 +793,13 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
     }
   }
   const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
-  gemm_tc_kernel<BN, KS><<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(a.map, b.map, cmap, p);
+  SB_LAUNCH_OK(launch_k(gemm_tc_kernel<BN, KS>, grid, kTcThreads, Cfg::kSmemBytes, s, a.map, b.map, cmap, p));
   SB_CUDA_OK(cudaGetLastError());
   if (p.splits > 1) {
     const long long total4 = g.batch * g.M * g.N / 4;
     const unsigned blocks = (unsigned)std::min<long long>((total4 + 255) / 256, (long long)sm_count() * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float*>(ws), p.splits, g.batch, g.M, g.N,
-                                                reinterpret_cast<__half*>(g.C), g.sCb, g.sCm, g.sCn, g.alpha);
+    SB_LAUNCH_OK(launch_k(splitk_reduce_kernel, blocks, 256, 0, s, reinterpret_cast<const float*>(ws), p.splits, g.batch, g.M, g.N,
+                                                reinterpret_cast<__half*>(g.C), g.sCb, g.sCm, g.sCn, g.alpha));
     SB_CUDA_OK(cudaGetLastError());
   }
   return SB_OK;
@@ -868,7 +871,7 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
   }
   const int budget = sm_count() / 2;
   const unsigned nclusters = (unsigned)std::max<long long>(1, std::min<long long>(p.tiles, std::min(clusters, budget)));
-  pair::gemm_tc_pair_kernel<<<2 * nclusters, kTcThreads, pair::kSmemBytes, s>>>(a.map, b.map, cmap, p);
+  SB_LAUNCH_OK(launch_k(pair::gemm_tc_pair_kernel, 2 * nclusters, kTcThreads, pair::kSmemBytes, s, a.map, b.map, cmap, p));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }

@@ -111,6 +111,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  grid_dependency_sync();
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
