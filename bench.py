@@ -524,7 +524,7 @@ def main():
                          'b8_l512 / b96_l128 (the reference\'s shipped configurations) or a .json path')
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
-    ap.add_argument('--comm-ctas', type=int, default=8, help='SMs left to NCCL when N > 1')
+    ap.add_argument('--comm-ctas', type=int, default=4, help='SMs left to NCCL when N > 1')
     ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (config 5 uses 24)')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')
