@@ -198,6 +198,23 @@ int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* da
  *     on the GPU (different streams) race; serialise them. */
 int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* datt, const sb_tensor* dbo);
 
+/* The score contraction and the softmax in one kernel: beta = scale * sum_p qq*kk,
+ * alpha = softmax_k(beta), drop = mask*alpha.  qq, kk: [P,H,B,J] projections (any strides TMA
+ * can address); beta, alpha, mask, drop: [H,B,J,K] and dense in that order.  The 128 x K score
+ * tile lives in tensor memory between the tcgen05 MMAs and the per-row softmax, so beta is
+ * written but never read back.  Needs P = 64, J = K a multiple of 64 and at most 512; otherwise
+ * SB_ERR_UNSUPPORTED and the caller runs sb_einsum + sb_softmax_dropout.
+ * Replaces the pair pytorch_module/encoder.cu:115-121. */
+int sb_attention_scores_softmax(void* stream, const sb_tensor* qq, const sb_tensor* kk,
+                                const sb_tensor* beta, const sb_tensor* alpha, const sb_tensor* mask,
+                                const sb_tensor* drop, float scale, const sb_dropout* dropout);
+
+/* dattn_drop = sum_p dgamma*vv and sb_backward_softmax in one kernel (dattn_drop is written
+ * but never read back).  Same requirements.  Replaces pytorch_module/encoder.cu:250-252 + :258-261. */
+int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, const sb_tensor* vv,
+                                         const sb_tensor* alpha, const sb_tensor* mask,
+                                         const sb_tensor* dattn_drop, const sb_tensor* dbeta);
+
 /* dbeta = alpha*(da - sum_k da*alpha), da = mask*dattn_drop.  All [H,B,J,K].
  * Replaces BackwardSoftmax::run, pytorch_module/block_bs.cuh:100-156. */
 int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,

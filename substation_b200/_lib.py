@@ -69,6 +69,8 @@ SIGNATURES = {
     'sb_backward_scale_bias_layernorm': (c_int, [c_void_p, c_void_p] + [_T] * 11),
     'sb_extended_backward_scale_bias_layernorm': (c_int, [c_void_p, c_void_p] + [_T] * 15),
     'sb_backward_attn_out_bias_noalloc': (c_int, [c_void_p, _T, _T]),
+    'sb_attention_scores_softmax': (c_int, [c_void_p, _T, _T, _T, _T, _T, _T, c_float, _D]),
+    'sb_attention_scores_softmax_backward': (c_int, [c_void_p, _T, _T, _T, _T, _T, _T]),
     'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
     'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
     'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),

@@ -188,6 +188,54 @@ extern "C" int sb_softmax_dropout(void* stream, const sb_tensor* beta, const sb_
   return launch_softmax_fwd((cudaStream_t)stream, dims4(beta), vb, va, vm, vd, scale, rng);
 }
 
+namespace {
+// [P,H,B,rows] projection as a View4 whose fields carry the (P,H,B,row) strides
+int to_proj(const sb_tensor* t, const sb_tensor* scores, const char* what, View4* v, int* P) {
+  SB_TRY(check_tensor(t, 4, what));
+  SB_TRY(fits_int(t, what));
+  if (t->size[1] != scores->size[0] || t->size[2] != scores->size[1] || t->size[3] != scores->size[2])
+    return fail(SB_ERR_ARG, std::string(what) + ": extent mismatch between operands");
+  v->p = t->ptr; v->sH = t->stride[0]; v->sB = t->stride[1]; v->sJ = t->stride[2]; v->sK = t->stride[3];
+  v->vec = 0;
+  *P = (int)t->size[0];
+  return SB_OK;
+}
+}  // namespace
+
+extern "C" int sb_attention_scores_softmax(void* stream, const sb_tensor* qq, const sb_tensor* kk,
+                                           const sb_tensor* beta, const sb_tensor* alpha, const sb_tensor* mask,
+                                           const sb_tensor* drop, float scale, const sb_dropout* dropout) {
+  View4 vq, vk, vb, va, vm, vd;
+  Rng rng;
+  int P = 0, P2 = 0;
+  SB_TRY(to_view4(beta, nullptr, false, "scores.beta", &vb));
+  SB_TRY(to_view4(alpha, beta, false, "scores.alpha", &va));
+  SB_TRY(to_view4(mask, beta, true, "scores.mask", &vm));
+  SB_TRY(to_view4(drop, beta, false, "scores.drop", &vd));
+  SB_TRY(to_proj(qq, beta, "scores.qq", &vq, &P));
+  SB_TRY(to_proj(kk, beta, "scores.kk", &vk, &P2));
+  if (P != P2) return fail(SB_ERR_ARG, "scores: head size differs between queries and keys");
+  if (beta->size[2] != beta->size[3]) return fail(SB_ERR_UNSUPPORTED, "scores: self-attention only (J must equal K)");
+  SB_TRY(to_rng(dropout, &rng));
+  return launch_attn_scores_fwd((cudaStream_t)stream, dims4(beta), P, vq, vk, vb, va, vm, vd, scale, rng);
+}
+
+extern "C" int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, const sb_tensor* vv,
+                                                    const sb_tensor* alpha, const sb_tensor* mask,
+                                                    const sb_tensor* dattn_drop, const sb_tensor* dbeta) {
+  View4 vg, vvv, va, vm, vd, vo;
+  int P = 0, P2 = 0;
+  SB_TRY(to_view4(alpha, nullptr, false, "scores_bwd.alpha", &va));
+  SB_TRY(to_view4(mask, alpha, true, "scores_bwd.mask", &vm));
+  SB_TRY(to_view4(dattn_drop, alpha, false, "scores_bwd.dattn_drop", &vd));
+  SB_TRY(to_view4(dbeta, alpha, false, "scores_bwd.dbeta", &vo));
+  SB_TRY(to_proj(dgamma, alpha, "scores_bwd.dgamma", &vg, &P));
+  SB_TRY(to_proj(vv, alpha, "scores_bwd.vv", &vvv, &P2));
+  if (P != P2) return fail(SB_ERR_ARG, "scores_bwd: head size differs between operands");
+  if (alpha->size[2] != alpha->size[3]) return fail(SB_ERR_UNSUPPORTED, "scores_bwd: self-attention only");
+  return launch_attn_scores_bwd((cudaStream_t)stream, dims4(alpha), P, vg, vvv, va, vm, vd, vo);
+}
+
 extern "C" int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,
                                    const sb_tensor* dattn_drop, const sb_tensor* dbeta) {
   View4 va, vm, vg, vo;
@@ -507,6 +555,14 @@ struct sb_encoder {
     return view(ptr, layout.at(name), logical_dims().at(name));
   }
 
+  // forget the operator just marked (a fused attempt declined before launching anything)
+  void unmark() {
+    --launches;
+    if (timing && !marks.empty()) {
+      event_pool.push_back(marks.back().second);
+      marks.pop_back();
+    }
+  }
   // rename the operator just marked (a fused attempt fell back to its first separate operator)
   void relabel(const char* name) {
     if (timing && !marks.empty()) marks.back().first = name;
@@ -702,15 +758,26 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
     sb_tensor bias = e->view(T["BKQV"], "BKQV");
     SB_TRY(sb_attention_input_biases(stream, &in, &bias, &out));
   }
-  // F2: scaled scores.  K and V views are the J-indexed projections relabelled with K.
-  SB_TRY(einsum(e, s, "QKT", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 0), lKK, q_slice("KKQQVV", 1),
-                L.at("BETA"), T["BETA"], 1.f / std::sqrt((float)e->P)));
+  // F2 + softmax.  K and V views are the J-indexed projections relabelled with K.
   {
-    e->mark(s, "softmax");
     sb_tensor beta = e->view(T["BETA"], "BETA"), alpha = e->view(T["ALPHA"], "ALPHA");
     sb_tensor mask = e->view(T["ATTN_DROP_MASK"], "ATTN_DROP_MASK"), dr = e->view(T["ATTN_DROP"], "ATTN_DROP");
     sb_dropout d = drop(e->p_softmax, mask_mode, seed, offset + 0);
-    SB_TRY(sb_softmax_dropout(stream, &beta, &alpha, &mask, &dr, 1.f, &d));
+    const float scale = 1.f / std::sqrt((float)e->P);
+    int st = SB_ERR_UNSUPPORTED;
+    if (e->fuse) {
+      e->mark(s, "QKT+softmax");
+      sb_tensor kk = e->view(q_slice("KKQQVV", 0), lKK, "PHBJ"), qq = e->view(q_slice("KKQQVV", 1), lKK, "PHBJ");
+      st = sb_attention_scores_softmax(stream, &qq, &kk, &beta, &alpha, &mask, &dr, scale, &d);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+      if (st == SB_ERR_UNSUPPORTED) e->unmark();
+    }
+    if (st == SB_ERR_UNSUPPORTED) {
+      SB_TRY(einsum(e, s, "QKT", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 0), lKK, q_slice("KKQQVV", 1),
+                    L.at("BETA"), T["BETA"], scale));
+      e->mark(s, "softmax");
+      SB_TRY(sb_softmax_dropout(stream, &beta, &alpha, &mask, &dr, 1.f, &d));
+    }
   }
   SB_TRY(einsum(e, s, "gamma", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 2), L.at("ATTN_DROP"), T["ATTN_DROP"],
                 L.at("GAMMA"), T["GAMMA"], 1.f));
@@ -835,14 +902,25 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
   const float scale = 1.f / std::sqrt((float)e->P);
   void *KK = q_slice(T["KKQQVV"], 0), *QQ = q_slice(T["KKQQVV"], 1), *VV = q_slice(T["KKQQVV"], 2);
   void *DKK = q_slice(T["DKKQQVV"], 0), *DQQ = q_slice(T["DKKQQVV"], 1), *DVV = q_slice(T["DKKQQVV"], 2);
-  SB_TRY(einsum(e, s, "dX1gamma", rename(lKK, 'J', 'K'), VV, L.at("DGAMMA"), T["DGAMMA"], L.at("DATTN_DROP"),
-                T["DATTN_DROP"], 1.f));
-  SB_TRY(einsum(e, s, "dX2gamma", L.at("DGAMMA"), T["DGAMMA"], L.at("ATTN_DROP"), T["ATTN_DROP"],
-                rename(lDKK, 'J', 'K'), DVV, 1.f));
   {
-    e->mark(s, "bs");
     sb_tensor alpha = v("ALPHA"), mask = v("ATTN_DROP_MASK"), g = v("DATTN_DROP"), o = v("DBETA");
-    SB_TRY(sb_backward_softmax(stream, &alpha, &mask, &g, &o));
+    int st = SB_ERR_UNSUPPORTED;
+    if (e->fuse) {
+      e->mark(s, "dX1gamma+bs");
+      sb_tensor dgm = e->view(T["DGAMMA"], "DGAMMA"), vvt = e->view(VV, lKK, "PHBJ");
+      st = sb_attention_scores_softmax_backward(stream, &dgm, &vvt, &alpha, &mask, &g, &o);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+      if (st == SB_ERR_UNSUPPORTED) e->unmark();
+    }
+    if (st == SB_ERR_UNSUPPORTED)
+      SB_TRY(einsum(e, s, "dX1gamma", rename(lKK, 'J', 'K'), VV, L.at("DGAMMA"), T["DGAMMA"], L.at("DATTN_DROP"),
+                    T["DATTN_DROP"], 1.f));
+    SB_TRY(einsum(e, s, "dX2gamma", L.at("DGAMMA"), T["DGAMMA"], L.at("ATTN_DROP"), T["ATTN_DROP"],
+                  rename(lDKK, 'J', 'K'), DVV, 1.f));
+    if (st == SB_ERR_UNSUPPORTED) {
+      e->mark(s, "bs");
+      SB_TRY(sb_backward_softmax(stream, &alpha, &mask, &g, &o));
+    }
   }
   SB_TRY(einsum(e, s, "dX1QKT", rename(lKK, 'J', 'K'), KK, L.at("DBETA"), T["DBETA"], lDKK, DQQ, scale));
   SB_TRY(einsum(e, s, "dX2QKT", lKK, QQ, L.at("DBETA"), T["DBETA"], rename(lDKK, 'J', 'K'), DKK, scale));

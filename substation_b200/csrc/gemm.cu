@@ -656,6 +656,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
 }
 
 #include "gemm_pair.cuh"
+#include "attn_fused.cuh"
 
 // ---- host side ------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -964,6 +965,83 @@ int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws, size_t ws
 }
 
 void set_gemm_sm_budget(int n) { g_sm_budget = n; }
+
+namespace {
+
+bool dense_scores(const View4& v, const Dims4& d) {
+  return v.sK == 1 && v.sJ == d.K && v.sB == (long long)d.J * d.K && (d.H == 1 || v.sH == (long long)d.B * d.J * d.K) &&
+         (reinterpret_cast<uintptr_t>(v.p) & 15u) == 0;
+}
+
+// Shared launcher: operands a [P,H,B,rows] (queries / DGAMMA) and b [P,H,B,rows] (keys / values).
+template <bool BWD>
+int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long long aP, long long aH, long long aB,
+                       long long aJ, const void* b_ptr, long long bP, long long bH, long long bB, long long bJ,
+                       void* o0, void* o1, void* o2, attn::Params p) {
+  std::call_once(g_encode_once, load_encode);
+  if (!g_encode) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int L = d.K;
+  if (P != 64 || d.J != d.K || L % 64 != 0 || L > attn::kMaxL)
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores need head size 64 and a sequence length that is a multiple of 64, at most 512");
+  if ((d.H > 1 && d.B > 1) && (aH != aB * d.B || bH != bB * d.B))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores: head and sample dims of the projections do not collapse");
+  const long long batch = (long long)d.H * d.B;
+  const long long sAb = d.B > 1 ? aB : aH, sBb = d.B > 1 ? bB : bH;
+  std::string why;
+  OperandMap a, b;
+  if (!make_operand_map(a_ptr, L, P, batch, aJ, aP, sAb, kBM, &a, &why))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores, first operand: " + why);
+  const int brows = std::min(256, L);
+  if (!make_operand_map(b_ptr, L, P, batch, bJ, bP, sBb, brows, &b, &why))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores, second operand: " + why);
+  CUtensorMap m0, m1, m2;
+  memset(&m2, 0, sizeof(m2));
+  int sw0 = 0, sw1 = 0, sw2 = 0;
+  if (!encode_map(o0, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m0, &sw0, &why) ||
+      !encode_map(o1, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m1, &sw1, &why) ||
+      (o2 && !encode_map(o2, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m2, &sw2, &why)))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores, output: " + why);
+  p.L = L;
+  p.tiles_j = (L + 127) / 128;
+  p.tiles = (long long)p.tiles_j * batch;
+  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
+  p.swap_o = sw0;
+  p.b_bytes = b.mn ? L * 128 : ((L + 255) / 256) * brows * 128;
+  SB_CUDA_OK(cudaFuncSetAttribute(attn::attn_scores_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemBytes));
+  const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
+  SB_LAUNCH_OK(launch_k(attn::attn_scores_kernel<BWD>, grid, kTcThreads, attn::kSmemBytes, s, a.map, b.map, m0, m1, m2, p));
+  return SB_OK;
+}
+
+}  // namespace
+
+int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, View4 beta, View4 alpha, View4 mask,
+                           View4 drop, float scale, Rng rng) {
+  if ((long long)d.H * d.B * d.J == 0) return SB_OK;
+  if (!dense_scores(beta, d) || !dense_scores(alpha, d) || !dense_scores(drop, d) || !dense_scores(mask, d))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores need score tensors dense as [H,B,J,K]");
+  attn::Params p{};
+  p.scale = scale;
+  p.rng = rng;
+  p.mask = reinterpret_cast<uint8_t*>(mask.p);
+  p.alpha = nullptr;
+  // projections arrive as [P,H,B,rows] views: sH/sB/sJ/sK of the View4 hold the P,H,B,row strides
+  return launch_attn_scores<false>(s, d, P, qq.p, qq.sH, qq.sB, qq.sJ, qq.sK, kk.p, kk.sH, kk.sB, kk.sJ, kk.sK, beta.p,
+                                   alpha.p, drop.p, p);
+}
+
+int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 vv, View4 alpha, View4 mask,
+                           View4 dattn_drop, View4 dbeta) {
+  if ((long long)d.H * d.B * d.J == 0) return SB_OK;
+  if (!dense_scores(alpha, d) || !dense_scores(dattn_drop, d) || !dense_scores(dbeta, d) || !dense_scores(mask, d))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores need score tensors dense as [H,B,J,K]");
+  attn::Params p{};
+  p.scale = 1.f;
+  p.mask = reinterpret_cast<uint8_t*>(mask.p);
+  p.alpha = reinterpret_cast<const __half*>(alpha.p);
+  return launch_attn_scores<true>(s, d, P, dgamma.p, dgamma.sH, dgamma.sB, dgamma.sJ, dgamma.sK, vv.p, vv.sH, vv.sB,
+                                  vv.sJ, vv.sK, dattn_drop.p, dbeta.p, nullptr, p);
+}
 
 int gemm_device_error(cudaStream_t s, int* code) {
   int v = 0;

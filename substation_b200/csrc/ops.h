@@ -47,6 +47,14 @@ int launch_lnbwd_b(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gam
                    View3 dlin2, View2 istd, View3 diff, View3 mask, View3 dln1, View3 dresid1, View3 datt,
                    void* dgamma1, void* dbeta1, void* dlinb2, void* dbo);
 
+// Fused attention scores.  qq/kk/dgamma/vv are [P,H,B,rows] projections passed as View4 whose
+// (sH,sB,sJ,sK) fields hold the (P,H,B,row) strides; d = {H,B,J,K}.  SB_ERR_UNSUPPORTED when
+// the shapes or layouts do not qualify.
+int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, View4 beta, View4 alpha, View4 mask,
+                           View4 drop, float scale, Rng rng);
+int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 vv, View4 alpha, View4 mask,
+                           View4 dattn_drop, View4 dbeta);
+
 // Contractions -----------------------------------------------------------------
 struct GemmProblem {
   long long batch, M, N, K;

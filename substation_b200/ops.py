@@ -78,6 +78,21 @@ def softmax_dropout(beta, alpha, mask, drop, scale=1.0, p=0.0, mode='explicit', 
                                          float(scale), ctypes.byref(d)))
 
 
+def attention_scores_softmax(qq, kk, beta, alpha, mask, drop, scale, p=0.0, mode='explicit', seed=0, offset=0):
+    """beta = scale*qq.kk, alpha = softmax(beta), drop = mask*alpha in one kernel; qq, kk are [P,H,B,J]."""
+    _check_cuda(qq, kk, beta); _half(qq, kk, beta, alpha, drop); _mask(mask)
+    d = _dropout(p, mode, seed, offset)
+    check(_lib.load().sb_attention_scores_softmax(_stream(), _d(qq), _d(kk), _d(beta), _d(alpha), _d(mask), _d(drop),
+                                                  float(scale), ctypes.byref(d)))
+
+
+def attention_scores_softmax_backward(dgamma, vv, alpha, mask, dattn_drop, dbeta):
+    """dattn_drop = dgamma.vv and the softmax backward in one kernel; dgamma, vv are [P,H,B,J]."""
+    _check_cuda(dgamma, vv, alpha); _half(dgamma, vv, alpha, dattn_drop, dbeta); _mask(mask)
+    check(_lib.load().sb_attention_scores_softmax_backward(_stream(), _d(dgamma), _d(vv), _d(alpha), _d(mask),
+                                                           _d(dattn_drop), _d(dbeta)))
+
+
 def backward_softmax(alpha, mask, dattn_drop, dbeta):
     _check_cuda(alpha, mask, dattn_drop, dbeta); _half(alpha, dattn_drop, dbeta); _mask(mask)
     check(_lib.load().sb_backward_softmax(_stream(), _d(alpha), _d(mask), _d(dattn_drop), _d(dbeta)))

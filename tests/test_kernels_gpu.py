@@ -310,3 +310,52 @@ def test_fused_layernorm_backward_declines_strided_views():
     with pytest.raises(SubstationError) as e:
         ops.backward_scale_bias_layernorm(x, x, v, s2, x, m, x, x, x, v, v)
     assert e.value.status == 3
+
+
+@pytest.mark.parametrize('H,B,L,lay', [(2, 2, 512, 'PHBJ'), (2, 3, 128, 'PHBJ'), (1, 2, 64, 'PHBJ'), (2, 1, 384, 'HBPJ'),
+                                       (3, 2, 256, 'HBJP')])
+@pytest.mark.parametrize('mode', ['explicit', 'philox'])
+def test_fused_attention_scores_forward_and_backward(H, B, L, lay, mode):
+    """QKT+softmax+dropout and dX1gamma+softmax-backward, each in one kernel with the score tile in
+    tensor memory, against the oracle's separate steps."""
+    ops = _ops()
+    P = 64
+    rng = np.random.default_rng(L + H)
+    qq, kk, vv, dg = (h16(rng.normal(0, 1, (P, H, B, L))) for _ in range(4))
+    mask = (rng.random((H, B, L, L)) >= 0.2).astype(np.uint8)
+    d_mask = place(mask, 'HBJK', 'HBJK', torch.uint8) if mode == 'explicit' else empty((H, B, L, L), 'HBJK', 'HBJK', torch.uint8)
+    d_beta, d_alpha, d_drop = (empty((H, B, L, L), 'HBJK', 'HBJK') for _ in range(3))
+    scale = 0.125
+    ops.attention_scores_softmax(place(qq, 'PHBJ', lay), place(kk, 'PHBJ', lay), d_beta, d_alpha, d_mask, d_drop, scale,
+                                 p=0.2, mode=mode, seed=77, offset=5)
+    assert ops.device_error() == 0
+    if mode == 'philox':
+        mask = get(d_mask).astype(np.uint8)
+        assert np.array_equal(mask, orc.philox_mask((H, B, L, L), 0.2, 77, 5))
+    beta = scale * np.einsum('phbk,phbj->hbjk', kk, qq)
+    alpha, drop = orc.softmax_dropout(beta, mask)
+    assert_close(d_beta, beta, what='BETA')
+    assert_close(d_alpha, alpha, what='ALPHA')
+    assert_close(d_drop, drop, what='ATTN_DROP')
+    assert np.array_equal(get(d_drop), get(d_alpha) * mask)
+
+    alpha16 = h16(alpha)
+    d_dad, d_dbeta = empty((H, B, L, L), 'HBJK', 'HBJK'), empty((H, B, L, L), 'HBJK', 'HBJK')
+    ops.attention_scores_softmax_backward(place(dg, 'PHBJ', lay), place(vv, 'PHBJ', lay), place(alpha16, 'HBJK', 'HBJK'),
+                                          place(mask, 'HBJK', 'HBJK', torch.uint8), d_dad, d_dbeta)
+    assert ops.device_error() == 0
+    dad = np.einsum('phbk,phbj->hbjk', vv, dg)
+    assert_close(d_dad, dad, what='DATTN_DROP')
+    assert_close(d_dbeta, orc.softmax_dropout_backward(alpha16, mask, h16(dad)), what='DBETA')
+
+
+def test_fused_attention_scores_decline_what_they_do_not_cover():
+    ops = _ops()
+    from substation_b200._lib import SubstationError
+    H, B, L, P = 1, 1, 96, 64                       # L not a multiple of 64
+    q = torch.zeros(P, H, B, L, dtype=torch.float16, device=DEV)
+    s = torch.zeros(H, B, L, L, dtype=torch.float16, device=DEV)
+    m = torch.zeros(H, B, L, L, dtype=torch.uint8, device=DEV)
+    with pytest.raises(SubstationError) as e:
+        ops.attention_scores_softmax(q, q, s, s.clone(), m, s.clone(), 1.0)
+    assert e.value.status == 3
