@@ -6,23 +6,36 @@
 //           (dX1gamma contraction + BackwardSoftmax of pytorch_module/encoder.cu:250-260)
 //
 // One CTA owns 128 query rows of one (head, sample) and ALL keys (at most 512): the 128 x L score
-// tile is produced by tcgen05.mma into tensor memory (L fp32 columns), where thread r of the four
-// epilogue warps owns row r.  Row maximum, row sum and the normalisation are therefore plain
-// per-thread loops over TMEM columns, with no shuffles and no second trip through HBM for the
-// scores: the forward kernel never reads BETA back, the backward kernel never reads DATTN_DROP
-// back.  Outputs leave through 128-byte-swizzled staging rows and TMA stores.
+// tile is produced by tcgen05.mma into tensor memory (L fp32 columns).  Eight epilogue warps read it
+// back: two per 32-lane quadrant of tensor memory, thread = one query row, the two warps of a
+// quadrant taking alternate 64-key chunks and exchanging their partial row maximum / row sums
+// through shared memory.  The scores never make a second trip through HBM: the forward kernel
+// does not read BETA back, the backward kernel does not read DATTN_DROP back (it keeps
+// (mask*dattn_drop, alpha) as an fp16 pair per tensor-memory word between its two passes).
+// Inputs that stream per row (the dropout mask, ALPHA in the backward kernel) arrive through
+// per-warp TMA slots, outputs leave through swizzled staging rows and TMA stores, so every HBM
+// access is a full 64- or 128-byte row segment.
 // Requirements: head size 64, sequence length a multiple of 64 and at most 512, score tensors
-// dense as [H,B,J,K]; otherwise the caller runs the separate operators.
+// dense as [H,B,J,K], scale > 0; otherwise the caller runs the separate operators.
 
 #pragma once
 
 namespace attn {
 
 constexpr int kMaxL = 512;
-constexpr int kStageBytes = kABytes + kMaxL * 128;  // 128 x 64 queries + up to 512 x 64 keys, fp16
-constexpr int kStages = 2;
-constexpr int kStagingPerWarp = 4 * 4096;           // four 32-row x 128-byte buffers
-constexpr int kSmemBytes = kStages * kStageBytes + 4 * kStagingPerWarp + 1024 + 256;
+constexpr int kNW = 2;                               // epilogue warps per tensor-memory quadrant
+constexpr int kEpiWarps = 4 * kNW;
+constexpr int kThreads = 64 + 32 * kEpiWarps;        // producer warp, MMA warp, epilogue warps
+constexpr int kOperandBytes = kABytes + kMaxL * 128; // 128 x 64 queries + up to 512 x 64 keys, fp16
+constexpr int kRedBytes = 2 * kNW * 128 * 4;         // partial row maxima and row sums
+
+template <bool BWD>
+struct Cfg {
+  static constexpr int kOutBufs = BWD ? 2 : 3;       // staging buffers (32 rows x 128 B) per warp
+  static constexpr int kInSlot = BWD ? 6144 : 2048;  // ALPHA rows (4 KiB) + mask rows (2 KiB) | mask rows
+  static constexpr int kStaging = kEpiWarps * kOutBufs * 4096;
+  static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot + kRedBytes + 1024 + 256;
+};
 
 struct Params {
   int L;                 // sequence length (rows and columns of a score tile)
@@ -30,11 +43,10 @@ struct Params {
   int b_bytes;           // bytes the key/value boxes of one tile deliver (out-of-range rows included)
   long long tiles;       // tiles_j * batch
   int a_mn, b_mn, a_swap, b_swap;
-  int swap_o;            // dims 1,2 of the output tensor maps exchanged
-  float scale;           // forward: BETA = scale * acc.  backward: 1 (DATTN_DROP = acc)
+  int swap_o;            // dims 1,2 of the score tensor maps exchanged
+  float scale;           // forward: BETA = scale * acc.  backward: unused (DATTN_DROP = acc)
   Rng rng;               // forward: dropout source
-  uint8_t* mask;         // [batch][L][L] bytes
-  const __half* alpha;   // backward: softmax output [batch][L][L]
+  uint8_t* mask;         // [batch][L][L] bytes (written directly when the mask is generated here)
 };
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
@@ -50,40 +62,82 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Write 64 fp16 values (this thread's part of a row) into a swizzled staging row.
-__device__ __forceinline__ void stage_row64(uint8_t* row, int lane, const uint4 v[8]) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(row + ((i ^ (lane & 7)) << 4)) = v[i];
+// Wait for the outstanding tensor-memory loads; the registers are operands so that no use of them
+// can be scheduled above the wait.
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :: "memory");
 }
 
-// BWD = false: forward (maps: Q, K; outputs BETA, ALPHA, ATTN_DROP)
-// BWD = true : backward (maps: DGAMMA, V; outputs DATTN_DROP, DBETA; the third map is unused)
+// Walk this warp's 64-column chunks (c = first, first + kNW, ...) in 32-column halves, keeping the
+// tensor-memory load of the next half in flight while f(c, half, r) works on the current one.
+template <class F>
+__device__ __forceinline__ void sweep(uint32_t trow, int first, int nc64, F&& f) {
+  if (first >= nc64) return;
+  uint32_t ra[32], rb[32];
+  tmem_ld32_nowait(trow + first * 64, ra);
+  for (int c = first; c < nc64; c += kNW) {
+    tmem_ld_wait32(ra);
+    tmem_ld32_nowait(trow + c * 64 + 32, rb);
+    f(c, 0, ra);
+    tmem_ld_wait32(rb);
+    if (c + kNW < nc64) tmem_ld32_nowait(trow + (c + kNW) * 64, ra);
+    f(c, 1, rb);
+  }
+}
+
+// Barrier among the epilogue warps with a bounded wait (one arrival per warp).
+__device__ __forceinline__ bool epi_barrier(uint32_t bar, uint32_t& uses, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, uses & 1u, 6);
+  ++uses;
+  return __all_sync(0xffffffffu, ok);
+}
+
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
+// BWD = false: forward  (maps: Q, K; score maps: BETA, ALPHA, ATTN_DROP; tmI unused)
+// BWD = true : backward (maps: DGAMMA, V; score maps: DATTN_DROP, DBETA, -; tmI = ALPHA)
+// tmM: the mask as a byte tensor (read when it is an input).
 template <bool BWD>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmO0, const __grid_constant__ CUtensorMap tmO1,
-                   const __grid_constant__ CUtensorMap tmO2, const Params p) {
-  constexpr int S = kStages;
+                   const __grid_constant__ CUtensorMap tmO2, const __grid_constant__ CUtensorMap tmI,
+                   const __grid_constant__ CUtensorMap tmM, const Params p) {
+  using C = Cfg<BWD>;
+  constexpr int NB = C::kOutBufs;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const uint32_t staging = tiles + S * kStageBytes;
-  const uint32_t bars = staging + 4 * kStagingPerWarp;  // full[S], empty[S], tmem_full, tmem_empty
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * S, bar_tfull = bars + 16 * S, bar_tempty = bars + 16 * S + 8;
-  uint8_t* gen_base = smem_raw + (tiles - raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + S * kStageBytes + 4 * kStagingPerWarp + 16 * S + 16);
+  const uint32_t operands = (raw + 1023u) & ~1023u;
+  const uint32_t staging = operands + kOperandBytes;
+  const uint32_t inslots = staging + C::kStaging;
+  const uint32_t red = inslots + kEpiWarps * C::kInSlot;
+  const uint32_t bars = red + kRedBytes;  // full, empty, tmem_full, tmem_empty, in_full[kEpiWarps], epilogue barrier, tmem slot
+  const uint32_t bar_full = bars, bar_empty = bars + 8, bar_tfull = bars + 16, bar_tempty = bars + 24, bar_in = bars + 32;
+  const uint32_t bar_epi = bar_in + 8 * kEpiWarps;
+  uint8_t* gen_base = smem_raw + (operands - raw);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 48 + 8 * kEpiWarps);
+  float* red_gen = reinterpret_cast<float*>(gen_base + (red - operands));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int L = p.L;
   const int nchunk = (L + 255) / 256;  // MMA column chunks of up to 256 keys
+  const bool mask_in = BWD || !p.rng.philox;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
+    mbar_init(bar_full, 1);
+    mbar_init(bar_empty, 1);
     mbar_init(bar_tfull, 1);
-    mbar_init(bar_tempty, 4);
+    mbar_init(bar_tempty, kEpiWarps);
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar_in + 8 * w, 1);
+    mbar_init(bar_epi, kEpiWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
@@ -91,6 +145,8 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO0) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO1) : "memory");
     if (!BWD) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO2) : "memory");
+    if (BWD) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmI) : "memory");
+    if (mask_in) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmM) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -104,40 +160,36 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   grid_dependency_sync();
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: the operands of one tile at a time ----------------
     uint32_t it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
       const int j0 = (int)(t % p.tiles_j) * 128;
       const int bt = (int)(t / p.tiles_j);
-      const int s = it % S;
-      const uint32_t ph = (it / S) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_empty, (it & 1u) ^ 1u, 1));
       if (!ok) break;
       if (lane == 0) {
-        const uint32_t full = bar_full + 8 * s;
-        mbar_expect_tx(full, (uint32_t)(kABytes + p.b_bytes));
-        const uint32_t sa = tiles + s * kStageBytes, sb_ = sa + kABytes;
+        mbar_expect_tx(bar_full, (uint32_t)(kABytes + p.b_bytes));
+        const uint32_t sa = operands, sb_ = sa + kABytes;
         if (!p.a_mn) {
-          if (p.a_swap) tma_load_3d(sa, &tmA, full, 0, bt, j0);
-          else tma_load_3d(sa, &tmA, full, 0, j0, bt);
+          if (p.a_swap) tma_load_3d(sa, &tmA, bar_full, 0, bt, j0);
+          else tma_load_3d(sa, &tmA, bar_full, 0, j0, bt);
         } else {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, full, j0 + 64 * h, bt, 0);
-            else tma_load_3d(sa + h * 8192, &tmA, full, j0 + 64 * h, 0, bt);
+            if (p.a_swap) tma_load_3d(sa + h * 8192, &tmA, bar_full, j0 + 64 * h, bt, 0);
+            else tma_load_3d(sa + h * 8192, &tmA, bar_full, j0 + 64 * h, 0, bt);
           }
         }
         if (!p.b_mn) {
-          // boxes of 64 x min(256, L) key rows
-          for (int c = 0; c < nchunk; ++c) {
-            if (p.b_swap) tma_load_3d(sb_ + c * 32768, &tmB, full, 0, bt, c * 256);
-            else tma_load_3d(sb_ + c * 32768, &tmB, full, 0, c * 256, bt);
+          for (int c = 0; c < nchunk; ++c) {  // boxes of 64 x min(256, L) key rows
+            if (p.b_swap) tma_load_3d(sb_ + c * 32768, &tmB, bar_full, 0, bt, c * 256);
+            else tma_load_3d(sb_ + c * 32768, &tmB, bar_full, 0, c * 256, bt);
           }
         } else {
           for (int h = 0; h < L / 64; ++h) {
-            if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, full, 64 * h, bt, 0);
-            else tma_load_3d(sb_ + h * 8192, &tmB, full, 64 * h, 0, bt);
+            if (p.b_swap) tma_load_3d(sb_ + h * 8192, &tmB, bar_full, 64 * h, bt, 0);
+            else tma_load_3d(sb_ + h * 8192, &tmB, bar_full, 64 * h, 0, bt);
           }
         }
       }
@@ -150,16 +202,14 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
-      const int s = it % S;
-      const uint32_t ph = (it / S) & 1u;
       // tensor memory holds one tile: the previous tile must have been read out completely
       ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty, (it & 1u) ^ 1u, 4));
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_full, it & 1u, 2));
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t sa = tiles + s * kStageBytes, sb_ = sa + kABytes;
+        const uint32_t sa = operands, sb_ = sa + kABytes;
         for (int c = 0; c < nchunk; ++c) {
           const int width = min(256, L - c * 256);
           const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) | ((uint32_t)(p.b_mn ? 1 : 0) << 16) |
@@ -171,255 +221,306 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             umma_f16(tmem_base + c * 256, da, db, idesc, k > 0 ? 1u : 0u);
           }
         }
-        umma_commit(bar_empty + 8 * s);
+        umma_commit(bar_empty);   // the operand buffer may be refilled for the next tile
         umma_commit(bar_tfull);
       }
       __syncwarp();
     }
   } else {
-    // ---------------- softmax / epilogue: thread = one query row ----------------
-    const int q = warp & 3;
-    const uint32_t my_stage = staging + (uint32_t)(warp - 2) * kStagingPerWarp;
-    uint8_t* my_stage_gen = gen_base + S * kStageBytes + (warp - 2) * kStagingPerWarp;
+    // ---------------- softmax / epilogue warps: thread = one query row ----------------
+    const int ew = warp - 2;
+    const int q = warp & 3;               // tensor-memory quadrant this warp may access
+    const int h = ew >> 2;                // which of the quadrant's warps: chunks h, h + kNW, ...
+    const int rt = q * 32 + lane;         // row within the tile
+    const int nc64 = L / 64;
+    const uint32_t my_stage = staging + (uint32_t)ew * NB * 4096;
+    uint8_t* my_stage_gen = gen_base + (my_stage - operands);
+    const uint32_t my_in = inslots + (uint32_t)ew * C::kInSlot;
+    const uint8_t* my_in_gen = gen_base + (my_in - operands);
+    const uint32_t my_bar = bar_in + 8 * ew;
     const float c2 = p.scale * 1.4426950408889634f;
-    uint32_t it = 0, ngroup = 0;
+    const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
+    const long long G = gridDim.x;
+
+    auto tile_has_rows = [&](long long t) { return (int)(t % p.tiles_j) * 128 + q * 32 < L; };
+    // fetch the row inputs of chunk c of tile t into this warp's slot (lane 0)
+    auto fetch_in = [&](long long t, int c) {
+      const int jr = (int)(t % p.tiles_j) * 128 + q * 32;
+      const int bt = (int)(t / p.tiles_j);
+      mbar_expect_tx(my_bar, (uint32_t)C::kInSlot);
+      if (BWD) {
+        if (p.swap_o) tma_load_3d(my_in, &tmI, my_bar, c * 64, bt, jr);
+        else tma_load_3d(my_in, &tmI, my_bar, c * 64, jr, bt);
+      }
+      const uint32_t md = my_in + (BWD ? 4096u : 0u);
+      if (p.swap_o) tma_load_3d(md, &tmM, my_bar, c * 64, bt, jr);
+      else tma_load_3d(md, &tmM, my_bar, c * 64, jr, bt);
+    };
+    // successor of (t, c) in this warp's sequence of input chunks
+    auto next_in = [&](long long& t, int& c) {
+      c += kNW;
+      if (c < nc64) return true;
+      c = h;
+      for (t += G; t < p.tiles; t += G)
+        if (tile_has_rows(t)) return true;
+      return false;
+    };
+    uint32_t n_in = 0;    // input chunks consumed (slot phase)
+    uint32_t n_out = 0;   // staging buffers filled (buffer = n_out % NB)
+    uint32_t n_bar = 0;   // uses of the epilogue barrier
+    if (mask_in && h < nc64 && lane == 0) {
+      long long t0 = blockIdx.x;
+      while (t0 < p.tiles && !tile_has_rows(t0)) t0 += G;
+      if (t0 < p.tiles) fetch_in(t0, h);
+    }
+
+    // staging: 16-byte piece i (0..7) of this thread's row in buffer b
+    auto stage_ptr = [&](uint32_t b, int i) {
+      return reinterpret_cast<uint4*>(my_stage_gen + b * 4096 + lane * 128 + ((i ^ (lane & 7)) << 4));
+    };
+    auto store_rows = [&](const CUtensorMap* map, uint32_t b, int c, int jr, int bt) {
+      if (p.swap_o) tma_store_3d(map, my_stage + b * 4096, c * 64, bt, jr);
+      else tma_store_3d(map, my_stage + b * 4096, c * 64, jr, bt);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    };
+
+    uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += G, ++it) {
       const int j0 = (int)(t % p.tiles_j) * 128;
-      const long long bt = t / p.tiles_j;
+      const int bt = (int)(t / p.tiles_j);
+      const int jr = j0 + q * 32;                          // first row of this warp
+      const bool rows = jr < L && h < nc64;                // warp-uniform: this warp has work in the tile
+      const long long row_off = ((long long)bt * L + (jr + lane)) * (long long)L;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull, it & 1u, 3));
-      if (!ok) break;
+      if (!ok) break;   // every epilogue warp waits on the same barrier and gives up with it
       tc_fence_after();
-      const int jr = j0 + q * 32;                    // first row of this warp
-      const int j = jr + lane;                       // this thread's row
-      const bool row_ok = j < L;
-      const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
-      const long long row_off = (bt * L + (row_ok ? j : 0)) * (long long)L;   // element offset of the row
-      const int nc64 = L / 64;
 
       if (!BWD) {
-        // pass 1: row maximum of t = acc * scale * log2(e)
+        // pass 1: row maximum of the raw accumulator (scale > 0)
         float mx = -INFINITY;
-        for (int c = 0; c < nc64; ++c) {
-          uint32_t r[64];
-          tmem_ld32_nowait(trow + c * 64, r);
-          tmem_ld32_nowait(trow + c * 64 + 32, r + 32);
-          tmem_ld_wait();
+        if (rows)
+          sweep(trow, h, nc64, [&](int, int, uint32_t* r) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(r[e]) * c2);
-        }
-        // pass 2: e = 2^(t - max) back into tensor memory, row sum, BETA out
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+          });
+        red_gen[h * 128 + rt] = mx;
+        ok = epi_barrier(bar_epi, n_bar, lane) && ok;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) mx = fmaxf(mx, red_gen[w * 128 + rt]);
+        const float mxs = mx * c2;
+        // pass 2: e = 2^(t - max) back into tensor memory, partial row sum, BETA out
         float sum = 0.f;
-        for (int c = 0; c < nc64; ++c) {
-          uint32_t r[64];
-          tmem_ld32_nowait(trow + c * 64, r);
-          tmem_ld32_nowait(trow + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-          uint4 beta[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float a = __uint_as_float(r[v * 8 + e]);
-              f[e] = a * p.scale;
-              const float ex = exp2f(fmaf(a, c2, -mx));
-              sum += ex;
-              r[v * 8 + e] = __float_as_uint(ex);
+        if (rows)
+          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+            const uint32_t b = n_out % NB;
+            if (hh == 0) {
+              if (lane == 0) bulk_wait_read<NB - 1>();
+              __syncwarp();
             }
-            beta[v] = pack8(f);
-          }
-          tmem_st32(trow + c * 64, r);
-          tmem_st32(trow + c * 64 + 32, r + 32);
-          const uint32_t sbuf = ngroup & 1u;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          stage_row64(my_stage_gen + sbuf * 4096 + lane * 128, lane, beta);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            if (jr < L) {
-              if (p.swap_o) tma_store_3d(&tmO0, my_stage + sbuf * 4096, c * 64, (int)bt, jr);
-              else tma_store_3d(&tmO0, my_stage + sbuf * 4096, c * 64, jr, (int)bt);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float a = __uint_as_float(r[v * 8 + e]);
+                f[e] = a * p.scale;
+                const float ex = exp2f(fmaf(a, c2, -mxs));
+                sum += ex;
+                r[v * 8 + e] = __float_as_uint(ex);
+              }
+              *stage_ptr(b, hh * 4 + v) = pack8(f);
             }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-          ++ngroup;
-        }
+            tmem_st32(trow + c * 64 + hh * 32, r);
+            if (hh == 1) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) store_rows(&tmO0, b, c, jr, bt);
+              ++n_out;
+            }
+          });
         tmem_st_wait();
+        red_gen[(kNW + h) * 128 + rt] = sum;
+        ok = epi_barrier(bar_epi, n_bar, lane) && ok;
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) sum += red_gen[(kNW + w) * 128 + rt];
         const float inv = 1.f / sum;
         // pass 3: ALPHA = e / sum, ATTN_DROP = mask * ALPHA
-        for (int c = 0; c < nc64; ++c) {
-          uint4 mraw[4];
-          if (!p.rng.philox && row_ok) {
-            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row_off + c * 64);
+        if (rows)
+          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+            // mask bytes of this thread's 32 columns, as 8 words
+            uint32_t mw[8];
+            if (!p.rng.philox) {
+              if (hh == 0) ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
+              if (ok) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) mraw[i] = mp[i];
-          }
-          uint32_t r[64];
-          tmem_ld32_nowait(trow + c * 64, r);
-          tmem_ld32_nowait(trow + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-          if (c == nc64 - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty);
-          }
-          if (p.rng.philox) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              uint32_t mm[8];
-              philox_keep8(p.rng, (unsigned long long)(row_off + c * 64 + v * 8) >> 3, mm);
-              const uint2 pk = mask_pack(mm);
-              reinterpret_cast<uint32_t*>(mraw)[2 * v] = pk.x;
-              reinterpret_cast<uint32_t*>(mraw)[2 * v + 1] = pk.y;
-            }
-            if (row_ok) {
-              uint4* mp = reinterpret_cast<uint4*>(p.mask + row_off + c * 64);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) mp[i] = mraw[i];
-            }
-          }
-          uint4 al[8], dr[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * inv;
-            al[v] = pack8(f);
-            const uint2 mk = make_uint2(reinterpret_cast<const uint32_t*>(mraw)[2 * v],
-                                        reinterpret_cast<const uint32_t*>(mraw)[2 * v + 1]);
-            dr[v] = mask_apply(al[v], mk);
-          }
-          const uint32_t sbuf = ngroup & 1u;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          stage_row64(my_stage_gen + sbuf * 4096 + lane * 128, lane, al);
-          stage_row64(my_stage_gen + (2 + sbuf) * 4096 + lane * 128, lane, dr);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            if (jr < L) {
-              if (p.swap_o) {
-                tma_store_3d(&tmO1, my_stage + sbuf * 4096, c * 64, (int)bt, jr);
-                tma_store_3d(&tmO2, my_stage + (2 + sbuf) * 4096, c * 64, (int)bt, jr);
+                for (int i = 0; i < 2; ++i) {
+                  const uint4 m = *reinterpret_cast<const uint4*>(my_in_gen + lane * 64 + (((hh * 2 + i) ^ ((lane >> 1) & 3)) << 4));
+                  mw[4 * i] = m.x; mw[4 * i + 1] = m.y; mw[4 * i + 2] = m.z; mw[4 * i + 3] = m.w;
+                }
               } else {
-                tma_store_3d(&tmO1, my_stage + sbuf * 4096, c * 64, jr, (int)bt);
-                tma_store_3d(&tmO2, my_stage + (2 + sbuf) * 4096, c * 64, jr, (int)bt);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mw[i] = 0;
+              }
+              if (hh == 1) {
+                // the slot has been read: fetch this warp's next chunk into it
+                ++n_in;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0 && ok) {
+                  long long tn = t;
+                  int cn = c;
+                  if (next_in(tn, cn)) fetch_in(tn, cn);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t mm[8];
+                philox_keep8(p.rng, (unsigned long long)(row_off + c * 64 + hh * 32 + v * 8) >> 3, mm);
+                const uint2 pk = mask_pack(mm);
+                mw[2 * v] = pk.x;
+                mw[2 * v + 1] = pk.y;
+              }
+              uint4* mp = reinterpret_cast<uint4*>(p.mask + row_off + c * 64 + hh * 32);
+              mp[0] = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+              mp[1] = make_uint4(mw[4], mw[5], mw[6], mw[7]);
+            }
+            const uint32_t b0 = n_out % NB, b1 = (n_out + 1) % NB;
+            if (hh == 0) {
+              if (lane == 0) bulk_wait_read<NB - 2>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * inv;
+              const uint4 al = pack8(f);
+              *stage_ptr(b0, hh * 4 + v) = al;
+              *stage_ptr(b1, hh * 4 + v) = mask_apply(al, make_uint2(mw[2 * v], mw[2 * v + 1]));
+            }
+            if (hh == 1) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                store_rows(&tmO1, b0, c, jr, bt);
+                store_rows(&tmO2, b1, c, jr, bt);
+              }
+              n_out += 2;
+            }
+          });
+      } else {
+        // backward pass 1: DATTN_DROP out; (da, alpha) with da = mask * DATTN_DROP kept as an fp16
+        // pair per tensor-memory word; partial s = sum da * alpha
+        float ssum = 0.f;
+        if (rows)
+          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+            if (hh == 0) ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
+            uint4 araw[4];
+            uint32_t mw[8];
+            if (ok) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                araw[i] = *reinterpret_cast<const uint4*>(my_in_gen + lane * 128 + (((hh * 4 + i) ^ (lane & 7)) << 4));
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const uint4 m = *reinterpret_cast<const uint4*>(my_in_gen + 4096 + lane * 64 +
+                                                                (((hh * 2 + i) ^ ((lane >> 1) & 3)) << 4));
+                mw[4 * i] = m.x; mw[4 * i + 1] = m.y; mw[4 * i + 2] = m.z; mw[4 * i + 3] = m.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) araw[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) mw[i] = 0;
+            }
+            if (hh == 1) {
+              ++n_in;
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0 && ok) {
+                long long tn = t;
+                int cn = c;
+                if (next_in(tn, cn)) fetch_in(tn, cn);
               }
             }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-          ++ngroup;
-        }
-      } else {
-        // backward pass 1: da = mask * acc (kept in tensor memory), s = sum da * alpha, DATTN_DROP out
-        float ssum = 0.f;
-        for (int c = 0; c < nc64; ++c) {
-          uint4 mraw[4], araw[8];
-          if (row_ok) {
-            const uint4* mp = reinterpret_cast<const uint4*>(p.mask + row_off + c * 64);
-            const uint4* ap = reinterpret_cast<const uint4*>(p.alpha + row_off + c * 64);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) mraw[i] = mp[i];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) araw[i] = ap[i];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) mraw[i] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) araw[i] = make_uint4(0, 0, 0, 0);
-          }
-          uint32_t r[64];
-          tmem_ld32_nowait(trow + c * 64, r);
-          tmem_ld32_nowait(trow + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-          uint4 dad[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            float f[8], a8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]);
-            dad[v] = pack8(f);   // DATTN_DROP as stored (fp16)
-            const uint2 mk = make_uint2(reinterpret_cast<const uint32_t*>(mraw)[2 * v],
-                                        reinterpret_cast<const uint32_t*>(mraw)[2 * v + 1]);
-            // continue from the fp16 value, as the separate softmax-backward operator would
-            unpack8(mask_apply(dad[v], mk), f);
-            unpack8(araw[v], a8);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              ssum = fmaf(f[e], a8[e], ssum);
-              r[v * 8 + e] = __float_as_uint(f[e]);
+            const uint32_t b = n_out % NB;
+            if (hh == 0) {
+              if (lane == 0) bulk_wait_read<NB - 1>();
+              __syncwarp();
             }
-          }
-          tmem_st32(trow + c * 64, r);
-          tmem_st32(trow + c * 64 + 32, r + 32);
-          const uint32_t sbuf = ngroup & 1u;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          stage_row64(my_stage_gen + sbuf * 4096 + lane * 128, lane, dad);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            if (jr < L) {
-              if (p.swap_o) tma_store_3d(&tmO0, my_stage + sbuf * 4096, c * 64, (int)bt, jr);
-              else tma_store_3d(&tmO0, my_stage + sbuf * 4096, c * 64, jr, (int)bt);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8], a8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]);
+              const uint4 dad = pack8(f);   // DATTN_DROP as stored (fp16)
+              *stage_ptr(b, hh * 4 + v) = dad;
+              // continue from the fp16 value, as the separate softmax-backward operator would
+              const uint4 da = mask_apply(dad, make_uint2(mw[2 * v], mw[2 * v + 1]));
+              unpack8(da, f);
+              unpack8(araw[v], a8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) ssum = fmaf(f[e], a8[e], ssum);
+              const uint32_t dw[4] = {da.x, da.y, da.z, da.w}, aw[4] = {araw[v].x, araw[v].y, araw[v].z, araw[v].w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                r[v * 8 + 2 * k] = __byte_perm(dw[k], aw[k], 0x5410);      // (da, alpha) of the even element
+                r[v * 8 + 2 * k + 1] = __byte_perm(dw[k], aw[k], 0x7632);  // ... of the odd element
+              }
             }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-          ++ngroup;
-        }
+            tmem_st32(trow + c * 64 + hh * 32, r);
+            if (hh == 1) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) store_rows(&tmO0, b, c, jr, bt);
+              ++n_out;
+            }
+          });
         tmem_st_wait();
+        red_gen[h * 128 + rt] = ssum;
+        ok = epi_barrier(bar_epi, n_bar, lane) && ok;
+        ssum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) ssum += red_gen[w * 128 + rt];
         // backward pass 2: DBETA = alpha * (da - s)
-        for (int c = 0; c < nc64; ++c) {
-          uint4 araw[8];
-          if (row_ok) {
-            const uint4* ap = reinterpret_cast<const uint4*>(p.alpha + row_off + c * 64);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) araw[i] = ap[i];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) araw[i] = make_uint4(0, 0, 0, 0);
-          }
-          uint32_t r[64];
-          tmem_ld32_nowait(trow + c * 64, r);
-          tmem_ld32_nowait(trow + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-          if (c == nc64 - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty);
-          }
-          uint4 db[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            float f[8], a8[8];
-            unpack8(araw[v], a8);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = a8[e] * (__uint_as_float(r[v * 8 + e]) - ssum);
-            db[v] = pack8(f);
-          }
-          const uint32_t sbuf = ngroup & 1u;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          stage_row64(my_stage_gen + sbuf * 4096 + lane * 128, lane, db);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            if (jr < L) {
-              if (p.swap_o) tma_store_3d(&tmO1, my_stage + sbuf * 4096, c * 64, (int)bt, jr);
-              else tma_store_3d(&tmO1, my_stage + sbuf * 4096, c * 64, jr, (int)bt);
+        if (rows)
+          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+            const uint32_t b = n_out % NB;
+            if (hh == 0) {
+              if (lane == 0) bulk_wait_read<NB - 1>();
+              __syncwarp();
             }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-          ++ngroup;
-        }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float2 da_al = __half22float2(*reinterpret_cast<const __half2*>(&r[v * 8 + e]));
+                f[e] = da_al.y * (da_al.x - ssum);
+              }
+              *stage_ptr(b, hh * 4 + v) = pack8(f);
+            }
+            if (hh == 1) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) store_rows(&tmO1, b, c, jr, bt);
+              ++n_out;
+            }
+          });
       }
+      // this warp's reads of the tile are complete: tensor memory may take the next one
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty);
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
   }
   if (*reinterpret_cast<volatile int*>(&g_tc_error) != 0) {
+    // a wait ran out somewhere: give copies still in flight time to land before the CTA retires
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
   }

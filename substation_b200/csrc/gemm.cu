@@ -676,17 +676,20 @@ struct OperandMap {
   int swap;  // dims 1 and 2 exchanged
 };
 
-// 3-D fp16 tensor map with 128-byte swizzle over dims (inner, d1, d2) with element strides
-// (1, s1, s2) and box (b0, b1, 1); dims 1 and 2 are exchanged when needed to keep strides increasing.
+// 3-D tensor map over dims (inner, d1, d2) with element strides (1, s1, s2) and box (b0, b1, 1);
+// dims 1 and 2 are exchanged when needed to keep strides increasing.  fp16 elements with 128-byte
+// swizzle, or (bytes = true) single bytes with 64-byte swizzle.
 bool encode_map(const void* ptr, cuuint64_t n0, cuuint64_t n1, cuuint64_t n2, long long s1, long long s2,
-                cuuint32_t b0, cuuint32_t b1, CUtensorMap* map, int* swapped, std::string* why) {
+                cuuint32_t b0, cuuint32_t b1, CUtensorMap* map, int* swapped, std::string* why, bool bytes = false) {
+  const long long esize = bytes ? 1 : 2;
   if (reinterpret_cast<uintptr_t>(ptr) & 15u) { *why = "base is not 16-byte aligned"; return false; }
   cuuint64_t dim[3] = {n0, n1, n2};
   long long str[3] = {1, s1, s2};
   cuuint32_t box[3] = {b0, b1, 1};
   // extent-1 dims: any legal stride (a multiple of 8 elements)
-  if (dim[1] == 1) str[1] = ((long long)dim[0] + 7) / 8 * 8;
-  if (dim[2] == 1) str[2] = std::max(str[1] * (long long)dim[1], ((long long)dim[0] + 7) / 8 * 8);
+  const long long unit = 16 / esize;
+  if (dim[1] == 1) str[1] = ((long long)dim[0] + unit - 1) / unit * unit;
+  if (dim[2] == 1) str[2] = std::max(str[1] * (long long)dim[1], ((long long)dim[0] + unit - 1) / unit * unit);
   *swapped = 0;
   if (str[2] < str[1]) {
     std::swap(dim[1], dim[2]);
@@ -695,13 +698,14 @@ bool encode_map(const void* ptr, cuuint64_t n0, cuuint64_t n1, cuuint64_t n2, lo
     *swapped = 1;
   }
   for (int i = 1; i < 3; ++i)
-    if (str[i] <= 0 || (str[i] * 2) % 16 != 0) { *why = "stride is not a positive multiple of 16 bytes"; return false; }
+    if (str[i] <= 0 || (str[i] * esize) % 16 != 0) { *why = "stride is not a positive multiple of 16 bytes"; return false; }
   for (int i = 0; i < 3; ++i)
     if (dim[i] == 0 || dim[i] > 0xffffffffull) { *why = "extent out of range"; return false; }
-  cuuint64_t gstr[2] = {(cuuint64_t)str[1] * 2, (cuuint64_t)str[2] * 2};
+  cuuint64_t gstr[2] = {(cuuint64_t)(str[1] * esize), (cuuint64_t)(str[2] * esize)};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dim, gstr, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUresult r = g_encode(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                              const_cast<void*>(ptr), dim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              bytes ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled rejected it (code " + std::to_string((int)r) + ")"; return false; }
   return true;
@@ -977,7 +981,7 @@ bool dense_scores(const View4& v, const Dims4& d) {
 template <bool BWD>
 int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long long aP, long long aH, long long aB,
                        long long aJ, const void* b_ptr, long long bP, long long bH, long long bB, long long bJ,
-                       void* o0, void* o1, void* o2, attn::Params p) {
+                       void* o0, void* o1, void* o2, const void* alpha_in, const void* mask_in, attn::Params p) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const int L = d.K;
@@ -994,22 +998,29 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
   const int brows = std::min(256, L);
   if (!make_operand_map(b_ptr, L, P, batch, bJ, bP, sBb, brows, &b, &why))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores, second operand: " + why);
-  CUtensorMap m0, m1, m2;
+  CUtensorMap m0, m1, m2, mi, mm;
   memset(&m2, 0, sizeof(m2));
-  int sw0 = 0, sw1 = 0, sw2 = 0;
+  memset(&mi, 0, sizeof(mi));
+  memset(&mm, 0, sizeof(mm));
+  int sw0 = 0, sw1 = 0, sw2 = 0, swi = 0, swm = 0;
   if (!encode_map(o0, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m0, &sw0, &why) ||
       !encode_map(o1, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m1, &sw1, &why) ||
       (o2 && !encode_map(o2, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m2, &sw2, &why)))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores, output: " + why);
+  if ((alpha_in && !encode_map(alpha_in, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &mi, &swi, &why)) ||
+      (mask_in && !encode_map(mask_in, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &mm, &swm, &why, true)))
+    return fail(SB_ERR_UNSUPPORTED, "fused attention scores, row inputs: " + why);
   p.L = L;
   p.tiles_j = (L + 127) / 128;
   p.tiles = (long long)p.tiles_j * batch;
   p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
   p.swap_o = sw0;
   p.b_bytes = b.mn ? L * 128 : ((L + 255) / 256) * brows * 128;
-  SB_CUDA_OK(cudaFuncSetAttribute(attn::attn_scores_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemBytes));
+  constexpr int smem = attn::Cfg<BWD>::kSmemBytes;
+  static_assert(smem <= 232448, "shared memory of the fused attention kernel");
+  SB_CUDA_OK(cudaFuncSetAttribute(attn::attn_scores_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
-  SB_LAUNCH_OK(launch_k(attn::attn_scores_kernel<BWD>, grid, kTcThreads, attn::kSmemBytes, s, a.map, b.map, m0, m1, m2, p));
+  SB_LAUNCH_OK(launch_k(attn::attn_scores_kernel<BWD>, grid, attn::kThreads, smem, s, a.map, b.map, m0, m1, m2, mi, mm, p));
   return SB_OK;
 }
 
@@ -1020,14 +1031,14 @@ int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, V
   if ((long long)d.H * d.B * d.J == 0) return SB_OK;
   if (!dense_scores(beta, d) || !dense_scores(alpha, d) || !dense_scores(drop, d) || !dense_scores(mask, d))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores need score tensors dense as [H,B,J,K]");
+  if (!(scale > 0.f)) return fail(SB_ERR_UNSUPPORTED, "fused attention scores need a positive scale");
   attn::Params p{};
   p.scale = scale;
   p.rng = rng;
   p.mask = reinterpret_cast<uint8_t*>(mask.p);
-  p.alpha = nullptr;
   // projections arrive as [P,H,B,rows] views: sH/sB/sJ/sK of the View4 hold the P,H,B,row strides
   return launch_attn_scores<false>(s, d, P, qq.p, qq.sH, qq.sB, qq.sJ, qq.sK, kk.p, kk.sH, kk.sB, kk.sJ, kk.sK, beta.p,
-                                   alpha.p, drop.p, p);
+                                   alpha.p, drop.p, nullptr, rng.philox ? nullptr : mask.p, p);
 }
 
 int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 vv, View4 alpha, View4 mask,
@@ -1038,9 +1049,8 @@ int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 v
   attn::Params p{};
   p.scale = 1.f;
   p.mask = reinterpret_cast<uint8_t*>(mask.p);
-  p.alpha = reinterpret_cast<const __half*>(alpha.p);
   return launch_attn_scores<true>(s, d, P, dgamma.p, dgamma.sH, dgamma.sB, dgamma.sJ, dgamma.sK, vv.p, vv.sH, vv.sB,
-                                  vv.sJ, vv.sK, dattn_drop.p, dbeta.p, nullptr, p);
+                                  vv.sJ, vv.sK, dattn_drop.p, dbeta.p, nullptr, alpha.p, mask.p, p);
 }
 
 int gemm_device_error(cudaStream_t s, int* code) {
