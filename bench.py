@@ -66,6 +66,7 @@ FUSED_BYTES = {
     # fused LayerNorm-backward passes: inputs once, outputs once
     'bsb+blnrd1': lambda B, L: 13 * B * L * E, 'ebsb+blnrd2+baob': lambda B, L: 17 * B * L * E,
     # fused attention scores: projections in, mask in, BETA/ALPHA/ATTN_DROP (resp. ALPHA in, DATTN_DROP/DBETA) out
+    'dX1QKT+dX2QKT': lambda B, L: H * B * (2 * L * L + 8 * P * L),
     'QKT+softmax': lambda B, L: H * B * (4 * P * L + 7 * L * L), 'dX1gamma+bs': lambda B, L: H * B * (4 * P * L + 7 * L * L),
 }
 

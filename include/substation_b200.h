@@ -215,6 +215,19 @@ int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, 
                                          const sb_tensor* alpha, const sb_tensor* mask,
                                          const sb_tensor* dattn_drop, const sb_tensor* dbeta);
 
+/* Contractions of a score tensor with head-size-64 projections, reading the scores once:
+ *   out_rows[p,h,b,j] = alpha * sum_k scores[h,b,j,k] * x[p,h,b,k]   (x and out_rows both NULL to skip)
+ *   out_cols[p,h,b,k] = alpha * sum_j scores[h,b,j,k] * y[p,h,b,j]   (y and out_cols both NULL to skip)
+ * One CTA per (head, sample) keeps x and y in shared memory and streams the scores through
+ * tcgen05 MMAs for both results.  scores: [H,B,J,K] dense in that order; projections [P,H,B,J]
+ * with any strides TMA can address.  Needs P = 64, J = K a multiple of 128 and at most 512;
+ * otherwise SB_ERR_UNSUPPORTED and the caller runs sb_einsum.  Replaces the contractions
+ * gamma (pytorch_module/encoder.cu:121-123), dX2gamma (:247-249) and the pair dX1QKT, dX2QKT
+ * (:262-267), the pair as one launch. */
+int sb_attention_score_contractions(void* stream, const sb_tensor* scores, const sb_tensor* x,
+                                    const sb_tensor* out_rows, const sb_tensor* y, const sb_tensor* out_cols,
+                                    float alpha);
+
 /* dbeta = alpha*(da - sum_k da*alpha), da = mask*dattn_drop.  All [H,B,J,K].
  * Replaces BackwardSoftmax::run, pytorch_module/block_bs.cuh:100-156. */
 int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,

@@ -71,6 +71,7 @@ SIGNATURES = {
     'sb_backward_attn_out_bias_noalloc': (c_int, [c_void_p, _T, _T]),
     'sb_attention_scores_softmax': (c_int, [c_void_p, _T, _T, _T, _T, _T, _T, c_float, _D]),
     'sb_attention_scores_softmax_backward': (c_int, [c_void_p, _T, _T, _T, _T, _T, _T]),
+    'sb_attention_score_contractions': (c_int, [c_void_p, _T, _T, _T, _T, _T, c_float]),
     'sb_backward_softmax': (c_int, [c_void_p, _T, _T, _T, _T]),
     'sb_backward_attention_input_biases': (c_int, [c_void_p, _T, _T]),
     'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),

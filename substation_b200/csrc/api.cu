@@ -236,6 +236,31 @@ extern "C" int sb_attention_scores_softmax_backward(void* stream, const sb_tenso
   return launch_attn_scores_bwd((cudaStream_t)stream, dims4(alpha), P, vg, vvv, va, vm, vd, vo);
 }
 
+extern "C" int sb_attention_score_contractions(void* stream, const sb_tensor* scores, const sb_tensor* x,
+                                               const sb_tensor* out_rows, const sb_tensor* y,
+                                               const sb_tensor* out_cols, float alpha) {
+  View4 vs, vx, vr, vy, vc;
+  if ((x == nullptr) != (out_rows == nullptr) || (y == nullptr) != (out_cols == nullptr))
+    return fail(SB_ERR_ARG, "score_contractions: an operand and its output are given together or not at all");
+  SB_TRY(to_view4(scores, nullptr, false, "score_contractions.scores", &vs));
+  if (scores->size[2] != scores->size[3]) return fail(SB_ERR_UNSUPPORTED, "score_contractions: self-attention only");
+  int P = 64, Pi = 0;
+  if (x) {
+    SB_TRY(to_proj(x, scores, "score_contractions.x", &vx, &P));
+    SB_TRY(to_proj(out_rows, scores, "score_contractions.out_rows", &vr, &Pi));
+    if (P != Pi) return fail(SB_ERR_ARG, "score_contractions: head size differs between operands");
+  }
+  if (y) {
+    SB_TRY(to_proj(y, scores, "score_contractions.y", &vy, &Pi));
+    if (x && P != Pi) return fail(SB_ERR_ARG, "score_contractions: head size differs between operands");
+    P = Pi;
+    SB_TRY(to_proj(out_cols, scores, "score_contractions.out_cols", &vc, &Pi));
+    if (P != Pi) return fail(SB_ERR_ARG, "score_contractions: head size differs between operands");
+  }
+  return launch_score_contract((cudaStream_t)stream, dims4(scores), P, vs, x ? &vx : nullptr, x ? &vr : nullptr,
+                               y ? &vy : nullptr, y ? &vc : nullptr, alpha);
+}
+
 extern "C" int sb_backward_softmax(void* stream, const sb_tensor* alpha, const sb_tensor* mask,
                                    const sb_tensor* dattn_drop, const sb_tensor* dbeta) {
   View4 va, vm, vg, vo;
@@ -779,8 +804,21 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
       SB_TRY(sb_softmax_dropout(stream, &beta, &alpha, &mask, &dr, 1.f, &d));
     }
   }
-  SB_TRY(einsum(e, s, "gamma", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 2), L.at("ATTN_DROP"), T["ATTN_DROP"],
-                L.at("GAMMA"), T["GAMMA"], 1.f));
+  {
+    // one CTA per (head, sample) streams ATTN_DROP once; short sequences keep the batched contraction
+    int st = SB_ERR_UNSUPPORTED;
+    if (e->fuse && e->S >= 256) {
+      e->mark(s, "gamma");
+      sb_tensor sc = e->view(T["ATTN_DROP"], "ATTN_DROP"), vv = e->view(q_slice("KKQQVV", 2), lKK, "PHBJ");
+      sb_tensor gm = e->view(T["GAMMA"], "GAMMA");
+      st = sb_attention_score_contractions(stream, &sc, &vv, &gm, nullptr, nullptr, 1.f);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+      if (st == SB_ERR_UNSUPPORTED) e->unmark();
+    }
+    if (st == SB_ERR_UNSUPPORTED)
+      SB_TRY(einsum(e, s, "gamma", rename(lKK, 'J', 'K'), q_slice("KKQQVV", 2), L.at("ATTN_DROP"), T["ATTN_DROP"],
+                    L.at("GAMMA"), T["GAMMA"], 1.f));
+  }
   SB_TRY(einsum(e, s, "out", L.at("WO"), T["WO"], L.at("GAMMA"), T["GAMMA"], L.at("ATT"), T["ATT"], 1.f));
   {
     e->mark(s, "bdrln1");
@@ -915,15 +953,41 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
     if (st == SB_ERR_UNSUPPORTED)
       SB_TRY(einsum(e, s, "dX1gamma", rename(lKK, 'J', 'K'), VV, L.at("DGAMMA"), T["DGAMMA"], L.at("DATTN_DROP"),
                     T["DATTN_DROP"], 1.f));
-    SB_TRY(einsum(e, s, "dX2gamma", L.at("DGAMMA"), T["DGAMMA"], L.at("ATTN_DROP"), T["ATTN_DROP"],
-                  rename(lDKK, 'J', 'K'), DVV, 1.f));
+    {
+      int st2 = SB_ERR_UNSUPPORTED;
+      if (e->fuse && e->S >= 256) {
+        e->mark(s, "dX2gamma");
+        sb_tensor sc = e->view(T["ATTN_DROP"], "ATTN_DROP"), dgm = e->view(T["DGAMMA"], "DGAMMA");
+        sb_tensor dvv = e->view(DVV, lDKK, "PHBJ");
+        st2 = sb_attention_score_contractions(stream, &sc, nullptr, nullptr, &dgm, &dvv, 1.f);
+        if (st2 != SB_OK && st2 != SB_ERR_UNSUPPORTED) return st2;
+        if (st2 == SB_ERR_UNSUPPORTED) e->unmark();
+      }
+      if (st2 == SB_ERR_UNSUPPORTED)
+        SB_TRY(einsum(e, s, "dX2gamma", L.at("DGAMMA"), T["DGAMMA"], L.at("ATTN_DROP"), T["ATTN_DROP"],
+                      rename(lDKK, 'J', 'K'), DVV, 1.f));
+    }
     if (st == SB_ERR_UNSUPPORTED) {
       e->mark(s, "bs");
       SB_TRY(sb_backward_softmax(stream, &alpha, &mask, &g, &o));
     }
   }
-  SB_TRY(einsum(e, s, "dX1QKT", rename(lKK, 'J', 'K'), KK, L.at("DBETA"), T["DBETA"], lDKK, DQQ, scale));
-  SB_TRY(einsum(e, s, "dX2QKT", lKK, QQ, L.at("DBETA"), T["DBETA"], rename(lDKK, 'J', 'K'), DKK, scale));
+  {
+    // both projection gradients from one pass over DBETA
+    int st = SB_ERR_UNSUPPORTED;
+    if (e->fuse && e->S >= 256) {
+      e->mark(s, "dX1QKT+dX2QKT");
+      sb_tensor sc = e->view(T["DBETA"], "DBETA"), kk = e->view(KK, lKK, "PHBJ"), qq = e->view(QQ, lKK, "PHBJ");
+      sb_tensor dqq = e->view(DQQ, lDKK, "PHBJ"), dkk = e->view(DKK, lDKK, "PHBJ");
+      st = sb_attention_score_contractions(stream, &sc, &kk, &dqq, &qq, &dkk, scale);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+      if (st == SB_ERR_UNSUPPORTED) e->unmark();
+    }
+    if (st == SB_ERR_UNSUPPORTED) {
+      SB_TRY(einsum(e, s, "dX1QKT", rename(lKK, 'J', 'K'), KK, L.at("DBETA"), T["DBETA"], lDKK, DQQ, scale));
+      SB_TRY(einsum(e, s, "dX2QKT", lKK, QQ, L.at("DBETA"), T["DBETA"], rename(lDKK, 'J', 'K'), DKK, scale));
+    }
+  }
   SB_TRY(einsum(e, s, "dXQKV-fused", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
                 T["DXATT"], 1.f));
   SB_TRY(einsum(e, s, "dWQKV-fused", L.at("X"), T["X"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("WKQV"),

@@ -657,6 +657,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
 
 #include "gemm_pair.cuh"
 #include "attn_fused.cuh"
+#include "score_contract.cuh"
 
 // ---- host side ------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -1051,6 +1052,59 @@ int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 v
   p.mask = reinterpret_cast<uint8_t*>(mask.p);
   return launch_attn_scores<true>(s, d, P, dgamma.p, dgamma.sH, dgamma.sB, dgamma.sJ, dgamma.sK, vv.p, vv.sH, vv.sB,
                                   vv.sJ, vv.sK, dattn_drop.p, dbeta.p, nullptr, alpha.p, mask.p, p);
+}
+
+int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const View4* x, const View4* out_r, const View4* y,
+                          const View4* out_c, float alpha) {
+  if ((long long)d.H * d.B * d.J == 0) return SB_OK;
+  if (!x && !y) return SB_OK;
+  std::call_once(g_encode_once, load_encode);
+  if (!g_encode) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int L = d.K;
+  if (P != 64 || d.J != d.K || L % 128 != 0 || L > 512)
+    return fail(SB_ERR_UNSUPPORTED, "score contractions need head size 64 and a sequence length that is a multiple of 128, at most 512");
+  if (!dense_scores(scores, d)) return fail(SB_ERR_UNSUPPORTED, "score contractions need the score tensor dense as [H,B,J,K]");
+  const long long batch = (long long)d.H * d.B;
+  if (batch > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, "score contractions: too many (head, sample) pairs");
+  // projections are [P,H,B,rows] views: sH/sB/sJ/sK of the View4 hold the (P,H,B,row) strides
+  auto unit_stride = [&](const View4& v, long long* su) {
+    if (d.H > 1 && d.B > 1 && v.sB != v.sJ * d.B) return false;
+    *su = d.B > 1 ? v.sJ : v.sB;
+    return true;
+  };
+  scon::Params p{};
+  p.L = L; p.nt = L / 128; p.units = (int)batch; p.alpha = alpha;
+  p.has_r = x ? 1 : 0; p.has_c = y ? 1 : 0;
+  std::string why;
+  CUtensorMap ms, mx, my;
+  memset(&mx, 0, sizeof(mx));
+  memset(&my, 0, sizeof(my));
+  if (!encode_map(scores.p, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 128, &ms, &p.s_swap, &why))
+    return fail(SB_ERR_UNSUPPORTED, "score contractions, scores: " + why);
+  long long su = 0;
+  if (x) {
+    OperandMap m;
+    if (!unit_stride(*x, &su) || !make_operand_map(x->p, 64, L, batch, x->sH, x->sK, su, 64, &m, &why))
+      return fail(SB_ERR_UNSUPPORTED, "score contractions, row operand: " + why);
+    mx = m.map; p.x_mn = m.mn; p.x_swap = m.swap;
+    if (!unit_stride(*out_r, &su)) return fail(SB_ERR_UNSUPPORTED, "score contractions: head and sample dims of the row output do not collapse");
+    p.out_r = reinterpret_cast<__half*>(out_r->p); p.r_sU = su; p.r_sRow = out_r->sK; p.r_sP = out_r->sH;
+  }
+  if (y) {
+    OperandMap m;
+    if (!unit_stride(*y, &su) || !make_operand_map(y->p, 64, L, batch, y->sH, y->sK, su, 64, &m, &why))
+      return fail(SB_ERR_UNSUPPORTED, "score contractions, column operand: " + why);
+    my = m.map; p.y_mn = m.mn; p.y_swap = m.swap;
+    if (!unit_stride(*out_c, &su)) return fail(SB_ERR_UNSUPPORTED, "score contractions: head and sample dims of the column output do not collapse");
+    p.out_c = reinterpret_cast<__half*>(out_c->p); p.c_sU = su; p.c_sRow = out_c->sK; p.c_sP = out_c->sH;
+  }
+  const int proj = (p.has_r + p.has_c) * L * 128;
+  p.nstages = std::min(scon::kMaxStages, (232448 - 1280 - proj) / scon::kStageBytes);
+  const int smem = proj + p.nstages * scon::kStageBytes + 1024 + 256;
+  SB_CUDA_OK(cudaFuncSetAttribute(scon::score_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+  const unsigned grid = (unsigned)std::min<long long>(batch, sm_count());
+  SB_LAUNCH_OK(launch_k(scon::score_contract_kernel, grid, kTcThreads, smem, s, ms, mx, my, p));
+  return SB_OK;
 }
 
 int gemm_device_error(cudaStream_t s, int* code) {

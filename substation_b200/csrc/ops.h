@@ -55,6 +55,13 @@ int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, V
 int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 vv, View4 alpha, View4 mask,
                            View4 dattn_drop, View4 dbeta);
 
+// Score-tensor contractions with head-size-64 projections, S read once:
+//   out_r[p,h,b,j] = alpha * sum_k scores[h,b,j,k] * x[p,h,b,k]   (x, out_r both null to skip)
+//   out_c[p,h,b,k] = alpha * sum_j scores[h,b,j,k] * y[p,h,b,j]   (y, out_c both null to skip)
+// Projections use the same View4 convention as above.  SB_ERR_UNSUPPORTED when not eligible.
+int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const View4* x, const View4* out_r, const View4* y,
+                          const View4* out_c, float alpha);
+
 // Contractions -----------------------------------------------------------------
 struct GemmProblem {
   long long batch, M, N, K;

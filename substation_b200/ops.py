@@ -93,6 +93,18 @@ def attention_scores_softmax_backward(dgamma, vv, alpha, mask, dattn_drop, dbeta
                                                            _d(dattn_drop), _d(dbeta)))
 
 
+def attention_score_contractions(scores, x=None, out_rows=None, y=None, out_cols=None, alpha=1.0):
+    """out_rows[p,h,b,j] = alpha * sum_k scores[h,b,j,k] x[p,h,b,k] and/or
+    out_cols[p,h,b,k] = alpha * sum_j scores[h,b,j,k] y[p,h,b,j], reading scores once."""
+    if (x is None) != (out_rows is None) or (y is None) != (out_cols is None):
+        raise ValueError('an operand and its output are given together or not at all')
+    given = [t for t in (x, out_rows, y, out_cols) if t is not None]
+    _check_cuda(scores, *given); _half(scores, *given)
+    opt = lambda t: _d(t) if t is not None else None
+    check(_lib.load().sb_attention_score_contractions(_stream(), _d(scores), opt(x), opt(out_rows), opt(y),
+                                                      opt(out_cols), float(alpha)))
+
+
 def backward_softmax(alpha, mask, dattn_drop, dbeta):
     _check_cuda(alpha, mask, dattn_drop, dbeta); _half(alpha, dattn_drop, dbeta); _mask(mask)
     check(_lib.load().sb_backward_softmax(_stream(), _d(alpha), _d(mask), _d(dattn_drop), _d(dbeta)))

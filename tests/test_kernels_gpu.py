@@ -359,3 +359,39 @@ def test_fused_attention_scores_decline_what_they_do_not_cover():
     with pytest.raises(SubstationError) as e:
         ops.attention_scores_softmax(q, q, s, s.clone(), m, s.clone(), 1.0)
     assert e.value.status == 3
+
+
+@pytest.mark.parametrize('H,B,L,lay_in,lay_out', [(2, 2, 512, 'PHBJ', 'PHBJ'), (1, 3, 128, 'PHBJ', 'PHBJ'),
+                                                  (2, 1, 256, 'HBPJ', 'PHBJ'), (3, 2, 384, 'HBJP', 'HBJP'),
+                                                  (2, 2, 256, 'PHBJ', 'HBJP')])
+@pytest.mark.parametrize('which', ['rows', 'cols', 'both'])
+def test_attention_score_contractions(H, B, L, lay_in, lay_out, which):
+    """gamma / dX2gamma / the dX1QKT+dX2QKT pair as one pass over the score tensor, against float64 einsums."""
+    ops = _ops()
+    P = 64
+    rng = np.random.default_rng(L + H + len(which))
+    sc = h16(rng.normal(0, 0.3, (H, B, L, L)))
+    x, y = h16(rng.normal(0, 1, (P, H, B, L))), h16(rng.normal(0, 1, (P, H, B, L)))
+    d_r, d_c = empty((P, H, B, L), 'PHBJ', lay_out), empty((P, H, B, L), 'PHBJ', lay_out)
+    kw = {}
+    if which in ('rows', 'both'):
+        kw.update(x=place(x, 'PHBJ', lay_in), out_rows=d_r)
+    if which in ('cols', 'both'):
+        kw.update(y=place(y, 'PHBJ', lay_in), out_cols=d_c)
+    ops.attention_score_contractions(place(sc, 'HBJK', 'HBJK'), alpha=0.125, **kw)
+    assert ops.device_error() == 0
+    if 'x' in kw:
+        assert_close(d_r, 0.125 * np.einsum('hbjk,phbk->phbj', sc, x), what='rows')
+    if 'y' in kw:
+        assert_close(d_c, 0.125 * np.einsum('hbjk,phbj->phbk', sc, y), what='cols')
+
+
+def test_attention_score_contractions_decline_what_they_do_not_cover():
+    ops = _ops()
+    from substation_b200._lib import SubstationError
+    H, B, L, P = 1, 1, 192, 64                      # L not a multiple of 128
+    sc = torch.zeros(H, B, L, L, dtype=torch.float16, device=DEV)
+    x = torch.zeros(P, H, B, L, dtype=torch.float16, device=DEV)
+    with pytest.raises(SubstationError) as e:
+        ops.attention_score_contractions(sc, x=x, out_rows=x.clone())
+    assert e.value.status == 3
