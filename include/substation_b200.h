@@ -318,6 +318,9 @@ int sb_encoder_set_timing(sb_encoder* enc, int enabled);
 int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* ms);
 /* Number of operators the most recent forward / backward launched. */
 int sb_encoder_launch_count(sb_encoder* enc);
+/* Kernels launched by the most recent forward plus the most recent backward (an operator may need
+ * a second, finishing kernel, so this can exceed the two operator counts). */
+int sb_encoder_kernel_count(sb_encoder* enc);
 /* Fused multi-operator kernels (on by default) can be switched off to run the reference's
  * one-kernel-per-operator sequence. */
 int sb_encoder_set_fusion(sb_encoder* enc, int enabled);

@@ -13,6 +13,7 @@
 #include "ops.h"
 
 namespace sb {
+thread_local long long g_kernel_launches = 0;
 
 namespace {
 thread_local std::string g_error;
@@ -527,6 +528,7 @@ struct sb_encoder {
   size_t gemm_ws_bytes = 0;
   int device = 0;
   int launches = 0;
+  long long kernels_fwd = 0, kernels_bwd = 0, kernel_base = 0;   // kernels launched by the most recent passes
   bool timing = false;
   bool fuse = true;            // use the fused multi-operator kernels where the layouts allow
   std::vector<std::pair<std::string, cudaEvent_t>> marks;
@@ -704,6 +706,7 @@ extern "C" int sb_encoder_set_timing(sb_encoder* e, int enabled) {
 }
 
 extern "C" int sb_encoder_launch_count(sb_encoder* e) { return e ? e->launches : 0; }
+extern "C" int sb_encoder_kernel_count(sb_encoder* e) { return e ? (int)(e->kernels_fwd + e->kernels_bwd) : 0; }
 extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
   if (!e) return fail(SB_ERR_ARG, "null handle");
   e->fuse = enabled != 0;
@@ -769,6 +772,7 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
   SB_TRY(gather(e, x, params, fwd, &T));
   T.p["SB2"] = y;
   e->launches = 0;
+  e->kernel_base = g_kernel_launches;
   const auto& L = e->layout;
   const long long slice = (long long)e->P * e->H * e->B * e->S;  // elements per stacked projection
   auto q_slice = [&](const char* name, int q) { return (void*)((__half*)T[name] + q * slice); };
@@ -855,6 +859,7 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
                                               &istd, &ln, &out, &d));
   }
   if (e->timing) { e->mark(s, ""); --e->launches; }
+  e->kernels_fwd = g_kernel_launches - e->kernel_base;
   return SB_OK;
 }
 
@@ -875,6 +880,7 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
     D[e->param_order[i]] = dparams[i];
   }
   e->launches = 0;
+  e->kernel_base = g_kernel_launches;
   const auto& L = e->layout;
   const long long slice = (long long)e->P * e->H * e->B * e->S;
   auto q_slice = [&](void* base, int q) { return (void*)((__half*)base + q * slice); };
@@ -1003,5 +1009,6 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
     SB_TRY(sb_backward_encoder_input(stream, &a, &b, &tDX));
   }
   if (e->timing) { e->mark(s, ""); --e->launches; }
+  e->kernels_bwd = g_kernel_launches - e->kernel_base;
   return SB_OK;
 }

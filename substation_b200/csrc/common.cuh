@@ -81,6 +81,9 @@ __device__ __forceinline__ void grid_dependency_sync() {
 
 bool pdl_enabled();  // false when the environment sets SUBSTATION_B200_PDL=0
 
+// Kernels launched through launch_k by this thread (the layer handle reports the difference over a pass).
+extern thread_local long long g_kernel_launches;
+
 template <class... KArgs, class... Args>
 cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                      Args&&... args) {
@@ -95,6 +98,7 @@ cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  ++g_kernel_launches;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

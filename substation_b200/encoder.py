@@ -316,8 +316,12 @@ class Encoder(torch.nn.Module):
         return [(names[i].decode(), ms[i]) for i in range(k)]
 
     def launch_count(self):
-        """Kernels launched by the most recent raw pass."""
+        """Operators launched by the most recent raw pass."""
         return 0 if self._handle is None else _lib.load().sb_encoder_launch_count(self._handle)
+
+    def kernel_count(self):
+        """Kernels launched by the most recent forward plus the most recent backward."""
+        return 0 if self._handle is None else _lib.load().sb_encoder_kernel_count(self._handle)
 
     def forward(self, X):
         """Run the encoder."""
