@@ -71,6 +71,13 @@ FUSED_BYTES = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=8, L=512, from the ncu --set full captures
+# summarised in profiles/top_kernels_b8_l512_full_captures.md (part of each kernel's output is still in L2
+# when it ends, so traffic can be below the algorithmic bytes)
+NCU_DRAM_BYTES = {'QKT+softmax': 195.45e6, 'dX1gamma+bs': 197.63e6, 'gamma': 78.56e6, 'dX2gamma': 78.29e6,
+                  'dX1QKT+dX2QKT': 87.82e6, 'bsb+blnrd1': 29.81e6, 'ebsb+blnrd2+baob': 51.64e6}
+
+
 def load_peaks():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -347,7 +354,10 @@ def run_ours(args):
     else:
         roof = {'kernel': top, 'bound': 'hbm', 'achieved': ops[top]['gbs'], 'peak': hbm, 'unit': 'GB/s',
                 'frac': round(ops[top]['gbs'] / hbm, 3)}
-    roof['traffic'] = None
+    # DRAM bytes (read + write) of one launch from the ncu capture of this workload; only known for B=8, L=512
+    roof['traffic'] = NCU_DRAM_BYTES.get(top) if (B, S) == (8, 512) else None
+    roof['traffic_unit'] = 'bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)'
+    roof['algorithmic_bytes'] = (FUSED_BYTES.get(top) or ATTN_BYTES.get(top, lambda b, l: None))(B, S)
     roof['peak_source'] = f'{peak_kind} (MEASURED_PEAKS.json: torch copy / cuBLAS bf16 burst)'
     roof['share_of_step'] = round(ops[top]['us'] / sum_us, 3)
 
