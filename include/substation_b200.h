@@ -222,8 +222,8 @@ int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, 
  * tcgen05 MMAs for both results.  scores: [H,B,J,K] dense in that order; projections [P,H,B,J]
  * with any strides TMA can address.  Needs P = 64, J = K a multiple of 128 and at most 512;
  * otherwise SB_ERR_UNSUPPORTED and the caller runs sb_einsum.  Replaces the contractions
- * gamma (pytorch_module/encoder.cu:121-123), dX2gamma (:247-249) and the pair dX1QKT, dX2QKT
- * (:262-267), the pair as one launch. */
+ * gamma (pytorch_module/encoder.cu:123-125), dX2gamma (:254-256) and the pair dX1QKT, dX2QKT
+ * (:263-269), the pair as one launch. */
 int sb_attention_score_contractions(void* stream, const sb_tensor* scores, const sb_tensor* x,
                                     const sb_tensor* out_rows, const sb_tensor* y, const sb_tensor* out_cols,
                                     float alpha);

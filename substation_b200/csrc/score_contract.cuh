@@ -2,9 +2,9 @@
 // shares its TMA / tcgen05 helpers):
 //
 //   rows:  R[p,h,b,j] = alpha * sum_k S[h,b,j,k] * X[p,h,b,k]
-//          (gamma and dX1QKT of pytorch_module/encoder.cu:121-123, 262-264)
+//          (gamma and dX1QKT of pytorch_module/encoder.cu:123-125, 263-265)
 //   cols:  C[p,h,b,k] = alpha * sum_j S[h,b,j,k] * Y[p,h,b,j]
-//          (dX2gamma and dX2QKT of pytorch_module/encoder.cu:247-249, 265-267)
+//          (dX2gamma and dX2QKT of pytorch_module/encoder.cu:254-256, 267-269)
 //
 // either one, or both from a single pass over S.  These are HBM-bound: 2 L^2 bytes of S per
 // (head, sample) against 4 * 64 * L of projections, so the kernel is organised around reading S
