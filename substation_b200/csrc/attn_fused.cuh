@@ -41,12 +41,13 @@ struct Params {
   int L;                 // sequence length (rows and columns of a score tile)
   int tiles_j;           // ceil(L / 128)
   int b_bytes;           // bytes the key/value boxes of one tile deliver (out-of-range rows included)
-  long long tiles;       // tiles_j * batch
+  int tiles;             // tiles_j * batch
   int a_mn, b_mn, a_swap, b_swap;
   int swap_o;            // dims 1,2 of the score tensor maps exchanged
   float scale;           // forward: BETA = scale * acc.  backward: unused (DATTN_DROP = acc)
   Rng rng;               // forward: dropout source
   uint8_t* mask;         // [batch][L][L] bytes (written directly when the mask is generated here)
+  int prefetch;          // producer warp asks for the row inputs of the next tile to be brought into L2
 };
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
@@ -97,6 +98,18 @@ __device__ __forceinline__ bool epi_barrier(uint32_t bar, uint32_t& uses, int la
   const bool ok = mbar_wait(bar, uses & 1u, 6);
   ++uses;
   return __all_sync(0xffffffffu, ok);
+}
+
+// 2^x for x <= 0 on the special-function unit (results below 2^-126 flush to zero)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Ask for a box to be brought into L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
 template <int N>
@@ -163,7 +176,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // ---------------- TMA producer: the operands of one tile at a time ----------------
     uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
       const int j0 = (int)(t % p.tiles_j) * 128;
       const int bt = (int)(t / p.tiles_j);
       ok = __all_sync(0xffffffffu, mbar_wait(bar_empty, (it & 1u) ^ 1u, 1));
@@ -194,6 +207,21 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
       }
       __syncwarp();
+      // The epilogue warps are still busy with the previous tile: bring this tile's row inputs (mask,
+      // and ALPHA in the backward kernel) into L2 now, so that their slot fetches find them there.
+      if (mask_in && p.prefetch) {
+        const int nbox = (min(128, L - j0) / 32) * (L / 64);
+        for (int b = lane; b < nbox; b += 32) {
+          const int jr = j0 + (b / (L / 64)) * 32, c0 = (b % (L / 64)) * 64;
+          if (p.swap_o) {
+            if (BWD) tma_prefetch_3d(&tmI, c0, bt, jr);
+            tma_prefetch_3d(&tmM, c0, bt, jr);
+          } else {
+            if (BWD) tma_prefetch_3d(&tmI, c0, jr, bt);
+            tma_prefetch_3d(&tmM, c0, jr, bt);
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -201,7 +229,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
     uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
       // tensor memory holds one tile: the previous tile must have been read out completely
       ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty, (it & 1u) ^ 1u, 4));
       if (!ok) break;
@@ -240,13 +268,13 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t my_bar = bar_in + 8 * ew;
     const float c2 = p.scale * 1.4426950408889634f;
     const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
-    const long long G = gridDim.x;
+    const int G = gridDim.x;
 
-    auto tile_has_rows = [&](long long t) { return (int)(t % p.tiles_j) * 128 + q * 32 < L; };
+    auto tile_has_rows = [&](int t) { return (t % p.tiles_j) * 128 + q * 32 < L; };
     // fetch the row inputs of chunk c of tile t into this warp's slot (lane 0)
-    auto fetch_in = [&](long long t, int c) {
-      const int jr = (int)(t % p.tiles_j) * 128 + q * 32;
-      const int bt = (int)(t / p.tiles_j);
+    auto fetch_in = [&](int t, int c) {
+      const int jr = (t % p.tiles_j) * 128 + q * 32;
+      const int bt = t / p.tiles_j;
       mbar_expect_tx(my_bar, (uint32_t)C::kInSlot);
       if (BWD) {
         if (p.swap_o) tma_load_3d(my_in, &tmI, my_bar, c * 64, bt, jr);
@@ -257,7 +285,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       else tma_load_3d(md, &tmM, my_bar, c * 64, jr, bt);
     };
     // successor of (t, c) in this warp's sequence of input chunks
-    auto next_in = [&](long long& t, int& c) {
+    auto next_in = [&](int& t, int& c) {
       c += kNW;
       if (c < nc64) return true;
       c = h;
@@ -269,7 +297,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t n_out = 0;   // staging buffers filled (buffer = n_out % NB)
     uint32_t n_bar = 0;   // uses of the epilogue barrier
     if (mask_in && h < nc64 && lane == 0) {
-      long long t0 = blockIdx.x;
+      int t0 = blockIdx.x;
       while (t0 < p.tiles && !tile_has_rows(t0)) t0 += G;
       if (t0 < p.tiles) fetch_in(t0, h);
     }
@@ -286,9 +314,9 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += G, ++it) {
-      const int j0 = (int)(t % p.tiles_j) * 128;
-      const int bt = (int)(t / p.tiles_j);
+    for (int t = blockIdx.x; t < p.tiles && ok; t += G, ++it) {
+      const int j0 = (t % p.tiles_j) * 128;
+      const int bt = t / p.tiles_j;
       const int jr = j0 + q * 32;                          // first row of this warp
       const bool rows = jr < L && h < nc64;                // warp-uniform: this warp has work in the tile
       const long long row_off = ((long long)bt * L + (jr + lane)) * (long long)L;
@@ -325,7 +353,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               for (int e = 0; e < 8; ++e) {
                 const float a = __uint_as_float(r[v * 8 + e]);
                 f[e] = a * p.scale;
-                const float ex = exp2f(fmaf(a, c2, -mxs));
+                const float ex = ex2_approx(fmaf(a, c2, -mxs));
                 sum += ex;
                 r[v * 8 + e] = __float_as_uint(ex);
               }
@@ -347,33 +375,32 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int w = 0; w < kNW; ++w) sum += red_gen[(kNW + w) * 128 + rt];
         const float inv = 1.f / sum;
         // pass 3: ALPHA = e / sum, ATTN_DROP = mask * ALPHA
+        uint32_t mall[16];  // the mask bytes of this thread's row for one 64-column chunk
         if (rows)
           sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
             // mask bytes of this thread's 32 columns, as 8 words
             uint32_t mw[8];
             if (!p.rng.philox) {
-              if (hh == 0) ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
-              if (ok) {
+              if (hh == 0) {
+                // take the whole chunk out of the slot at once, so that the next fetch starts early
+                ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                  const uint4 m = *reinterpret_cast<const uint4*>(my_in_gen + lane * 64 + (((hh * 2 + i) ^ ((lane >> 1) & 3)) << 4));
-                  mw[4 * i] = m.x; mw[4 * i + 1] = m.y; mw[4 * i + 2] = m.z; mw[4 * i + 3] = m.w;
+                for (int i = 0; i < 4; ++i) {
+                  uint4 m = make_uint4(0, 0, 0, 0);
+                  if (ok) m = *reinterpret_cast<const uint4*>(my_in_gen + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4));
+                  mall[4 * i] = m.x; mall[4 * i + 1] = m.y; mall[4 * i + 2] = m.z; mall[4 * i + 3] = m.w;
                 }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) mw[i] = 0;
-              }
-              if (hh == 1) {
-                // the slot has been read: fetch this warp's next chunk into it
                 ++n_in;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0 && ok) {
-                  long long tn = t;
+                  int tn = t;
                   int cn = c;
                   if (next_in(tn, cn)) fetch_in(tn, cn);
                 }
               }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) mw[i] = mall[hh * 8 + i];
             } else {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -415,37 +442,39 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // backward pass 1: DATTN_DROP out; (da, alpha) with da = mask * DATTN_DROP kept as an fp16
         // pair per tensor-memory word; partial s = sum da * alpha
         float ssum = 0.f;
+        uint4 aall[8];      // ALPHA of this thread's row for one 64-column chunk
+        uint32_t mall[16];  // and its mask bytes
         if (rows)
           sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
-            if (hh == 0) ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
-            uint4 araw[4];
-            uint32_t mw[8];
-            if (ok) {
+            if (hh == 0) {
+              // take the whole chunk (ALPHA and mask rows) out of the slot, then refill it at once
+              ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                araw[i] = *reinterpret_cast<const uint4*>(my_in_gen + lane * 128 + (((hh * 4 + i) ^ (lane & 7)) << 4));
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const uint4 m = *reinterpret_cast<const uint4*>(my_in_gen + 4096 + lane * 64 +
-                                                                (((hh * 2 + i) ^ ((lane >> 1) & 3)) << 4));
-                mw[4 * i] = m.x; mw[4 * i + 1] = m.y; mw[4 * i + 2] = m.z; mw[4 * i + 3] = m.w;
+              for (int i = 0; i < 8; ++i) {
+                aall[i] = make_uint4(0, 0, 0, 0);
+                if (ok) aall[i] = *reinterpret_cast<const uint4*>(my_in_gen + lane * 128 + ((i ^ (lane & 7)) << 4));
               }
-            } else {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) araw[i] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) mw[i] = 0;
-            }
-            if (hh == 1) {
+              for (int i = 0; i < 4; ++i) {
+                uint4 m = make_uint4(0, 0, 0, 0);
+                if (ok) m = *reinterpret_cast<const uint4*>(my_in_gen + 4096 + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4));
+                mall[4 * i] = m.x; mall[4 * i + 1] = m.y; mall[4 * i + 2] = m.z; mall[4 * i + 3] = m.w;
+              }
               ++n_in;
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0 && ok) {
-                long long tn = t;
+                int tn = t;
                 int cn = c;
                 if (next_in(tn, cn)) fetch_in(tn, cn);
               }
             }
+            uint4 araw[4];
+            uint32_t mw[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) araw[i] = aall[hh * 4 + i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mw[i] = mall[hh * 8 + i];
             const uint32_t b = n_out % NB;
             if (hh == 0) {
               if (lane == 0) bulk_wait_read<NB - 1>();

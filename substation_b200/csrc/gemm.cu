@@ -1011,9 +1011,13 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
   if ((alpha_in && !encode_map(alpha_in, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &mi, &swi, &why)) ||
       (mask_in && !encode_map(mask_in, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &mm, &swm, &why, true)))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores, row inputs: " + why);
+  // measured: the L2 prefetch of the next tile's mask rows helps the forward kernel; in the backward kernel the
+  // extra requests (ALPHA too) queue in front of the slot fetches and cost more than they save
+  p.prefetch = BWD ? 0 : 1;
   p.L = L;
   p.tiles_j = (L + 127) / 128;
-  p.tiles = (long long)p.tiles_j * batch;
+  if ((long long)p.tiles_j * batch > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, "fused attention scores: too many tiles");
+  p.tiles = (int)(p.tiles_j * batch);
   p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
   p.swap_o = sw0;
   p.b_bytes = b.mn ? L * 128 : ((L + 255) / 256) * brows * 128;
