@@ -416,8 +416,10 @@ def run_ours(args):
         e2e_drain()
         barrier()
         e0.record()
+        t_host = time.perf_counter()
         for i in range(args.steps):
             e2e_step(i)
+        t_host = time.perf_counter() - t_host      # host time to issue the steps (no synchronisation inside)
         e2e_drain()
         e1.record()
         barrier()
@@ -425,7 +427,7 @@ def run_ours(args):
         nbytes = hX.numel() * 2
         e2e = {'value': world * B * args.steps / (e2e_ms / 1e3), 'unit': UNIT,
                'h2d_bytes_per_step': 2 * nbytes, 'd2h_bytes_per_step': 2 * nbytes,
-               'ms_per_step': e2e_ms / args.steps}
+               'ms_per_step': e2e_ms / args.steps, 'host_issue_ms_per_step': 1e3 * t_host / args.steps}
 
     # ---- CPU baseline (rank 0, N=1 only): bounded sample of the same workload ------------
     cpu = None

@@ -74,20 +74,32 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t* r) {
                :: "memory");
 }
 
-// Walk this warp's 64-column chunks (c = first, first + kNW, ...) in 32-column halves, keeping the
-// tensor-memory load of the next half in flight while f(c, half, r) works on the current one.
+// Walk this warp's 64-column chunks (c = first, first + kNW, ... < end) in 32-column halves, keeping
+// the tensor-memory load of the next half in flight while f(c, half, r) works on the current one.
 template <class F>
-__device__ __forceinline__ void sweep(uint32_t trow, int first, int nc64, F&& f) {
-  if (first >= nc64) return;
+__device__ __forceinline__ void sweep(uint32_t trow, int first, int end, F&& f) {
+  if (first >= end) return;
   uint32_t ra[32], rb[32];
   tmem_ld32_nowait(trow + first * 64, ra);
-  for (int c = first; c < nc64; c += kNW) {
+  for (int c = first; c < end; c += kNW) {
     tmem_ld_wait32(ra);
     tmem_ld32_nowait(trow + c * 64 + 32, rb);
     f(c, 0, ra);
     tmem_ld_wait32(rb);
-    if (c + kNW < nc64) tmem_ld32_nowait(trow + (c + kNW) * 64, ra);
+    if (c + kNW < end) tmem_ld32_nowait(trow + (c + kNW) * 64, ra);
     f(c, 1, rb);
+  }
+}
+
+// The same walk, one 256-column half of tensor memory at a time (the MMAs fill and the last pass
+// releases the halves separately): pre(half) runs before the first read of a half, post(half) after
+// the last.
+template <class Pre, class Post, class F>
+__device__ __forceinline__ void sweep_halves(uint32_t trow, int h, int nc64, Pre&& pre, Post&& post, F&& f) {
+  for (int hf = 0; hf * 4 < nc64; ++hf) {
+    pre(hf);
+    sweep(trow, hf * 4 + h, min(nc64, hf * 4 + 4), f);
+    post(hf);
   }
 }
 
@@ -132,11 +144,11 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t staging = operands + kOperandBytes;
   const uint32_t inslots = staging + C::kStaging;
   const uint32_t red = inslots + kEpiWarps * C::kInSlot;
-  const uint32_t bars = red + kRedBytes;  // full, empty, tmem_full, tmem_empty, in_full[kEpiWarps], epilogue barrier, tmem slot
-  const uint32_t bar_full = bars, bar_empty = bars + 8, bar_tfull = bars + 16, bar_tempty = bars + 24, bar_in = bars + 32;
+  const uint32_t bars = red + kRedBytes;  // full, empty, tmem_full, tmem_empty, tmem_full[2], tmem_empty[2], in_full[kEpiWarps], epilogue barrier, tmem slot
+  const uint32_t bar_full = bars, bar_empty = bars + 8, bar_tfull = bars + 16, bar_tempty = bars + 32, bar_in = bars + 48;
   const uint32_t bar_epi = bar_in + 8 * kEpiWarps;
   uint8_t* gen_base = smem_raw + (operands - raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 48 + 8 * kEpiWarps);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 64 + 8 * kEpiWarps);
   float* red_gen = reinterpret_cast<float*>(gen_base + (red - operands));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -147,8 +159,10 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(bar_full, 1);
     mbar_init(bar_empty, 1);
-    mbar_init(bar_tfull, 1);
-    mbar_init(bar_tempty, kEpiWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull + 8 * i, 1);
+      mbar_init(bar_tempty + 8 * i, kEpiWarps);
+    }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar_in + 8 * w, 1);
     mbar_init(bar_epi, kEpiWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -230,15 +244,19 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
-      // tensor memory holds one tile: the previous tile must have been read out completely
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty, (it & 1u) ^ 1u, 4));
-      if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_full, it & 1u, 2));
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t sa = operands, sb_ = sa + kABytes;
-        for (int c = 0; c < nchunk; ++c) {
+      // tensor memory holds one tile, in two halves of 256 columns that are filled (and, by the last
+      // epilogue pass of the previous tile, released) separately: the MMAs of the first half run
+      // while the previous tile's second half is still being read
+      for (int c = 0; c < nchunk && ok; ++c) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * c, (it & 1u) ^ 1u, 4));
+        if (!ok) break;
+        if (c == 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_full, it & 1u, 2));
+          if (!ok) break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = operands, sb_ = sa + kABytes;
           const int width = min(256, L - c * 256);
           const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) | ((uint32_t)(p.b_mn ? 1 : 0) << 16) |
                                  ((uint32_t)(width >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
@@ -248,11 +266,11 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const uint64_t db = make_desc(sb_ + c * 32768 + k * b_step, b_lbo, 1024u);
             umma_f16(tmem_base + c * 256, da, db, idesc, k > 0 ? 1u : 0u);
           }
+          umma_commit(bar_tfull + 8 * c);
+          if (c == nchunk - 1) umma_commit(bar_empty);   // the operand buffer may be refilled for the next tile
         }
-        umma_commit(bar_empty);   // the operand buffer may be refilled for the next tile
-        umma_commit(bar_tfull);
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else {
     // ---------------- softmax / epilogue warps: thread = one query row ----------------
@@ -320,15 +338,23 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int jr = j0 + q * 32;                          // first row of this warp
       const bool rows = jr < L && h < nc64;                // warp-uniform: this warp has work in the tile
       const long long row_off = ((long long)bt * L + (jr + lane)) * (long long)L;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull, it & 1u, 3));
-      if (!ok) break;   // every epilogue warp waits on the same barrier and gives up with it
-      tc_fence_after();
+      // first reads of a half wait for its MMAs; the last pass hands the halves back one by one
+      auto wait_half = [&](int hf) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * hf, it & 1u, 3)) && ok;
+        tc_fence_after();
+      };
+      auto release_half = [&](int hf) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * hf);
+      };
+      auto no_op = [](int) {};
 
       if (!BWD) {
         // pass 1: row maximum of the raw accumulator (scale > 0)
         float mx = -INFINITY;
         if (rows)
-          sweep(trow, h, nc64, [&](int, int, uint32_t* r) {
+          sweep_halves(trow, h, nc64, wait_half, no_op, [&](int, int, uint32_t* r) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
           });
@@ -377,7 +403,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // pass 3: ALPHA = e / sum, ATTN_DROP = mask * ALPHA
         uint32_t mall[16];  // the mask bytes of this thread's row for one 64-column chunk
         if (rows)
-          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+          sweep_halves(trow, h, nc64, no_op, release_half, [&](int c, int hh, uint32_t* r) {
             // mask bytes of this thread's 32 columns, as 8 words
             uint32_t mw[8];
             if (!p.rng.philox) {
@@ -445,7 +471,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         uint4 aall[8];      // ALPHA of this thread's row for one 64-column chunk
         uint32_t mall[16];  // and its mask bytes
         if (rows)
-          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+          sweep_halves(trow, h, nc64, wait_half, no_op, [&](int c, int hh, uint32_t* r) {
             if (hh == 0) {
               // take the whole chunk (ALPHA and mask rows) out of the slot, then refill it at once
               ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
@@ -516,7 +542,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int w = 0; w < kNW; ++w) ssum += red_gen[w * 128 + rt];
         // backward pass 2: DBETA = alpha * (da - s)
         if (rows)
-          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+          sweep_halves(trow, h, nc64, no_op, release_half, [&](int c, int hh, uint32_t* r) {
             const uint32_t b = n_out % NB;
             if (hh == 0) {
               if (lane == 0) bulk_wait_read<NB - 1>();
@@ -540,10 +566,9 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           });
       }
-      // this warp's reads of the tile are complete: tensor memory may take the next one
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty);
+      // a warp without rows in this tile reads nothing: it hands both halves back here
+      if (!rows)
+        for (int hf = 0; hf * 4 < nc64; ++hf) release_half(hf);
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();

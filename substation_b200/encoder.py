@@ -97,20 +97,36 @@ class Encoder(torch.nn.Module):
         self._fwd_plan = self._plan(layouts['forward_interm'])
         self._bwd_plan = self._plan(layouts['backward_interm'])
         self._grad_plan = self._plan(layouts['params'])
+        # (shape, contiguous strides, element offset) of each parameter gradient inside the gradient arena
+        self._grad_views = []
+        for _, shape, _, off, _ in self._grad_plan[0]:
+            strides, acc = [], 1
+            for extent in reversed(shape):
+                strides.append(acc)
+                acc *= extent
+            self._grad_views.append((tuple(shape), tuple(reversed(strides)), off // 2))
 
         outer = self
 
         class EncoderFunction(torch.autograd.Function):
             @staticmethod
             def forward(ctx, X, *weights):
+                # Hot path: one arena per pass, pointers computed from the plan's offsets; tensor views
+                # over the arena are only built when somebody asks for them (debug, or a caller of views()).
+                outer._check_input(X, 'X')
+                X = X.contiguous()
+                weights = tuple(w if w.is_contiguous() else w.contiguous() for w in weights)
                 Y = torch.empty_like(X)
-                fwd = outer._alloc(outer._fwd_plan, X.device)
-                if outer.mask_mode == 'explicit':
-                    fwd.update(outer._explicit_masks(X.device))
-                outer.forward_raw(X, weights, fwd, Y)
-                ctx.save_for_backward(*weights, *(fwd[n] for n in outer._fwd_names), X)
+                plan, total = outer._fwd_plan
+                arena = torch.empty(max(total, 1), dtype=torch.uint8, device=X.device)
+                over = outer._explicit_masks(X.device) if outer.mask_mode == 'explicit' else {}
+                outer._forward_ptrs(X, weights, outer._plan_ptrs(plan, arena, over), Y)
+                ctx.save_for_backward(*weights, arena, X)
+                ctx.masks = over
                 if outer.enable_debug:
                     torch.cuda.synchronize()
+                    fwd = outer.views('forward', arena)
+                    fwd.update(over)
                     for name in outer._fwd_names:
                         outer.debug[name] = fwd[name].detach().cpu().numpy()
                     for name, w in zip(outer._param_names, weights):
@@ -120,21 +136,27 @@ class Encoder(torch.nn.Module):
             @staticmethod
             def backward(ctx, DY):
                 saved = ctx.saved_tensors
-                np_, nf = len(outer._param_names), len(outer._fwd_names)
-                weights, fwd_list, X = saved[:np_], saved[np_:np_ + nf], saved[-1]
-                fwd = dict(zip(outer._fwd_names, fwd_list))
+                np_ = len(outer._param_names)
+                weights, arena, X = saved[:np_], saved[np_], saved[-1]
+                outer._check_input(DY, 'DY')
                 DY = DY.contiguous()
                 DX = torch.empty_like(DY)
-                bwd = outer._alloc(outer._bwd_plan, DY.device)
-                grads = outer._alloc(outer._grad_plan, DY.device)
-                outer.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
+                bplan, btotal = outer._bwd_plan
+                gplan, gtotal = outer._grad_plan
+                barena = torch.empty(max(btotal, 1), dtype=torch.uint8, device=DY.device)
+                garena = torch.empty(max(gtotal, 1), dtype=torch.uint8, device=DY.device)
+                outer._backward_ptrs(DY, outer._plan_ptrs(gplan, garena, {}), outer._plan_ptrs(bplan, barena, {}), weights,
+                                     outer._plan_ptrs(outer._fwd_plan[0], arena, ctx.masks), X, DX)
+                g16 = garena.view(outer.torch_dtype)
+                grads = tuple(torch.as_strided(g16, shape, strides, off) for shape, strides, off in outer._grad_views)
                 if outer.enable_debug:
                     torch.cuda.synchronize()
+                    bwd = outer.views('backward', barena)
                     for name in outer._bwd_names:
                         outer.debug[name] = bwd[name].detach().cpu().numpy()
-                    for name in outer._param_names:
-                        outer.debug['D' + name] = grads[name].detach().cpu().numpy()
-                return (DX, *(grads[n] for n in outer._param_names))
+                    for name, g in zip(outer._param_names, grads):
+                        outer.debug['D' + name] = g.detach().cpu().numpy()
+                return (DX, *grads)
 
         self.encoder_func = EncoderFunction
 
@@ -269,6 +291,35 @@ class Encoder(torch.nn.Module):
         if X.dtype != self.torch_dtype or tuple(X.shape) != want:
             raise ValueError(f'{what} must be {self.torch_dtype} of shape {want} '
                              f'(layout {self._table["X"]}), got {X.dtype} {tuple(X.shape)}')
+
+    # ------------------------------------------------------------------ pointer-level passes
+    @staticmethod
+    def _plan_ptrs(plan, arena, overrides):
+        """Device pointers of a plan's tensors inside ``arena`` (plan order); ``overrides``: name ->
+        tensor that lives elsewhere (the caller's explicit masks)."""
+        base = arena.data_ptr()
+        arr = (ctypes.c_void_p * len(plan))()
+        for i, (name, _, _, off, _) in enumerate(plan):
+            t = overrides.get(name) if overrides else None
+            arr[i] = base + off if t is None else t.data_ptr()
+        return arr
+
+    def _forward_ptrs(self, X, weights, fwd_ptrs, Y):
+        lib = _lib.load()
+        h = self._native(X.device)
+        mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
+        stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
+        _lib.check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
+                                          ctypes.c_void_p(Y.data_ptr()), mode, self.seed, self.philox_offset))
+        self.philox_offset += 4
+
+    def _backward_ptrs(self, DY, grad_ptrs, bwd_ptrs, weights, fwd_ptrs, X, DX):
+        lib = _lib.load()
+        h = self._native(DY.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
+        _lib.check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
+                                           self._ptrs(weights), fwd_ptrs, ctypes.c_void_p(X.data_ptr()),
+                                           ctypes.c_void_p(DX.data_ptr())))
 
     # ------------------------------------------------------------------ raw passes (no autograd)
     def forward_raw(self, X, weights, fwd, Y):
