@@ -378,6 +378,7 @@ def run_ours(args):
         ev_free = [torch.cuda.Event() for _ in range(2)]       # compute no longer reads input buffer b
         ev_out = [torch.cuda.Event() for _ in range(2)]
         keep = [None, None]
+        works = [None, None]
         for prm in enc.params:
             prm.requires_grad_(True)
 
@@ -394,8 +395,17 @@ def run_ours(args):
             y.backward(dyd[b])
             ev_free[b].record(cur)
             if world > 1:
-                for prm in enc.params:
-                    dist.all_reduce(prm.grad, op=dist.ReduceOp.SUM)
+                # all twelve gradients are views into one bucket: one allreduce, asynchronous, waited for
+                # two steps later (each step's backward gets a fresh bucket)
+                bucket = enc.grad_bucket()
+                lo, hi = bucket.data_ptr(), bucket.data_ptr() + bucket.numel() * 2
+                if all(lo <= prm.grad.data_ptr() < hi for prm in enc.params):
+                    if works[b] is not None:
+                        works[b].wait()
+                    works[b] = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, async_op=True)
+                else:
+                    for prm in enc.params:
+                        dist.all_reduce(prm.grad, op=dist.ReduceOp.SUM)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_free[b])
                 s_out.wait_event(ev_out[b])                    # previous copy out of these host buffers done
@@ -408,6 +418,9 @@ def run_ours(args):
             enc.zero_grad(set_to_none=True)
 
         def e2e_drain():
+            for w in works:
+                if w is not None:
+                    w.wait()
             cur.wait_stream(s_in)
             cur.wait_stream(s_out)
 

@@ -148,6 +148,7 @@ class Encoder(torch.nn.Module):
                 outer._backward_ptrs(DY, outer._plan_ptrs(gplan, garena, {}), outer._plan_ptrs(bplan, barena, {}), weights,
                                      outer._plan_ptrs(outer._fwd_plan[0], arena, ctx.masks), X, DX)
                 g16 = garena.view(outer.torch_dtype)
+                outer._grad_bucket = g16
                 grads = tuple(torch.as_strided(g16, shape, strides, off) for shape, strides, off in outer._grad_views)
                 if outer.enable_debug:
                     torch.cuda.synchronize()
@@ -365,6 +366,11 @@ class Encoder(torch.nn.Module):
         ms = (ctypes.c_float * n)()
         k = lib.sb_encoder_get_timing(self._handle, n, names, ms)
         return [(names[i].decode(), ms[i]) for i in range(k)]
+
+    def grad_bucket(self):
+        """The flat fp16 tensor that holds all 12 parameter gradients of the most recent autograd backward
+        (each ``.grad`` is a view into it): a data-parallel caller sums one tensor instead of twelve."""
+        return self.__dict__.get('_grad_bucket')
 
     def launch_count(self):
         """Operators launched by the most recent raw pass."""
