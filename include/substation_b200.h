@@ -317,6 +317,10 @@ int sb_encoder_backward(sb_encoder* enc, void* stream, const void* dy, void* con
 int sb_encoder_set_timing(sb_encoder* enc, int enabled);
 int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* ms);
 /* Number of operators the most recent forward / backward launched. */
+/* A pass whose pointer arguments repeat (explicit masks, timing off) is captured once as a CUDA graph and
+ * replayed with a single launch afterwards; 0 switches that off for the handle (default on; the environment
+ * variable SUBSTATION_B200_GRAPHS=0 switches it off for the process). */
+int sb_encoder_set_graphs(sb_encoder* enc, int enabled);
 int sb_encoder_launch_count(sb_encoder* enc);
 /* Kernels launched by the most recent forward plus the most recent backward (an operator may need
  * a second, finishing kernel, so this can exceed the two operator counts). */

@@ -529,6 +529,23 @@ struct sb_encoder {
   int device = 0;
   int launches = 0;
   long long kernels_fwd = 0, kernels_bwd = 0, kernel_base = 0;   // kernels launched by the most recent passes
+  // Replay of whole passes as CUDA graphs: a pass whose pointer arguments repeat is captured once (on a private
+  // stream, the second time the same arguments are seen) and replayed from then on with one graph launch.
+  struct PassGraph {
+    std::vector<uint64_t> key;
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+    long long kernels = 0;
+    unsigned long long last_use = 0;
+  };
+  struct GraphCache {
+    std::vector<PassGraph> entries;
+    std::vector<std::vector<uint64_t>> seen;   // arguments of recent eager calls (a repeat gets captured)
+    unsigned long long tick = 0;
+  };
+  GraphCache graph_fwd, graph_bwd;
+  cudaStream_t capture_stream = nullptr;
+  bool graphs = true;           // sb_encoder_set_graphs / SUBSTATION_B200_GRAPHS=0
   bool timing = false;
   bool fuse = true;            // use the fused multi-operator kernels where the layouts allow
   std::vector<std::pair<std::string, cudaEvent_t>> marks;
@@ -695,6 +712,9 @@ extern "C" int sb_encoder_destroy(sb_encoder* e) {
   for (auto ev : e->event_pool) cudaEventDestroy(ev);
   if (e->workspace) cudaFree(e->workspace);
   if (e->gemm_ws) cudaFree(e->gemm_ws);
+  for (auto* c : {&e->graph_fwd, &e->graph_bwd})
+    for (auto& g : c->entries) cudaGraphExecDestroy(g.exec);
+  if (e->capture_stream) cudaStreamDestroy(e->capture_stream);
   delete e;
   return SB_OK;
 }
@@ -710,6 +730,12 @@ extern "C" int sb_encoder_kernel_count(sb_encoder* e) { return e ? (int)(e->kern
 extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
   if (!e) return fail(SB_ERR_ARG, "null handle");
   e->fuse = enabled != 0;
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_set_graphs(sb_encoder* e, int enabled) {
+  if (!e) return fail(SB_ERR_ARG, "null handle");
+  e->graphs = enabled != 0;
   return SB_OK;
 }
 
@@ -762,8 +788,8 @@ sb_dropout drop(float p, int mode, uint64_t seed, uint64_t offset) {
 
 }  // namespace
 
-extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, const void* const* params,
-                                  void* const* fwd, void* y, int mask_mode, uint64_t seed, uint64_t offset) {
+static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* const* params,
+                        void* const* fwd, void* y, int mask_mode, uint64_t seed, uint64_t offset) {
   if (!e || !y) return fail(SB_ERR_ARG, "sb_encoder_forward: null argument");
   if (mask_mode != SB_MASK_EXPLICIT && mask_mode != SB_MASK_PHILOX)
     return fail(SB_ERR_ARG, "sb_encoder_forward: unknown mask mode");
@@ -863,9 +889,9 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
   return SB_OK;
 }
 
-extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, void* const* dparams,
-                                   void* const* bwd, const void* const* params, void* const* fwd,
-                                   const void* x, void* dx) {
+static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* const* dparams,
+                         void* const* bwd, const void* const* params, void* const* fwd,
+                         const void* x, void* dx) {
   if (!e || !dy || !dparams || !bwd || !dx) return fail(SB_ERR_ARG, "sb_encoder_backward: null argument");
   cudaStream_t s = (cudaStream_t)stream;
   Ptrs T;
@@ -1012,3 +1038,119 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
   e->kernels_bwd = g_kernel_launches - e->kernel_base;
   return SB_OK;
 }
+
+// ---- whole-pass CUDA graphs ---------------------------------------------------------------
+namespace {
+
+bool graphs_allowed(const sb_encoder* e) {
+  static const bool env_on = [] {
+    const char* v = getenv("SUBSTATION_B200_GRAPHS");
+    return !(v && v[0] == '0');
+  }();
+  return env_on && e->graphs && !e->timing;
+}
+
+// Runs `pass(stream)` eagerly, or replays / captures it as a graph when its arguments repeat.
+// `counted(launches, kernels)` restores the handle's counters on a replay.
+template <class Pass>
+int run_pass(sb_encoder* e, sb_encoder::GraphCache& cache, std::vector<uint64_t>&& key, cudaStream_t s, int* launches,
+             long long* kernels, Pass&& pass) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (!graphs_allowed(e) || cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return pass(s);
+  }
+  ++cache.tick;
+  for (auto& g : cache.entries)
+    if (g.key == key) {
+      g.last_use = cache.tick;
+      SB_CUDA_OK(cudaGraphLaunch(g.exec, s));
+      *launches = g.launches;
+      *kernels = g.kernels;
+      return SB_OK;
+    }
+  bool seen_before = false;
+  for (size_t i = 0; i < cache.seen.size(); ++i)
+    if (cache.seen[i] == key) {
+      seen_before = true;
+      cache.seen.erase(cache.seen.begin() + i);
+      break;
+    }
+  if (!seen_before) {  // first sighting: run it as it is and remember the arguments
+    if (cache.seen.size() >= 8) cache.seen.erase(cache.seen.begin());
+    cache.seen.push_back(key);
+    return pass(s);
+  }
+  // second sighting: capture on the private stream, then launch the graph on the caller's stream
+  if (!e->capture_stream && cudaStreamCreateWithFlags(&e->capture_stream, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    e->graphs = false;
+    return pass(s);
+  }
+  if (cudaStreamBeginCapture(e->capture_stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+    cudaGetLastError();
+    e->graphs = false;
+    return pass(s);
+  }
+  const int st = pass(e->capture_stream);
+  cudaGraph_t graph = nullptr;
+  const cudaError_t ce = cudaStreamEndCapture(e->capture_stream, &graph);
+  cudaGraphExec_t exec = nullptr;
+  if (st != SB_OK || ce != cudaSuccess || !graph || cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+    // nothing has run yet (the launches only went into the capture): this handle goes back to plain
+    // launches for good, and a real error shows again in the eager pass
+    cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    e->graphs = false;
+    return pass(s);
+  }
+  cudaGraphDestroy(graph);
+  if (cache.entries.size() >= 8) {  // drop the least recently used
+    size_t victim = 0;
+    for (size_t i = 1; i < cache.entries.size(); ++i)
+      if (cache.entries[i].last_use < cache.entries[victim].last_use) victim = i;
+    cudaGraphExecDestroy(cache.entries[victim].exec);
+    cache.entries.erase(cache.entries.begin() + victim);
+  }
+  sb_encoder::PassGraph g;
+  g.key = std::move(key);
+  g.exec = exec;
+  g.launches = *launches;
+  g.kernels = *kernels;
+  g.last_use = cache.tick;
+  cache.entries.push_back(std::move(g));
+  SB_CUDA_OK(cudaGraphLaunch(exec, s));
+  return SB_OK;
+}
+
+}  // namespace
+
+extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, const void* const* params,
+                                  void* const* fwd, void* y, int mask_mode, uint64_t seed, uint64_t offset) {
+  if (!e || !y || !params || !fwd) return fail(SB_ERR_ARG, "sb_encoder_forward: null argument");
+  auto pass = [&](cudaStream_t s) { return forward_pass(e, (void*)s, x, params, fwd, y, mask_mode, seed, offset); };
+  // in-kernel masks take a new offset every call, so only explicit-mask passes repeat
+  if (mask_mode != SB_MASK_EXPLICIT) return pass((cudaStream_t)stream);
+  std::vector<uint64_t> key{(uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)y, (uint64_t)e->fuse, (uint64_t)gemm_sm_budget()};
+  for (size_t i = 0; i < e->param_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)params[i]);
+  for (size_t i = 0; i < e->fwd_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)fwd[i]);
+  return run_pass(e, e->graph_fwd, std::move(key), (cudaStream_t)stream, &e->launches, &e->kernels_fwd, pass);
+}
+
+extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, void* const* dparams,
+                                   void* const* bwd, const void* const* params, void* const* fwd,
+                                   const void* x, void* dx) {
+  if (!e || !dy || !dparams || !bwd || !dx || !params || !fwd)
+    return fail(SB_ERR_ARG, "sb_encoder_backward: null argument");
+  auto pass = [&](cudaStream_t s) { return backward_pass(e, (void*)s, dy, dparams, bwd, params, fwd, x, dx); };
+  std::vector<uint64_t> key{(uint64_t)(uintptr_t)dy, (uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)dx, (uint64_t)e->fuse,
+                            (uint64_t)gemm_sm_budget()};
+  for (size_t i = 0; i < e->param_order.size(); ++i) {
+    key.push_back((uint64_t)(uintptr_t)dparams[i]);
+    key.push_back((uint64_t)(uintptr_t)params[i]);
+  }
+  for (size_t i = 0; i < e->bwd_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)bwd[i]);
+  for (size_t i = 0; i < e->fwd_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)fwd[i]);
+  return run_pass(e, e->graph_bwd, std::move(key), (cudaStream_t)stream, &e->launches, &e->kernels_bwd, pass);
+}
+

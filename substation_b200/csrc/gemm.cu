@@ -970,6 +970,7 @@ int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws, size_t ws
 }
 
 void set_gemm_sm_budget(int n) { g_sm_budget = n; }
+int gemm_sm_budget() { return g_sm_budget; }
 
 namespace {
 

@@ -84,6 +84,7 @@ int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws = nullptr,
 extern thread_local int g_last_gemm_impl;
 // Number of SMs the persistent contraction kernels may occupy (0 = all).
 void set_gemm_sm_budget(int n);
+int gemm_sm_budget();
 // Non-zero once a tcgen05 kernel on this process reported a bounded wait running out.
 int gemm_device_error(cudaStream_t s, int* code);
 

@@ -264,6 +264,7 @@ class Encoder(torch.nn.Module):
             if self.profiling:
                 _lib.check(lib.sb_encoder_set_timing(handle, 1))
             _lib.check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
+            self._graphs_state = None
         self._handle, self._handle_device = handle, device
         return handle
 
@@ -305,9 +306,18 @@ class Encoder(torch.nn.Module):
             arr[i] = base + off if t is None else t.data_ptr()
         return arr
 
+    def _graphs_now(self, h, on):
+        """Graph replay pays when the buffers of a pass repeat (raw passes into caller-held arenas); the autograd
+        path allocates fresh arenas per step, where capturing would only cost host time."""
+        on = bool(on and self.__dict__.get('_graphs', True))
+        if self.__dict__.get('_graphs_state') != on:
+            _lib.check(_lib.load().sb_encoder_set_graphs(h, int(on)))
+            self._graphs_state = on
+
     def _forward_ptrs(self, X, weights, fwd_ptrs, Y):
         lib = _lib.load()
         h = self._native(X.device)
+        self._graphs_now(h, False)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
         _lib.check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
@@ -317,6 +327,7 @@ class Encoder(torch.nn.Module):
     def _backward_ptrs(self, DY, grad_ptrs, bwd_ptrs, weights, fwd_ptrs, X, DX):
         lib = _lib.load()
         h = self._native(DY.device)
+        self._graphs_now(h, False)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
         _lib.check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
                                            self._ptrs(weights), fwd_ptrs, ctypes.c_void_p(X.data_ptr()),
@@ -330,6 +341,7 @@ class Encoder(torch.nn.Module):
         X = X.contiguous()
         lib = _lib.load()
         h = self._native(X.device)
+        self._graphs_now(h, True)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
         wl = [w.contiguous() for w in weights]
@@ -345,6 +357,7 @@ class Encoder(torch.nn.Module):
         self._check_input(DY, 'DY')
         lib = _lib.load()
         h = self._native(DY.device)
+        self._graphs_now(h, True)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
         wl = [w.contiguous() for w in weights]
         _lib.check(lib.sb_encoder_backward(
@@ -371,6 +384,11 @@ class Encoder(torch.nn.Module):
         """The flat fp16 tensor that holds all 12 parameter gradients of the most recent autograd backward
         (each ``.grad`` is a view into it): a data-parallel caller sums one tensor instead of twelve."""
         return self.__dict__.get('_grad_bucket')
+
+    def set_graphs(self, enabled):
+        """Replay passes whose buffers repeat as CUDA graphs (default) or launch every kernel each time."""
+        self._graphs = bool(enabled)
+        self._graphs_state = None
 
     def launch_count(self):
         """Operators launched by the most recent raw pass."""
