@@ -539,7 +539,7 @@ def run_stack(args):
         ms = float(t.item())
     if rank == 0:
         cfg = workload_config(args, args.layouts)
-        cfg['workload'] = f'{args.layers}-layer stack of: ' + cfg['workload'] + ' (Philox masks)'
+        cfg['workload'] = (f'{args.layers}-layer stack of: ' + cfg['workload']).replace('seeded explicit masks', 'in-kernel Philox masks')
         cfg['layers'] = args.layers
         print(json.dumps({
             'metric': METRIC, 'value': world * args.batch * args.steps / (ms / 1e3), 'unit': UNIT, 'n_gpus': world,
