@@ -45,6 +45,9 @@ GEMM_FLOPS = {
     'dWout': lambda B, L: 2 * E * E * B * L, 'dXout': lambda B, L: 2 * E * E * B * L,
     'dXQKV-fused': lambda B, L: 2 * 3 * E * E * B * L, 'dWQKV-fused': lambda B, L: 2 * 3 * E * E * B * L,
 }
+GEMM_FLOPS['QKV-fused+aib'] = GEMM_FLOPS['QKV-fused']
+GEMM_FLOPS['lin1+bad'] = GEMM_FLOPS['lin1']
+GEMM_FLOPS['dXQKV-fused+bei'] = GEMM_FLOPS['dXQKV-fused']
 for _n in ('QKT', 'gamma', 'dX1gamma', 'dX2gamma', 'dX1QKT', 'dX2QKT'):
     GEMM_FLOPS[_n] = lambda B, L: 2 * H * B * L * L * P
 # attention contractions are HBM-bound: minimum operand bytes (two [P,L] operands + one [L,L], or v.v.)

@@ -256,6 +256,33 @@ int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, const char* 
               int impl, void* workspace, size_t workspace_bytes);
 /* Which kernel the last sb_einsum on this thread ran: SB_GEMM_TCGEN05 or SB_GEMM_SIMT. */
 int sb_einsum_last_impl(void);
+
+/* Elementwise operators folded into the epilogue of a contraction: c is written as by sb_einsum, and the
+ * operator that would read it next is applied to the rounded fp16 values on their way out, with the same
+ * arithmetic as the separate kernel (results are bit-identical to sb_einsum followed by that operator):
+ *   SB_EPI_BIAS              out2 = c + bias               (sb_attention_input_biases, pytorch_module/encoder.cu:105-113)
+ *   SB_EPI_RESIDUAL          out2 = c + resid              (sb_backward_encoder_input, pytorch_module/encoder.cu:294-296)
+ *   SB_EPI_BIAS_ACT_DROPOUT  out2 = c + bias, out3 = mask * act(out2)   (sb_bias_activation_dropout, :142-145)
+ * resid, mask, out2, out3: dims, sizes and strides of c (mask in bytes).  bias: a dense vector over exactly the
+ * indices c shares with only one of the operands, nested as in c.  With SB_MASK_PHILOX the mask is generated
+ * and written; c must then be dense in the order logical_dims gives.  SB_ERR_UNSUPPORTED unless the
+ * contraction runs on the paired-CTA tcgen05 kernel (single batch, M, N, K >= 256, unit-stride columns,
+ * N a multiple of 64); the caller then runs the two calls separately. */
+typedef enum sb_epilogue_kind { SB_EPI_BIAS = 1, SB_EPI_RESIDUAL = 2, SB_EPI_BIAS_ACT_DROPOUT = 3 } sb_epilogue_kind;
+typedef struct sb_epilogue {
+  int kind;
+  const char* bias_dims;
+  const sb_tensor* bias;
+  const sb_tensor* resid;
+  const sb_tensor* mask;
+  const sb_tensor* out2;
+  const sb_tensor* out3;
+  int activation;
+  const sb_dropout* dropout;
+  const char* logical_dims;
+} sb_epilogue;
+int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
+                    const char* c_dims, const sb_tensor* c, float alpha, const sb_epilogue* epilogue);
 /* Every wait inside the tcgen05 kernel is bounded; when one runs out the kernel
  * records a code (1 producer, 2 MMA issuer, 3 epilogue), drains and returns.
  * This reads that sticky per-process flag after synchronising `stream`

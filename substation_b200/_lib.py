@@ -29,6 +29,14 @@ class SbDropout(ctypes.Structure):
                 ('offset', ctypes.c_uint64)]
 
 
+class SbEpilogue(ctypes.Structure):
+    _fields_ = [('kind', ctypes.c_int32), ('bias_dims', c_char_p), ('bias', ctypes.POINTER(SbTensor)),
+                ('resid', ctypes.POINTER(SbTensor)), ('mask', ctypes.POINTER(SbTensor)),
+                ('out2', ctypes.POINTER(SbTensor)), ('out3', ctypes.POINTER(SbTensor)),
+                ('activation', ctypes.c_int32), ('dropout', ctypes.POINTER(SbDropout)),
+                ('logical_dims', c_char_p)]
+
+
 class SbEncoderConfig(ctypes.Structure):
     _fields_ = [('batch', ctypes.c_int32), ('seq', ctypes.c_int32), ('heads', ctypes.c_int32),
                 ('embed', ctypes.c_int32), ('activation', ctypes.c_int32),
@@ -77,6 +85,7 @@ SIGNATURES = {
     'sb_backward_encoder_input': (c_int, [c_void_p, _T, _T, _T]),
     'sb_einsum': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, c_int, c_void_p,
                         ctypes.c_size_t]),
+    'sb_einsum_fused': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, ctypes.POINTER(SbEpilogue)]),
     'sb_einsum_last_impl': (c_int, []),
     'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
     'sb_set_sm_budget': (c_int, [c_int]),

@@ -465,6 +465,85 @@ extern "C" int sb_einsum(void* stream, const char* a_dims, const sb_tensor* a, c
     return fail(SB_ERR_ALIGNMENT, "einsum: workspace must be 16-byte aligned");
   return run_gemm((cudaStream_t)stream, g, impl, workspace, workspace ? workspace_bytes : 0);
 }
+namespace {
+bool same_geometry(const sb_tensor* t, const sb_tensor* c) {
+  if (!t || !t->ptr || t->ndim != c->ndim) return false;
+  for (int i = 0; i < c->ndim; ++i)
+    if (t->size[i] != c->size[i] || t->stride[i] != c->stride[i]) return false;
+  return true;
+}
+}  // namespace
+
+extern "C" int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims,
+                               const sb_tensor* b, const char* c_dims, const sb_tensor* c, float alpha,
+                               const sb_epilogue* ep) {
+  if (!ep) return fail(SB_ERR_ARG, "einsum_fused: null epilogue");
+  GemmProblem g;
+  SB_TRY(plan_einsum(a_dims, a, b_dims, b, c_dims, c, alpha, &g));
+  GemmEpilogue ge{};
+  ge.kind = ep->kind;
+  if (ep->kind != SB_EPI_BIAS && ep->kind != SB_EPI_RESIDUAL && ep->kind != SB_EPI_BIAS_ACT_DROPOUT)
+    return fail(SB_ERR_ARG, "einsum_fused: unknown epilogue kind");
+  if (!same_geometry(ep->out2, c)) return fail(SB_ERR_ARG, "einsum_fused: out2 must have the sizes and strides of c");
+  ge.out2 = ep->out2->ptr;
+  const std::string ad(a_dims), bd(b_dims), cd(c_dims);
+  if (ep->kind == SB_EPI_BIAS || ep->kind == SB_EPI_BIAS_ACT_DROPOUT) {
+    if (!ep->bias || !ep->bias->ptr || !ep->bias_dims) return fail(SB_ERR_ARG, "einsum_fused: bias missing");
+    const std::string vd(ep->bias_dims);
+    if ((int)vd.size() != ep->bias->ndim) return fail(SB_ERR_ARG, "einsum_fused: bias dims do not match its rank");
+    // the bias indices must be exactly the indices of c that come from one operand only
+    auto only = [&](const std::string& mine, const std::string& other) {
+      std::string r;
+      for (char ch : cd)
+        if (mine.find(ch) != std::string::npos && other.find(ch) == std::string::npos) r += ch;
+      return r;
+    };
+    const std::string m_group = only(ad, bd), n_group = only(bd, ad);
+    auto same_set = [](std::string x, std::string y) {
+      std::sort(x.begin(), x.end());
+      std::sort(y.begin(), y.end());
+      return x == y;
+    };
+    int along_m;
+    if (same_set(vd, m_group)) along_m = 1;
+    else if (same_set(vd, n_group)) along_m = 0;
+    else return fail(SB_ERR_UNSUPPORTED, "einsum_fused: bias does not span one operand's own indices of c");
+    const long long unit = along_m ? g.sCm : g.sCn;
+    for (size_t i = 0; i < vd.size(); ++i) {
+      const size_t ci = cd.find(vd[i]);
+      if (ep->bias->size[i] != c->size[ci]) return fail(SB_ERR_ARG, "einsum_fused: bias extent differs from c");
+      if (c->size[ci] > 1 && c->stride[ci] != ep->bias->stride[i] * unit)
+        return fail(SB_ERR_UNSUPPORTED, "einsum_fused: bias is not nested like the matching indices of c");
+    }
+    ge.vec = ep->bias->ptr;
+    ge.vec_along_m = along_m;
+  }
+  if (ep->kind == SB_EPI_RESIDUAL) {
+    if (!same_geometry(ep->resid, c)) return fail(SB_ERR_ARG, "einsum_fused: resid must have the sizes and strides of c");
+    ge.resid = ep->resid->ptr;
+  }
+  if (ep->kind == SB_EPI_BIAS_ACT_DROPOUT) {
+    if (!same_geometry(ep->out3, c) || !same_geometry(ep->mask, c))
+      return fail(SB_ERR_ARG, "einsum_fused: out3 and mask must have the sizes and strides of c");
+    SB_TRY(check_activation(ep->activation));
+    SB_TRY(to_rng(ep->dropout, &ge.rng));
+    ge.out3 = ep->out3->ptr;
+    ge.mask = ep->mask->ptr;
+    ge.activation = ep->activation;
+    if (ge.rng.philox) {
+      // the generator is keyed by the logical element index: c must be dense in logical order
+      if (!ep->logical_dims || cd != ep->logical_dims)
+        return fail(SB_ERR_UNSUPPORTED, "einsum_fused: in-kernel masks need c stored in its logical order");
+      long long dense = 1;
+      for (int i = c->ndim - 1; i >= 0; --i) {
+        if (c->size[i] > 1 && c->stride[i] != dense)
+          return fail(SB_ERR_UNSUPPORTED, "einsum_fused: in-kernel masks need a dense c");
+        dense *= c->size[i];
+      }
+    }
+  }
+  return run_gemm_fused((cudaStream_t)stream, g, ge);
+}
 extern "C" int sb_einsum_last_impl(void) { return g_last_gemm_impl; }
 extern "C" int sb_set_sm_budget(int n_sms) {
   if (n_sms < 0) return fail(SB_ERR_ARG, "sb_set_sm_budget: negative SM count");
@@ -644,6 +723,21 @@ int einsum(sb_encoder* e, cudaStream_t s, const char* name, const std::string& a
   return run_gemm(s, g, SB_GEMM_AUTO, e->gemm_ws, e->gemm_ws_bytes);
 }
 
+// Contraction with the following elementwise operator in its epilogue; SB_ERR_UNSUPPORTED (nothing launched,
+// nothing marked) when the contraction kernel that can do it does not take this problem.
+int einsum_fused(sb_encoder* e, cudaStream_t s, const char* name, const std::string& ad, const void* a,
+                 const std::string& bd, const void* b, const std::string& cd, void* c, float alpha,
+                 const sb_epilogue* ep) {
+  e->mark(s, name);
+  const sb_tensor ta = e->mem(a, ad), tb = e->mem(b, bd), tc = e->mem(c, cd);
+  const int st = sb_einsum_fused((void*)s, ad.c_str(), &ta, bd.c_str(), &tb, cd.c_str(), &tc, alpha, ep);
+  if (st == SB_ERR_UNSUPPORTED || st == SB_ERR_ALIGNMENT) {
+    e->unmark();
+    return SB_ERR_UNSUPPORTED;
+  }
+  return st;
+}
+
 }  // namespace
 
 extern "C" int sb_encoder_create(const sb_encoder_config* cfg, sb_encoder** out) {
@@ -805,13 +899,28 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
   const std::string lKK = L.at("KKQQVV").substr(1);
 
   // F1: stacked K,Q,V projections
-  SB_TRY(einsum(e, s, "QKV-fused", L.at("X"), T["X"], L.at("WKQV"), T["WKQV"], L.at("WKKWQQWVV"),
-                T["WKKWQQWVV"], 1.f));
   {
-    e->mark(s, "aib");
-    sb_tensor in = e->view(T["WKKWQQWVV"], "WKKWQQWVV"), out = e->view(T["KKQQVV"], "KKQQVV");
-    sb_tensor bias = e->view(T["BKQV"], "BKQV");
-    SB_TRY(sb_attention_input_biases(stream, &in, &bias, &out));
+    // the input biases ride on the projection's epilogue when both stacked tensors share a layout
+    int st = SB_ERR_UNSUPPORTED;
+    if (e->fuse && L.at("WKKWQQWVV") == L.at("KKQQVV")) {
+      const sb_tensor out2 = e->mem(T["KKQQVV"], L.at("KKQQVV")), bias = e->mem(T["BKQV"], L.at("BKQV"));
+      sb_epilogue ep{};
+      ep.kind = SB_EPI_BIAS;
+      ep.bias_dims = L.at("BKQV").c_str();
+      ep.bias = &bias;
+      ep.out2 = &out2;
+      st = einsum_fused(e, s, "QKV-fused+aib", L.at("X"), T["X"], L.at("WKQV"), T["WKQV"], L.at("WKKWQQWVV"),
+                        T["WKKWQQWVV"], 1.f, &ep);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+    }
+    if (st == SB_ERR_UNSUPPORTED) {
+      SB_TRY(einsum(e, s, "QKV-fused", L.at("X"), T["X"], L.at("WKQV"), T["WKQV"], L.at("WKKWQQWVV"),
+                    T["WKKWQQWVV"], 1.f));
+      e->mark(s, "aib");
+      sb_tensor in = e->view(T["WKKWQQWVV"], "WKKWQQWVV"), out = e->view(T["KKQQVV"], "KKQQVV");
+      sb_tensor bias = e->view(T["BKQV"], "BKQV");
+      SB_TRY(sb_attention_input_biases(stream, &in, &bias, &out));
+    }
   }
   // F2 + softmax.  K and V views are the J-indexed projections relabelled with K.
   {
@@ -861,15 +970,36 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
     SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask, &in, &diff,
                                               &istd, &ln, &out, &d));
   }
-  SB_TRY(einsum(e, s, "lin1", L.at("SB1"), T["SB1"], L.at("LINW1"), T["LINW1"], L.at("SB1_LINW1"),
-                T["SB1_LINW1"], 1.f));
   {
-    e->mark(s, "bad");
-    sb_tensor in = e->view(T["SB1_LINW1"], "SB1_LINW1"), bias = e->view(T["LINB1"], "LINB1");
-    sb_tensor mask = e->view(T["DROP2MASK"], "DROP2MASK"), lin1 = e->view(T["LIN1"], "LIN1");
-    sb_tensor d2 = e->view(T["DROP2"], "DROP2");
+    // bias + activation + dropout in the epilogue of the first feed-forward contraction
     sb_dropout d = drop(e->p_act, mask_mode, seed, offset + 2);
-    SB_TRY(sb_bias_activation_dropout(stream, &in, &bias, &mask, &lin1, &d2, e->activation, &d));
+    int st = SB_ERR_UNSUPPORTED;
+    const std::string& lc = L.at("SB1_LINW1");
+    if (e->fuse && lc == L.at("LIN1") && lc == L.at("DROP2") && lc == L.at("DROP2MASK")) {
+      const sb_tensor out2 = e->mem(T["LIN1"], lc), out3 = e->mem(T["DROP2"], lc), mask = e->mem(T["DROP2MASK"], lc);
+      const sb_tensor bias = e->mem(T["LINB1"], L.at("LINB1"));
+      sb_epilogue ep{};
+      ep.kind = SB_EPI_BIAS_ACT_DROPOUT;
+      ep.bias_dims = L.at("LINB1").c_str();
+      ep.bias = &bias;
+      ep.mask = &mask;
+      ep.out2 = &out2;
+      ep.out3 = &out3;
+      ep.activation = e->activation;
+      ep.dropout = &d;
+      ep.logical_dims = "BJU";
+      st = einsum_fused(e, s, "lin1+bad", L.at("SB1"), T["SB1"], L.at("LINW1"), T["LINW1"], lc, T["SB1_LINW1"], 1.f, &ep);
+      if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
+    }
+    if (st == SB_ERR_UNSUPPORTED) {
+      SB_TRY(einsum(e, s, "lin1", L.at("SB1"), T["SB1"], L.at("LINW1"), T["LINW1"], L.at("SB1_LINW1"),
+                    T["SB1_LINW1"], 1.f));
+      e->mark(s, "bad");
+      sb_tensor in = e->view(T["SB1_LINW1"], "SB1_LINW1"), bias = e->view(T["LINB1"], "LINB1");
+      sb_tensor mask = e->view(T["DROP2MASK"], "DROP2MASK"), lin1 = e->view(T["LIN1"], "LIN1");
+      sb_tensor d2 = e->view(T["DROP2"], "DROP2");
+      SB_TRY(sb_bias_activation_dropout(stream, &in, &bias, &mask, &lin1, &d2, e->activation, &d));
+    }
   }
   SB_TRY(einsum(e, s, "lin2", L.at("DROP2"), T["DROP2"], L.at("LINW2"), T["LINW2"], L.at("DROP2_LINW2"),
                 T["DROP2_LINW2"], 1.f));
@@ -1020,8 +1150,21 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
       SB_TRY(einsum(e, s, "dX2QKT", lKK, QQ, L.at("DBETA"), T["DBETA"], rename(lDKK, 'J', 'K'), DKK, scale));
     }
   }
-  SB_TRY(einsum(e, s, "dXQKV-fused", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
-                T["DXATT"], 1.f));
+  // the encoder-input gradient (DXATT + DRESID1) rides on the epilogue of the contraction that produces DXATT
+  int st_bei = SB_ERR_UNSUPPORTED;
+  if (e->fuse && L.at("DXATT") == L.at("DRESID1") && L.at("DXATT") == L.at("X")) {
+    const sb_tensor resid = e->mem(T["DRESID1"], L.at("DRESID1")), out2 = e->mem(dx, L.at("X"));
+    sb_epilogue ep{};
+    ep.kind = SB_EPI_RESIDUAL;
+    ep.resid = &resid;
+    ep.out2 = &out2;
+    st_bei = einsum_fused(e, s, "dXQKV-fused+bei", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
+                          T["DXATT"], 1.f, &ep);
+    if (st_bei != SB_OK && st_bei != SB_ERR_UNSUPPORTED) return st_bei;
+  }
+  if (st_bei == SB_ERR_UNSUPPORTED)
+    SB_TRY(einsum(e, s, "dXQKV-fused", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
+                  T["DXATT"], 1.f));
   SB_TRY(einsum(e, s, "dWQKV-fused", L.at("X"), T["X"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("WKQV"),
                 D.at("WKQV"), 1.f));
   {
@@ -1029,7 +1172,7 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     sb_tensor d = v("DKKQQVV"), db = dv("BKQV");
     SB_TRY(sb_backward_attention_input_biases(stream, &d, &db));
   }
-  {
+  if (st_bei == SB_ERR_UNSUPPORTED) {
     e->mark(s, "bei");
     sb_tensor a = v("DXATT"), b = v("DRESID1");
     SB_TRY(sb_backward_encoder_input(stream, &a, &b, &tDX));

@@ -272,6 +272,24 @@ __device__ __forceinline__ uint4 mask_apply(const uint4& v, const uint2& m) {
   return o;
 }
 
+// lane-wise sum of 8 packed halves (fp16 arithmetic, one rounding, like the flat elementwise kernels)
+__device__ __forceinline__ uint4 hadd8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&a);
+  const __half2* y = reinterpret_cast<const __half2*>(&b);
+  __half2* q = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = __hadd2(x[i], y[i]);
+  return o;
+}
+
+__device__ __forceinline__ float act_fwd(float x, int activation) {
+  if (activation == SB_ACT_RELU) return fmaxf(x, 0.f);
+  // tanh-form GELU
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+
 // Contiguous per-feature vectors (bias, gamma, beta): [F], unit stride.
 __device__ __forceinline__ void load8p(const void* base, int f, int F, int vec, float v[8]) {
   load8h(base, 0, 1, vec, f, F, v, 0.f);

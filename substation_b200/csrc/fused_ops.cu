@@ -34,12 +34,6 @@ __device__ __forceinline__ void philox8(const Rng& r, unsigned long long e0, uin
   else philox_keep8_unaligned(r, e0, m);
 }
 
-__device__ __forceinline__ float act_fwd(float x, int activation) {
-  if (activation == SB_ACT_RELU) return fmaxf(x, 0.f);
-  // tanh-form GELU
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.f + tanhf(u));
-}
 __device__ __forceinline__ float act_bwd(float x, float dy, int activation) {
   if (activation == SB_ACT_RELU) return x > 0.f ? dy : 0.f;
   const float x3 = x * x * x;
@@ -56,15 +50,6 @@ __device__ __forceinline__ uint4 hmul8(const uint4& a, const uint4& b) {
   __half2* q = reinterpret_cast<__half2*>(&o);
 #pragma unroll
   for (int i = 0; i < 4; ++i) q[i] = __hmul2(x[i], y[i]);
-  return o;
-}
-__device__ __forceinline__ uint4 hadd8(const uint4& a, const uint4& b) {
-  uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&a);
-  const __half2* y = reinterpret_cast<const __half2*>(&b);
-  __half2* q = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) q[i] = __hadd2(x[i], y[i]);
   return o;
 }
 

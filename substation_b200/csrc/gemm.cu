@@ -242,6 +242,22 @@ constexpr unsigned long long kWaitNs = 2000000000ull;
 
 __device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel in this process
 
+// Work fused behind a contraction's epilogue (paired-CTA kernel, TMA-store mode).  All extra tensors have C's
+// geometry; the arithmetic on the stored fp16 values is the flat elementwise kernels', so results are identical
+// to running those kernels on C afterwards.
+//   kind 1: out2 = C + bias                        (attention input biases)
+//   kind 2: out2 = C + resid                       (encoder-input gradient)
+//   kind 3: out2 = C + bias, out3 = mask * act(out2)   (bias + activation + dropout)
+struct EpiParams {
+  int kind;
+  int vec_along_m;       // bias indexed by the row (m) instead of the column (n)
+  const __half* vec;
+  const __half* resid;   // [M][N], row stride sCm
+  uint8_t* mask;         // [M][N] bytes, row stride sCm; read, or written when rng.philox
+  int activation;
+  Rng rng;
+};
+
 struct TcParams {
   long long M, N, K;
   long long sCb, sCm, sCn;
@@ -254,6 +270,7 @@ struct TcParams {
   int tiles_m, tiles_n, batch;
   int splits, kt_per_split;  // split-K: K stages per split
   long long tiles;     // tiles_m * tiles_n * batch * splits
+  EpiParams epi;       // paired-CTA kernel only
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -819,7 +836,7 @@ int pair_clusters() {
   if (dev != cached_dev) {
     cached_dev = dev;
     cached = 0;
-    if (cudaFuncSetAttribute(pair::gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(pair::gemm_tc_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              pair::kSmemBytes) == cudaSuccess) {
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
@@ -832,7 +849,7 @@ int pair_clusters() {
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, pair::gemm_tc_pair_kernel, &cfg) == cudaSuccess) cached = n;
+      if (cudaOccupancyMaxActiveClusters(&n, pair::gemm_tc_pair_kernel<0>, &cfg) == cudaSuccess) cached = n;
       else cudaGetLastError();
     } else {
       cudaGetLastError();
@@ -849,8 +866,10 @@ bool pair_enabled() {
   return on;
 }
 
-int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b, int clusters) {
+int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b, int clusters,
+                   const GemmEpilogue* epi = nullptr, bool vec_flipped = false) {
   TcParams p;
+  memset(&p.epi, 0, sizeof(p.epi));
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
   p.C = g.C;
@@ -877,7 +896,41 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
   }
   const int budget = sm_count() / 2;
   const unsigned nclusters = (unsigned)std::max<long long>(1, std::min<long long>(p.tiles, std::min(clusters, budget)));
-  SB_LAUNCH_OK(launch_k(pair::gemm_tc_pair_kernel, 2 * nclusters, kTcThreads, pair::kSmemBytes, s, a.map, b.map, cmap, p));
+  CUtensorMap cmap2, cmap3;
+  memset(&cmap2, 0, sizeof(cmap2));
+  memset(&cmap3, 0, sizeof(cmap3));
+  if (epi) {
+    // fused epilogue work needs the TMA-store path and whole 64-column blocks
+    if (p.c_mode != 2 || g.N % 64 != 0)
+      return fail(SB_ERR_UNSUPPORTED, "fused epilogue: output rows must be TMA-addressable with N a multiple of 64");
+    std::string why;
+    int sw = 0;
+    if (!encode_map(epi->out2, (cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch, g.sCm, g.sCb, 64, 32, &cmap2, &sw, &why) ||
+        sw != p.c_swap)
+      return fail(SB_ERR_UNSUPPORTED, "fused epilogue, second output: " + why);
+    if (epi->kind == 3 && (!encode_map(epi->out3, (cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch, g.sCm, g.sCb, 64, 32, &cmap3,
+                                       &sw, &why) || sw != p.c_swap))
+      return fail(SB_ERR_UNSUPPORTED, "fused epilogue, third output: " + why);
+    p.epi.kind = epi->kind;
+    p.epi.vec_along_m = vec_flipped ? !epi->vec_along_m : epi->vec_along_m;
+    p.epi.vec = reinterpret_cast<const __half*>(epi->vec);
+    p.epi.resid = reinterpret_cast<const __half*>(epi->resid);
+    p.epi.mask = reinterpret_cast<uint8_t*>(epi->mask);
+    p.epi.activation = epi->activation;
+    p.epi.rng = epi->rng;
+  }
+  const int kind = epi ? epi->kind : 0;
+  auto launch = [&](auto kernel) {
+    // per-device attribute; setting it is cheap and idempotent
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes) != cudaSuccess)
+      return cudaGetLastError();
+    return launch_k(kernel, 2 * nclusters, kTcThreads, pair::kSmemBytes, s, a.map, b.map, cmap, cmap2, cmap3, p);
+  };
+  if (kind == 0) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<0>));
+  else if (kind == 1) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<1>));
+  else if (kind == 2) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<2>));
+  else if (kind == 3) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<3>));
+  else return fail(SB_ERR_ARG, "fused epilogue: unknown kind");
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -913,7 +966,7 @@ bool tcgen05_supported(const GemmProblem& g, std::string* why) {
   return true;
 }
 
-int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0, void* ws, size_t ws_bytes) {
+int launch_gemm_tcgen05_epi(cudaStream_t s, const GemmProblem& g0, void* ws, size_t ws_bytes, const GemmEpilogue* epi) {
   std::string why;
   if (!tcgen05_supported(g0, &why)) return fail(SB_ERR_UNSUPPORTED, "tcgen05 contraction: " + why);
   std::call_once(g_encode_once, load_encode);
@@ -943,11 +996,12 @@ int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0, void* ws, size_t 
         return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
       if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, 128, &b, &why))
         return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand B: " + why);
-      const int st2 = launch_tc_pair(s, g, a, b, clusters);
+      const int st2 = launch_tc_pair(s, g, a, b, clusters, epi, swap);
       if (st2 == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
       return st2;
     }
   }
+  if (epi) return fail(SB_ERR_UNSUPPORTED, "fused epilogue: only the paired-CTA kernel (large single-batch problems) has it");
   if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
     return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
   if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))
@@ -958,6 +1012,14 @@ int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g0, void* ws, size_t 
   else st = launch_tc<64, 2>(s, g, a, b, ws, ws_bytes);
   if (st == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
   return st;
+}
+
+int launch_gemm_tcgen05(cudaStream_t s, const GemmProblem& g, void* ws, size_t ws_bytes) {
+  return launch_gemm_tcgen05_epi(s, g, ws, ws_bytes, nullptr);
+}
+
+int run_gemm_fused(cudaStream_t s, const GemmProblem& g, const GemmEpilogue& epi) {
+  return launch_gemm_tcgen05_epi(s, g, nullptr, 0, &epi);
 }
 
 int run_gemm(cudaStream_t s, const GemmProblem& g, int impl, void* ws, size_t ws_bytes) {

@@ -68,9 +68,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
 }
 
 // Persistent: cluster c works on pair tiles c, c + (#clusters), ...; n fastest, then m (256 rows), then batch.
+// EPI: 0 plain, else EpiParams::kind (extra outputs through tmC2 / tmC3, TMA-store mode only).
+template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
+                    const __grid_constant__ CUtensorMap tmC3, const TcParams p) {
   constexpr int S = kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -101,6 +104,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
     if (p.c_mode == 2) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC) : "memory");
+    if (EPI != 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC2) : "memory");
+    if (EPI == 3) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmC3) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -231,26 +236,109 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);
           }
-          const uint32_t sbuf = nstore & 1u;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          uint8_t* row = my_stage_gen + sbuf * 4096 + lane * 128;
+          const int nc = n0 + c * 64, mc = m0 + q * 32;
+          const bool in_range = nc < p.N && mc < p.M;
+          // stage 8 x 16 bytes of this thread's row and store the warp's 32 x 64 block through `map`
+          auto put = [&](const CUtensorMap* map, const uint4* v8) {
+            const uint32_t sbuf = nstore & 1u;
+            // the store issued two blocks ago must have finished reading this buffer
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint8_t* row = my_stage_gen + sbuf * 4096 + lane * 128;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(row + ((v ^ (lane & 7)) << 4)) = v8[v];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && in_range) {
+              if (p.c_swap) tma_store_3d(map, my_stage + sbuf * 4096, nc, (int)bt, mc);
+              else tma_store_3d(map, my_stage + sbuf * 4096, nc, mc, (int)bt);
+            }
+            if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            ++nstore;
+          };
+          // side inputs of the fused work: requested before the arithmetic on the accumulator
+          uint4 side[8];
+          uint2 mk[8];
+          const bool row_ok = m < p.M && nc < p.N;
+          if (EPI == 1 || EPI == 3) {
+            if (p.epi.vec_along_m) {
+              const __half2 b2 = __half2half2(m < p.M ? p.epi.vec[m] : __float2half(0.f));
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(&b2);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) side[v] = make_uint4(w, w, w, w);
+            } else if (nc < p.N) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) side[v] = *reinterpret_cast<const uint4*>(p.epi.vec + nc + 8 * v);
+            }
+          }
+          if (EPI == 2 && row_ok) {
+            const __half* rp = p.epi.resid + m * p.sCm + nc;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) side[v] = *reinterpret_cast<const uint4*>(rp + 8 * v);
+          }
+          if (EPI == 3 && !p.epi.rng.philox && row_ok) {
+            const uint8_t* kp = p.epi.mask + m * p.sCm + nc;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 t4 = *reinterpret_cast<const uint4*>(kp + 16 * v);
+              mk[2 * v] = make_uint2(t4.x, t4.y);
+              mk[2 * v + 1] = make_uint2(t4.z, t4.w);
+            }
+          }
+          uint4 o1[8];
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             float f[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
-            *reinterpret_cast<uint4*>(row + ((v ^ (lane & 7)) << 4)) = pack8(f);
+            o1[v] = pack8(f);
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          const int nc = n0 + c * 64, mc = m0 + q * 32;
-          if (lane == 0 && nc < p.N && mc < p.M) {
-            if (p.c_swap) tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, (int)bt, mc);
-            else tma_store_3d(&tmC, my_stage + sbuf * 4096, nc, mc, (int)bt);
+          put(&tmC, o1);
+          if (EPI == 1 || EPI == 2) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) o1[v] = hadd8(o1[v], side[v]);
+            put(&tmC2, o1);
           }
-          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          ++nstore;
+          if (EPI == 3) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) o1[v] = hadd8(o1[v], side[v]);   // the biased pre-activation
+            put(&tmC2, o1);
+            if (p.epi.rng.philox) {
+              // keep flags of the logical elements (m, nc + 8v ..): C is dense in logical order, so the
+              // element index is the memory offset
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                uint32_t mm[8];
+                philox_keep8(p.epi.rng, (unsigned long long)(m * p.sCm + nc + 8 * v) >> 3, mm);
+                mk[v] = mask_pack(mm);
+              }
+              if (row_ok) {
+                uint8_t* kp = p.epi.mask + m * p.sCm + nc;
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                  *reinterpret_cast<uint4*>(kp + 16 * v) = make_uint4(mk[2 * v].x, mk[2 * v].y, mk[2 * v + 1].x, mk[2 * v + 1].y);
+              }
+            }
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint4 a;
+              if (p.epi.activation == SB_ACT_RELU) {
+                const __half2* h = reinterpret_cast<const __half2*>(&o1[v]);
+                __half2* qq = reinterpret_cast<__half2*>(&a);
+                const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qq[i] = __hmax2(h[i], zero);
+              } else {
+                float x[8];
+                unpack8(o1[v], x);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = act_fwd(x[e], SB_ACT_GELU);
+                a = pack8(x);
+              }
+              o1[v] = mask_apply(a, mk[v]);
+            }
+            put(&tmC3, o1);
+          }
         }
       } else {
         __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;

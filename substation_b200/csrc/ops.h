@@ -73,6 +73,23 @@ struct GemmProblem {
   void* C;
   float alpha;
 };
+// Elementwise work fused behind the epilogue of a contraction (see EpiParams in gemm.cu).  out2 / out3 / resid /
+// mask have C's shape and strides (mask: in bytes); vec is a dense vector over C's rows (vec_along_m) or columns.
+struct GemmEpilogue {
+  int kind;            // 1 bias -> out2; 2 residual -> out2; 3 bias + activation + dropout -> out2, out3
+  int vec_along_m;
+  const void* vec;
+  const void* resid;
+  void* mask;
+  int activation;
+  Rng rng;
+  void* out2;
+  void* out3;
+};
+// The contraction with fused epilogue work; SB_ERR_UNSUPPORTED unless the problem runs on the paired-CTA
+// kernel with TMA stores (large, single batch, unit-stride columns, N a multiple of 64).
+int run_gemm_fused(cudaStream_t s, const GemmProblem& g, const GemmEpilogue& epi);
+
 // Collapse an einsum over strided operands into one batched GEMM (error if it is not one).
 int plan_einsum(const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
                 const char* c_dims, const sb_tensor* c, float alpha, GemmProblem* out);

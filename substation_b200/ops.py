@@ -210,6 +210,41 @@ def einsum(spec, a, b, c, alpha=1.0, impl='auto', workspace=None):
     return {SB_GEMM_TCGEN05: 'tcgen05', SB_GEMM_SIMT: 'simt'}.get(lib.sb_einsum_last_impl(), '?')
 
 
+def einsum_fused(spec, a, b, c, alpha=1.0, *, kind, out2, bias=None, bias_dims=None, resid=None, mask=None, out3=None,
+                 activation='relu', p=0.0, mode='explicit', seed=0, offset=0, logical_dims=None):
+    """einsum into c with the next elementwise operator folded into the contraction's epilogue:
+    kind='bias' (out2 = c + bias), 'residual' (out2 = c + resid) or 'bias_act_dropout'
+    (out2 = c + bias, out3 = mask * act(out2)).  Raises SubstationError with status 3 when the
+    contraction does not run on the kernel that supports it."""
+    _check_cuda(a, b, c, out2); _half(a, b, c, out2)
+    lhs, cd = spec.replace(' ', '').split('->')
+    ad, bd = lhs.split(',')
+    ep = _lib.SbEpilogue()
+    ep.kind = {'bias': 1, 'residual': 2, 'bias_act_dropout': 3}[kind]
+    keep = [tensor_desc(out2)]
+    ep.out2 = ctypes.pointer(keep[-1])
+    if bias is not None:
+        _half(bias)
+        keep.append(tensor_desc(bias)); ep.bias = ctypes.pointer(keep[-1])
+        ep.bias_dims = bias_dims.encode()
+    if resid is not None:
+        _half(resid)
+        keep.append(tensor_desc(resid)); ep.resid = ctypes.pointer(keep[-1])
+    if mask is not None:
+        _mask(mask)
+        keep.append(tensor_desc(mask)); ep.mask = ctypes.pointer(keep[-1])
+    if out3 is not None:
+        _half(out3)
+        keep.append(tensor_desc(out3)); ep.out3 = ctypes.pointer(keep[-1])
+    ep.activation = _ACT[activation]
+    d = _dropout(p, mode, seed, offset)
+    ep.dropout = ctypes.pointer(d)
+    if logical_dims is not None:
+        ep.logical_dims = logical_dims.encode()
+    check(_lib.load().sb_einsum_fused(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
+                                      float(alpha), ctypes.byref(ep)))
+
+
 def device_error():
     """Sticky code set when a bounded wait inside the tcgen05 kernel ran out (0 = never)."""
     code = ctypes.c_int(0)

@@ -186,3 +186,73 @@ def test_paired_cta_kernel_on_large_problems(M, N, K, a_mn, b_mn, c_mn):
     ref = 2.0 * torch.einsum('bmk,bnk->bmn', A.float(), B.float())
     assert torch.isfinite(dC).all()
     assert ((dC.float() - ref).norm() / ref.norm()).item() < 1e-3
+
+
+def _rand(shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, device=DEV, generator=g) * scale).half()
+
+
+def test_fused_epilogue_bias_matches_einsum_then_input_biases():
+    """QKV projection with the attention input biases in its epilogue (bias along the rows of the swapped
+    problem) against sb_einsum followed by sb_attention_input_biases: bit-identical."""
+    ops = _ops()
+    B, J, I, Q, P, H = 4, 512, 256, 3, 64, 8
+    x, w, bias = _rand((B, J, I), 1, 1), _rand((Q, P, H, I), 0.05, 2), _rand((Q, P, H), 0.5, 3)
+    c, out2 = (torch.empty(Q, P, H, B, J, device=DEV, dtype=torch.float16) for _ in range(2))
+    ops.einsum_fused('bji,qphi->qphbj', x, w, c, kind='bias', bias=bias, bias_dims='qph', out2=out2)
+    c_ref, out_ref = torch.empty_like(c), torch.empty_like(c)
+    ops.einsum('bji,qphi->qphbj', x, w, c_ref)
+    ops.attention_input_biases(c_ref, bias, out_ref)
+    assert ops.device_error() == 0
+    assert torch.equal(c, c_ref) and torch.equal(out2, out_ref)
+    want = np.einsum('bji,qphi->qphbj', get(x), get(w))
+    assert_close(c, want, what='c')
+    assert_close(out2, want + get(bias)[..., None, None], what='c + bias')
+
+
+def test_fused_epilogue_residual_matches_einsum_then_encoder_input():
+    ops = _ops()
+    B, J, I, Q, P, H = 4, 512, 1280, 3, 64, 4
+    w, d, resid = _rand((Q, P, H, I), 0.05, 4), _rand((Q, P, H, B, J), 1, 5), _rand((B, J, I), 1, 6)
+    c, out2 = (torch.empty(B, J, I, device=DEV, dtype=torch.float16) for _ in range(2))
+    ops.einsum_fused('qphi,qphbj->bji', w, d, c, kind='residual', resid=resid, out2=out2)
+    c_ref, out_ref = torch.empty_like(c), torch.empty_like(c)
+    ops.einsum('qphi,qphbj->bji', w, d, c_ref)
+    ops.backward_encoder_input(c_ref, resid, out_ref)
+    assert ops.device_error() == 0
+    assert torch.equal(c, c_ref) and torch.equal(out2, out_ref)
+    assert_close(c, np.einsum('qphi,qphbj->bji', get(w), get(d)), what='c')
+
+
+@pytest.mark.parametrize('mode', ['explicit', 'philox'])
+@pytest.mark.parametrize('activation', ['relu', 'gelu'])
+def test_fused_epilogue_bias_activation_dropout_matches_separate_operator(mode, activation):
+    ops = _ops()
+    B, J, I, U = 4, 512, 256, 1280
+    x, w, bias = _rand((B, J, I), 1, 7), _rand((I, U), 0.08, 8), _rand((U,), 0.5, 9)
+    g = torch.Generator(device=DEV).manual_seed(10)
+    mask = (torch.rand(B, J, U, device=DEV, generator=g) >= 0.1).to(torch.uint8)
+    mask_ref = mask.clone()
+    c, lin1, drop2 = (torch.empty(B, J, U, device=DEV, dtype=torch.float16) for _ in range(3))
+    ops.einsum_fused('bji,iu->bju', x, w, c, kind='bias_act_dropout', bias=bias, bias_dims='u', mask=mask, out2=lin1,
+                     out3=drop2, activation=activation, p=0.1, mode=mode, seed=21, offset=2, logical_dims='bju')
+    c_ref, lin_ref, drop_ref = (torch.empty_like(c) for _ in range(3))
+    ops.einsum('bji,iu->bju', x, w, c_ref)
+    ops.bias_activation_dropout(c_ref, bias, mask_ref, lin_ref, drop_ref, activation=activation, p=0.1, mode=mode,
+                                seed=21, offset=2)
+    assert ops.device_error() == 0
+    assert torch.equal(mask, mask_ref)
+    if mode == 'philox':
+        assert np.array_equal(get(mask).astype(np.uint8), orc.philox_mask((B, J, U), 0.1, 21, 2))
+    assert torch.equal(c, c_ref) and torch.equal(lin1, lin_ref) and torch.equal(drop2, drop_ref)
+
+
+def test_fused_epilogue_declines_small_problems():
+    ops = _ops()
+    from substation_b200._lib import SubstationError
+    x, w, bias = _rand((2, 64, 128)), _rand((128, 256)), _rand((256,))
+    c, out2 = (torch.empty(2, 64, 256, device=DEV, dtype=torch.float16) for _ in range(2))
+    with pytest.raises(SubstationError) as e:
+        ops.einsum_fused('bji,iu->bju', x, w, c, kind='bias', bias=bias, bias_dims='u', out2=out2)
+    assert e.value.status == 3
