@@ -196,24 +196,36 @@ lnbwd_kernel(LnBwdParams p) {
   }
 }
 
-// out[q][f] = sum over the P partial rows (fixed order); one thread per (q, f), 4 chunks of rows
-// added by 4 thread groups and combined through shared memory.
-__global__ void __launch_bounds__(256)
+// out[q][f] = sum over the P partial rows in a fixed order: 16 thread groups take every 16th row each (loads
+// issued eight at a time, then added in row order) and are combined through shared memory in group order.
+constexpr int kFinishParts = 16;
+__global__ void __launch_bounds__(64 * kFinishParts)
 colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, void* o0, void* o1, void* o2, void* o3) {
   grid_dependency_sync();
-  __shared__ float sm[4][64];
+  __shared__ float sm[kFinishParts][64];
   const int q = blockIdx.y;
   const int fl = threadIdx.x & 63, part = threadIdx.x >> 6;
   const int f = blockIdx.x * 64 + fl;
   float v = 0.f;
   if (f < F) {
     const float* base = partial + (long long)q * P * kMaxF + f;
-    for (int c = part; c < P; c += 4) v += __ldcg(base + (long long)c * kMaxF);
+    for (int c0 = part; c0 < P; c0 += 8 * kFinishParts) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + u * kFinishParts;
+        x[u] = c < P ? __ldcg(base + (long long)c * kMaxF) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v += x[u];
+    }
   }
   sm[part][fl] = v;
   __syncthreads();
   if (part == 0 && f < F) {
-    const float total = sm[0][fl] + sm[1][fl] + sm[2][fl] + sm[3][fl];
+    float total = 0.f;
+#pragma unroll
+    for (int g = 0; g < kFinishParts; ++g) total += sm[g][fl];
     void* outs[4] = {o0, o1, o2, o3};
     reinterpret_cast<__half*>(outs[q])[f] = __float2half_rn(total);
   }
@@ -245,7 +257,7 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   SB_LAUNCH_OK(launch_k(lnbwd_kernel<MODE>, P, kThreads, smem, s, p));
   SB_CUDA_OK(cudaGetLastError());
   dim3 grid((p.d.F + 63) / 64, NQ);
-  SB_LAUNCH_OK(launch_k(colsum_finish_kernel, grid, 256, 0, s, p.partial, P, p.d.F, NQ, outs[0], outs[1], outs[2], outs[3]));
+  SB_LAUNCH_OK(launch_k(colsum_finish_kernel, grid, 64 * kFinishParts, 0, s, p.partial, P, p.d.F, NQ, outs[0], outs[1], outs[2], outs[3]));
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
