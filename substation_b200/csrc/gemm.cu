@@ -649,10 +649,15 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
   const long long total4 = batch * M * N / 4;  // N % 4 == 0
   const long long plane = batch * M * N;
   for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total4; i += (long long)gridDim.x * 256) {
-    float4 acc = __ldcs(reinterpret_cast<const float4*>(ws) + i);
-    for (int s = 1; s < splits; ++s) {
-      const float4 v = __ldcs(reinterpret_cast<const float4*>(ws + s * plane) + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    // all partials of this element are requested before any is added (splits <= 4), then added in split order
+    float4 part[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      part[s] = s < splits ? __ldcs(reinterpret_cast<const float4*>(ws + s * plane) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = part[0];
+#pragma unroll
+    for (int s = 1; s < 4; ++s) {
+      acc.x += part[s].x; acc.y += part[s].y; acc.z += part[s].z; acc.w += part[s].w;
     }
     const long long e = i * 4;
     const long long n = e % N, m = (e / N) % M, b = e / (N * M);
