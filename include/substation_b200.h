@@ -348,6 +348,8 @@ int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* m
  * replayed with a single launch afterwards; 0 switches that off for the handle (default on; the environment
  * variable SUBSTATION_B200_GRAPHS=0 switches it off for the process). */
 int sb_encoder_set_graphs(sb_encoder* enc, int enabled);
+/* How many passes were captured as graphs and how many were replayed since the handle was created. */
+int sb_encoder_graph_stats(sb_encoder* enc, long long* captures, long long* replays);
 int sb_encoder_launch_count(sb_encoder* enc);
 /* Kernels launched by the most recent forward plus the most recent backward (an operator may need
  * a second, finishing kernel, so this can exceed the two operator counts). */

@@ -621,6 +621,7 @@ struct sb_encoder {
     std::vector<PassGraph> entries;
     std::vector<std::vector<uint64_t>> seen;   // arguments of recent eager calls (a repeat gets captured)
     unsigned long long tick = 0;
+    long long captures = 0, replays = 0;
   };
   GraphCache graph_fwd, graph_bwd;
   cudaStream_t capture_stream = nullptr;
@@ -830,6 +831,13 @@ extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
 extern "C" int sb_encoder_set_graphs(sb_encoder* e, int enabled) {
   if (!e) return fail(SB_ERR_ARG, "null handle");
   e->graphs = enabled != 0;
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_graph_stats(sb_encoder* e, long long* captures, long long* replays) {
+  if (!e || !captures || !replays) return fail(SB_ERR_ARG, "sb_encoder_graph_stats: null argument");
+  *captures = e->graph_fwd.captures + e->graph_bwd.captures;
+  *replays = e->graph_fwd.replays + e->graph_bwd.replays;
   return SB_OK;
 }
 
@@ -1207,6 +1215,7 @@ int run_pass(sb_encoder* e, sb_encoder::GraphCache& cache, std::vector<uint64_t>
   for (auto& g : cache.entries)
     if (g.key == key) {
       g.last_use = cache.tick;
+      ++cache.replays;
       SB_CUDA_OK(cudaGraphLaunch(g.exec, s));
       *launches = g.launches;
       *kernels = g.kernels;
@@ -1220,7 +1229,7 @@ int run_pass(sb_encoder* e, sb_encoder::GraphCache& cache, std::vector<uint64_t>
       break;
     }
   if (!seen_before) {  // first sighting: run it as it is and remember the arguments
-    if (cache.seen.size() >= 8) cache.seen.erase(cache.seen.begin());
+    if (cache.seen.size() >= 32) cache.seen.erase(cache.seen.begin());
     cache.seen.push_back(key);
     return pass(s);
   }
@@ -1248,7 +1257,12 @@ int run_pass(sb_encoder* e, sb_encoder::GraphCache& cache, std::vector<uint64_t>
     return pass(s);
   }
   cudaGraphDestroy(graph);
-  if (cache.entries.size() >= 8) {  // drop the least recently used
+  static const size_t max_graphs = [] {
+    const char* v = getenv("SUBSTATION_B200_GRAPH_CACHE");
+    const int n = v ? atoi(v) : 0;
+    return (size_t)(n > 0 ? n : 16);
+  }();
+  if (cache.entries.size() >= max_graphs) {  // drop the least recently used
     size_t victim = 0;
     for (size_t i = 1; i < cache.entries.size(); ++i)
       if (cache.entries[i].last_use < cache.entries[victim].last_use) victim = i;
@@ -1262,6 +1276,7 @@ int run_pass(sb_encoder* e, sb_encoder::GraphCache& cache, std::vector<uint64_t>
   g.kernels = *kernels;
   g.last_use = cache.tick;
   cache.entries.push_back(std::move(g));
+  ++cache.captures;
   SB_CUDA_OK(cudaGraphLaunch(exec, s));
   return SB_OK;
 }

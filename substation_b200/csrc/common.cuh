@@ -81,6 +81,58 @@ __device__ __forceinline__ void grid_dependency_sync() {
 
 bool pdl_enabled();  // false when the environment sets SUBSTATION_B200_PDL=0
 
+// ---- per-device facts asked of the runtime once per thread, not once per launch ----------------
+struct DeviceFacts {
+  int device = -1;
+  int sms = 148;
+};
+// Current device and its SM count (one cudaGetDevice per call; the attribute is cached per device).
+inline const DeviceFacts& device_facts() {
+  static thread_local DeviceFacts facts[64];
+  static thread_local DeviceFacts fallback;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) {
+    fallback.device = dev;
+    cudaDeviceGetAttribute(&fallback.sms, cudaDevAttrMultiProcessorCount, dev);
+    return fallback;
+  }
+  DeviceFacts& f = facts[dev];
+  if (f.device != dev) {
+    f.device = dev;
+    if (cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) f.sms = 148;
+  }
+  return f;
+}
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device, size) and thread.
+inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Done { const void* fn; int dev; int bytes; };
+  static thread_local Done done[64];
+  static thread_local int ndone = 0;
+  const int dev = device_facts().device;
+  for (int i = 0; i < ndone; ++i)
+    if (done[i].fn == kernel && done[i].dev == dev && done[i].bytes == bytes) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && ndone < 64) done[ndone++] = Done{kernel, dev, bytes};
+  return e;
+}
+// Resident CTAs per SM of a kernel at a block size (no dynamic shared memory), cached like the above.
+inline int cached_blocks_per_sm(const void* kernel, int threads) {
+  struct Occ { const void* fn; int dev; int threads; int per_sm; };
+  static thread_local Occ occ[64];
+  static thread_local int nocc = 0;
+  const int dev = device_facts().device;
+  for (int i = 0; i < nocc; ++i)
+    if (occ[i].fn == kernel && occ[i].dev == dev && occ[i].threads == threads) return occ[i].per_sm;
+  int per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    per_sm = 1;
+  }
+  if (nocc < 64) occ[nocc++] = Occ{kernel, dev, threads, per_sm};
+  return per_sm;
+}
+
 // Kernels launched through launch_k by this thread (the layer handle reports the difference over a pass).
 extern thread_local long long g_kernel_launches;
 

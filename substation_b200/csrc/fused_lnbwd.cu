@@ -245,15 +245,13 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   constexpr int NQ = MODE == 0 ? 2 : 4;
   LnBwdParams p = p0;
   const long long R = (long long)p.d.B * p.d.J;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = device_facts().sms;
   const int P = (int)std::max<long long>(1, std::min<long long>(sms, (R + kGroups * kRows - 1) / (kGroups * kRows)));
   if ((size_t)NQ * P * kMaxF * sizeof(float) > kWsBytes - kWsCounterBytes)
     return fail(SB_ERR_UNSUPPORTED, "fused LayerNorm backward: workspace too small");
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
   const size_t smem = (size_t)kGroups * NQ * kMaxF * sizeof(float);
-  SB_CUDA_OK(cudaFuncSetAttribute(lnbwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_kernel<MODE>), (int)smem));
   SB_LAUNCH_OK(launch_k(lnbwd_kernel<MODE>, P, kThreads, smem, s, p));
   SB_CUDA_OK(cudaGetLastError());
   dim3 grid((p.d.F + 63) / 64, NQ);

@@ -938,12 +938,8 @@ bool all_vec(const V&... v) {
 // Persistent grid: enough CTAs to fill every SM at the kernel's occupancy, no more than the work needs.
 template <class K>
 unsigned persistent_blocks(K kernel, int threads, unsigned long long work_blocks) {
-  int dev = 0, sms = 148, per_sm = 1;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1)
-    per_sm = 1;
-  const unsigned long long cap = (unsigned long long)sms * per_sm;
+  const int per_sm = cached_blocks_per_sm(reinterpret_cast<const void*>(kernel), threads);
+  const unsigned long long cap = (unsigned long long)device_facts().sms * per_sm;
   return (unsigned)std::max<unsigned long long>(1, std::min(work_blocks, cap));
 }
 

@@ -785,7 +785,7 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
               size_t ws_bytes) {
   using Cfg = TcCfg<BN, KS>;
   // per-device attribute; setting it is cheap and idempotent
-  SB_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<BN, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<BN, KS>), Cfg::kSmemBytes));
   TcParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
@@ -927,8 +927,8 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
   const int kind = epi ? epi->kind : 0;
   auto launch = [&](auto kernel) {
     // per-device attribute; setting it is cheap and idempotent
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes) != cudaSuccess)
-      return cudaGetLastError();
+    const cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), pair::kSmemBytes);
+    if (ea != cudaSuccess) return ea;
     return launch_k(kernel, 2 * nclusters, kTcThreads, pair::kSmemBytes, s, a.map, b.map, cmap, cmap2, cmap3, p);
   };
   if (kind == 0) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<0>));
@@ -1091,7 +1091,7 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
   p.b_bytes = b.mn ? L * 128 : ((L + 255) / 256) * brows * 128;
   constexpr int smem = attn::Cfg<BWD>::kSmemBytes;
   static_assert(smem <= 232448, "shared memory of the fused attention kernel");
-  SB_CUDA_OK(cudaFuncSetAttribute(attn::attn_scores_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(attn::attn_scores_kernel<BWD>), smem));
   const unsigned grid = (unsigned)std::min<long long>(p.tiles, sm_count());
   SB_LAUNCH_OK(launch_k(attn::attn_scores_kernel<BWD>, grid, attn::kThreads, smem, s, a.map, b.map, m0, m1, m2, mi, mm, p));
   return SB_OK;
@@ -1173,7 +1173,7 @@ int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const Vi
   const int proj = (p.has_r + p.has_c) * L * 128;
   p.nstages = std::min(scon::kMaxStages, (232448 - 1280 - proj) / scon::kStageBytes);
   const int smem = proj + p.nstages * scon::kStageBytes + 1024 + 256;
-  SB_CUDA_OK(cudaFuncSetAttribute(scon::score_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(scon::score_contract_kernel), 232448));
   const unsigned grid = (unsigned)std::min<long long>(batch, sm_count());
   SB_LAUNCH_OK(launch_k(scon::score_contract_kernel, grid, kTcThreads, smem, s, ms, mx, my, p));
   return SB_OK;

@@ -20,6 +20,7 @@ There is no CPU path: tensors must be on a CUDA device.
 """
 
 import ctypes
+import os
 import math
 
 import torch
@@ -33,6 +34,11 @@ _ALIGN = 256
 def _round_up(n, a=_ALIGN):
     return (n + a - 1) // a * a
 
+
+# Replay of repeated passes as CUDA graphs inside the autograd path: off unless asked for.  The arenas, outputs
+# and gradients of that path come from torch's caching allocator, whose blocks do not repeat reliably from step
+# to step (measured: one capture per three steps, no gain), unlike the caller-held arenas of the raw passes.
+_AUTOGRAD_GRAPHS = os.environ.get('SUBSTATION_B200_AUTOGRAD_GRAPHS', '0') == '1'
 
 class Encoder(torch.nn.Module):
     """Optimized BERT encoder layer (API of pytorch_module/encoder.py:19-25)."""
@@ -317,7 +323,7 @@ class Encoder(torch.nn.Module):
     def _forward_ptrs(self, X, weights, fwd_ptrs, Y):
         lib = _lib.load()
         h = self._native(X.device)
-        self._graphs_now(h, False)
+        self._graphs_now(h, _AUTOGRAD_GRAPHS)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
         _lib.check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
@@ -327,7 +333,7 @@ class Encoder(torch.nn.Module):
     def _backward_ptrs(self, DY, grad_ptrs, bwd_ptrs, weights, fwd_ptrs, X, DX):
         lib = _lib.load()
         h = self._native(DY.device)
-        self._graphs_now(h, False)
+        self._graphs_now(h, _AUTOGRAD_GRAPHS)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
         _lib.check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
                                            self._ptrs(weights), fwd_ptrs, ctypes.c_void_p(X.data_ptr()),
@@ -389,6 +395,14 @@ class Encoder(torch.nn.Module):
         """Replay passes whose buffers repeat as CUDA graphs (default) or launch every kernel each time."""
         self._graphs = bool(enabled)
         self._graphs_state = None
+
+    def graph_stats(self):
+        """(passes captured as CUDA graphs, passes replayed) since the native handle was created."""
+        if self._handle is None:
+            return 0, 0
+        c, r = ctypes.c_longlong(0), ctypes.c_longlong(0)
+        _lib.check(_lib.load().sb_encoder_graph_stats(self._handle, ctypes.byref(c), ctypes.byref(r)))
+        return c.value, r.value
 
     def launch_count(self):
         """Operators launched by the most recent raw pass."""
