@@ -787,6 +787,7 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
   // per-device attribute; setting it is cheap and idempotent
   SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<BN, KS>), Cfg::kSmemBytes));
   TcParams p;
+  memset(&p.epi, 0, sizeof(p.epi));
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
   p.C = g.C;

@@ -171,40 +171,41 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
       const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
       const uint32_t peer_empty = map_to_rank(bar_empty, 1), peer_accf = map_to_rank(bar_accf, 1);
-      uint32_t it = 0, lt = 0;
-      bool ok = true;
-      for (long long t = cluster_id; t < p.tiles && ok; t += nclusters, ++lt) {
-        const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_acce + 8 * buf, aph ^ 1u, 4));
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * kBN;
-        for (int kb = 0; kb < KT; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
-          ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, 2));
+      // One thread runs the whole issue loop (no warp-wide votes on its path), and the shared-memory
+      // descriptors are a base plus an address increment: the MMA issue rate of this thread is what
+      // bounds the kernel once the operands arrive in time.
+      if (lane == 0) {
+        const uint64_t da_base = make_desc(tiles, a_lbo, 1024u), db_base = make_desc(tiles + kABytes, b_lbo, 1024u);
+        const uint64_t a_inc = a_step >> 4, b_inc = b_step >> 4, stage_inc = (uint64_t)kStageBytes >> 4;
+        uint32_t it = 0, lt = 0;
+        bool ok = true;
+        for (long long t = cluster_id; t < p.tiles && ok; t += nclusters, ++lt) {
+          const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
+          ok = mbar_wait(bar_acce + 8 * buf, aph ^ 1u, 4);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t sa = tiles + s * kStageBytes, sb_ = sa + kABytes;
+          const uint32_t tmem_d = tmem_base + buf * kBN;
+          for (int kb = 0; kb < KT; ++kb, ++it) {
+            const uint32_t s = it % S;
+            const uint32_t ph = (it / S) & 1u;
+            ok = mbar_wait(bar_full + 8 * s, ph, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = da_base + s * stage_inc, db = db_base + s * stage_inc;
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              const uint64_t da = make_desc(sa + k * a_step, a_lbo, 1024u);
-              const uint64_t db = make_desc(sb_ + k * b_step, b_lbo, 1024u);
-              umma_f16_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_f16_pair(tmem_d, da + k * a_inc, db + k * b_inc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             // the stage is free in both CTAs once these MMAs have read it
             umma_commit_pair(bar_empty + 8 * s);
             umma_commit_pair(peer_empty + 8 * s);
           }
-          __syncwarp();
+          if (ok) {
+            umma_commit_pair(bar_accf + 8 * buf);
+            umma_commit_pair(peer_accf + 8 * buf);
+          }
         }
-        if (ok && lane == 0) {
-          umma_commit_pair(bar_accf + 8 * buf);
-          umma_commit_pair(peer_accf + 8 * buf);
-        }
-        __syncwarp();
       }
+      __syncwarp();
     }
   } else {
     // ---------------- epilogue (both CTAs; each stores its own 128 rows) ----------------
