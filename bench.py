@@ -77,8 +77,8 @@ FUSED_BYTES = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=8, L=512, from the ncu --set full captures
 # summarised in profiles/top_kernels_b8_l512_full_captures.md (part of each kernel's output is still in L2
 # when it ends, so traffic can be below the algorithmic bytes)
-NCU_DRAM_BYTES = {'QKT+softmax': 195.45e6, 'dX1gamma+bs': 197.63e6, 'gamma': 78.56e6, 'dX2gamma': 78.29e6,
-                  'dX1QKT+dX2QKT': 87.82e6, 'bsb+blnrd1': 29.81e6, 'ebsb+blnrd2+baob': 51.64e6}
+NCU_DRAM_BYTES = {'QKT+softmax': 207.69e6, 'dX1gamma+bs': 200.28e6, 'gamma': 78.86e6, 'dX2gamma': 77.23e6,
+                  'dX1QKT+dX2QKT': 87.78e6, 'bsb+blnrd1': 29.86e6, 'ebsb+blnrd2+baob': 51.58e6}
 
 
 def load_peaks():
