@@ -1171,7 +1171,10 @@ int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const Vi
     if (!unit_stride(*out_c, &su)) return fail(SB_ERR_UNSUPPORTED, "score contractions: head and sample dims of the column output do not collapse");
     p.out_c = reinterpret_cast<__half*>(out_c->p); p.c_sU = su; p.c_sRow = out_c->sK; p.c_sP = out_c->sH;
   }
-  const int proj = (p.has_r + p.has_c) * L * 128;
+  // two sets of projections and column accumulators when they fit (L <= 256): the next (head, sample) loads
+  // while this one computes, which is what matters when a unit is only one or four tiles long
+  p.nbuf = L <= 256 ? 2 : 1;
+  const int proj = p.nbuf * (p.has_r + p.has_c) * L * 128;
   p.nstages = std::min(scon::kMaxStages, (232448 - 1280 - proj) / scon::kStageBytes);
   const int smem = proj + p.nstages * scon::kStageBytes + 1024 + 256;
   SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(scon::score_contract_kernel), 232448));

@@ -29,6 +29,7 @@ struct Params {
   int has_r, has_c;
   int x_mn, x_swap, y_mn, y_swap, s_swap;
   int nstages;
+  int nbuf;               // 1 or 2 sets of (X, Y, column accumulators): with 2, the next unit loads while this one computes
   float alpha;
   __half* out_r; long long r_sU, r_sRow, r_sP;   // strides of R over (unit, j, p)
   __half* out_c; long long c_sU, c_sRow, c_sP;   // strides of C over (unit, k, p)
@@ -58,22 +59,25 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
   const uint32_t base = (raw + 1023u) & ~1023u;
   const int L = p.L, nt = p.nt, NS = p.nstages;
   const uint32_t proj_bytes = (uint32_t)L * 128u;  // one projection of one unit: 64 x L fp16
+  const uint32_t nbuf = (uint32_t)p.nbuf;
   const uint32_t sx = base;
-  const uint32_t sy = sx + (p.has_r ? proj_bytes : 0u);
-  const uint32_t ring = sy + (p.has_c ? proj_bytes : 0u);
+  const uint32_t sy = sx + (p.has_r ? nbuf * proj_bytes : 0u);
+  const uint32_t ring = sy + (p.has_c ? nbuf * proj_bytes : 0u);
   const uint32_t bars = ring + (uint32_t)NS * kStageBytes;
-  const uint32_t bar_xyf = bars, bar_xye = bars + 8, bar_cf = bars + 16, bar_ce = bars + 24;
-  const uint32_t bar_rf = bars + 32, bar_re = bars + 48, bar_sf = bars + 64, bar_se = bar_sf + 8 * kMaxStages;
+  const uint32_t bar_xyf = bars, bar_xye = bars + 16, bar_cf = bars + 32, bar_ce = bars + 48;   // two of each
+  const uint32_t bar_rf = bars + 64, bar_re = bars + 80, bar_sf = bars + 96, bar_se = bar_sf + 8 * kMaxStages;
   uint8_t* gen_base = smem_raw + (base - raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - base) + 64 + 16 * kMaxStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - base) + 96 + 16 * kMaxStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_xyf, 1);
-    mbar_init(bar_xye, 1);
-    mbar_init(bar_cf, 1);
-    mbar_init(bar_ce, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_xyf + 8 * i, 1);
+      mbar_init(bar_xye + 8 * i, 1);
+      mbar_init(bar_cf + 8 * i, 1);
+      mbar_init(bar_ce + 8 * i, 4);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_rf + 8 * i, 1);
       mbar_init(bar_re + 8 * i, 4);
@@ -105,21 +109,23 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
     uint32_t un = 0, sit = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++un) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_xye, (un & 1u) ^ 1u, 1));
+      const uint32_t xb = un % nbuf, xph = (un / nbuf) & 1u;
+      const uint32_t xyf = bar_xyf + 8 * xb;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_xye + 8 * xb, xph ^ 1u, 1));
       if (!ok) break;
       if (lane == 0) {
-        mbar_expect_tx(bar_xyf, (uint32_t)(p.has_r + p.has_c) * proj_bytes);
+        mbar_expect_tx(xyf, (uint32_t)(p.has_r + p.has_c) * proj_bytes);
         for (int blk = 0; blk < L / 64; ++blk) {
           const int k0 = blk * 64;
           if (p.has_r) {
-            const uint32_t dst = sx + blk * 8192;
-            if (!p.x_mn) { if (p.x_swap) tma_load_3d(dst, &tmX, bar_xyf, k0, u, 0); else tma_load_3d(dst, &tmX, bar_xyf, k0, 0, u); }
-            else { if (p.x_swap) tma_load_3d(dst, &tmX, bar_xyf, 0, u, k0); else tma_load_3d(dst, &tmX, bar_xyf, 0, k0, u); }
+            const uint32_t dst = sx + xb * proj_bytes + blk * 8192;
+            if (!p.x_mn) { if (p.x_swap) tma_load_3d(dst, &tmX, xyf, k0, u, 0); else tma_load_3d(dst, &tmX, xyf, k0, 0, u); }
+            else { if (p.x_swap) tma_load_3d(dst, &tmX, xyf, 0, u, k0); else tma_load_3d(dst, &tmX, xyf, 0, k0, u); }
           }
           if (p.has_c) {
-            const uint32_t dst = sy + blk * 8192;
-            if (!p.y_mn) { if (p.y_swap) tma_load_3d(dst, &tmY, bar_xyf, k0, u, 0); else tma_load_3d(dst, &tmY, bar_xyf, k0, 0, u); }
-            else { if (p.y_swap) tma_load_3d(dst, &tmY, bar_xyf, 0, u, k0); else tma_load_3d(dst, &tmY, bar_xyf, 0, k0, u); }
+            const uint32_t dst = sy + xb * proj_bytes + blk * 8192;
+            if (!p.y_mn) { if (p.y_swap) tma_load_3d(dst, &tmY, xyf, k0, u, 0); else tma_load_3d(dst, &tmY, xyf, k0, 0, u); }
+            else { if (p.y_swap) tma_load_3d(dst, &tmY, xyf, 0, u, k0); else tma_load_3d(dst, &tmY, xyf, 0, k0, u); }
           }
         }
       }
@@ -154,10 +160,13 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
     uint32_t un = 0, sit = 0, rn = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++un) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_xyf, un & 1u, 2));
+      const uint32_t xb = un % nbuf, xph = (un / nbuf) & 1u;
+      const uint32_t sxb = sx + xb * proj_bytes, syb = sy + xb * proj_bytes;
+      const uint32_t tmem_cb = tmem_c + xb * (uint32_t)nt * 64u;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_xyf + 8 * xb, xph, 2));
       if (!ok) break;
-      if (p.has_c) {  // the previous unit's column accumulators must have been read out
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_ce, (un & 1u) ^ 1u, 4));
+      if (p.has_c) {  // the column accumulators of this set must have been read out by its previous unit
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_ce + 8 * xb, xph ^ 1u, 4));
         if (!ok) break;
       }
       for (int jt = 0; jt < nt && ok; ++jt) {
@@ -180,7 +189,7 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                   const uint64_t da = make_desc(st + i * 16384 + k * 32, 16u, 1024u);
-                  const uint64_t db = make_desc(sx + (kc * 2 + i) * 8192 + k * x_step, x_lbo, 1024u);
+                  const uint64_t db = make_desc(sxb + (kc * 2 + i) * 8192 + k * x_step, x_lbo, 1024u);
                   umma_f16(tmem_base + rb * 64, da, db, idesc_r, (kc | i | k) != 0 ? 1u : 0u);
                 }
             }
@@ -189,8 +198,8 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
               for (int k = 0; k < 8; ++k) {
                 // the same tile as an MN-major operand: M = k index (two 64-wide blocks 16 KiB apart), K = j
                 const uint64_t da = make_desc(st + k * 2048, 16384u, 1024u);
-                const uint64_t db = make_desc(sy + (jt * 2 + (k >> 2)) * 8192 + (k & 3) * y_step, y_lbo, 1024u);
-                umma_f16(tmem_c + kc * 64, da, db, idesc_c, (jt | k) != 0 ? 1u : 0u);
+                const uint64_t db = make_desc(syb + (jt * 2 + (k >> 2)) * 8192 + (k & 3) * y_step, y_lbo, 1024u);
+                umma_f16(tmem_cb + kc * 64, da, db, idesc_c, (jt | k) != 0 ? 1u : 0u);
               }
             }
             umma_commit(bar_se + 8 * s);
@@ -204,8 +213,8 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
         }
       }
       if (ok && lane == 0) {
-        if (p.has_c) umma_commit(bar_cf);
-        umma_commit(bar_xye);  // X and Y may be replaced once every MMA of the unit has completed
+        if (p.has_c) umma_commit(bar_cf + 8 * xb);
+        umma_commit(bar_xye + 8 * xb);  // X and Y may be replaced once every MMA of the unit has completed
       }
       __syncwarp();
     }
@@ -235,18 +244,20 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
         if (!ok) break;
       }
       if (p.has_c) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_cf, un & 1u, 3));
+        const uint32_t xb = un % nbuf, xph = (un / nbuf) & 1u;
+        const uint32_t tmem_cb = tmem_c + xb * (uint32_t)nt * 64u;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_cf + 8 * xb, xph, 3));
         if (!ok) break;
         tc_fence_after();
         for (int kc = 0; kc < nt; ++kc) {
           uint32_t r[64];
-          tmem_ld32_nowait(tmem_c + kc * 64 + lane_off, r);
-          tmem_ld32_nowait(tmem_c + kc * 64 + 32 + lane_off, r + 32);
+          tmem_ld32_nowait(tmem_cb + kc * 64 + lane_off, r);
+          tmem_ld32_nowait(tmem_cb + kc * 64 + 32 + lane_off, r + 32);
           tmem_ld_wait();
           if (kc == nt - 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_ce);
+            if (lane == 0) mbar_arrive(bar_ce + 8 * xb);
           }
           const long long row = (long long)kc * 128 + q * 32 + lane;
           store_row64(p.out_c + (long long)u * p.c_sU + row * p.c_sRow, p.c_sP, r, p.alpha);
