@@ -484,7 +484,7 @@ def run_ours(args):
 
 
 def run_stack(args):
-    """--layers N > 1: a stack of N layers with independent weights (BASELINE.json config 5 at N=24);
+    """--layers N > 1: a stack of N layers with independent weights (the 24-layer stack configuration at N=24);
     one step = forward through all layers + backward through all layers, each layer's gradient
     bucket allreduced while the next layer's backward runs."""
     import torch

@@ -36,7 +36,7 @@ CASES = {
 
 
 def import_reference():
-    ref = os.environ.get('SUBSTATION_REF', '/root/reference')
+    ref = os.environ.get('SUBSTATION_REF') or sys.exit('set SUBSTATION_REF to a checkout of spcl/substation')
     sys.modules.setdefault('dace', mock.MagicMock())
     sys.path.insert(0, ref)
     import substation.transformer as tr  # noqa

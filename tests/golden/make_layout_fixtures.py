@@ -11,10 +11,11 @@ tree can load them.
 
 import json
 import os
+import sys
 import pickle
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get('SUBSTATION_REF', '/root/reference')
+REF = os.environ.get('SUBSTATION_REF') or sys.exit('set SUBSTATION_REF to a checkout of spcl/substation')
 
 for tag in ('b8-l512', 'b96-l128'):
     with open(os.path.join(REF, 'pytorch_module', f'layouts-bert-{tag}-h16-e1024.pickle'), 'rb') as f:
