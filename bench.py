@@ -261,11 +261,23 @@ def run_ours(args):
     reducer = GradientBucketReducer(enc.arena_bytes('grads'), dev, buffers=2)
     Y, DX = torch.empty_like(X), torch.empty_like(X)
 
+    # The whole bucket is allreduced beside the next step.  With --early-allreduce 1 the gradients of the
+    # feed-forward half, final in the middle of the backward pass, are allreduced beside the attention half of the
+    # pass instead: measured slower (8 GPUs: 0.75 against 0.67 ms per step), the allreduce then competes with the
+    # HBM-bound attention kernels rather than with the next step's tensor-bound projections.
+    early = None
+    if world > 1 and args.early_allreduce:
+        ffn_event = torch.cuda.Event()
+        enc.set_ffn_grads_event(ffn_event)
+        early = (enc.early_grad_offset(), ffn_event)
+    grad_views = [enc.views('grads', reducer.arenas[b]) for b in range(len(reducer.arenas))]
+
     def step(i):
-        grads = enc.views('grads', reducer.arena(i))     # waits if this bucket is still being reduced
+        reducer.wait(i)                                   # this bucket's previous reduction has finished
+        grads = grad_views[i % len(grad_views)]
         enc.forward_raw(X, weights, fwd, Y)
         enc.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
-        reducer.reduce_async(i)
+        reducer.reduce_async(i, early=early)
 
     drain = reducer.drain
 
@@ -566,6 +578,9 @@ def main():
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
     ap.add_argument('--comm-ctas', type=int, default=4, help='SMs left to NCCL when N > 1')
+    ap.add_argument('--early-allreduce', type=int, default=0,
+                    help='N > 1: sum the feed-forward gradients beside the attention half of backward (1) or the whole '
+                         'bucket beside the next step (0)')
     ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (config 5 uses 24)')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')

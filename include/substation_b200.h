@@ -348,6 +348,12 @@ int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* m
  * replayed with a single launch afterwards; 0 switches that off for the handle (default on; the environment
  * variable SUBSTATION_B200_GRAPHS=0 switches it off for the process). */
 int sb_encoder_set_graphs(sb_encoder* enc, int enabled);
+/* A CUDA event (cudaEvent_t, caller-owned; NULL to stop) that every backward pass records on its stream as soon
+ * as the gradients of the feed-forward half and of both LayerNorms are final (LINW1, LINB1, LINW2, LINB2, S1,
+ * B1, S2, B2, BO: in the parameter order these are everything from LINB1 on, plus S1, B1, BO), i.e. before
+ * the attention half of the backward pass runs.  A data-parallel host waits for it on its communication
+ * stream and starts the allreduce of that part of the gradient bucket while the pass continues. */
+int sb_encoder_set_ffn_grads_event(sb_encoder* enc, void* event);
 /* How many passes were captured as graphs and how many were replayed since the handle was created. */
 int sb_encoder_graph_stats(sb_encoder* enc, long long* captures, long long* replays);
 int sb_encoder_launch_count(sb_encoder* enc);

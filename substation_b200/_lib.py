@@ -99,6 +99,7 @@ SIGNATURES = {
     'sb_encoder_get_timing': (c_int, [c_void_p, c_int, ctypes.POINTER(c_char_p),
                                       ctypes.POINTER(c_float)]),
     'sb_encoder_set_graphs': (c_int, [c_void_p, c_int]),
+    'sb_encoder_set_ffn_grads_event': (c_int, [c_void_p, c_void_p]),
     'sb_encoder_graph_stats': (c_int, [c_void_p, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]),
     'sb_encoder_launch_count': (c_int, [c_void_p]),
     'sb_encoder_kernel_count': (c_int, [c_void_p]),

@@ -625,6 +625,7 @@ struct sb_encoder {
   };
   GraphCache graph_fwd, graph_bwd;
   cudaStream_t capture_stream = nullptr;
+  cudaEvent_t ffn_grads_event = nullptr;   // recorded in backward once the feed-forward gradients are final
   bool graphs = true;           // sb_encoder_set_graphs / SUBSTATION_B200_GRAPHS=0
   bool timing = false;
   bool fuse = true;            // use the fused multi-operator kernels where the layouts allow
@@ -831,6 +832,18 @@ extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
 extern "C" int sb_encoder_set_graphs(sb_encoder* e, int enabled) {
   if (!e) return fail(SB_ERR_ARG, "null handle");
   e->graphs = enabled != 0;
+  return SB_OK;
+}
+
+extern "C" int sb_encoder_set_ffn_grads_event(sb_encoder* e, void* event) {
+  if (!e) return fail(SB_ERR_ARG, "null handle");
+  if (e->ffn_grads_event != (cudaEvent_t)event) {
+    // graphs captured so far record the previous event (or none): drop them
+    for (auto& g : e->graph_bwd.entries) cudaGraphExecDestroy(g.exec);
+    e->graph_bwd.entries.clear();
+    e->graph_bwd.seen.clear();
+  }
+  e->ffn_grads_event = (cudaEvent_t)event;
   return SB_OK;
 }
 
@@ -1104,6 +1117,16 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     } else if (st != SB_OK) {
       return st;
     }
+  }
+  if (e->ffn_grads_event) {
+    // Everything the feed-forward half and both LayerNorms contribute to the parameter gradients (LINW1, LINB1,
+    // LINW2, LINB2, S1, B1, S2, B2, BO) is final here: a data-parallel caller can start summing those while the
+    // attention half of the backward pass still runs.  Inside a stream capture the record becomes an
+    // event-record node that code outside the graph may wait for.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    SB_CUDA_OK(cudaStreamIsCapturing(s, &cap));
+    SB_CUDA_OK(cudaEventRecordWithFlags(e->ffn_grads_event, s,
+                                        cap == cudaStreamCaptureStatusActive ? cudaEventRecordExternal : cudaEventRecordDefault));
   }
   SB_TRY(einsum(e, s, "dWout", L.at("GAMMA"), T["GAMMA"], L.at("DATT"), T["DATT"], L.at("WO"), D.at("WO"), 1.f));
   SB_TRY(einsum(e, s, "dXout", L.at("WO"), T["WO"], L.at("DATT"), T["DATT"], L.at("DGAMMA"), T["DGAMMA"], 1.f));

@@ -39,6 +39,7 @@ class GradientBucketReducer:
         self.arenas = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(buffers)]
         self.pending = [None] * buffers
         self.reductions = 0
+        self._side = None   # stream that waits for the mid-pass event of an early part
         if verify and self.world > 1:
             self._verify(device)
 
@@ -63,21 +64,47 @@ class GradientBucketReducer:
     def flat(self, i):
         return self.arenas[i % len(self.arenas)].view(self.dtype)
 
-    def reduce_async(self, i):
+    def reduce_async(self, i, early=None):
         """Start the sum-allreduce of bucket i (ordered after work already queued on the
-        current stream); returns at once."""
+        current stream); returns at once.  ``early`` = (byte offset, event): the part of the bucket from that
+        offset on is final as soon as ``event`` fires (an event recorded in the middle of the backward pass
+        already queued), so its allreduce is queued behind the event only and runs beside the rest of the pass;
+        the first part follows as usual."""
         b = i % len(self.arenas)
         if self.pending[b] is not None:
             raise RuntimeError(f'bucket {b} is already being reduced')
         if self.world > 1:
-            self.pending[b] = dist.all_reduce(self.flat(b), op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            flat = self.flat(b)
+            works = []
+            k = 0
+            if early is not None:
+                off, event = early
+                itemsize = flat.element_size()
+                if off % itemsize or not 0 <= off <= self.nbytes:
+                    raise ValueError('early part must start on an element boundary inside the bucket')
+                k = off // itemsize
+            if early is not None and 0 < k < flat.numel():
+                tail = flat[k:]
+                if flat.is_cuda:
+                    if self._side is None:
+                        self._side = torch.cuda.Stream(flat.device)
+                    self._side.wait_event(event)
+                    with torch.cuda.stream(self._side):
+                        works.append(dist.all_reduce(tail, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                else:
+                    works.append(dist.all_reduce(tail, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                works.append(dist.all_reduce(flat[:k], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            else:
+                works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            self.pending[b] = works
         self.reductions += 1
 
     def wait(self, i):
         """Make the current stream (or the host, on CPU backends) wait for bucket i's reduction."""
         b = i % len(self.arenas)
         if self.pending[b] is not None:
-            self.pending[b].wait()
+            for w in self.pending[b]:
+                w.wait()
             self.pending[b] = None
 
     def drain(self):

@@ -272,6 +272,8 @@ class Encoder(torch.nn.Module):
             _lib.check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
             self._graphs_state = None
         self._handle, self._handle_device = handle, device
+        with torch.cuda.device(device):
+            self._apply_ffn_event()
         return handle
 
     def _destroy(self):
@@ -385,6 +387,37 @@ class Encoder(torch.nn.Module):
         ms = (ctypes.c_float * n)()
         k = lib.sb_encoder_get_timing(self._handle, n, names, ms)
         return [(names[i].decode(), ms[i]) for i in range(k)]
+
+    # parameters whose gradients are final before the attention half of the backward pass runs
+    _EARLY_GRADS = frozenset(('LINW1', 'LINB1', 'LINW2', 'LINB2', 'S1', 'B1', 'S2', 'B2', 'BO'))
+
+    def early_grad_offset(self):
+        """Byte offset in the gradient arena from which on every gradient belongs to the feed-forward half or a
+        LayerNorm (final when the event of ``set_ffn_grads_event`` fires); equals the arena size if the
+        configuration's parameter order ends with an attention parameter."""
+        plan, total = self._grad_plan
+        off = total
+        for name, _, _, o, _ in reversed(plan):
+            if name not in self._EARLY_GRADS:
+                break
+            off = o
+        return off
+
+    def set_ffn_grads_event(self, event):
+        """``event``: a torch.cuda.Event that every backward pass records once those gradients are final, or None.
+        A data-parallel caller waits for it on its communication stream (see GradientBucketReducer.reduce_async)."""
+        self._ffn_event = event
+        if self._handle is not None:
+            self._apply_ffn_event()
+
+    def _apply_ffn_event(self):
+        ev = self.__dict__.get('_ffn_event')
+        handle = None
+        if ev is not None:
+            if not ev.cuda_event:      # created lazily: a first record makes the handle exist
+                ev.record()
+            handle = ctypes.c_void_p(ev.cuda_event)
+        _lib.check(_lib.load().sb_encoder_set_ffn_grads_event(self._handle, handle))
 
     def grad_bucket(self):
         """The flat fp16 tensor that holds all 12 parameter gradients of the most recent autograd backward

@@ -52,6 +52,32 @@ def _worker_reduce(rank, world, port, q):
             dist.destroy_process_group()
 
 
+def _worker_reduce_in_two_parts(rank, world, port, q):
+    """The bucket reduced as an early tail part and the rest gives the same sums as one allreduce."""
+    try:
+        _init(rank, world, port)
+        n = 1000
+        red = GradientBucketReducer(n * 4, 'cpu', buffers=2, dtype=torch.float32)
+        for step in range(4):
+            flat = red.arena(step).view(torch.float32)
+            flat.copy_(torch.arange(n, dtype=torch.float32) * (rank + 1) + step)
+            red.reduce_async(step, early=(4 * 300, None))     # elements 300.. first, then 0..299
+            red.wait(step)
+            want = torch.arange(n, dtype=torch.float32) * sum(r + 1 for r in range(world)) + world * step
+            assert torch.equal(red.flat(step), want), f'step {step}'
+        try:
+            red.reduce_async(0, early=(3, None))
+            raise AssertionError('an offset inside an element must be rejected')
+        except ValueError:
+            pass
+        q.put((rank, 'ok'))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, repr(e)))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
 def _worker_mismatch(rank, world, port, q):
     try:
         _init(rank, world, port)
@@ -99,6 +125,10 @@ def _run(worker, world=2, timeout=90):
 
 def test_bucket_allreduce_two_ranks_double_buffered():
     assert _run(_worker_reduce) == {0: 'ok', 1: 'ok'}
+
+
+def test_bucket_allreduce_in_an_early_part_and_the_rest():
+    assert _run(_worker_reduce_in_two_parts) == {0: 'ok', 1: 'ok'}
 
 
 def test_mismatched_buckets_are_rejected_on_every_rank_before_any_gradient_moves():

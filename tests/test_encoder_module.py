@@ -68,3 +68,13 @@ def test_shipped_configurations_validate():
     for which in ('b8_l512', 'b96_l128'):
         t = L.validate(get_layouts(which))
         assert len(t) == 51 and t['X'] == t['SB2']
+
+
+def test_early_gradient_part_is_a_suffix_of_the_bucket():
+    """The gradients that are final before the attention half of backward form the tail of the bucket."""
+    enc = Encoder('/tmp/unused', 2, 8, 2, 16, L.uniform_layouts(), torch.float16, 0, 0, 0, 0)
+    plan, total = enc._grad_plan
+    off = enc.early_grad_offset()
+    names = [n for n, _, _, o, _ in plan if o >= off]
+    assert names == ['BO', 'S1', 'B1', 'LINB1', 'LINW1', 'S2', 'B2', 'LINB2', 'LINW2']
+    assert 0 < off < total and off % 2 == 0
