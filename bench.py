@@ -339,6 +339,7 @@ def run_ours(args):
     peaks, peak_kind = load_peaks()
     hbm = float(peaks['hbm_gbs'])
     tf_burst = float(peaks['bf16_tflops'])
+    tf_sustained = float(peaks.get('bf16_tflops_sustained', tf_burst))
     ops = {}
     ideal_us = 0.0
     for name, v in per.items():
@@ -362,6 +363,9 @@ def run_ours(args):
         ideal_us += ideal
         ops[name] = rec
     sum_us = sum(r['us'] for r in ops.values())
+    T_tok = B * S
+    ref_list_us = ((142 * T_tok * E + 14 * H * B * S * S) / (hbm * 1e3) +
+                   (72 * E * E * T_tok + 12 * B * S * S * E) / (tf_sustained * 1e6))
     top = max(ops, key=lambda n: ops[n]['us'])
     if top in GEMM_FLOPS and top not in ATTN_BYTES:
         roof = {'kernel': f'gemm_tc_kernel ({top})', 'bound': 'tensor', 'achieved': ops[top]['tflops'],
@@ -487,7 +491,12 @@ def run_ours(args):
                       'frac_of_summed_roofline': round(ideal_us / sum_us, 3),
                       # the same ideal against the device time of a whole step (kernels overlap their
                       # neighbours' ramp-up and tail under programmatic dependent launch)
-                      'roofline_us_over_step_us': round(ideal_us / (ms_per_step * 1e3), 3)},
+                      'roofline_us_over_step_us': round(ideal_us / (ms_per_step * 1e3), 3),
+                      # the reference's own operator list (32 separate operators: 142*T*E + 14*S bytes of
+                      # elementwise traffic, 72*E^2*T + 12*B*L^2*E flops) at the measured copy bandwidth and the
+                      # sustained tensor rate, which is the figure that applies inside a long step
+                      'reference_list_roofline_us': round(ref_list_us, 1),
+                      'reference_list_roofline_over_step': round(ref_list_us / (ms_per_step * 1e3), 3)},
             'operators': ops,
         }
         print(json.dumps(line))
