@@ -81,6 +81,16 @@ NCU_DRAM_BYTES = {'QKT+softmax': 207.69e6, 'dX1gamma+bs': 200.28e6, 'gamma': 78.
                   'dX1QKT+dX2QKT': 87.78e6, 'bsb+blnrd1': 29.86e6, 'ebsb+blnrd2+baob': 51.58e6}
 
 
+# the same operators when the intermediates nothing reads again are not stored (the default; --keep-all 1 stores them):
+# LIN (2*T*E) in both bdrln calls, DLN (2*T*E) in both LayerNorm-backward passes, BETA / DATTN_DROP (2*S)
+FUSED_BYTES_SKIP = dict(FUSED_BYTES)
+FUSED_BYTES_SKIP.update({
+    'bdrln1': lambda B, L: 11 * B * L * E, 'bdrln2': lambda B, L: 11 * B * L * E,
+    'bsb+blnrd1': lambda B, L: 11 * B * L * E, 'ebsb+blnrd2+baob': lambda B, L: 15 * B * L * E,
+    'QKT+softmax': lambda B, L: H * B * (4 * P * L + 5 * L * L), 'dX1gamma+bs': lambda B, L: H * B * (4 * P * L + 5 * L * L),
+})
+
+
 def load_peaks():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -233,7 +243,9 @@ def run_ours(args):
     lay = get_layouts(args.layouts)
     table = L.validate(lay)
     enc = Encoder('/tmp/substation_b200_unused', B, S, H, E, lay, torch.float16,
-                  P_DROP, P_DROP, P_DROP, P_DROP, profiling=True, mask_mode='explicit').to(dev)
+                  P_DROP, P_DROP, P_DROP, P_DROP, profiling=True, mask_mode='explicit',
+                  keep_all_intermediates=bool(args.keep_all)).to(dev)
+    fused_bytes = FUSED_BYTES if args.keep_all else FUSED_BYTES_SKIP
     gen = torch.Generator(device=dev).manual_seed(1234)        # same weights on every rank
     with torch.no_grad():
         for (name, layout), prm in zip(lay['params'], enc.params):
@@ -356,7 +368,7 @@ def run_ours(args):
                 rec['frac_hbm'] = round(by / us / 1e3 / hbm, 3)
                 ideal = max(ideal, by / (hbm * 1e3))
         else:
-            by = FUSED_BYTES[name](B, S)
+            by = fused_bytes[name](B, S)
             rec['gbs'] = round(by / us / 1e3, 1)
             rec['frac_hbm'] = round(by / us / 1e3 / hbm, 3)
             ideal = by / (hbm * 1e3)
@@ -374,9 +386,9 @@ def run_ours(args):
         roof = {'kernel': top, 'bound': 'hbm', 'achieved': ops[top]['gbs'], 'peak': hbm, 'unit': 'GB/s',
                 'frac': round(ops[top]['gbs'] / hbm, 3)}
     # DRAM bytes (read + write) of one launch from the ncu capture of this workload; only known for B=8, L=512
-    roof['traffic'] = NCU_DRAM_BYTES.get(top) if (B, S) == (8, 512) else None
+    roof['traffic'] = NCU_DRAM_BYTES.get(top) if (B, S) == (8, 512) and args.keep_all else None
     roof['traffic_unit'] = 'bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)'
-    roof['algorithmic_bytes'] = (FUSED_BYTES.get(top) or ATTN_BYTES.get(top, lambda b, l: None))(B, S)
+    roof['algorithmic_bytes'] = (fused_bytes.get(top) or ATTN_BYTES.get(top, lambda b, l: None))(B, S)
     roof['peak_source'] = f'{peak_kind} (MEASURED_PEAKS.json: torch copy / cuBLAS bf16 burst)'
     roof['share_of_step'] = round(ops[top]['us'] / sum_us, 3)
 
@@ -591,6 +603,8 @@ def main():
                     help='N > 1: sum the feed-forward gradients beside the attention half of backward (1) or the whole '
                          'bucket beside the next step (0)')
     ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (config 5 uses 24)')
+    ap.add_argument('--keep-all', type=int, default=0,
+                    help='1: also store the nine intermediates nothing reads again (what enable_debug does)')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')
     args = ap.parse_args()

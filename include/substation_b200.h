@@ -109,7 +109,8 @@ int sb_softmax_dropout(void* stream, const sb_tensor* beta, const sb_tensor* alp
 /* lin = in + bias; r = mask*lin + resid; LayerNorm over the last dim:
  * diff = r - mean, istd = rsqrt(var + 1e-5), ln = diff*istd, out = ln*gamma + beta.
  * in, resid, mask, lin, diff, ln, out: [B,J,I]; istd: [B,J]; bias/gamma/beta: [I].
- * lin may alias in (same strides).  Replaces BiasDropoutResidualLinearNorm::run,
+ * lin may alias in (same strides), or be NULL when the caller does not need it (the layer's
+ * backward pass never reads it): it is then not stored.  Replaces BiasDropoutResidualLinearNorm::run,
  * pytorch_module/block_bdrln.cuh:105-180 and :275-352. */
 int sb_bias_dropout_residual_layernorm(void* stream, const sb_tensor* in, const sb_tensor* bias,
                                        const sb_tensor* resid, const sb_tensor* gamma,
@@ -159,7 +160,8 @@ int sb_extended_backward_scale_bias(void* stream, void* workspace, const sb_tens
                                     const sb_tensor* dbeta1, const sb_tensor* dlinb2);
 
 /* sb_backward_scale_bias followed by sb_backward_layernorm_residual_dropout in one pass over
- * the data (dln is still written): 13 instead of 15 bytes per element and one launch less.
+ * the data: 13 instead of 15 bytes per element and one launch less.  dln (dln1 in the extended
+ * form below) is only an intermediate of the pair: pass NULL and it is not stored (11 bytes).
  * Needs feature-innermost views of at most 1024 features, otherwise SB_ERR_UNSUPPORTED and the
  * caller runs the two operators.  Replaces the pair pytorch_module/encoder.cu:160-175. */
 int sb_backward_scale_bias_layernorm(void* stream, void* workspace, const sb_tensor* dy,
@@ -190,7 +192,7 @@ int sb_backward_attn_out_bias(void* stream, void* workspace, const sb_tensor* da
  * (every GPU that loads the library holds it until the process exits).
  * Limits and rules:
  *   - the feature extent (last dim of datt) may be at most 16384, larger ones are
- *     refused with SB_ERR_UNSUPPORTED; any number of tokens is fine;
+ *     refused with SB_ERR_UNSUPPORTED, and so are more than 2^31-1 tokens (B*J);
  *   - the first call on each device looks up that device's copy of the array
  *     (the stream's device must be current); make that first call outside of any
  *     stream capture;
@@ -202,7 +204,8 @@ int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* datt, const
  * alpha = softmax_k(beta), drop = mask*alpha.  qq, kk: [P,H,B,J] projections (any strides TMA
  * can address); beta, alpha, mask, drop: [H,B,J,K] and dense in that order.  The 128 x K score
  * tile lives in tensor memory between the tcgen05 MMAs and the per-row softmax, so beta is
- * written but never read back.  Needs P = 64, J = K a multiple of 64 and at most 512; otherwise
+ * written but never read back; pass beta = NULL and it is not written at all.  Needs P = 64,
+ * J = K a multiple of 64 and at most 512; otherwise
  * SB_ERR_UNSUPPORTED and the caller runs sb_einsum + sb_softmax_dropout.
  * Replaces the pair pytorch_module/encoder.cu:115-121. */
 int sb_attention_scores_softmax(void* stream, const sb_tensor* qq, const sb_tensor* kk,
@@ -210,7 +213,7 @@ int sb_attention_scores_softmax(void* stream, const sb_tensor* qq, const sb_tens
                                 const sb_tensor* drop, float scale, const sb_dropout* dropout);
 
 /* dattn_drop = sum_p dgamma*vv and sb_backward_softmax in one kernel (dattn_drop is written
- * but never read back).  Same requirements.  Replaces pytorch_module/encoder.cu:250-252 + :258-261. */
+ * but never read back; NULL: not written at all).  Same requirements.  Replaces pytorch_module/encoder.cu:250-252 + :258-261. */
 int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, const sb_tensor* vv,
                                          const sb_tensor* alpha, const sb_tensor* mask,
                                          const sb_tensor* dattn_drop, const sb_tensor* dbeta);
@@ -280,15 +283,21 @@ typedef struct sb_epilogue {
   int activation;
   const sb_dropout* dropout;
   const char* logical_dims;
+  int discard_c; /* non-zero: c itself is not stored, only out2 / out3 (c still gives the geometry) */
 } sb_epilogue;
 int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
                     const char* c_dims, const sb_tensor* c, float alpha, const sb_epilogue* epilogue);
-/* Every wait inside the tcgen05 kernel is bounded; when one runs out the kernel
- * records a code (1 producer, 2 MMA issuer, 3 epilogue), drains and returns.
- * This reads that sticky per-process flag after synchronising `stream`
- * (0 = no wait ever ran out).  The reference has no counterpart: its CHECK
- * macro aborts the process (pytorch_module/all.cuh:7-13). */
+/* Every wait inside the tcgen05 kernels is bounded; when one runs out the kernel
+ * records a code (1 producer, 2 MMA issuer, 3 epilogue, ...), drains and returns.
+ * This reads that flag after synchronising `stream` (0 = no wait ran out since the
+ * last reset).  The flag is per device (the device current when the call is made) and
+ * sticky: while it is set, every later tcgen05 kernel on that device gives up its waits
+ * at once, so its output is garbage.  sb_device_error_reset clears it (after
+ * synchronising `stream`) once the caller has dealt with the failed pass.  The
+ * reference has no counterpart: its CHECK macro aborts the process
+ * (pytorch_module/all.cuh:7-13). */
 int sb_device_error(void* stream, int* code);
+int sb_device_error_reset(void* stream);
 /* The contraction kernels are persistent: one CTA per SM walks the output tiles.  When
  * another kernel must run next to them (the NCCL gradient allreduce of the data-parallel
  * path), tell the library to occupy only n_sms SMs so that no CTA of a contraction waits
@@ -363,6 +372,14 @@ int sb_encoder_kernel_count(sb_encoder* enc);
 /* Fused multi-operator kernels (on by default) can be switched off to run the reference's
  * one-kernel-per-operator sequence. */
 int sb_encoder_set_fusion(sb_encoder* enc, int enabled);
+/* Nine tensors of the reference's pointer tables are written by the layer but read by nothing
+ * afterwards once the fused operators run (pytorch_module/encoder.cu:158-299 lists what backward
+ * reads): BETA, WKKWQQWVV, SB1_LINW1, LIN2 and the bias written back over ATT in the forward pass;
+ * DATTN_DROP, DLN2, DLN1 and DXATT in the backward pass, 235 MB per step at B=8, L=512.  enabled = 1 (the
+ * default) writes them all, as the reference does; 0 leaves them untouched wherever a fused
+ * operator makes them unnecessary (their pointers must still be valid: an operator that declines
+ * falls back to the separate kernels, which need them). */
+int sb_encoder_set_dead_stores(sb_encoder* enc, int enabled);
 
 #ifdef __cplusplus
 }

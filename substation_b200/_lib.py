@@ -34,7 +34,7 @@ class SbEpilogue(ctypes.Structure):
                 ('resid', ctypes.POINTER(SbTensor)), ('mask', ctypes.POINTER(SbTensor)),
                 ('out2', ctypes.POINTER(SbTensor)), ('out3', ctypes.POINTER(SbTensor)),
                 ('activation', ctypes.c_int32), ('dropout', ctypes.POINTER(SbDropout)),
-                ('logical_dims', c_char_p)]
+                ('logical_dims', c_char_p), ('discard_c', ctypes.c_int32)]
 
 
 class SbEncoderConfig(ctypes.Structure):
@@ -88,6 +88,7 @@ SIGNATURES = {
     'sb_einsum_fused': (c_int, [c_void_p, c_char_p, _T, c_char_p, _T, c_char_p, _T, c_float, ctypes.POINTER(SbEpilogue)]),
     'sb_einsum_last_impl': (c_int, []),
     'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    'sb_device_error_reset': (c_int, [c_void_p]),
     'sb_set_sm_budget': (c_int, [c_int]),
     'sb_encoder_create': (c_int, [ctypes.POINTER(SbEncoderConfig), ctypes.POINTER(c_void_p)]),
     'sb_encoder_destroy': (c_int, [c_void_p]),
@@ -104,6 +105,7 @@ SIGNATURES = {
     'sb_encoder_launch_count': (c_int, [c_void_p]),
     'sb_encoder_kernel_count': (c_int, [c_void_p]),
     'sb_encoder_set_fusion': (c_int, [c_void_p, c_int]),
+    'sb_encoder_set_dead_stores': (c_int, [c_void_p, c_int]),
 }
 
 _lib = None
@@ -114,13 +116,20 @@ def lib_path():
 
 
 def load():
-    """Load (building first if the .so is absent and nvcc is available)."""
+    """Load the library, (re)building it first whenever nvcc is at hand and the sources changed since the
+    last build.  Without nvcc a library whose stamp does not match the sources is refused: results from a
+    stale binary would describe code that no longer exists."""
     global _lib
     if _lib is not None:
         return _lib
     path = lib_path()
-    if not os.path.exists(path):
-        _build.build()
+    if _build.have_nvcc():
+        _build.build()                # returns at once when the digest of the sources matches the stamp
+    elif not os.path.exists(path):
+        raise RuntimeError(f'{path} is missing and nvcc is not available to build it')
+    elif not _build.stamp_matches():
+        raise RuntimeError(f'{path} was built from other sources than the ones in csrc/ (stamp mismatch) '
+                           'and nvcc is not available to rebuild it')
     lib = ctypes.CDLL(path)
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)      # AttributeError if a declared symbol is missing

@@ -19,7 +19,7 @@ LIB_NAME = 'libsubstation_b200.so'
 LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
 SOURCES = ('api.cu', 'fused_ops.cu', 'fused_lnbwd.cu', 'gemm.cu')
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
-              '-Xcompiler', '-fPIC', '-shared']
+              '-Xcompiler', '-fPIC', '-shared', '--threads', '0']
 
 
 def _nvcc():
@@ -27,6 +27,23 @@ def _nvcc():
         if cand and os.path.exists(cand):
             return cand
     raise RuntimeError('nvcc not found; set NVCC or put it on PATH')
+
+
+def have_nvcc():
+    try:
+        _nvcc()
+        return True
+    except RuntimeError:
+        return False
+
+
+def stamp_matches():
+    """True when the library on disk was built from the current sources."""
+    stamp = LIB_PATH + '.md5'
+    if not (os.path.exists(LIB_PATH) and os.path.exists(stamp)):
+        return False
+    with open(stamp) as f:
+        return f.read().strip() == source_digest()
 
 
 def source_digest():

@@ -209,16 +209,17 @@ extern "C" int sb_attention_scores_softmax(void* stream, const sb_tensor* qq, co
   View4 vq, vk, vb, va, vm, vd;
   Rng rng;
   int P = 0, P2 = 0;
-  SB_TRY(to_view4(beta, nullptr, false, "scores.beta", &vb));
-  SB_TRY(to_view4(alpha, beta, false, "scores.alpha", &va));
-  SB_TRY(to_view4(mask, beta, true, "scores.mask", &vm));
-  SB_TRY(to_view4(drop, beta, false, "scores.drop", &vd));
-  SB_TRY(to_proj(qq, beta, "scores.qq", &vq, &P));
-  SB_TRY(to_proj(kk, beta, "scores.kk", &vk, &P2));
+  SB_TRY(to_view4(alpha, nullptr, false, "scores.alpha", &va));
+  if (beta) SB_TRY(to_view4(beta, alpha, false, "scores.beta", &vb));
+  else { vb = va; vb.p = nullptr; }   // not wanted: never stored
+  SB_TRY(to_view4(mask, alpha, true, "scores.mask", &vm));
+  SB_TRY(to_view4(drop, alpha, false, "scores.drop", &vd));
+  SB_TRY(to_proj(qq, alpha, "scores.qq", &vq, &P));
+  SB_TRY(to_proj(kk, alpha, "scores.kk", &vk, &P2));
   if (P != P2) return fail(SB_ERR_ARG, "scores: head size differs between queries and keys");
-  if (beta->size[2] != beta->size[3]) return fail(SB_ERR_UNSUPPORTED, "scores: self-attention only (J must equal K)");
+  if (alpha->size[2] != alpha->size[3]) return fail(SB_ERR_UNSUPPORTED, "scores: self-attention only (J must equal K)");
   SB_TRY(to_rng(dropout, &rng));
-  return launch_attn_scores_fwd((cudaStream_t)stream, dims4(beta), P, vq, vk, vb, va, vm, vd, scale, rng);
+  return launch_attn_scores_fwd((cudaStream_t)stream, dims4(alpha), P, vq, vk, vb, va, vm, vd, scale, rng);
 }
 
 extern "C" int sb_attention_scores_softmax_backward(void* stream, const sb_tensor* dgamma, const sb_tensor* vv,
@@ -228,7 +229,8 @@ extern "C" int sb_attention_scores_softmax_backward(void* stream, const sb_tenso
   int P = 0, P2 = 0;
   SB_TRY(to_view4(alpha, nullptr, false, "scores_bwd.alpha", &va));
   SB_TRY(to_view4(mask, alpha, true, "scores_bwd.mask", &vm));
-  SB_TRY(to_view4(dattn_drop, alpha, false, "scores_bwd.dattn_drop", &vd));
+  if (dattn_drop) SB_TRY(to_view4(dattn_drop, alpha, false, "scores_bwd.dattn_drop", &vd));
+  else { vd = va; vd.p = nullptr; }   // not wanted: never stored
   SB_TRY(to_view4(dbeta, alpha, false, "scores_bwd.dbeta", &vo));
   SB_TRY(to_proj(dgamma, alpha, "scores_bwd.dgamma", &vg, &P));
   SB_TRY(to_proj(vv, alpha, "scores_bwd.vv", &vvv, &P2));
@@ -285,7 +287,8 @@ extern "C" int sb_bias_dropout_residual_layernorm(void* stream, const sb_tensor*
   SB_TRY(to_view3(in, nullptr, false, "bdrln.in", &vin));
   SB_TRY(to_view3(resid, in, false, "bdrln.resid", &vres));
   SB_TRY(to_view3(mask, in, true, "bdrln.mask", &vmask));
-  SB_TRY(to_view3(lin, in, false, "bdrln.lin", &vlin));
+  if (lin) SB_TRY(to_view3(lin, in, false, "bdrln.lin", &vlin));
+  else { vlin = vin; vlin.p = nullptr; }   // not wanted: never stored
   SB_TRY(to_view3(diff, in, false, "bdrln.diff", &vdiff));
   SB_TRY(to_view3(ln, in, false, "bdrln.ln", &vln));
   SB_TRY(to_view3(out, in, false, "bdrln.out", &vout));
@@ -294,7 +297,7 @@ extern "C" int sb_bias_dropout_residual_layernorm(void* stream, const sb_tensor*
   SB_TRY(to_param(gamma, in->size[2], "bdrln.gamma", &pg));
   SB_TRY(to_param(beta, in->size[2], "bdrln.beta", &pbt));
   SB_TRY(to_rng(dropout, &rng));
-  if (lin->ptr == in->ptr && (vlin.sB != vin.sB || vlin.sJ != vin.sJ || vlin.sF != vin.sF))
+  if (lin && lin->ptr == in->ptr && (vlin.sB != vin.sB || vlin.sJ != vin.sJ || vlin.sF != vin.sF))
     return fail(SB_ERR_ARG, "bdrln: lin aliases in but has different strides");
   return launch_bdrln((cudaStream_t)stream, dims3(in), vin, pb, vres, pg, pbt, vmask, vlin, vdiff, vistd,
                       vln, vout, rng);
@@ -391,7 +394,8 @@ extern "C" int sb_backward_scale_bias_layernorm(void* stream, void* workspace, c
   SB_TRY(to_view3(ln, dy, false, "bsb+blnrd.ln", &vn));
   SB_TRY(to_view3(diff, dy, false, "bsb+blnrd.diff", &vd));
   SB_TRY(to_view3(mask, dy, true, "bsb+blnrd.mask", &vm));
-  SB_TRY(to_view3(dln, dy, false, "bsb+blnrd.dln", &vg));
+  if (dln) SB_TRY(to_view3(dln, dy, false, "bsb+blnrd.dln", &vg));
+  else { vg = vy; vg.p = nullptr; }   // not wanted: never stored
   SB_TRY(to_view3(dresid, dy, false, "bsb+blnrd.dresid", &vr));
   SB_TRY(to_view3(dlin, dy, false, "bsb+blnrd.dlin", &vl));
   SB_TRY(to_view2(istd, dy, "bsb+blnrd.istd", &vs));
@@ -415,7 +419,8 @@ extern "C" int sb_extended_backward_scale_bias_layernorm(
   SB_TRY(to_view3(dlin2, ln1, false, "ebsb+blnrd.dlin2", &vl2));
   SB_TRY(to_view3(diff, ln1, false, "ebsb+blnrd.diff", &vd));
   SB_TRY(to_view3(mask, ln1, true, "ebsb+blnrd.mask", &vm));
-  SB_TRY(to_view3(dln1, ln1, false, "ebsb+blnrd.dln1", &vg));
+  if (dln1) SB_TRY(to_view3(dln1, ln1, false, "ebsb+blnrd.dln1", &vg));
+  else { vg = vn; vg.p = nullptr; }   // not wanted: never stored
   SB_TRY(to_view3(dresid1, ln1, false, "ebsb+blnrd.dresid1", &vr));
   SB_TRY(to_view3(datt, ln1, false, "ebsb+blnrd.datt", &va));
   SB_TRY(to_view2(istd, ln1, "ebsb+blnrd.istd", &vs));
@@ -542,6 +547,13 @@ extern "C" int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor
       }
     }
   }
+  ge.skip_c = ep->discard_c ? 1 : 0;
+  // The epilogue reads bias, residual and mask with 128-bit accesses: refuse operands it could not read that
+  // way before anything is launched (the caller then runs the two operators separately).
+  if (ge.vec && !aligned(ge.vec, 16)) return fail(SB_ERR_ALIGNMENT, "einsum_fused: bias must be 16-byte aligned");
+  if (ge.resid && !aligned(ge.resid, 16)) return fail(SB_ERR_ALIGNMENT, "einsum_fused: resid must be 16-byte aligned");
+  if (ge.mask && (!aligned(ge.mask, 16) || std::max(g.sCm, g.sCn) % 16 != 0))
+    return fail(SB_ERR_ALIGNMENT, "einsum_fused: mask must be 16-byte aligned and the row pitch of c a multiple of 16");
   return run_gemm_fused((cudaStream_t)stream, g, ge);
 }
 extern "C" int sb_einsum_last_impl(void) { return g_last_gemm_impl; }
@@ -554,6 +566,7 @@ extern "C" int sb_device_error(void* stream, int* code) {
   if (!code) return fail(SB_ERR_ARG, "sb_device_error: null argument");
   return gemm_device_error((cudaStream_t)stream, code);
 }
+extern "C" int sb_device_error_reset(void* stream) { return gemm_device_error_reset((cudaStream_t)stream); }
 
 // ---------------------------------------------------------------------------
 // Whole layer
@@ -629,6 +642,7 @@ struct sb_encoder {
   bool graphs = true;           // sb_encoder_set_graphs / SUBSTATION_B200_GRAPHS=0
   bool timing = false;
   bool fuse = true;            // use the fused multi-operator kernels where the layouts allow
+  bool dead_stores = true;     // write the intermediates nothing reads again (sb_encoder_set_dead_stores)
   std::vector<std::pair<std::string, cudaEvent_t>> marks;
   std::vector<cudaEvent_t> event_pool;
   std::vector<std::pair<std::string, float>> last_times;
@@ -829,6 +843,12 @@ extern "C" int sb_encoder_set_fusion(sb_encoder* e, int enabled) {
   return SB_OK;
 }
 
+extern "C" int sb_encoder_set_dead_stores(sb_encoder* e, int enabled) {
+  if (!e) return fail(SB_ERR_ARG, "null handle");
+  e->dead_stores = enabled != 0;
+  return SB_OK;
+}
+
 extern "C" int sb_encoder_set_graphs(sb_encoder* e, int enabled) {
   if (!e) return fail(SB_ERR_ARG, "null handle");
   e->graphs = enabled != 0;
@@ -930,6 +950,7 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
       ep.bias_dims = L.at("BKQV").c_str();
       ep.bias = &bias;
       ep.out2 = &out2;
+      ep.discard_c = e->dead_stores ? 0 : 1;   // WKKWQQWVV: only the bias operator reads it
       st = einsum_fused(e, s, "QKV-fused+aib", L.at("X"), T["X"], L.at("WKQV"), T["WKQV"], L.at("WKKWQQWVV"),
                         T["WKKWQQWVV"], 1.f, &ep);
       if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
@@ -953,7 +974,8 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
     if (e->fuse) {
       e->mark(s, "QKT+softmax");
       sb_tensor kk = e->view(q_slice("KKQQVV", 0), lKK, "PHBJ"), qq = e->view(q_slice("KKQQVV", 1), lKK, "PHBJ");
-      st = sb_attention_scores_softmax(stream, &qq, &kk, &beta, &alpha, &mask, &dr, scale, &d);
+      // BETA is consumed inside the kernel
+      st = sb_attention_scores_softmax(stream, &qq, &kk, e->dead_stores ? &beta : nullptr, &alpha, &mask, &dr, scale, &d);
       if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
       if (st == SB_ERR_UNSUPPORTED) e->unmark();
     }
@@ -987,9 +1009,9 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
     sb_tensor mask = e->view(T["DROP1MASK"], "DROP1MASK"), diff = e->view(T["LN1DIFF"], "LN1DIFF");
     sb_tensor istd = e->view(T["LN1STD"], "LN1STD"), ln = e->view(T["LN1"], "LN1"), out = e->view(T["SB1"], "SB1");
     sb_dropout d = drop(e->p_resid1, mask_mode, seed, offset + 1);
-    // the biased projection is written back over ATT
-    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask, &in, &diff,
-                                              &istd, &ln, &out, &d));
+    // the biased projection is written back over ATT (nothing reads it again)
+    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask,
+                                              e->dead_stores ? &in : nullptr, &diff, &istd, &ln, &out, &d));
   }
   {
     // bias + activation + dropout in the epilogue of the first feed-forward contraction
@@ -1009,6 +1031,7 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
       ep.activation = e->activation;
       ep.dropout = &d;
       ep.logical_dims = "BJU";
+      ep.discard_c = e->dead_stores ? 0 : 1;   // SB1_LINW1: only the bias operator reads it
       st = einsum_fused(e, s, "lin1+bad", L.at("SB1"), T["SB1"], L.at("LINW1"), T["LINW1"], lc, T["SB1_LINW1"], 1.f, &ep);
       if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
     }
@@ -1032,8 +1055,9 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
     sb_tensor diff = e->view(T["LN2DIFF"], "LN2DIFF"), istd = e->view(T["LN2STD"], "LN2STD");
     sb_tensor ln = e->view(T["LN2"], "LN2"), out = e->view(T["SB2"], "SB2");
     sb_dropout d = drop(e->p_resid2, mask_mode, seed, offset + 3);
-    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask, &lin, &diff,
-                                              &istd, &ln, &out, &d));
+    // LIN2 is never read again
+    SB_TRY(sb_bias_dropout_residual_layernorm(stream, &in, &bias, &resid, &gamma, &beta, &mask,
+                                              e->dead_stores ? &lin : nullptr, &diff, &istd, &ln, &out, &d));
   }
   if (e->timing) { e->mark(s, ""); --e->launches; }
   e->kernels_fwd = g_kernel_launches - e->kernel_base;
@@ -1074,8 +1098,8 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     sb_tensor ln = v("LN2"), gamma = pv("S2"), dln = v("DLN2"), dg = dv("S2"), db = dv("B2");
     sb_tensor istd = v("LN2STD"), diff = v("LN2DIFF"), mask = v("DROP3MASK"), dres = v("DRESID2"), dlin = v("DLIN2");
     e->mark(s, "bsb+blnrd1");
-    int st = e->fuse ? sb_backward_scale_bias_layernorm(stream, ws, &tDY, &ln, &gamma, &istd, &diff, &mask, &dln, &dres,
-                                                         &dlin, &dg, &db)
+    int st = e->fuse ? sb_backward_scale_bias_layernorm(stream, ws, &tDY, &ln, &gamma, &istd, &diff, &mask,
+                                                         e->dead_stores ? &dln : nullptr, &dres, &dlin, &dg, &db)
                      : SB_ERR_UNSUPPORTED;
     if (st == SB_ERR_UNSUPPORTED) {
       e->relabel("bsb");
@@ -1105,7 +1129,8 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     sb_tensor istd = v("LN1STD"), diff = v("LN1DIFF"), mask = v("DROP1MASK"), dres1 = v("DRESID1"), datt = v("DATT");
     e->mark(s, "ebsb+blnrd2+baob");
     int st = e->fuse ? sb_extended_backward_scale_bias_layernorm(stream, ws, &ln1, &gamma, &dres2, &dlw, &dlin2, &istd,
-                                                                  &diff, &mask, &dln1, &dres1, &datt, &dg, &db, &dlb2, &dbo)
+                                                                  &diff, &mask, e->dead_stores ? &dln1 : nullptr, &dres1,
+                                                                  &datt, &dg, &db, &dlb2, &dbo)
                      : SB_ERR_UNSUPPORTED;
     if (st == SB_ERR_UNSUPPORTED) {
       e->relabel("ebsb");
@@ -1139,7 +1164,7 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     if (e->fuse) {
       e->mark(s, "dX1gamma+bs");
       sb_tensor dgm = e->view(T["DGAMMA"], "DGAMMA"), vvt = e->view(VV, lKK, "PHBJ");
-      st = sb_attention_scores_softmax_backward(stream, &dgm, &vvt, &alpha, &mask, &g, &o);
+      st = sb_attention_scores_softmax_backward(stream, &dgm, &vvt, &alpha, &mask, e->dead_stores ? &g : nullptr, &o);
       if (st != SB_OK && st != SB_ERR_UNSUPPORTED) return st;
       if (st == SB_ERR_UNSUPPORTED) e->unmark();
     }
@@ -1189,6 +1214,7 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
     ep.kind = SB_EPI_RESIDUAL;
     ep.resid = &resid;
     ep.out2 = &out2;
+    ep.discard_c = e->dead_stores ? 0 : 1;   // DXATT: only the encoder-input sum reads it
     st_bei = einsum_fused(e, s, "dXQKV-fused+bei", L.at("WKQV"), T["WKQV"], L.at("DKKQQVV"), T["DKKQQVV"], L.at("DXATT"),
                           T["DXATT"], 1.f, &ep);
     if (st_bei != SB_OK && st_bei != SB_ERR_UNSUPPORTED) return st_bei;
@@ -1312,7 +1338,8 @@ extern "C" int sb_encoder_forward(sb_encoder* e, void* stream, const void* x, co
   auto pass = [&](cudaStream_t s) { return forward_pass(e, (void*)s, x, params, fwd, y, mask_mode, seed, offset); };
   // in-kernel masks take a new offset every call, so only explicit-mask passes repeat
   if (mask_mode != SB_MASK_EXPLICIT) return pass((cudaStream_t)stream);
-  std::vector<uint64_t> key{(uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)y, (uint64_t)e->fuse, (uint64_t)gemm_sm_budget()};
+  std::vector<uint64_t> key{(uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)y, (uint64_t)e->fuse | ((uint64_t)e->dead_stores << 1),
+                            (uint64_t)gemm_sm_budget()};
   for (size_t i = 0; i < e->param_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)params[i]);
   for (size_t i = 0; i < e->fwd_order.size(); ++i) key.push_back((uint64_t)(uintptr_t)fwd[i]);
   return run_pass(e, e->graph_fwd, std::move(key), (cudaStream_t)stream, &e->launches, &e->kernels_fwd, pass);
@@ -1324,7 +1351,7 @@ extern "C" int sb_encoder_backward(sb_encoder* e, void* stream, const void* dy, 
   if (!e || !dy || !dparams || !bwd || !dx || !params || !fwd)
     return fail(SB_ERR_ARG, "sb_encoder_backward: null argument");
   auto pass = [&](cudaStream_t s) { return backward_pass(e, (void*)s, dy, dparams, bwd, params, fwd, x, dx); };
-  std::vector<uint64_t> key{(uint64_t)(uintptr_t)dy, (uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)dx, (uint64_t)e->fuse,
+  std::vector<uint64_t> key{(uint64_t)(uintptr_t)dy, (uint64_t)(uintptr_t)x, (uint64_t)(uintptr_t)dx, (uint64_t)e->fuse | ((uint64_t)e->dead_stores << 1),
                             (uint64_t)gemm_sm_budget()};
   for (size_t i = 0; i < e->param_order.size(); ++i) {
     key.push_back((uint64_t)(uintptr_t)dparams[i]);

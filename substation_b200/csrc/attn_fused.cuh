@@ -48,6 +48,7 @@ struct Params {
   Rng rng;               // forward: dropout source
   uint8_t* mask;         // [batch][L][L] bytes (written directly when the mask is generated here)
   int prefetch;          // producer warp asks for the row inputs of the next tile to be brought into L2
+  int skip_o0;           // the first score output (BETA forward, DATTN_DROP backward) is not wanted: never stored
 };
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
@@ -169,7 +170,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO0) : "memory");
+    if (!p.skip_o0) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO0) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO1) : "memory");
     if (!BWD) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO2) : "memory");
     if (BWD) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmI) : "memory");
@@ -368,7 +369,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (rows)
           sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
             const uint32_t b = n_out % NB;
-            if (hh == 0) {
+            if (hh == 0 && !p.skip_o0) {
               if (lane == 0) bulk_wait_read<NB - 1>();
               __syncwarp();
             }
@@ -383,10 +384,10 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 sum += ex;
                 r[v * 8 + e] = __float_as_uint(ex);
               }
-              *stage_ptr(b, hh * 4 + v) = pack8(f);
+              if (!p.skip_o0) *stage_ptr(b, hh * 4 + v) = pack8(f);
             }
             tmem_st32(trow + c * 64 + hh * 32, r);
-            if (hh == 1) {
+            if (hh == 1 && !p.skip_o0) {
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) store_rows(&tmO0, b, c, jr, bt);
@@ -502,7 +503,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 8; ++i) mw[i] = mall[hh * 8 + i];
             const uint32_t b = n_out % NB;
-            if (hh == 0) {
+            if (hh == 0 && !p.skip_o0) {
               if (lane == 0) bulk_wait_read<NB - 1>();
               __syncwarp();
             }
@@ -512,7 +513,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]);
               const uint4 dad = pack8(f);   // DATTN_DROP as stored (fp16)
-              *stage_ptr(b, hh * 4 + v) = dad;
+              if (!p.skip_o0) *stage_ptr(b, hh * 4 + v) = dad;
               // continue from the fp16 value, as the separate softmax-backward operator would
               const uint4 da = mask_apply(dad, make_uint2(mw[2 * v], mw[2 * v + 1]));
               unpack8(da, f);
@@ -527,7 +528,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               }
             }
             tmem_st32(trow + c * 64 + hh * 32, r);
-            if (hh == 1) {
+            if (hh == 1 && !p.skip_o0) {
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) store_rows(&tmO0, b, c, jr, bt);

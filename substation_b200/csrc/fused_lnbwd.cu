@@ -169,7 +169,7 @@ lnbwd_kernel(LnBwdParams p) {
         for (int e = 0; e < 8; ++e) o[e] = fmaf(g[r][e], s[r], -c1) - d8[r][e] * c2;
         const uint4 dres = pack8(o);
         const uint4 dl = mask_apply(dres, mk[r]);
-        store8h_raw(p.dln.p, off_out[r][0], 1, 1, f, F, pack8(g[r]));
+        if (p.dln.p) store8h_raw(p.dln.p, off_out[r][0], 1, 1, f, F, pack8(g[r]));
         store8h_raw(p.dresid.p, off_out[r][1], 1, 1, f, F, dres);
         store8h_raw(p.dlin.p, off_out[r][2], 1, 1, f, F, dl);
         if (MODE == 1) {

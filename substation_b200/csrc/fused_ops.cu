@@ -261,7 +261,7 @@ bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma
         unpack8(rr[i], rs);
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] += bb[e];
-        store8h_raw(lin.p, o_lin, lin.sF, SB_VEC(lin), f, d.F, pack8(x));
+        if (lin.p) store8h_raw(lin.p, o_lin, lin.sF, SB_VEC(lin), f, d.F, pack8(x));  // null: the caller does not want it
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           r[i][e] = (AV || f + e < d.F) ? (mask_keep(mr[i], e) ? x[e] : 0.f) + rs[e] : 0.f;
@@ -899,9 +899,10 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
   if (slices > (int)(kWsCounterBytes / sizeof(unsigned)))
     return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace counters");
   const long long R = (long long)d.B * d.J;
+  if (R > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, "token reductions over more than 2^31-1 tokens are not supported");
   const long long Fp = (long long)slices * 256;
   // as many 8-warp CTAs per SM as the kernel's register budget allows; bounded by rows and by the workspace
-  long long P = (148 * Op::MINB + slices - 1) / slices;
+  long long P = ((long long)device_facts().sms * Op::MINB + slices - 1) / slices;
   const long long cap = (long long)((kWsBytes - kWsCounterBytes) / (Op::NQ * Fp * sizeof(float)));
   if (cap < 1) return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace");
   if (P > cap) P = cap;
@@ -1237,7 +1238,9 @@ extern "C" int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* 
   const Dims3 d{(int)B, (int)J, (int)F};
   const int slices = (int)((F + 255) / 256);
   const long long R = B * J, Fp = (long long)slices * 256;
-  long long P = (148 * 4 + slices - 1) / slices;
+  if (R > 0x7fffffffLL)   // the kernel indexes tokens with 32-bit arithmetic
+    return fail(SB_ERR_UNSUPPORTED, "baob (no-alloc): more than 2^31-1 tokens (B*J) are not supported");
+  long long P = ((long long)device_facts().sms * 4 + slices - 1) / slices;
   const long long cap = (long long)(kStaticPartialBytes / (Fp * sizeof(float)));  // >= 16 for F <= 16384
   if (P > cap) P = cap;
   if (P > (R + 7) / 8) P = (R + 7) / 8;

@@ -240,7 +240,7 @@ constexpr int kABytes = kBM * kBK * 2;   // 16 KiB per 64-wide K block
 constexpr int kStageOutBytes = 4 * 2 * 4096;  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B)
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
-__device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel in this process
+__device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel on this device since the last reset
 
 // Work fused behind a contraction's epilogue (paired-CTA kernel, TMA-store mode).  All extra tensors have C's
 // geometry; the arithmetic on the stored fp16 values is the flat elementwise kernels', so results are identical
@@ -255,6 +255,7 @@ struct EpiParams {
   const __half* resid;   // [M][N], row stride sCm
   uint8_t* mask;         // [M][N] bytes, row stride sCm; read, or written when rng.philox
   int activation;
+  int skip_c;            // C itself is not stored (nothing reads it once the fused outputs exist)
   Rng rng;
 };
 
@@ -919,10 +920,19 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
       return fail(SB_ERR_UNSUPPORTED, "fused epilogue, third output: " + why);
     p.epi.kind = epi->kind;
     p.epi.vec_along_m = vec_flipped ? !epi->vec_along_m : epi->vec_along_m;
+    // the epilogue reads its side inputs with 128-bit accesses at (row * sCm + 64-column block)
+    auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+    if ((epi->kind == 1 || epi->kind == 3) && !p.epi.vec_along_m && misaligned(epi->vec))
+      return fail(SB_ERR_ALIGNMENT, "fused epilogue: a bias along the columns must be 16-byte aligned");
+    if (epi->kind == 2 && misaligned(epi->resid))
+      return fail(SB_ERR_ALIGNMENT, "fused epilogue: the residual must be 16-byte aligned");
+    if (epi->kind == 3 && (misaligned(epi->mask) || g.sCm % 16 != 0))
+      return fail(SB_ERR_ALIGNMENT, "fused epilogue: the mask must be 16-byte aligned with a row pitch that is a multiple of 16");
     p.epi.vec = reinterpret_cast<const __half*>(epi->vec);
     p.epi.resid = reinterpret_cast<const __half*>(epi->resid);
     p.epi.mask = reinterpret_cast<uint8_t*>(epi->mask);
     p.epi.activation = epi->activation;
+    p.epi.skip_c = epi->skip_c;
     p.epi.rng = epi->rng;
   }
   const int kind = epi ? epi->kind : 0;
@@ -1069,11 +1079,13 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
   if (!make_operand_map(b_ptr, L, P, batch, bJ, bP, sBb, brows, &b, &why))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores, second operand: " + why);
   CUtensorMap m0, m1, m2, mi, mm;
+  memset(&m0, 0, sizeof(m0));
   memset(&m2, 0, sizeof(m2));
   memset(&mi, 0, sizeof(mi));
   memset(&mm, 0, sizeof(mm));
   int sw0 = 0, sw1 = 0, sw2 = 0, swi = 0, swm = 0;
-  if (!encode_map(o0, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m0, &sw0, &why) ||
+  // o0 (BETA forward, DATTN_DROP backward) may be absent: the kernel then never stores it
+  if ((o0 && !encode_map(o0, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m0, &sw0, &why)) ||
       !encode_map(o1, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m1, &sw1, &why) ||
       (o2 && !encode_map(o2, (cuuint64_t)L, (cuuint64_t)L, (cuuint64_t)batch, L, (long long)L * L, 64, 32, &m2, &sw2, &why)))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores, output: " + why);
@@ -1088,7 +1100,8 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
   if ((long long)p.tiles_j * batch > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, "fused attention scores: too many tiles");
   p.tiles = (int)(p.tiles_j * batch);
   p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap;
-  p.swap_o = sw0;
+  p.swap_o = sw1;      // every score tensor has the same geometry
+  p.skip_o0 = o0 ? 0 : 1;
   p.b_bytes = b.mn ? L * 128 : ((L + 255) / 256) * brows * 128;
   constexpr int smem = attn::Cfg<BWD>::kSmemBytes;
   static_assert(smem <= 232448, "shared memory of the fused attention kernel");
@@ -1103,7 +1116,7 @@ int launch_attn_scores(cudaStream_t s, Dims4 d, int P, const void* a_ptr, long l
 int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, View4 beta, View4 alpha, View4 mask,
                            View4 drop, float scale, Rng rng) {
   if ((long long)d.H * d.B * d.J == 0) return SB_OK;
-  if (!dense_scores(beta, d) || !dense_scores(alpha, d) || !dense_scores(drop, d) || !dense_scores(mask, d))
+  if ((beta.p && !dense_scores(beta, d)) || !dense_scores(alpha, d) || !dense_scores(drop, d) || !dense_scores(mask, d))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores need score tensors dense as [H,B,J,K]");
   if (!(scale > 0.f)) return fail(SB_ERR_UNSUPPORTED, "fused attention scores need a positive scale");
   attn::Params p{};
@@ -1118,7 +1131,7 @@ int launch_attn_scores_fwd(cudaStream_t s, Dims4 d, int P, View4 qq, View4 kk, V
 int launch_attn_scores_bwd(cudaStream_t s, Dims4 d, int P, View4 dgamma, View4 vv, View4 alpha, View4 mask,
                            View4 dattn_drop, View4 dbeta) {
   if ((long long)d.H * d.B * d.J == 0) return SB_OK;
-  if (!dense_scores(alpha, d) || !dense_scores(dattn_drop, d) || !dense_scores(dbeta, d) || !dense_scores(mask, d))
+  if (!dense_scores(alpha, d) || (dattn_drop.p && !dense_scores(dattn_drop, d)) || !dense_scores(dbeta, d) || !dense_scores(mask, d))
     return fail(SB_ERR_UNSUPPORTED, "fused attention scores need score tensors dense as [H,B,J,K]");
   attn::Params p{};
   p.scale = 1.f;
@@ -1188,6 +1201,13 @@ int gemm_device_error(cudaStream_t s, int* code) {
   SB_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_tc_error, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
   SB_CUDA_OK(cudaStreamSynchronize(s));
   *code = v;
+  return SB_OK;
+}
+
+int gemm_device_error_reset(cudaStream_t s) {
+  const int zero = 0;
+  SB_CUDA_OK(cudaStreamSynchronize(s));
+  SB_CUDA_OK(cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice));
   return SB_OK;
 }
 

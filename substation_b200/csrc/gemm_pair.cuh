@@ -294,7 +294,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
             o1[v] = pack8(f);
           }
-          put(&tmC, o1);
+          if (EPI == 0 || !p.epi.skip_c) put(&tmC, o1);
           if (EPI == 1 || EPI == 2) {
 #pragma unroll
             for (int v = 0; v < 8; ++v) o1[v] = hadd8(o1[v], side[v]);

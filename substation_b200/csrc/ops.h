@@ -85,6 +85,7 @@ struct GemmEpilogue {
   Rng rng;
   void* out2;
   void* out3;
+  int skip_c;          // do not store C itself (only the fused outputs are wanted)
 };
 // The contraction with fused epilogue work; SB_ERR_UNSUPPORTED unless the problem runs on the paired-CTA
 // kernel with TMA stores (large, single batch, unit-stride columns, N a multiple of 64).
@@ -102,7 +103,8 @@ extern thread_local int g_last_gemm_impl;
 // Number of SMs the persistent contraction kernels may occupy (0 = all).
 void set_gemm_sm_budget(int n);
 int gemm_sm_budget();
-// Non-zero once a tcgen05 kernel on this process reported a bounded wait running out.
+// Non-zero once a tcgen05 kernel on the current device reported a bounded wait running out (until reset).
 int gemm_device_error(cudaStream_t s, int* code);
+int gemm_device_error_reset(cudaStream_t s);
 
 }  // namespace sb

@@ -48,7 +48,7 @@ class Encoder(torch.nn.Module):
                  softmax_dropout_probability, residual1_dropout_probability,
                  activation_dropout_probability, residual2_dropout_probability,
                  enable_debug=False, profiling=False, *,
-                 activation='relu', mask_mode='philox', seed=0, fuse=True):
+                 activation='relu', mask_mode='philox', seed=0, fuse=True, keep_all_intermediates=None):
         super().__init__()
         if torch_dtype != torch.float16:
             raise NotImplementedError(
@@ -81,6 +81,10 @@ class Encoder(torch.nn.Module):
         self.mask_mode = mask_mode
         self.seed = int(seed)
         self.fuse = bool(fuse)          # fused multi-operator kernels where layouts allow (False: one kernel per reference operator)
+        # Nine intermediates are read by nothing once the fused operators run (BETA, WKKWQQWVV, SB1_LINW1, LIN2,
+        # the bias written back over ATT, DATTN_DROP, DLN2, DLN1, DXATT).  They are still written when somebody
+        # can look at them (enable_debug) or asks for it; otherwise the kernels skip those stores.
+        self.keep_all_intermediates = bool(enable_debug) if keep_all_intermediates is None else bool(keep_all_intermediates)
         self.philox_offset = 0          # advanced by 4 per forward, one per dropout site
         self._masks = None
         self._handle = None
@@ -270,6 +274,7 @@ class Encoder(torch.nn.Module):
             if self.profiling:
                 _lib.check(lib.sb_encoder_set_timing(handle, 1))
             _lib.check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
+            _lib.check(lib.sb_encoder_set_dead_stores(handle, 1 if self.keep_all_intermediates else 0))
             self._graphs_state = None
         self._handle, self._handle_device = handle, device
         with torch.cuda.device(device):
@@ -342,17 +347,33 @@ class Encoder(torch.nn.Module):
                                            ctypes.c_void_p(DX.data_ptr())))
 
     # ------------------------------------------------------------------ raw passes (no autograd)
+    @staticmethod
+    def _check_raw(device, **named):
+        """The raw passes hand bare pointers to the library: every buffer must be dense and on the handle's
+        device.  Nothing is copied silently (a copy would also change the pointers the graph cache keys on)."""
+        for what, t in named.items():
+            if isinstance(t, dict):
+                Encoder._check_raw(device, **{f'{what}[{k}]': v for k, v in t.items() if k != '__arena__'})
+            elif isinstance(t, (list, tuple)):
+                Encoder._check_raw(device, **{f'{what}[{i}]': v for i, v in enumerate(t)})
+            else:
+                if t.device != device:
+                    raise ValueError(f'{what} lives on {t.device}, the pass runs on {device}')
+                if not t.is_contiguous():
+                    raise ValueError(f'{what} must be contiguous (the raw passes take pointers, not views)')
+
     def forward_raw(self, X, weights, fwd, Y):
         """One forward pass into caller-provided buffers.  ``fwd``: name -> tensor for
-        the 23 forward intermediates (see ``_alloc``)."""
+        the 23 forward intermediates (see ``_alloc``).  All buffers contiguous, on one device."""
         self._check_input(X, 'X')
-        X = X.contiguous()
+        self._check_input(Y, 'Y')
+        self._check_raw(X.device, X=X, Y=Y, weights=list(weights), fwd={n: fwd[n] for n in self._fwd_names})
         lib = _lib.load()
         h = self._native(X.device)
         self._graphs_now(h, True)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
-        wl = [w.contiguous() for w in weights]
+        wl = list(weights)
         _lib.check(lib.sb_encoder_forward(
             h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(wl),
             self._ptrs([fwd[n] for n in self._fwd_names]), ctypes.c_void_p(Y.data_ptr()),
@@ -363,11 +384,16 @@ class Encoder(torch.nn.Module):
     def backward_raw(self, DY, grads, bwd, weights, fwd, X, DX):
         """One backward pass; ``grads``/``bwd``: name -> preallocated tensor."""
         self._check_input(DY, 'DY')
+        self._check_input(DX, 'DX')
+        self._check_input(X, 'X')
+        self._check_raw(DY.device, DY=DY, DX=DX, X=X, weights=list(weights),
+                        grads={n: grads[n] for n in self._param_names}, bwd={n: bwd[n] for n in self._bwd_names},
+                        fwd={n: fwd[n] for n in self._fwd_names})
         lib = _lib.load()
         h = self._native(DY.device)
         self._graphs_now(h, True)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
-        wl = [w.contiguous() for w in weights]
+        wl = list(weights)
         _lib.check(lib.sb_encoder_backward(
             h, stream, ctypes.c_void_p(DY.data_ptr()),
             self._ptrs([grads[n] for n in self._param_names]),

@@ -64,6 +64,15 @@ def _d(t):
     return ctypes.byref(tensor_desc(t))
 
 
+def _opt(t):
+    """Descriptor of an output the caller may leave out (None -> NULL: the operator does not store it)."""
+    return None if t is None else _d(t)
+
+
+def _given(*tensors):
+    return [t for t in tensors if t is not None]
+
+
 def attention_input_biases(inp, bias, out):
     """out[n,p,h,b,j] = inp[n,p,h,b,j] + bias[n,p,h]."""
     _check_cuda(inp, bias, out); _half(inp, bias, out)
@@ -79,18 +88,20 @@ def softmax_dropout(beta, alpha, mask, drop, scale=1.0, p=0.0, mode='explicit', 
 
 
 def attention_scores_softmax(qq, kk, beta, alpha, mask, drop, scale, p=0.0, mode='explicit', seed=0, offset=0):
-    """beta = scale*qq.kk, alpha = softmax(beta), drop = mask*alpha in one kernel; qq, kk are [P,H,B,J]."""
-    _check_cuda(qq, kk, beta); _half(qq, kk, beta, alpha, drop); _mask(mask)
+    """beta = scale*qq.kk, alpha = softmax(beta), drop = mask*alpha in one kernel; qq, kk are [P,H,B,J].
+    ``beta=None``: the scores themselves are not stored."""
+    _check_cuda(qq, kk, alpha); _half(qq, kk, alpha, drop, *_given(beta)); _mask(mask)
     d = _dropout(p, mode, seed, offset)
-    check(_lib.load().sb_attention_scores_softmax(_stream(), _d(qq), _d(kk), _d(beta), _d(alpha), _d(mask), _d(drop),
+    check(_lib.load().sb_attention_scores_softmax(_stream(), _d(qq), _d(kk), _opt(beta), _d(alpha), _d(mask), _d(drop),
                                                   float(scale), ctypes.byref(d)))
 
 
 def attention_scores_softmax_backward(dgamma, vv, alpha, mask, dattn_drop, dbeta):
-    """dattn_drop = dgamma.vv and the softmax backward in one kernel; dgamma, vv are [P,H,B,J]."""
-    _check_cuda(dgamma, vv, alpha); _half(dgamma, vv, alpha, dattn_drop, dbeta); _mask(mask)
+    """dattn_drop = dgamma.vv and the softmax backward in one kernel; dgamma, vv are [P,H,B,J].
+    ``dattn_drop=None``: that intermediate is not stored."""
+    _check_cuda(dgamma, vv, alpha); _half(dgamma, vv, alpha, dbeta, *_given(dattn_drop)); _mask(mask)
     check(_lib.load().sb_attention_scores_softmax_backward(_stream(), _d(dgamma), _d(vv), _d(alpha), _d(mask),
-                                                           _d(dattn_drop), _d(dbeta)))
+                                                           _opt(dattn_drop), _d(dbeta)))
 
 
 def attention_score_contractions(scores, x=None, out_rows=None, y=None, out_cols=None, alpha=1.0):
@@ -112,10 +123,11 @@ def backward_softmax(alpha, mask, dattn_drop, dbeta):
 
 def bias_dropout_residual_layernorm(inp, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out,
                                     p=0.0, mode='explicit', seed=0, offset=0):
-    _check_cuda(inp, out); _half(inp, bias, resid, gamma, beta, lin, diff, istd, ln, out); _mask(mask)
+    """``lin=None``: the biased input is not stored."""
+    _check_cuda(inp, out); _half(inp, bias, resid, gamma, beta, diff, istd, ln, out, *_given(lin)); _mask(mask)
     d = _dropout(p, mode, seed, offset)
     check(_lib.load().sb_bias_dropout_residual_layernorm(
-        _stream(), _d(inp), _d(bias), _d(resid), _d(gamma), _d(beta), _d(mask), _d(lin), _d(diff),
+        _stream(), _d(inp), _d(bias), _d(resid), _d(gamma), _d(beta), _d(mask), _opt(lin), _d(diff),
         _d(istd), _d(ln), _d(out), ctypes.byref(d)))
 
 
@@ -158,23 +170,24 @@ def extended_backward_scale_bias(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1,
 
 
 def backward_scale_bias_layernorm(dy, ln, gamma, istd, diff, mask, dln, dresid, dlin, dgamma, dbeta):
-    """backward_scale_bias + backward_layernorm_residual_dropout in one pass."""
-    _check_cuda(dy); _half(dy, ln, gamma, istd, diff, dln, dresid, dlin, dgamma, dbeta); _mask(mask)
+    """backward_scale_bias + backward_layernorm_residual_dropout in one pass (``dln=None``: not stored)."""
+    _check_cuda(dy); _half(dy, ln, gamma, istd, diff, dresid, dlin, dgamma, dbeta, *_given(dln)); _mask(mask)
     ws = workspace(dy.device)
     check(_lib.load().sb_backward_scale_bias_layernorm(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy), _d(ln), _d(gamma), _d(istd), _d(diff), _d(mask),
-        _d(dln), _d(dresid), _d(dlin), _d(dgamma), _d(dbeta)))
+        _opt(dln), _d(dresid), _d(dlin), _d(dgamma), _d(dbeta)))
 
 
 def extended_backward_scale_bias_layernorm(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, mask, dln1,
                                            dresid1, datt, dgamma1, dbeta1, dlinb2, dbo):
-    """extended_backward_scale_bias + backward_layernorm_residual_dropout + backward_attn_out_bias in one pass."""
+    """extended_backward_scale_bias + backward_layernorm_residual_dropout + backward_attn_out_bias in one pass
+    (``dln1=None``: not stored)."""
     _check_cuda(ln1); _mask(mask)
-    _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, dln1, dresid1, datt, dgamma1, dbeta1, dlinb2, dbo)
+    _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, dresid1, datt, dgamma1, dbeta1, dlinb2, dbo, *_given(dln1))
     ws = workspace(ln1.device)
     check(_lib.load().sb_extended_backward_scale_bias_layernorm(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ln1), _d(gamma1), _d(dresid2), _d(dlin1_linw1), _d(dlin2),
-        _d(istd), _d(diff), _d(mask), _d(dln1), _d(dresid1), _d(datt), _d(dgamma1), _d(dbeta1), _d(dlinb2), _d(dbo)))
+        _d(istd), _d(diff), _d(mask), _opt(dln1), _d(dresid1), _d(datt), _d(dgamma1), _d(dbeta1), _d(dlinb2), _d(dbo)))
 
 
 def backward_attn_out_bias(datt, dbo):
@@ -211,7 +224,7 @@ def einsum(spec, a, b, c, alpha=1.0, impl='auto', workspace=None):
 
 
 def einsum_fused(spec, a, b, c, alpha=1.0, *, kind, out2, bias=None, bias_dims=None, resid=None, mask=None, out3=None,
-                 activation='relu', p=0.0, mode='explicit', seed=0, offset=0, logical_dims=None):
+                 activation='relu', p=0.0, mode='explicit', seed=0, offset=0, logical_dims=None, discard_c=False):
     """einsum into c with the next elementwise operator folded into the contraction's epilogue:
     kind='bias' (out2 = c + bias), 'residual' (out2 = c + resid) or 'bias_act_dropout'
     (out2 = c + bias, out3 = mask * act(out2)).  Raises SubstationError with status 3 when the
@@ -241,15 +254,23 @@ def einsum_fused(spec, a, b, c, alpha=1.0, *, kind, out2, bias=None, bias_dims=N
     ep.dropout = ctypes.pointer(d)
     if logical_dims is not None:
         ep.logical_dims = logical_dims.encode()
+    ep.discard_c = 1 if discard_c else 0      # c then only gives the geometry; it is not stored
     check(_lib.load().sb_einsum_fused(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
                                       float(alpha), ctypes.byref(ep)))
 
 
 def device_error():
-    """Sticky code set when a bounded wait inside the tcgen05 kernel ran out (0 = never)."""
+    """Code set on the current device when a bounded wait inside a tcgen05 kernel ran out (0 = none since the
+    last ``device_error_reset``)."""
     code = ctypes.c_int(0)
     check(_lib.load().sb_device_error(_stream(), ctypes.byref(code)))
     return code.value
+
+
+def device_error_reset():
+    """Clear that code once the failed pass has been dealt with (while it is set, every tcgen05 kernel on the
+    device gives up its waits at once)."""
+    check(_lib.load().sb_device_error_reset(_stream()))
 
 
 def set_sm_budget(n_sms):

@@ -140,3 +140,44 @@ def test_operator_argument_validation_without_a_device():
     assert lib.sb_backward_scale_bias(None, None, ctypes.byref(x3), ctypes.byref(x3), ctypes.byref(vec),
                                       ctypes.byref(x3), ctypes.byref(vec), ctypes.byref(vec)) == 1
     assert b'workspace' in lib.sb_last_error()
+
+
+def test_fused_epilogue_refuses_misaligned_side_inputs_before_any_launch():
+    """The paired-CTA epilogue reads bias, residual and mask with 128-bit accesses; operands it could not read
+    that way come back as SB_ERR_ALIGNMENT from the pointer values alone (no CUDA call has been made when the
+    status returns: this runs without a device)."""
+    lib = _lib.load()
+    M, N, K = 512, 512, 256
+    a = _tensor([M, K], [K, 1])
+    b = _tensor([N, K], [K, 1])
+    c = _tensor([M, N], [N, 1], ptr=0x100000)
+    out2 = _tensor([M, N], [N, 1], ptr=0x200000)
+
+    def call(ep):
+        return lib.sb_einsum_fused(None, b'mk', ctypes.byref(a), b'nk', ctypes.byref(b), b'mn', ctypes.byref(c), 1.0,
+                                   ctypes.byref(ep))
+    # bias: a slice that starts one element into an aligned buffer
+    bias = _tensor([N], [1], ptr=0x300000 + 2)
+    ep = _lib.SbEpilogue()
+    ep.kind, ep.bias_dims, ep.bias, ep.out2 = 1, b'n', ctypes.pointer(bias), ctypes.pointer(out2)
+    assert call(ep) == 5, lib.sb_last_error()
+    assert b'bias' in lib.sb_last_error()
+    # residual with an odd base
+    resid = _tensor([M, N], [N, 1], ptr=0x400000 + 8)
+    ep = _lib.SbEpilogue()
+    ep.kind, ep.resid, ep.out2 = 2, ctypes.pointer(resid), ctypes.pointer(out2)
+    assert call(ep) == 5 and b'resid' in lib.sb_last_error()
+    # mask: aligned base but a padded row pitch that is a multiple of 8 only
+    Np = N + 8
+    cp = _tensor([M, N], [Np, 1], ptr=0x100000)
+    o2, o3 = _tensor([M, N], [Np, 1], ptr=0x200000), _tensor([M, N], [Np, 1], ptr=0x500000)
+    mask = _tensor([M, N], [Np, 1], ptr=0x600000)
+    bias = _tensor([N], [1], ptr=0x300000)
+    d = _lib.SbDropout()
+    d.p, d.mode = 0.1, 0
+    ep = _lib.SbEpilogue()
+    ep.kind, ep.bias_dims, ep.bias, ep.mask = 3, b'n', ctypes.pointer(bias), ctypes.pointer(mask)
+    ep.out2, ep.out3, ep.activation, ep.dropout = ctypes.pointer(o2), ctypes.pointer(o3), 0, ctypes.pointer(d)
+    st = lib.sb_einsum_fused(None, b'mk', ctypes.byref(a), b'nk', ctypes.byref(b), b'mn', ctypes.byref(cp), 1.0,
+                             ctypes.byref(ep))
+    assert st == 5 and b'mask' in lib.sb_last_error()

@@ -256,3 +256,32 @@ def test_fused_epilogue_declines_small_problems():
     with pytest.raises(SubstationError) as e:
         ops.einsum_fused('bji,iu->bju', x, w, c, kind='bias', bias=bias, bias_dims='u', out2=out2)
     assert e.value.status == 3
+
+
+@pytest.mark.parametrize('kind', ['bias', 'residual', 'bias_act_dropout'])
+def test_fused_epilogue_can_discard_c(kind):
+    """discard_c: the contraction's own output is not stored (it stays as the caller left it), the fused outputs
+    keep their bits."""
+    ops = _ops()
+    B, J, I, U = 4, 512, 256, 1280
+    x, w, bias, resid = _rand((B, J, I), 1, 7), _rand((I, U), 0.08, 8), _rand((U,), 0.5, 9), _rand((B, J, U), 1, 11)
+    g = torch.Generator(device=DEV).manual_seed(10)
+    mask = (torch.rand(B, J, U, device=DEV, generator=g) >= 0.1).to(torch.uint8)
+    res = {}
+    for discard in (False, True):
+        c = torch.full((B, J, U), 7.0, device=DEV, dtype=torch.float16)
+        out2, out3 = (torch.full((B, J, U), float('nan'), device=DEV, dtype=torch.float16) for _ in range(2))
+        kw = dict(kind=kind, out2=out2, discard_c=discard)
+        if kind != 'residual':
+            kw.update(bias=bias, bias_dims='u')
+        if kind == 'residual':
+            kw.update(resid=resid)
+        if kind == 'bias_act_dropout':
+            kw.update(mask=mask, out3=out3, p=0.1)
+        ops.einsum_fused('bji,iu->bju', x, w, c, **kw)
+        res[discard] = (c, out2, out3)
+    assert ops.device_error() == 0
+    assert (res[True][0] == 7.0).all() and not (res[False][0] == 7.0).all()
+    assert torch.equal(res[True][1], res[False][1])
+    if kind == 'bias_act_dropout':
+        assert torch.equal(res[True][2], res[False][2])

@@ -395,3 +395,52 @@ def test_attention_score_contractions_decline_what_they_do_not_cover():
     with pytest.raises(SubstationError) as e:
         ops.attention_score_contractions(sc, x=x, out_rows=x.clone())
     assert e.value.status == 3
+
+
+def test_optional_outputs_can_be_left_out_without_changing_the_others():
+    """BETA, DATTN_DROP, LIN and DLN are only intermediates of their fused operators: with None in their place the
+    operator stores nothing for them and every other output keeps its bits."""
+    ops = _ops()
+    g = torch.Generator(device=DEV).manual_seed(31)
+    rnd = lambda *shape: torch.randn(*shape, device=DEV, generator=g).half()
+    nan = lambda *shape: torch.full(shape, float('nan'), dtype=torch.float16, device=DEV)
+    # fused attention scores, forward and backward
+    H, B, L, P = 2, 3, 256, 64
+    qq, kk, vv, dg = (rnd(P, H, B, L) for _ in range(4))
+    mask = (torch.rand(H, B, L, L, device=DEV, generator=g) >= 0.2).to(torch.uint8)
+    outs = {}
+    for keep in (True, False):
+        beta, alpha, drop = (nan(H, B, L, L) for _ in range(3))
+        ops.attention_scores_softmax(qq, kk, beta if keep else None, alpha, mask, drop, 0.125)
+        dad, dbeta = nan(H, B, L, L), nan(H, B, L, L)
+        ops.attention_scores_softmax_backward(dg, vv, alpha, mask, dad if keep else None, dbeta)
+        outs[keep] = (alpha, drop, dbeta)
+    assert ops.device_error() == 0
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.isfinite(b).all() and torch.equal(a, b)
+    # bias + dropout + residual + LayerNorm
+    B, J, F = 4, 96, 1024
+    x, resid, bias, gamma, beta_ = rnd(B, J, F), rnd(B, J, F), rnd(F), rnd(F), rnd(F)
+    m3 = (torch.rand(B, J, F, device=DEV, generator=g) >= 0.1).to(torch.uint8)
+    outs = {}
+    for keep in (True, False):
+        lin, diff, ln, out = (nan(B, J, F) for _ in range(4))
+        istd = nan(B, J)
+        ops.bias_dropout_residual_layernorm(x, bias, resid, gamma, beta_, m3, lin if keep else None, diff, istd, ln, out)
+        outs[keep] = (diff, istd, ln, out)
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.isfinite(b).all() and torch.equal(a, b)
+    # fused LayerNorm backward, both forms
+    dy, lnv, dfv, r2, lw, l2 = (rnd(B, J, F) for _ in range(6))
+    istd = (torch.rand(B, J, device=DEV, generator=g) + 0.5).half()
+    outs = {}
+    for keep in (True, False):
+        dln, dres, dlin = (nan(B, J, F) for _ in range(3))
+        v = [nan(F) for _ in range(6)]
+        ops.backward_scale_bias_layernorm(dy, lnv, gamma, istd, dfv, m3, dln if keep else None, dres, dlin, v[0], v[1])
+        dln1, dres1, datt = (nan(B, J, F) for _ in range(3))
+        ops.extended_backward_scale_bias_layernorm(lnv, gamma, r2, lw, l2, istd, dfv, m3, dln1 if keep else None, dres1,
+                                                   datt, *v[2:])
+        outs[keep] = (dres, dlin, dres1, datt, *v)
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.isfinite(b).all() and torch.equal(a, b)

@@ -25,7 +25,8 @@ def _call_noalloc(datt, dbo):
                                                  ctypes.byref(_lib.tensor_desc(dbo)))
 
 
-@pytest.mark.parametrize('B,J,F,permute', [(8, 512, 1024, False), (3, 37, 200, False), (4, 64, 256, True)])
+@pytest.mark.parametrize('B,J,F,permute', [(8, 512, 1024, False), (3, 37, 200, False), (4, 64, 256, True),
+                                               (2, 48, 16384, False)])   # the last: the largest feature extent accepted
 def test_noalloc_matches_workspace_version_on_consecutive_calls(B, J, F, permute):
     from substation_b200 import _lib, ops
     g = torch.Generator(device='cuda:0').manual_seed(B * J + F)
@@ -55,3 +56,13 @@ def test_noalloc_refuses_what_the_builtin_scratch_cannot_hold():
     assert _call_noalloc(datt, dbo) == 3
     msg = lib.sb_last_error().decode()
     assert '16384' in msg and 'workspace' in msg
+    # more tokens than the kernel's 32-bit token index can count: refused from the sizes alone (the tensor
+    # descriptor below points at one element and is never dereferenced)
+    one = torch.zeros(8, dtype=torch.float16, device='cuda:0')
+    t = _lib.SbTensor()
+    t.ptr, t.ndim = one.data_ptr(), 3
+    for i, (sz, st) in enumerate(zip((65536, 65536, 8), (0, 0, 1))):
+        t.size[i], t.stride[i] = sz, st
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.sb_backward_attn_out_bias_noalloc(stream, ctypes.byref(t), ctypes.byref(_lib.tensor_desc(one))) == 3
+    assert 'tokens' in lib.sb_last_error().decode()
