@@ -298,6 +298,13 @@ int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor* a, const 
  * (pytorch_module/all.cuh:7-13). */
 int sb_device_error(void* stream, int* code);
 int sb_device_error_reset(void* stream);
+/* Measurement aid: one launch in which every cluster of two CTAs issues k_blocks * 4 tcgen05.mma instructions
+ * (cta_group::2, 256 x 256 x 16, fp16 or bf16 operands, fp32 accumulation: the instruction of the contraction
+ * kernels) on operands already resident in shared memory, with no loads and no epilogue.  *flops receives the
+ * floating-point operations of the launch; the caller times it with events on `stream`.  The result is the
+ * tensor-pipe rate these kernels could reach if nothing but the MMAs cost time.  Stands in for the reference's
+ * tensor-core microbenchmark (tc_profiling/microbenchmark/tensorcores.cu:16-40). */
+int sb_mma_peak_probe(void* stream, int k_blocks, int bf16, double* flops);
 /* The contraction kernels are persistent: one CTA per SM walks the output tiles.  When
  * another kernel must run next to them (the NCCL gradient allreduce of the data-parallel
  * path), tell the library to occupy only n_sms SMs so that no CTA of a contraction waits

@@ -89,6 +89,7 @@ SIGNATURES = {
     'sb_einsum_last_impl': (c_int, []),
     'sb_device_error': (c_int, [c_void_p, ctypes.POINTER(c_int)]),
     'sb_device_error_reset': (c_int, [c_void_p]),
+    'sb_mma_peak_probe': (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(ctypes.c_double)]),
     'sb_set_sm_budget': (c_int, [c_int]),
     'sb_encoder_create': (c_int, [ctypes.POINTER(SbEncoderConfig), ctypes.POINTER(c_void_p)]),
     'sb_encoder_destroy': (c_int, [c_void_p]),

@@ -567,6 +567,9 @@ extern "C" int sb_device_error(void* stream, int* code) {
   return gemm_device_error((cudaStream_t)stream, code);
 }
 extern "C" int sb_device_error_reset(void* stream) { return gemm_device_error_reset((cudaStream_t)stream); }
+extern "C" int sb_mma_peak_probe(void* stream, int k_blocks, int bf16, double* flops) {
+  return run_mma_peak_probe((cudaStream_t)stream, k_blocks, bf16, flops);
+}
 
 // ---------------------------------------------------------------------------
 // Whole layer

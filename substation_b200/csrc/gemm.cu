@@ -22,6 +22,7 @@
 // (strides that are not multiples of 16 bytes, or no unit-stride index).
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cudaTypedefs.h>
 
 #include <algorithm>
@@ -681,6 +682,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
 #include "gemm_pair.cuh"
 #include "attn_fused.cuh"
 #include "score_contract.cuh"
+#include "peak_probe.cuh"
 
 // ---- host side ------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -835,6 +837,15 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
   return SB_OK;
 }
 
+// Epilogue warps per CTA of the paired kernel: 8 unless the environment asks for 4 (see pair::Cfg).
+int pair_epi_warps() {
+  static const int ew = [] {
+    const char* e = getenv("SUBSTATION_B200_EPI_WARPS");
+    return (e && e[0] == '4') ? 4 : 8;
+  }();
+  return ew;
+}
+
 // Paired-CTA launch: 256 x 256 tiles, one cluster of two CTAs per tile.
 int pair_clusters() {
   static thread_local int cached_dev = -1, cached = 0;
@@ -843,20 +854,23 @@ int pair_clusters() {
   if (dev != cached_dev) {
     cached_dev = dev;
     cached = 0;
-    if (cudaFuncSetAttribute(pair::gemm_tc_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             pair::kSmemBytes) == cudaSuccess) {
+    const bool ew8 = pair_epi_warps() == 8;
+    const void* fn = ew8 ? reinterpret_cast<const void*>(pair::gemm_tc_pair_kernel<0, 8>)
+                         : reinterpret_cast<const void*>(pair::gemm_tc_pair_kernel<0, 4>);
+    const int smem = ew8 ? pair::Cfg<8>::kSmemBytes : pair::Cfg<4>::kSmemBytes;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
       cfg.gridDim = dim3(2 * 74);
-      cfg.blockDim = dim3(kTcThreads);
-      cfg.dynamicSmemBytes = pair::kSmemBytes;
+      cfg.blockDim = dim3(ew8 ? pair::Cfg<8>::kThreads : pair::Cfg<4>::kThreads);
+      cfg.dynamicSmemBytes = smem;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, pair::gemm_tc_pair_kernel<0>, &cfg) == cudaSuccess) cached = n;
+      if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess) cached = n;
       else cudaGetLastError();
     } else {
       cudaGetLastError();
@@ -936,17 +950,20 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
     p.epi.rng = epi->rng;
   }
   const int kind = epi ? epi->kind : 0;
-  auto launch = [&](auto kernel) {
+  auto launch = [&](auto kernel, int threads, int smem) {
     // per-device attribute; setting it is cheap and idempotent
-    const cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), pair::kSmemBytes);
+    const cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (ea != cudaSuccess) return ea;
-    return launch_k(kernel, 2 * nclusters, kTcThreads, pair::kSmemBytes, s, a.map, b.map, cmap, cmap2, cmap3, p);
+    return launch_k(kernel, 2 * nclusters, threads, smem, s, a.map, b.map, cmap, cmap2, cmap3, p);
   };
-  if (kind == 0) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<0>));
-  else if (kind == 1) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<1>));
-  else if (kind == 2) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<2>));
-  else if (kind == 3) SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<3>));
-  else return fail(SB_ERR_ARG, "fused epilogue: unknown kind");
+  if (kind < 0 || kind > 3) return fail(SB_ERR_ARG, "fused epilogue: unknown kind");
+#define SB_PAIR_CASE(K, EW)                                                                             \
+  if (kind == K && ew == EW)                                                                            \
+    SB_LAUNCH_OK(launch(pair::gemm_tc_pair_kernel<K, EW>, pair::Cfg<EW>::kThreads, pair::Cfg<EW>::kSmemBytes))
+  const int ew = pair_epi_warps();
+  SB_PAIR_CASE(0, 4); SB_PAIR_CASE(1, 4); SB_PAIR_CASE(2, 4); SB_PAIR_CASE(3, 4);
+  SB_PAIR_CASE(0, 8); SB_PAIR_CASE(1, 8); SB_PAIR_CASE(2, 8); SB_PAIR_CASE(3, 8);
+#undef SB_PAIR_CASE
   SB_CUDA_OK(cudaGetLastError());
   return SB_OK;
 }
@@ -1201,6 +1218,17 @@ int gemm_device_error(cudaStream_t s, int* code) {
   SB_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_tc_error, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
   SB_CUDA_OK(cudaStreamSynchronize(s));
   *code = v;
+  return SB_OK;
+}
+
+int run_mma_peak_probe(cudaStream_t s, int k_blocks, int bf16, double* flops) {
+  if (k_blocks < 1 || k_blocks > (1 << 24)) return fail(SB_ERR_ARG, "peak probe: K-block count out of range");
+  const int clusters = std::min(pair_clusters(), sm_count() / 2);
+  if (clusters < 1) return fail(SB_ERR_UNSUPPORTED, "peak probe: no cluster of two CTAs fits on this device");
+  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(probe::mma_peak_kernel), probe::kSmemBytes));
+  SB_LAUNCH_OK(launch_k(probe::mma_peak_kernel, 2 * clusters, probe::kThreads, probe::kSmemBytes, s, k_blocks, bf16 ? 1 : 0));
+  SB_CUDA_OK(cudaGetLastError());
+  if (flops) *flops = (double)clusters * k_blocks * 4.0 * 2.0 * 256.0 * 256.0 * 16.0;
   return SB_OK;
 }
 

@@ -26,10 +26,20 @@ namespace pair {
 constexpr int kBN = 256;
 constexpr int kHalfBBytes = 128 * kBK * 2;                 // this CTA's half of B per K block
 constexpr int kStageBytes = kABytes + kHalfBBytes;         // 32 KiB
-constexpr int kStages = 6;
-constexpr int kTileBytes = kStages * kStageBytes;          // 192 KiB
 constexpr int kTmemCols = 512;                             // two 256-column accumulators
-constexpr int kSmemBytes = kTileBytes + kStageOutBytes + 1024 + 256;
+
+// EW epilogue warps per CTA: 4 (one per 32-lane quadrant of tensor memory, each draining all 256 columns of its
+// rows) or 8 (two per quadrant, 128 columns each: the drain of a tile, which nothing overlaps when a cluster has
+// a single tile, takes half as long).  Each epilogue warp owns two 4 KiB staging buffers, so the eight-warp
+// form keeps five operand stages instead of six.
+template <int EW>
+struct Cfg {
+  static constexpr int kThreads = 64 + 32 * EW;
+  static constexpr int kStages = EW == 8 ? 5 : 6;
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kStageOut = EW * 2 * 4096;
+  static constexpr int kSmemBytes = kTileBytes + kStageOut + 1024 + 256;
+};
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -69,21 +79,24 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
 
 // Persistent: cluster c works on pair tiles c, c + (#clusters), ...; n fastest, then m (256 rows), then batch.
 // EPI: 0 plain, else EpiParams::kind (extra outputs through tmC2 / tmC3, TMA-store mode only).
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+template <int EPI, int EW>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<EW>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
                     const __grid_constant__ CUtensorMap tmC3, const TcParams p) {
-  constexpr int S = kStages;
+  using C = Cfg<EW>;
+  constexpr int S = C::kStages;
+  constexpr int kTileBytes = C::kTileBytes;
+  constexpr int kChunks = (kBN / 64) * 4 / EW;       // 64-column chunks each epilogue warp drains per tile
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const uint32_t stage_out = tiles + kTileBytes;
-  const uint32_t bars = stage_out + kStageOutBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t bars = stage_out + C::kStageOut;  // full[S], empty[S], acc_full[2], acc_empty[2]
   const uint32_t bar_full = bars, bar_empty = bars + 8 * S;
   const uint32_t bar_accf = bars + 16 * S, bar_acce = bars + 16 * S + 16;
   uint8_t* gen_base = smem_raw + (tiles - raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kTileBytes + kStageOutBytes + 16 * S + 32);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kTileBytes + C::kStageOut + 16 * S + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();          // 0 = leader
@@ -97,7 +110,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_accf + 8 * b, 1);
-      mbar_init(bar_acce + 8 * b, 8);  // four epilogue warps of each CTA
+      mbar_init(bar_acce + 8 * b, 2 * EW);  // the epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -209,7 +222,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ---------------- epilogue (both CTAs; each stores its own 128 rows) ----------------
-    const int q = warp & 3;
+    const int q = warp & 3;                    // the 32-lane quadrant of tensor memory this warp may read
+    const int c_first = ((warp - 2) >> 2) * kChunks;   // its share of the tile's four 64-column chunks
     const uint32_t leader_acce = map_to_rank(bar_acce, 0);
     const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
     uint8_t* my_stage_gen = gen_base + kTileBytes + (warp - 2) * 8192;
@@ -227,12 +241,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t tsrc = tmem_base + buf * kBN + ((uint32_t)(q * 32) << 16);
       if (p.c_mode == 2) {
 #pragma unroll 1
-        for (int c = 0; c < kBN / 64; ++c) {
+        for (int c = c_first; c < c_first + kChunks; ++c) {
           uint32_t r[64];
           tmem_ld32_nowait(tsrc + (uint32_t)(c * 64), r);
           tmem_ld32_nowait(tsrc + (uint32_t)(c * 64 + 32), r + 32);
           tmem_ld_wait();
-          if (c == kBN / 64 - 1) {
+          if (c == c_first + kChunks - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);
@@ -344,11 +358,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       } else {
         __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;
 #pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
+        for (int c = 2 * c_first; c < 2 * (c_first + kChunks); ++c) {
           uint32_t r[32];
           tmem_ld32_nowait(tsrc + (uint32_t)(c * 32), r);
           tmem_ld_wait();
-          if (c == kBN / 32 - 1) {
+          if (c == 2 * (c_first + kChunks) - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);

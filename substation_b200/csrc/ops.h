@@ -106,5 +106,7 @@ int gemm_sm_budget();
 // Non-zero once a tcgen05 kernel on the current device reported a bounded wait running out (until reset).
 int gemm_device_error(cudaStream_t s, int* code);
 int gemm_device_error_reset(cudaStream_t s);
+// MMA-only loop of the paired-CTA instruction on operands resident in shared memory (see peak_probe.cuh).
+int run_mma_peak_probe(cudaStream_t s, int k_blocks, int bf16, double* flops);
 
 }  // namespace sb

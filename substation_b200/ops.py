@@ -273,6 +273,13 @@ def device_error_reset():
     check(_lib.load().sb_device_error_reset(_stream()))
 
 
+def mma_peak_probe(k_blocks, bf16=False):
+    """Enqueue one MMA-only launch (see ``sb_mma_peak_probe``) on the current stream; returns its FLOP count."""
+    fl = ctypes.c_double(0.0)
+    check(_lib.load().sb_mma_peak_probe(_stream(), int(k_blocks), 1 if bf16 else 0, ctypes.byref(fl)))
+    return fl.value
+
+
 def set_sm_budget(n_sms):
     """Let the persistent contraction kernels occupy only ``n_sms`` SMs (0 = all), leaving the
     rest to a kernel that runs beside them, e.g. the NCCL allreduce of the data-parallel path."""

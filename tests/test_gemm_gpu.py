@@ -285,3 +285,24 @@ def test_fused_epilogue_can_discard_c(kind):
     assert torch.equal(res[True][1], res[False][1])
     if kind == 'bias_act_dropout':
         assert torch.equal(res[True][2], res[False][2])
+
+
+@pytest.mark.parametrize('bf16', [False, True])
+def test_mma_peak_probe_runs_and_reports_its_flops(bf16):
+    """The MMA-only launch the bench uses as the tensor-pipe yardstick: completes without a bounded wait running
+    out, and a longer launch takes longer (the instructions are really issued)."""
+    ops = _ops()
+    times = []
+    for k_blocks in (256, 4096):
+        ops.mma_peak_probe(64, bf16)                 # warm-up
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        flops = ops.mma_peak_probe(k_blocks, bf16)
+        e.record()
+        torch.cuda.synchronize()
+        assert flops == pytest.approx(flops // (k_blocks * 4 * 2 * 256 * 256 * 16) * k_blocks * 4 * 2 * 256 * 256 * 16)
+        times.append((s.elapsed_time(e), flops))
+    assert ops.device_error() == 0
+    (t0, f0), (t1, f1) = times
+    assert t1 > 4 * t0 and f1 == 16 * f0
+    assert 100e12 < f1 / (t1 * 1e-3) < 3000e12, f'{f1 / (t1 * 1e-3) / 1e12:.0f} TFLOP/s is not a plausible tensor rate'
