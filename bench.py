@@ -1,7 +1,9 @@
 """Benchmark of the encoder-layer hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--layouts b200_b8_l512|uniform|b8_l512|b96_l128] [--batch B] [--seq L]
+                    [--layouts b200_b8_l512|uniform|b8_l512|b96_l128|<file.json>] [--batch B] [--seq L]
+    python bench.py --kernels        every fused operator alone at the kernel-sweep shapes, one JSON line
+    python bench.py --layers 24      the 24-layer stack, one JSON line
 
 One "step" = one BERT-large encoder layer forward+backward (B=8, L=512, H=16,
 E=1024, fp16 storage / fp32 accumulation, dropout p=0.1 with seeded explicit
@@ -9,13 +11,24 @@ masks) on each GPU; with N>1 every rank runs its own batch of 8 (weak scaling)
 and the layer's 12 parameter gradients are sum-allreduced over NCCL, overlapped
 with the next step.  Rank 0 prints ONE JSON line.
 
-value      sequences/s over all ranks, inputs resident in HBM, CUDA-event timed
-e2e        same through the public ``Encoder`` module with host buffers:
-           pinned-host X and dY copied in, Y and dX copied out, every step
-roofline   the operator with the largest device time: algorithmic FLOPs (or
-           bytes) / its mean duration, against MEASURED_PEAKS.json
-cpu_baseline  the numpy port of the reference path (oracle/) timed on the host
---impl reference  that same numpy port as its own arm (rank 0 only)
+value        sequences/s over all ranks, inputs resident in HBM, CUDA-event timed
+e2e          same through the public ``Encoder`` module with host buffers:
+             pinned-host X and dY copied in, Y and dX copied out, every step;
+             copy_only_ms_per_step = the same copies with no compute
+sustained    the same step repeated for at least two seconds, with the SM clock
+             sampled while it runs (ms x MHz is the clock-normalised figure)
+roofline     the operator with the largest device time: algorithmic bytes (or
+             FLOPs) / its mean duration, against MEASURED_PEAKS.json
+operators    every operator of the step: device time, GB/s or TFLOP/s, and for the
+             large contractions the time torch.matmul (cuBLAS) takes for the same
+             shape on this GPU (measured outside the timed region, never on the
+             product path)
+fused_kernels  each fused operator alone at H=16, B=96, J=K=128 (kernel sweep)
+cpu_baseline the numpy port of the reference path (oracle/) timed on the host
+N>1 only     dp_check (summed gradients against the sum of the gathered per-rank
+             gradients and against one GPU on the concatenated batch), strong
+             (global batch 96 at L=128 split over the ranks), stack (24 layers)
+--impl reference  the numpy port as its own arm (rank 0 only)
 """
 
 import argparse
@@ -35,6 +48,7 @@ P_DROP = 0.1
 METRIC = 'bert_large_encoder_layer_fwd_bwd_sequences_per_s'
 UNIT = 'seq/s'
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
+NOMINAL_HBM_GBS = 8000.0
 
 # contraction name -> FLOPs as a function of (B, L): 2*batch*M*N*K of the 18 einsums
 GEMM_FLOPS = {
@@ -50,12 +64,16 @@ GEMM_FLOPS['lin1+bad'] = GEMM_FLOPS['lin1']
 GEMM_FLOPS['dXQKV-fused+bei'] = GEMM_FLOPS['dXQKV-fused']
 for _n in ('QKT', 'gamma', 'dX1gamma', 'dX2gamma', 'dX1QKT', 'dX2QKT'):
     GEMM_FLOPS[_n] = lambda B, L: 2 * H * B * L * L * P
-# attention contractions are HBM-bound: minimum operand bytes (two [P,L] operands + one [L,L], or v.v.)
-ATTN_BYTES = {
-    'QKT': lambda B, L: 2 * H * B * (2 * P * L + L * L), 'gamma': lambda B, L: 2 * H * B * (2 * P * L + L * L),
-    'dX1gamma': lambda B, L: 2 * H * B * (2 * P * L + L * L), 'dX2gamma': lambda B, L: 2 * H * B * (2 * P * L + L * L),
-    'dX1QKT': lambda B, L: 2 * H * B * (2 * P * L + L * L), 'dX2QKT': lambda B, L: 2 * H * B * (2 * P * L + L * L),
+# (M, N, K) of the twelve large contractions as functions of the token count T
+GEMM_SHAPES = {
+    'QKV-fused': lambda T: (T, 3 * E, E), 'out': lambda T: (T, E, E), 'lin1': lambda T: (T, U, E),
+    'lin2': lambda T: (T, E, U), 'dXlin2': lambda T: (T, U, E), 'dWlin2': lambda T: (U, E, T),
+    'dXlin1': lambda T: (T, E, U), 'dWlin1': lambda T: (E, U, T), 'dWout': lambda T: (E, E, T),
+    'dXout': lambda T: (T, E, E), 'dXQKV-fused': lambda T: (T, E, 3 * E), 'dWQKV-fused': lambda T: (3 * E, E, T),
 }
+# attention contractions are HBM-bound: minimum operand bytes (two [P,L] operands + one [L,L], or v.v.)
+ATTN_BYTES = {n: (lambda B, L: 2 * H * B * (2 * P * L + L * L))
+              for n in ('QKT', 'gamma', 'dX1gamma', 'dX2gamma', 'dX1QKT', 'dX2QKT')}
 # fused operators: algorithmic bytes, every input read once + every output written once,
 # 2 B per fp16 element, 1 B per mask element (T = B*L tokens, S = H*B*L*L scores)
 FUSED_BYTES = {
@@ -72,15 +90,6 @@ FUSED_BYTES = {
     'dX1QKT+dX2QKT': lambda B, L: H * B * (2 * L * L + 8 * P * L),
     'QKT+softmax': lambda B, L: H * B * (4 * P * L + 7 * L * L), 'dX1gamma+bs': lambda B, L: H * B * (4 * P * L + 7 * L * L),
 }
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=8, L=512, from the ncu --set full captures
-# summarised in profiles/top_kernels_b8_l512_full_captures.md (part of each kernel's output is still in L2
-# when it ends, so traffic can be below the algorithmic bytes)
-NCU_DRAM_BYTES = {'QKT+softmax': 207.69e6, 'dX1gamma+bs': 200.28e6, 'gamma': 78.86e6, 'dX2gamma': 77.23e6,
-                  'dX1QKT+dX2QKT': 87.78e6, 'bsb+blnrd1': 29.86e6, 'ebsb+blnrd2+baob': 51.58e6}
-
-
 # the same operators when the intermediates nothing reads again are not stored (the default; --keep-all 1 stores them):
 # LIN (2*T*E) in both bdrln calls, DLN (2*T*E) in both LayerNorm-backward passes, BETA / DATTN_DROP (2*S)
 FUSED_BYTES_SKIP = dict(FUSED_BYTES)
@@ -100,24 +109,48 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), 'fallback'
 
 
+def load_dram_traffic(B, S, keep_all):
+    """DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/: the table rows of
+    profiles/dram_traffic_b8_l512.md, '| operator | bytes | stores |' (the file names the capture command that
+    regenerates it).  Only known for the shapes and store setting that were captured."""
+    if (B, S) != (8, 512):
+        return {}
+    path = os.path.join(ROOT, 'profiles', 'dram_traffic_b8_l512.md')
+    out = {}
+    try:
+        with open(path) as f:
+            for line in f:
+                c = [x.strip() for x in line.strip().strip('|').split('|')]
+                if len(c) >= 3 and c[2] in ('all', 'live'):
+                    try:
+                        nbytes = float(c[1])
+                    except ValueError:
+                        continue
+                    if (c[2] == 'all') == bool(keep_all):
+                        out[c[0]] = nbytes
+    except OSError:
+        pass
+    return out
+
+
 class ClockSampler:
     """nvidia-smi clock/throttle samples while the timed region runs."""
     Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
          'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
          'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
-    def __init__(self, gpu_index):
-        self.proc, self.rows, self.idx = None, [], gpu_index
+    def __init__(self, gpu_index, interval_ms=100):
+        self.proc, self.rows, self.idx, self.interval = None, [], gpu_index, interval_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '100',
+                ['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', str(self.interval),
                  '-i', str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, skip_first=0):
         if self.proc is None:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
         time.sleep(0.15)
@@ -127,8 +160,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
-        for line in out.strip().splitlines():
+        sm, smax, power, reasons = [], [], [], set()
+        for line in out.strip().splitlines()[skip_first:]:
             c = [x.strip() for x in line.split(',')]
             if len(c) < 9:
                 continue
@@ -136,12 +169,16 @@ class ClockSampler:
                 sm.append(float(c[1])); smax.append(float(c[2]))
             except ValueError:
                 continue
+            try:
+                power.append(float(c[3]))
+            except ValueError:
+                pass
             for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), c[5:9]):
                 if val.lower().startswith('active'):
                     reasons.add(name)
         return {'sm_mhz': statistics.median(sm) if sm else None,
                 'sm_max_mhz': max(smax) if smax else None, 'samples': len(sm),
-                'reasons': sorted(reasons)}
+                'power_w_max': max(power) if power else None, 'reasons': sorted(reasons)}
 
 
 # ------------------------------------------------------------------------------------------
@@ -199,20 +236,24 @@ def workload_config(args, layouts_name):
                         f'E={E}, U={U}, ReLU, dropout p={P_DROP} (seeded explicit masks)',
             'batch_per_gpu': args.batch, 'seq_len': args.seq, 'layouts': layouts_name,
             'parallelism': f'dp{args.gpus}', 'comm_ctas': args.comm_ctas if args.gpus > 1 else 0,
+            'intermediates': 'all stored' if args.keep_all else 'the nine tensors nothing reads again are not stored',
             'l2': 'per-step working set (~0.9 GB of intermediates) is larger than the 126 MB L2; no flush needed'}
+
+
+def resolve_layouts(name):
+    """--layouts value -> configuration dict.  'b8_l512' and 'b96_l128' are the reference's two shipped
+    configurations, kept as JSON data files beside the golden vectors."""
+    from substation_b200 import layouts as L
+    if name in ('b8_l512', 'b96_l128'):
+        name = os.path.join(ROOT, 'tests', 'golden', f'layouts_{name}.json')
+    return L.named_layouts(name)
 
 
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def run_ours(args):
-    import numpy as np
+def dist_env(args):
     import torch
-    import torch.distributed as dist
-    from substation_b200 import Encoder, layouts as L
-    from substation_b200.data_parallel import GradientBucketReducer
-    from tests.layer_harness import get_layouts
-
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
@@ -221,74 +262,257 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: the product path has no CPU fallback')
     torch.cuda.set_device(local_rank)
-    dev = torch.device('cuda', local_rank)
-    comm_ctas = 0
-    if world > 1:
-        # Few NCCL CTAs are enough for a 25 MB bucket over NVLink; the persistent contraction
-        # kernels leave exactly those SMs free so that the allreduce runs beside them.
-        comm_ctas = args.comm_ctas
+    return world, rank, local_rank, torch.device('cuda', local_rank)
+
+
+def init_nccl(args, world, dev):
+    """One process per GPU over NCCL.  Few NCCL CTAs are enough for a 25 MB bucket over NVLink; the persistent
+    contraction kernels leave exactly those SMs free so that the allreduce runs beside them."""
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return
+    opts = None
+    try:
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.config.max_ctas = args.comm_ctas
+        opts.config.min_ctas = min(4, args.comm_ctas)
+    except Exception:
         opts = None
-        try:
-            opts = dist.ProcessGroupNCCL.Options()
-            opts.config.max_ctas = comm_ctas
-            opts.config.min_ctas = min(4, comm_ctas)
-        except Exception:
-            opts = None
-        dist.init_process_group('nccl', device_id=dev, pg_options=opts)
-        from substation_b200 import ops as _ops
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        _ops.set_sm_budget(sms - comm_ctas)
+    dist.init_process_group('nccl', device_id=dev, pg_options=opts)
+    from substation_b200 import ops as _ops
+    _ops.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - args.comm_ctas)
 
+
+class LayerBench:
+    """One encoder layer with preallocated buffers and seeded inputs: what a step runs on."""
+
+    def __init__(self, B, S, lay, dev, rank, keep_all, weight_seed=1234, data_seed=100, heads=H, embed=E,
+                 profiling=True, X=None, DY=None, masks=None):
+        import torch
+        from substation_b200 import Encoder, layouts as L
+        self.B, self.S, self.dev = B, S, dev
+        self.table = L.validate(lay)
+        self.enc = Encoder('/tmp/substation_b200_unused', B, S, heads, embed, lay, torch.float16,
+                           P_DROP, P_DROP, P_DROP, P_DROP, profiling=profiling, mask_mode='explicit',
+                           keep_all_intermediates=bool(keep_all)).to(dev)
+        enc = self.enc
+        gen = torch.Generator(device=dev).manual_seed(weight_seed)        # same weights on every rank
+        with torch.no_grad():
+            for (name, layout), prm in zip(lay['params'], enc.params):
+                if name in ('WKQV', 'WO', 'LINW1', 'LINW2'):
+                    prm.copy_((torch.randn(prm.shape, device=dev, generator=gen) * 0.02).half())
+                elif name in ('S1', 'S2'):
+                    prm.fill_(1.0)
+                else:
+                    prm.zero_()
+        gen = torch.Generator(device=dev).manual_seed(data_seed + rank)    # different data per rank
+        shape_x = L.shape_of(self.table['X'], enc.sizes)
+        self.X = torch.randn(shape_x, device=dev, generator=gen).half() if X is None else X
+        self.DY = torch.randn(shape_x, device=dev, generator=gen).half() if DY is None else DY
+        if masks is None:
+            masks = {}
+            for n in L.MASKS:
+                shp = L.shape_of(self.table[n], enc.sizes)
+                masks[n] = (torch.rand(shp, device=dev, generator=gen) >= P_DROP).to(torch.uint8)
+        self.masks = masks
+        enc.set_masks(masks)
+        self.weights = [p.detach() for p in enc.params]
+        self.fwd = enc._alloc(enc._fwd_plan, dev)
+        self.fwd.update(masks)
+        self.bwd = enc._alloc(enc._bwd_plan, dev)
+        self.Y, self.DX = torch.empty_like(self.X), torch.empty_like(self.X)
+
+    def run(self, grads):
+        self.enc.forward_raw(self.X, self.weights, self.fwd, self.Y)
+        self.enc.backward_raw(self.DY, grads, self.bwd, self.weights, self.fwd, self.X, self.DX)
+
+
+def event_time_ms(fn, n, torch):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def cublas_anchors(T, dev, torch, reps=20, nset=4):
+    """torch.matmul (cuBLAS) fp16 time of the twelve large contractions at the layer's shapes, both operands
+    K-major, over rotating operand sets so that every call starts cold in L2.  A yardstick only."""
+    out = {}
+    for name, shape in GEMM_SHAPES.items():
+        M, N, K = shape(T)
+        As = [torch.randn(M, K, device=dev, dtype=torch.float16) for _ in range(nset)]
+        Bs = [torch.randn(N, K, device=dev, dtype=torch.float16) for _ in range(nset)]
+        Cs = [torch.empty(M, N, device=dev, dtype=torch.float16) for _ in range(nset)]
+        f = lambda i: torch.matmul(As[i % nset], Bs[i % nset].t(), out=Cs[i % nset])
+        for i in range(nset + 2):
+            f(i)
+        torch.cuda.synchronize()
+        out[name] = 1e3 * event_time_ms(f, reps, torch) / reps
+        del As, Bs, Cs
+    return out
+
+
+def tensor_peak_probe(torch):
+    """fp16 tcgen05 rate with operands resident in shared memory (no loads, no epilogue): a short burst and a
+    ~50 ms run (the power cap pulls the clock down within a few milliseconds of dense MMA work)."""
+    from substation_b200 import ops
+    res = {}
+    for label, kb in (('burst', 4096), ('long', 200000)):
+        ops.mma_peak_probe(64)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fl = ops.mma_peak_probe(kb)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        res[label] = {'tflops': round(fl / ms / 1e9, 1), 'ms': round(ms, 3)}
+    if ops.device_error() != 0:
+        res['error'] = 'a bounded wait ran out'
+        ops.device_error_reset()
+    return res
+
+
+# ---- kernel sweep: every fused operator alone -------------------------------------------------------
+def fused_kernel_sweep(dev, torch, warmup=20, reps=200, Hh=16, B=96, L=128, nset=2):
+    """Each fused operator and its backward counterpart alone at H=16, B=96, J=K=128, E=1024, U=4096: scores
+    ~ N(0,4) with scale 1/8 and dropout p=0.1, bdrln over [B,J,E] with bias ~ N(0,0.02) and residual ~ N(0,1),
+    bad over [B,J,U], gradients ~ N(0,1), saved tensors from the matching forward.  20 + 200 launches over
+    rotating buffer sets (a set is 50-350 MB, above the 126 MB L2), CUDA events, GB/s = algorithmic bytes / time.
+    Mirrors the reference's per-kernel harness (pytorch_module/benchmark.py:375-393, :1475-1493)."""
+    from substation_b200 import ops
+    peaks, _ = load_peaks()
+    hbm = float(peaks['hbm_gbs'])
+    g = torch.Generator(device=dev).manual_seed(7)
+    Pp = E // Hh
+    rnd = lambda *s, std=1.0: (torch.randn(*s, device=dev, generator=g) * std).half()
+    empty = lambda *s: torch.empty(*s, device=dev, dtype=torch.float16)
+    keep = lambda *s: (torch.rand(*s, device=dev, generator=g) >= P_DROP).to(torch.uint8)
+    results = {}
+
+    def timed(name, nbytes, calls):
+        for i in range(warmup):
+            calls[i % len(calls)]()
+        torch.cuda.synchronize()
+        ms = event_time_ms(lambda i: calls[i % len(calls)](), reps, torch)
+        us = 1e3 * ms / reps
+        results[name] = {'us': round(us, 2), 'gbs': round(nbytes / us / 1e3, 1),
+                         'frac_of_measured_copy': round(nbytes / us / 1e3 / hbm, 3),
+                         'frac_of_8tbs': round(nbytes / us / 1e3 / NOMINAL_HBM_GBS, 3)}
+
+    S4, T3, TU = (Hh, B, L, L), (B, L, E), (B, L, U)
+    ns, nt, nu = Hh * B * L * L, B * L * E, B * L * U
+    # ---- softmax + dropout, and its backward (separate operators and the fused attention-score forms)
+    sets = []
+    for _ in range(nset):
+        d = {'beta': rnd(*S4, std=2.0), 'alpha': empty(*S4), 'mask': keep(*S4), 'drop': empty(*S4),
+             'dad': rnd(*S4), 'dbeta': empty(*S4), 'qq': rnd(Pp, Hh, B, L), 'kk': rnd(Pp, Hh, B, L),
+             'vv': rnd(Pp, Hh, B, L), 'dg': rnd(Pp, Hh, B, L)}
+        sets.append(d)
+    timed('softmax', 7 * ns, [lambda d=d: ops.softmax_dropout(d['beta'], d['alpha'], d['mask'], d['drop'], 0.125, P_DROP)
+                              for d in sets])
+    timed('bs', 7 * ns, [lambda d=d: ops.backward_softmax(d['alpha'], d['mask'], d['dad'], d['dbeta']) for d in sets])
+    timed('QKT+softmax', 5 * ns + 4 * nt, [lambda d=d: ops.attention_scores_softmax(
+        d['qq'], d['kk'], None, d['alpha'], d['mask'], d['drop'], 0.125, P_DROP) for d in sets])
+    timed('dX1gamma+bs', 5 * ns + 4 * nt, [lambda d=d: ops.attention_scores_softmax_backward(
+        d['dg'], d['vv'], d['alpha'], d['mask'], None, d['dbeta']) for d in sets])
+    del sets
+    # ---- bias + dropout + residual + LayerNorm and the LayerNorm backward family over [B,J,E]
+    vec = lambda std=1.0: rnd(E, std=std)
+    sets = []
+    for _ in range(nset + 1):
+        d = {'in': rnd(*T3), 'resid': rnd(*T3), 'mask': keep(*T3), 'lin': empty(*T3), 'diff': empty(*T3),
+             'istd': empty(B, L), 'ln': empty(*T3), 'out': empty(*T3), 'dy': rnd(*T3), 'dln': empty(*T3),
+             'dres': empty(*T3), 'dlin': empty(*T3), 'r2': rnd(*T3), 'lw': rnd(*T3), 'l2': rnd(*T3),
+             'bias': vec(0.02), 'gamma': vec(), 'beta': vec(), 'v': [empty(E) for _ in range(4)]}
+        sets.append(d)
+    timed('bdrln', 13 * nt, [lambda d=d: ops.bias_dropout_residual_layernorm(
+        d['in'], d['bias'], d['resid'], d['gamma'], d['beta'], d['mask'], d['lin'], d['diff'], d['istd'], d['ln'], d['out'],
+        P_DROP) for d in sets])
+    timed('bsb', 6 * nt, [lambda d=d: ops.backward_scale_bias(d['dy'], d['ln'], d['gamma'], d['dln'], d['v'][0], d['v'][1])
+                          for d in sets])
+    timed('blnrd', 9 * nt, [lambda d=d: ops.backward_layernorm_residual_dropout(
+        d['dln'], d['istd'], d['diff'], d['mask'], d['dres'], d['dlin']) for d in sets])
+    timed('ebsb', 10 * nt, [lambda d=d: ops.extended_backward_scale_bias(
+        d['ln'], d['gamma'], d['r2'], d['lw'], d['l2'], d['dln'], d['v'][0], d['v'][1], d['v'][2]) for d in sets])
+    timed('baob', 2 * nt, [lambda d=d: ops.backward_attn_out_bias(d['dlin'], d['v'][3]) for d in sets])
+    timed('bei', 6 * nt, [lambda d=d: ops.backward_encoder_input(d['r2'], d['lw'], d['dres']) for d in sets])
+    timed('bsb+blnrd', 11 * nt, [lambda d=d: ops.backward_scale_bias_layernorm(
+        d['dy'], d['ln'], d['gamma'], d['istd'], d['diff'], d['mask'], None, d['dres'], d['dlin'], d['v'][0], d['v'][1])
+        for d in sets])
+    timed('ebsb+blnrd+baob', 15 * nt, [lambda d=d: ops.extended_backward_scale_bias_layernorm(
+        d['ln'], d['gamma'], d['r2'], d['lw'], d['l2'], d['istd'], d['diff'], d['mask'], None, d['dres'], d['dlin'], *d['v'])
+        for d in sets])
+    del sets
+    # ---- attention input biases and their gradient over [3,P,H,B,J]
+    sets = [{'in': rnd(3, Pp, Hh, B, L), 'out': empty(3, Pp, Hh, B, L), 'bias': rnd(3, Pp, Hh), 'db': empty(3, Pp, Hh)}
+            for _ in range(nset + 1)]
+    timed('aib', 12 * nt, [lambda d=d: ops.attention_input_biases(d['in'], d['bias'], d['out']) for d in sets])
+    timed('baib', 6 * nt, [lambda d=d: ops.backward_attention_input_biases(d['in'], d['db']) for d in sets])
+    del sets
+    # ---- bias + activation + dropout and its backward over [B,J,U]
+    sets = [{'in': rnd(*TU), 'bias': rnd(U, std=0.02), 'mask': keep(*TU), 'lin1': empty(*TU), 'drop2': empty(*TU),
+             'dd': rnd(*TU), 'dlin1': empty(*TU), 'db': empty(U)} for _ in range(nset)]
+    timed('bad', 7 * nu, [lambda d=d: ops.bias_activation_dropout(d['in'], d['bias'], d['mask'], d['lin1'], d['drop2'],
+                                                                  'relu', P_DROP) for d in sets])
+    timed('bdrlb', 7 * nu, [lambda d=d: ops.backward_dropout_activation_bias(d['dd'], d['mask'], d['lin1'], d['dlin1'],
+                                                                             d['db'], 'relu') for d in sets])
+    del sets
+    torch.cuda.empty_cache()
+    return {'shape': f'H={Hh}, B={B}, J=K={L}, E={E}, U={U}', 'launches_per_operator': f'{warmup} + {reps}',
+            'peaks_gbs': {'measured_copy': hbm, 'nominal': NOMINAL_HBM_GBS}, 'operators': results}
+
+
+def run_kernels(args):
+    import torch
+    _, rank, _, dev = dist_env(args)
+    if rank != 0:
+        return
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    sweep = fused_kernel_sweep(dev, torch)
+    clocks = sampler.stop()
+    worst = min(sweep['operators'], key=lambda n: sweep['operators'][n]['frac_of_measured_copy'])
+    print(json.dumps({'metric': 'fused_operator_hbm_gbs', 'unit': 'GB/s', 'value': sweep['operators'][worst]['gbs'],
+                      'value_is': f'the slowest operator of the sweep ({worst})', 'higher_is_better': True,
+                      'n_gpus': 1, 'dtype': 'f16', 'data': 'synthetic', 'clocks': clocks,
+                      'config': {'workload': 'each fused operator alone, ' + sweep['shape']}, **sweep}))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from substation_b200 import layouts as L
+    from substation_b200.data_parallel import GradientBucketReducer, shard_batch
+
+    world, rank, local_rank, dev = dist_env(args)
+    init_nccl(args, world, dev)
     B, S = args.batch, args.seq
-    lay = get_layouts(args.layouts)
-    table = L.validate(lay)
-    enc = Encoder('/tmp/substation_b200_unused', B, S, H, E, lay, torch.float16,
-                  P_DROP, P_DROP, P_DROP, P_DROP, profiling=True, mask_mode='explicit',
-                  keep_all_intermediates=bool(args.keep_all)).to(dev)
+    lay = resolve_layouts(args.layouts)
+    lb = LayerBench(B, S, lay, dev, rank, args.keep_all)
+    enc = lb.enc
     fused_bytes = FUSED_BYTES if args.keep_all else FUSED_BYTES_SKIP
-    gen = torch.Generator(device=dev).manual_seed(1234)        # same weights on every rank
-    with torch.no_grad():
-        for (name, layout), prm in zip(lay['params'], enc.params):
-            if name in ('WKQV', 'WO', 'LINW1', 'LINW2'):
-                prm.copy_((torch.randn(prm.shape, device=dev, generator=gen) * 0.02).half())
-            elif name in ('S1', 'S2'):
-                prm.fill_(1.0)
-            else:
-                prm.zero_()
-    gen = torch.Generator(device=dev).manual_seed(100 + rank)  # different data per rank
-    shape_x = L.shape_of(table['X'], enc.sizes)
-    X = torch.randn(shape_x, device=dev, generator=gen).half()
-    DY = torch.randn(shape_x, device=dev, generator=gen).half()
-    masks = {}
-    for n in L.MASKS:
-        shp = L.shape_of(table[n], enc.sizes)
-        masks[n] = (torch.rand(shp, device=dev, generator=gen) >= P_DROP).to(torch.uint8)
-    enc.set_masks(masks)
-
-    weights = [p.detach() for p in enc.params]
-    fwd = enc._alloc(enc._fwd_plan, dev)
-    fwd.update(masks)
-    bwd = enc._alloc(enc._bwd_plan, dev)
     # double-buffered gradient buckets: the allreduce of step i overlaps step i+1
     reducer = GradientBucketReducer(enc.arena_bytes('grads'), dev, buffers=2)
-    Y, DX = torch.empty_like(X), torch.empty_like(X)
+    grad_views = [enc.views('grads', reducer.arenas[b]) for b in range(len(reducer.arenas))]
 
     # The whole bucket is allreduced beside the next step.  With --early-allreduce 1 the gradients of the
     # feed-forward half, final in the middle of the backward pass, are allreduced beside the attention half of the
-    # pass instead: measured slower (8 GPUs: 0.75 against 0.67 ms per step), the allreduce then competes with the
-    # HBM-bound attention kernels rather than with the next step's tensor-bound projections.
+    # pass instead: measured slower in steady state (the allreduce then competes with the HBM-bound attention
+    # kernels rather than with the next step's tensor-bound projections).
     early = None
     if world > 1 and args.early_allreduce:
         ffn_event = torch.cuda.Event()
         enc.set_ffn_grads_event(ffn_event)
         early = (enc.early_grad_offset(), ffn_event)
-    grad_views = [enc.views('grads', reducer.arenas[b]) for b in range(len(reducer.arenas))]
 
     def step(i):
         reducer.wait(i)                                   # this bucket's previous reduction has finished
-        grads = grad_views[i % len(grad_views)]
-        enc.forward_raw(X, weights, fwd, Y)
-        enc.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
+        lb.run(grad_views[i % len(grad_views)])
         reducer.reduce_async(i, early=early)
 
     drain = reducer.drain
@@ -310,27 +534,44 @@ def run_ours(args):
     def set_timing(on):
         lib.sb_encoder_set_timing(enc._native(dev), 1 if on else 0)
 
+    def timed_region(n_steps, sampler=None):
+        """n_steps steps bracketed by barrier + synchronize; device time, max over ranks."""
+        barrier()
+        if sampler is not None and rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_steps):
+            step(i)
+        drain()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
     # ---- headline: K steps, device timed, per-operator events off -----------------------
     set_timing(False)
     for i in range(args.warmup):
         step(i)
     drain()
     sampler = ClockSampler(local_rank)
-    barrier()
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    drain()
-    e1.record()
-    barrier()
+    total_ms = timed_region(args.steps, sampler)
     clocks = sampler.stop() if rank == 0 else None
-    total_ms = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = total_ms / args.steps
     value = world * B * args.steps / (total_ms / 1e3)
-    launches = None   # filled from the library's own count below
+
+    # ---- the same step for at least --sustain-s seconds: what the power cap leaves of the short-run figure ----
+    sustained = None
+    if args.sustain_s > 0:
+        n_sus = max(args.steps, int(args.sustain_s * 1e3 / ms_per_step) + 1)
+        sampler = ClockSampler(local_rank)
+        sus_ms = timed_region(n_sus, sampler)
+        sc = sampler.stop(skip_first=2) if rank == 0 else None      # the first samples precede the load
+        sustained = {'steps': n_sus, 'seconds': round(sus_ms / 1e3, 3), 'ms_per_step': sus_ms / n_sus,
+                     'value': world * B * n_sus / (sus_ms / 1e3), 'clocks': sc}
+        if sc and sc.get('sm_mhz'):
+            sustained['ms_x_mhz'] = round(sus_ms / n_sus * sc['sm_mhz'], 1)
+    if clocks and clocks.get('sm_mhz'):
+        clocks['ms_x_mhz'] = round(ms_per_step * clocks['sm_mhz'], 1)
 
     # ---- per-operator device times (CUDA events on the launching stream around every launch) ----
     launches_per_step = []
@@ -352,6 +593,13 @@ def run_ours(args):
     hbm = float(peaks['hbm_gbs'])
     tf_burst = float(peaks['bf16_tflops'])
     tf_sustained = float(peaks.get('bf16_tflops_sustained', tf_burst))
+
+    # ---- yardsticks, outside every timed region (rank 0 of a single-GPU run) ----
+    anchors, probe = {}, None
+    if rank == 0 and world == 1 and not args.no_anchors:
+        anchors = cublas_anchors(B * S, dev, torch)
+        probe = tensor_peak_probe(torch)
+
     ops = {}
     ideal_us = 0.0
     for name, v in per.items():
@@ -367,6 +615,9 @@ def run_ours(args):
                 rec['gbs'] = round(by / us / 1e3, 1)
                 rec['frac_hbm'] = round(by / us / 1e3 / hbm, 3)
                 ideal = max(ideal, by / (hbm * 1e3))
+            base = name.split('+')[0]
+            if base in anchors:
+                rec['cublas_us'] = round(anchors[base], 2)      # the plain contraction of the same shape
         else:
             by = fused_bytes[name](B, S)
             rec['gbs'] = round(by / us / 1e3, 1)
@@ -376,18 +627,19 @@ def run_ours(args):
         ops[name] = rec
     sum_us = sum(r['us'] for r in ops.values())
     T_tok = B * S
-    ref_list_us = ((142 * T_tok * E + 14 * H * B * S * S) / (hbm * 1e3) +
-                   (72 * E * E * T_tok + 12 * B * S * S * E) / (tf_sustained * 1e6))
+    ref_bytes = 142 * T_tok * E + 14 * H * B * S * S
+    ref_flops = 72 * E * E * T_tok + 12 * B * S * S * E
+    ref_list_us = ref_bytes / (hbm * 1e3) + ref_flops / (tf_sustained * 1e6)
+    ref_list_burst_us = ref_bytes / (hbm * 1e3) + ref_flops / (tf_burst * 1e6)
     top = max(ops, key=lambda n: ops[n]['us'])
     if top in GEMM_FLOPS and top not in ATTN_BYTES:
-        roof = {'kernel': f'gemm_tc_kernel ({top})', 'bound': 'tensor', 'achieved': ops[top]['tflops'],
+        roof = {'kernel': f'gemm_tc_pair_kernel ({top})', 'bound': 'tensor', 'achieved': ops[top]['tflops'],
                 'peak': tf_burst, 'unit': 'TFLOP/s', 'frac': round(ops[top]['tflops'] / tf_burst, 3)}
     else:
         roof = {'kernel': top, 'bound': 'hbm', 'achieved': ops[top]['gbs'], 'peak': hbm, 'unit': 'GB/s',
                 'frac': round(ops[top]['gbs'] / hbm, 3)}
-    # DRAM bytes (read + write) of one launch from the ncu capture of this workload; only known for B=8, L=512
-    roof['traffic'] = NCU_DRAM_BYTES.get(top) if (B, S) == (8, 512) and args.keep_all else None
-    roof['traffic_unit'] = 'bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)'
+    roof['traffic'] = load_dram_traffic(B, S, args.keep_all).get(top)
+    roof['traffic_unit'] = 'bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum; null: not captured for this setting)'
     roof['algorithmic_bytes'] = (fused_bytes.get(top) or ATTN_BYTES.get(top, lambda b, l: None))(B, S)
     roof['peak_source'] = f'{peak_kind} (MEASURED_PEAKS.json: torch copy / cuBLAS bf16 burst)'
     roof['share_of_step'] = round(ops[top]['us'] / sum_us, 3)
@@ -395,6 +647,7 @@ def run_ours(args):
     # ---- end to end through the public module with host buffers -------------------------
     e2e = None
     if not args.no_e2e:
+        X, DY = lb.X, lb.DY
         hX, hDY = X.cpu().pin_memory(), DY.cpu().pin_memory()
         hY, hDX = torch.empty_like(hX).pin_memory(), torch.empty_like(hX).pin_memory()
 
@@ -405,6 +658,7 @@ def run_ours(args):
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         xd = [torch.empty_like(X) for _ in range(2)]
         dyd = [torch.empty_like(X) for _ in range(2)]
+        yd = [torch.empty_like(X) for _ in range(2)]
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_free = [torch.cuda.Event() for _ in range(2)]       # compute no longer reads input buffer b
         ev_out = [torch.cuda.Event() for _ in range(2)]
@@ -412,6 +666,9 @@ def run_ours(args):
         works = [None, None]
         for prm in enc.params:
             prm.requires_grad_(True)
+        # the autograd path writes its gradients into these two caller-held buckets in turn, so the collective
+        # sees the same two buffers every step
+        enc.set_grad_arenas([torch.empty(enc.arena_bytes('grads'), dtype=torch.uint8, device=dev) for _ in range(2)])
 
         def copy_in(i):
             b = i & 1
@@ -421,6 +678,14 @@ def run_ours(args):
                 dyd[b].copy_(hDY, non_blocking=True)
                 ev_in[b].record(s_in)
 
+        def copy_out(b, y, dx):
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_free[b])
+                s_out.wait_event(ev_out[b])                    # previous copy out of these host buffers done
+                hY.copy_(y, non_blocking=True)
+                hDX.copy_(dx, non_blocking=True)
+                ev_out[b].record(s_out)
+
         def e2e_step(i):
             # the inputs of step i+1 start moving before the kernels of step i are enqueued, so the copy
             # runs beside this step's compute however far ahead of the GPU the host happens to be
@@ -428,31 +693,27 @@ def run_ours(args):
             copy_in(i + 1)
             cur.wait_event(ev_in[b])
             x = xd[b].detach().requires_grad_(True)
+            if works[b] is not None:                           # the bucket this backward writes is free again
+                works[b].wait()
+                works[b] = None
             y = enc(x)
             y.backward(dyd[b])
             ev_free[b].record(cur)
             if world > 1:
-                # all twelve gradients are views into one bucket: one allreduce, asynchronous, waited for
-                # two steps later (each step's backward gets a fresh bucket)
-                bucket = enc.grad_bucket()
-                lo, hi = bucket.data_ptr(), bucket.data_ptr() + bucket.numel() * 2
-                if all(lo <= prm.grad.data_ptr() < hi for prm in enc.params):
-                    if works[b] is not None:
-                        works[b].wait()
-                    works[b] = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, async_op=True)
-                else:
-                    for prm in enc.params:
-                        dist.all_reduce(prm.grad, op=dist.ReduceOp.SUM)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_free[b])
-                s_out.wait_event(ev_out[b])                    # previous copy out of these host buffers done
-                y.record_stream(s_out)
-                x.grad.record_stream(s_out)
-                hY.copy_(y.detach(), non_blocking=True)
-                hDX.copy_(x.grad, non_blocking=True)
-                ev_out[b].record(s_out)
+                # all twelve gradients are views into one bucket: one allreduce, asynchronous
+                works[b] = dist.all_reduce(enc.grad_bucket(), op=dist.ReduceOp.SUM, async_op=True)
+            y.record_stream(s_out)
+            x.grad.record_stream(s_out)
+            copy_out(b, y.detach(), x.grad)
             keep[b] = (x, y)
             enc.zero_grad(set_to_none=True)
+
+        def copy_only_step(i):
+            b = i & 1
+            copy_in(i + 1)
+            cur.wait_event(ev_in[b])
+            ev_free[b].record(cur)
+            copy_out(b, yd[b], xd[b])
 
         def e2e_drain():
             for w in works:
@@ -461,27 +722,55 @@ def run_ours(args):
             cur.wait_stream(s_in)
             cur.wait_stream(s_out)
 
+        def e2e_region(stepfn, first, n):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            t_host = time.perf_counter()
+            for i in range(first, first + n):
+                stepfn(i)
+            t_host = time.perf_counter() - t_host      # host time to issue the steps (no synchronisation inside)
+            e2e_drain()
+            e1.record()
+            barrier()
+            return max_over_ranks(e0.elapsed_time(e1)), t_host
+
         n_warm = max(3, args.warmup)
         copy_in(0)
         for i in range(n_warm):
             e2e_step(i)
         e2e_drain()
-        barrier()
-        e0.record()
-        t_host = time.perf_counter()
         # step i's inputs were copied during step i-1 (the first one during warm-up); every step issues
         # exactly one copy in and one copy out, so the timed region holds `steps` of each
-        for i in range(n_warm, n_warm + args.steps):
-            e2e_step(i)
-        t_host = time.perf_counter() - t_host      # host time to issue the steps (no synchronisation inside)
+        e2e_ms, t_host = e2e_region(e2e_step, n_warm, args.steps)
+        first = n_warm + args.steps
+        for i in range(first, first + 2):
+            copy_only_step(i)
         e2e_drain()
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+        copy_ms, _ = e2e_region(copy_only_step, first + 2, args.steps)
+        enc.set_grad_arenas(None)
         nbytes = hX.numel() * 2
         e2e = {'value': world * B * args.steps / (e2e_ms / 1e3), 'unit': UNIT,
                'h2d_bytes_per_step': 2 * nbytes, 'd2h_bytes_per_step': 2 * nbytes,
-               'ms_per_step': e2e_ms / args.steps, 'host_issue_ms_per_step': 1e3 * t_host / args.steps}
+               'ms_per_step': e2e_ms / args.steps, 'host_issue_ms_per_step': 1e3 * t_host / args.steps,
+               # the same host<->device copies with no compute between them: what the host side of the box allows
+               'copy_only_ms_per_step': copy_ms / args.steps,
+               'over_max_of_copy_and_compute': round((e2e_ms / args.steps) / max(copy_ms / args.steps, ms_per_step), 3)}
+
+    # ---- multi-GPU evidence, outside the timed regions ------------------------------------
+    dp_check = strong = stack = None
+    if world > 1 and not args.no_extras:
+        dp_check = data_parallel_check(lb, reducer, grad_views, world, rank, dev, lay, args)
+    if not args.no_extras:
+        strong = strong_scaling_record(args, world, rank, dev, barrier, max_over_ranks)
+        stack = stack_record(args, world, rank, dev, barrier, max_over_ranks)
+
+    # ---- every fused operator alone at the kernel-sweep shapes (single-GPU run) ------------
+    sweep = None
+    if rank == 0 and world == 1 and not args.no_sweep:
+        del lb
+        torch.cuda.empty_cache()
+        sweep = fused_kernel_sweep(dev, torch)
 
     # ---- CPU baseline (rank 0, N=1 only): bounded sample of the same workload ------------
     cpu = None
@@ -493,27 +782,187 @@ def run_ours(args):
                          f'port of substation/transformer.py ({t:.1f} s)'}
 
     if rank == 0:
+        layer = {'sum_of_operator_us': round(sum_us, 1), 'sum_of_roofline_us': round(ideal_us, 1),
+                 'frac_of_summed_roofline': round(ideal_us / sum_us, 3),
+                 # the same ideal against the device time of a whole step (kernels overlap their
+                 # neighbours' ramp-up and tail under programmatic dependent launch)
+                 'roofline_us_over_step_us': round(ideal_us / (ms_per_step * 1e3), 3),
+                 # the reference's own operator list (32 separate operators: 142*T*E + 14*S bytes of
+                 # elementwise traffic, 72*E^2*T + 12*B*L^2*E flops) at the measured copy bandwidth and the
+                 # tensor rate: burst peak against the short run, sustained peak against the sustained run
+                 'reference_list_roofline_us': round(ref_list_us, 1),
+                 'reference_list_roofline_burst_us': round(ref_list_burst_us, 1),
+                 'reference_list_roofline_over_step': round(ref_list_us / (ms_per_step * 1e3), 3),
+                 'reference_list_burst_roofline_over_step': round(ref_list_burst_us / (ms_per_step * 1e3), 3)}
+        if sustained:
+            layer['reference_list_roofline_over_sustained_step'] = round(ref_list_us / (sustained['ms_per_step'] * 1e3), 3)
         line = {
             'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
             'config': workload_config(args, args.layouts),
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches, 'roofline': roof, 'cpu_baseline': cpu,
-            'layer': {'sum_of_operator_us': round(sum_us, 1), 'sum_of_roofline_us': round(ideal_us, 1),
-                      'frac_of_summed_roofline': round(ideal_us / sum_us, 3),
-                      # the same ideal against the device time of a whole step (kernels overlap their
-                      # neighbours' ramp-up and tail under programmatic dependent launch)
-                      'roofline_us_over_step_us': round(ideal_us / (ms_per_step * 1e3), 3),
-                      # the reference's own operator list (32 separate operators: 142*T*E + 14*S bytes of
-                      # elementwise traffic, 72*E^2*T + 12*B*L^2*E flops) at the measured copy bandwidth and the
-                      # sustained tensor rate, which is the figure that applies inside a long step
-                      'reference_list_roofline_us': round(ref_list_us, 1),
-                      'reference_list_roofline_over_step': round(ref_list_us / (ms_per_step * 1e3), 3)},
-            'operators': ops,
+            'sustained': sustained, 'layer': layer, 'fp16_tflops_probe': probe, 'operators': ops,
+            'dp_check': dp_check, 'strong': strong, 'stack': stack, 'fused_kernels': sweep,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def data_parallel_check(lb, reducer, grad_views, world, rank, dev, lay, args):
+    """(a) the allreduced bucket against the fp32 sum of the gathered per-rank buckets; (b) at a small shape, the
+    allreduced gradients of a batch sharded over the ranks against one GPU running the concatenated batch."""
+    import torch
+    import torch.distributed as dist
+    from substation_b200 import layouts as L
+    from substation_b200.data_parallel import shard_batch
+
+    def rel_l2(a, b):
+        return float(((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30)).item())
+
+    res = {}
+    # (a) the bench's own shape
+    reducer.drain()
+    lb.run(grad_views[0])
+    local = reducer.flat(0).clone()
+    gathered = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(gathered, local)
+    want = torch.zeros(local.numel(), dtype=torch.float32, device=dev)
+    for g in gathered:
+        want += g.float()
+    reducer.reduce_async(0)
+    reducer.drain()
+    torch.cuda.synchronize(dev)
+    res['allreduced_vs_fp32_sum_of_gathered'] = rel_l2(reducer.flat(0).float(), want)
+    del gathered, want
+    # (b) small shape: global batch 2*world at L=128, BERT-large widths
+    b_loc, S = 2, 128
+    Bg = b_loc * world
+    table = L.validate(lay)
+    if table['X'] != 'BJI' or any(table[n][0] != 'B' for n in ('DROP1MASK', 'DROP2MASK', 'DROP3MASK')) or \
+            table['ATTN_DROP_MASK'][:2] != 'HB':
+        res['sharded_vs_one_gpu'] = None     # slicing below assumes batch-major masks
+        return res
+    gen = torch.Generator(device=dev).manual_seed(4321)          # the same global batch on every rank
+    Xg = torch.randn(Bg, S, E, device=dev, generator=gen).half()
+    DYg = torch.randn(Bg, S, E, device=dev, generator=gen).half()
+    mg = {'ATTN_DROP_MASK': (torch.rand(H, Bg, S, S, device=dev, generator=gen) >= P_DROP).to(torch.uint8),
+          'DROP1MASK': (torch.rand(Bg, S, E, device=dev, generator=gen) >= P_DROP).to(torch.uint8),
+          'DROP2MASK': (torch.rand(Bg, S, U, device=dev, generator=gen) >= P_DROP).to(torch.uint8),
+          'DROP3MASK': (torch.rand(Bg, S, E, device=dev, generator=gen) >= P_DROP).to(torch.uint8)}
+    lo, hi = shard_batch(Bg, world, rank)
+    ml = {n: (m[:, lo:hi] if n == 'ATTN_DROP_MASK' else m[lo:hi]).contiguous() for n, m in mg.items()}
+    small = LayerBench(hi - lo, S, lay, dev, rank, args.keep_all, profiling=False,
+                       X=Xg[lo:hi].contiguous(), DY=DYg[lo:hi].contiguous(), masks=ml)
+    bucket = torch.zeros(small.enc.arena_bytes('grads'), dtype=torch.uint8, device=dev)
+    small.run(small.enc.views('grads', bucket))
+    flat = bucket.view(torch.float16)
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+    worst = None
+    if rank == 0:
+        full = LayerBench(Bg, S, lay, dev, rank, args.keep_all, profiling=False, X=Xg, DY=DYg, masks=mg)
+        fb = torch.zeros(full.enc.arena_bytes('grads'), dtype=torch.uint8, device=dev)
+        fg = full.enc.views('grads', fb)
+        full.run(fg)
+        torch.cuda.synchronize(dev)
+        sg = small.enc.views('grads', bucket)
+        worst = max(rel_l2(sg[n], fg[n]) for n in fg if n != '__arena__')
+    dist.barrier()
+    res['sharded_vs_one_gpu'] = worst
+    res['sharded_shape'] = f'global batch {Bg} (L={S}) as {b_loc} per rank; worst rel-L2 over the 12 gradients'
+    res['tolerance'] = 1e-2
+    return res
+
+
+def strong_scaling_record(args, world, rank, dev, barrier, max_over_ranks, global_batch=96, S=128, steps=10):
+    """Global batch 96 at L=128 (the small-sequence, large-batch configuration) split over the ranks: every rank runs
+    96 / N sequences per step, gradients allreduced beside the next step.  With N > 1, rank 0 also times the whole
+    batch alone so that the line carries both sides of the ratio."""
+    import torch
+    from substation_b200 import layouts as L
+    from substation_b200.data_parallel import GradientBucketReducer, shard_batch
+    lay = L.uniform_layouts()
+    lo, hi = shard_batch(global_batch, world, rank)
+
+    def measure(Bl, reduce):
+        lb = LayerBench(Bl, S, lay, dev, rank, args.keep_all, profiling=False)
+        red = GradientBucketReducer(lb.enc.arena_bytes('grads'), dev, buffers=2, verify=reduce) if reduce else None
+        arenas = red.arenas if red else [torch.empty(lb.enc.arena_bytes('grads'), dtype=torch.uint8, device=dev)
+                                         for _ in range(2)]
+        views = [lb.enc.views('grads', a) for a in arenas]
+
+        def step(i):
+            if red:
+                red.wait(i)
+            lb.run(views[i & 1])
+            if red:
+                red.reduce_async(i)
+        for i in range(4):
+            step(i)
+        if red:
+            red.drain()
+        if reduce:
+            barrier()
+        else:
+            torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        if red:
+            red.drain()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        del lb
+        torch.cuda.empty_cache()
+        return ms
+
+    ms = max_over_ranks(measure(hi - lo, world > 1)) / steps
+    rec = {'global_batch': global_batch, 'seq_len': S, 'per_gpu_batch': hi - lo, 'layouts': 'uniform',
+           'ms_per_step': ms, 'value': global_batch / (ms / 1e3), 'unit': UNIT}
+    if world > 1:
+        one = measure(global_batch, False) / steps if rank == 0 else 0.0
+        barrier()
+        one = max_over_ranks(one)
+        rec['one_gpu_ms_per_step'] = one
+        rec['speedup_over_one_gpu'] = round(one / ms, 3)
+    return rec
+
+
+def stack_record(args, world, rank, dev, barrier, max_over_ranks, layers=24, steps=4):
+    """24 layers with independent weights, per-GPU batch 8 at L=512: forward through all layers, backward through all
+    layers, each layer's gradient bucket allreduced while the next layer's backward runs."""
+    import torch
+    from substation_b200.stack import EncoderStack
+    lay = resolve_layouts(args.layouts)
+    st = EncoderStack(layers, 8, 512, H, E, lay, dropout_p=P_DROP, device=dev, seed=1234)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    X = torch.randn(st.acts[0].shape, device=dev, generator=gen).half()
+    DY = torch.randn(st.acts[0].shape, device=dev, generator=gen).half()
+
+    def step():
+        st.forward(X)
+        st.backward(DY)
+    for _ in range(2):
+        step()
+    st.wait_gradients()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    st.wait_gradients()
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    rec = {'layers': layers, 'per_gpu_batch': 8, 'seq_len': 512, 'ms_per_step': ms, 'ms_per_layer': ms / layers,
+           'value': world * 8 / (ms / 1e3), 'unit': UNIT, 'memory_gb': round(st.memory_bytes() / 2 ** 30, 2),
+           'masks': 'in-kernel Philox'}
+    del st
+    torch.cuda.empty_cache()
+    return rec
 
 
 def run_stack(args):
@@ -522,23 +971,10 @@ def run_stack(args):
     bucket allreduced while the next layer's backward runs."""
     import torch
     import torch.distributed as dist
-    from substation_b200 import ops as _ops
     from substation_b200.stack import EncoderStack
-    from tests.layer_harness import get_layouts
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
-    if world != args.gpus:
-        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run')
-    torch.cuda.set_device(local_rank)
-    dev = torch.device('cuda', local_rank)
-    if world > 1:
-        opts = dist.ProcessGroupNCCL.Options()
-        opts.config.max_ctas = args.comm_ctas
-        opts.config.min_ctas = min(4, args.comm_ctas)
-        dist.init_process_group('nccl', device_id=dev, pg_options=opts)
-        _ops.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - args.comm_ctas)
-    lay = get_layouts(args.layouts)
+    world, rank, local_rank, dev = dist_env(args)
+    init_nccl(args, world, dev)
+    lay = resolve_layouts(args.layouts)
     st = EncoderStack(args.layers, args.batch, args.seq, H, E, lay, dropout_p=P_DROP, device=dev, seed=1234)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     X = torch.randn(st.acts[0].shape, device=dev, generator=gen).half()
@@ -602,16 +1038,23 @@ def main():
     ap.add_argument('--early-allreduce', type=int, default=0,
                     help='N > 1: sum the feed-forward gradients beside the attention half of backward (1) or the whole '
                          'bucket beside the next step (0)')
-    ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (config 5 uses 24)')
+    ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (the 24-layer configuration uses 24)')
+    ap.add_argument('--kernels', action='store_true', help='time every fused operator alone at the kernel-sweep shapes')
     ap.add_argument('--keep-all', type=int, default=0,
                     help='1: also store the nine intermediates nothing reads again (what enable_debug does)')
+    ap.add_argument('--sustain-s', type=float, default=2.0, help='length of the sustained run in seconds (0: skip)')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu', action='store_true')
+    ap.add_argument('--no-anchors', action='store_true', help='skip the cuBLAS yardstick and the tensor-peak probe')
+    ap.add_argument('--no-sweep', action='store_true', help='skip the fused-operator sweep')
+    ap.add_argument('--no-extras', action='store_true', help='skip dp_check / strong / stack')
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == 'ours':
         args.warmup = 3
     if args.impl == 'reference':
         run_reference_arm(args)
+    elif args.kernels:
+        run_kernels(args)
     elif args.layers > 1:
         run_stack(args)
     else:

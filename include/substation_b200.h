@@ -287,8 +287,9 @@ typedef struct sb_epilogue {
 } sb_epilogue;
 int sb_einsum_fused(void* stream, const char* a_dims, const sb_tensor* a, const char* b_dims, const sb_tensor* b,
                     const char* c_dims, const sb_tensor* c, float alpha, const sb_epilogue* epilogue);
-/* Every wait inside the tcgen05 kernels is bounded; when one runs out the kernel
- * records a code (1 producer, 2 MMA issuer, 3 epilogue, ...), drains and returns.
+/* Every wait inside the tcgen05 kernels and the ring-fed LayerNorm kernels is bounded; when one runs
+ * out the kernel records a code (tcgen05: 1 producer, 2 MMA issuer, 3 epilogue, ...; ring: 11-14),
+ * drains and returns.
  * This reads that flag after synchronising `stream` (0 = no wait ran out since the
  * last reset).  The flag is per device (the device current when the call is made) and
  * sticky: while it is set, every later tcgen05 kernel on that device gives up its waits

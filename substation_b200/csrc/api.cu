@@ -564,9 +564,15 @@ extern "C" int sb_set_sm_budget(int n_sms) {
 }
 extern "C" int sb_device_error(void* stream, int* code) {
   if (!code) return fail(SB_ERR_ARG, "sb_device_error: null argument");
-  return gemm_device_error((cudaStream_t)stream, code);
+  // tcgen05 kernels record codes 1-7, the ring-fed LayerNorm kernels 11-14
+  SB_TRY(gemm_device_error((cudaStream_t)stream, code));
+  if (*code == 0) SB_TRY(ring_device_error((cudaStream_t)stream, code));
+  return SB_OK;
 }
-extern "C" int sb_device_error_reset(void* stream) { return gemm_device_error_reset((cudaStream_t)stream); }
+extern "C" int sb_device_error_reset(void* stream) {
+  SB_TRY(gemm_device_error_reset((cudaStream_t)stream));
+  return ring_device_error_reset((cudaStream_t)stream);
+}
 extern "C" int sb_mma_peak_probe(void* stream, int k_blocks, int bf16, double* flops) {
   return run_mma_peak_probe((cudaStream_t)stream, k_blocks, bf16, flops);
 }

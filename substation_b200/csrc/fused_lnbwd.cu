@@ -1,26 +1,30 @@
-// Fused LayerNorm-backward operators: the LayerNorm scale/bias gradients, the
-// LayerNorm backward-data with dropout, and the bias gradients that are plain
-// sums over tokens of tensors this pass touches anyway, in ONE pass over the data.
+// LayerNorm operators that stream whole token rows.
 //
+// Backward, fused: the LayerNorm scale/bias gradients, the LayerNorm backward-data with dropout, and the bias
+// gradients that are plain sums over tokens of tensors this pass touches anyway, in ONE pass over the data.
 //   mode A  = backward_scale_bias + backward_layernorm_residual_dropout
 //             (pytorch_module/block_bsb_ebsb.cuh:171-216, block_blnrd.cuh:71-129)
 //   mode B  = extended_backward_scale_bias + backward_layernorm_residual_dropout
 //             + backward_attn_out_bias
 //             (block_bsb_ebsb.cuh:368-420, block_blnrd.cuh:195-259, block_baob.cuh:75-97)
-//
 // Both need sums over features (per token) AND sums over tokens (per feature).
-// Mapping: a CTA has 4 row groups of 128 threads; the 128 threads of a group span
-// one token (8 features each, up to 1024 features) and walk tokens with a grid
-// stride, two tokens in flight.  Per-token sums: warp shuffles, then the group's
-// 4 warps exchange through shared memory behind a group-local named barrier.
-// Per-feature sums: each thread accumulates its 8 features in registers over all
-// of its tokens; at the end the 4 groups are added in order, the CTA writes one
-// fp32 partial row per quantity, and a second small kernel adds the partial rows
-// in order (deterministic).
+// Mapping: a CTA has 4 row groups of 128 threads; the 128 threads of a group span one token (8 features each,
+// up to 1024 features).  Per-token sums: warp shuffles, then the group's 4 warps exchange through shared
+// memory behind a group-local named barrier.  Per-feature sums: each thread accumulates its 8 features in
+// registers over all of its tokens; at the end the 4 groups are added in order, the CTA writes one fp32
+// partial row per quantity, and a second small kernel adds the partial rows in order (deterministic).
+// Two kernels share that mapping: lnbwd_ring_kernel takes its input rows from a shared-memory ring that a
+// producer warp fills with bulk copies (see ring.cuh; rows of 16-byte multiples), lnbwd_kernel loads them
+// straight from global memory (any feature count that is a multiple of 8).
+//
+// Forward: bias + dropout + residual + LayerNorm (pytorch_module/block_bdrln.cuh:105-180, :275-352) with the same
+// ring, one warp per token: bdrln_ring_kernel.
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "ops.h"
+#include "ring.cuh"
 
 namespace sb {
 
@@ -196,6 +200,206 @@ lnbwd_kernel(LnBwdParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same pass with its inputs staged through a shared-memory ring.  Thread layout: warps 0-15 = four row groups
+// (as above), warp 16 = producer.  Token sequence of a CTA: rows blockIdx.x + i * gridDim.x, i = 0, 1, ...; token
+// i goes to group i % 4 and to ring stage i % NS.  A stage holds the token's input rows back to back:
+//   mode A: DY, LN, DIFF (2F bytes each), mask (F bytes);   mode B: LN1, DRESID2, DLIN1_LINW1, DLIN2, DIFF, mask.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kRingThreads = kThreads + 32;
+
+template <int MODE>
+struct RingCfg {
+  static constexpr int NQ = MODE == 0 ? 2 : 4;
+  static constexpr int NIN = MODE == 0 ? 3 : 5;                 // fp16 input rows per token (incl. DIFF)
+  static constexpr int kColredBytes = kGroups * NQ * kMaxF * 4;
+  static constexpr int kMaxStage = NIN * 2 * kMaxF + kMaxF;     // bytes at 1024 features
+  static constexpr int kBudget = 232448 - kColredBytes - 2048;  // ring bytes available
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kRingThreads, 1)
+lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
+  using C = RingCfg<MODE>;
+  constexpr int NQ = C::NQ;
+  constexpr int NIN = C::NIN;
+  extern __shared__ __align__(128) uint8_t smem[];
+  // layout: colred [kGroups][NQ][1024] floats | ring | red | barriers
+  float* colred = reinterpret_cast<float*>(smem);
+  uint8_t* ring_gen = smem + C::kColredBytes;
+  const uint32_t ring_s = ring::smem_u32(ring_gen);
+  float* red = reinterpret_cast<float*>(ring_gen + (size_t)nstages * stage_bytes);   // [kGroups][2][4][2]
+  const uint32_t bars = ring::smem_u32(red) + kGroups * 2 * 4 * 2 * 4;                 // full[NS], empty[NS]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * nstages;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int F = p.d.F;
+  const unsigned R = (unsigned)p.d.B * (unsigned)p.d.J;
+  const unsigned G = gridDim.x;
+  const unsigned n_i = blockIdx.x < R ? (R - blockIdx.x + G - 1) / G : 0;   // tokens of this CTA
+  const uint32_t row_bytes = 2u * (uint32_t)F;
+
+  if (tid == 0) {
+    for (int s = 0; s < nstages; ++s) {
+      ring::mbar_init(bar_full + 8 * s, 1);
+      ring::mbar_init(bar_empty + 8 * s, kGroupThreads / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  grid_dependency_sync();
+
+  if (warp == kThreads / 32) {
+    // ---------------- producer: one elected lane issues the copies of token after token ----------------
+    bool ok = true;
+    for (unsigned i = 0; i < n_i && ok; ++i) {
+      const int s = (int)(i % (unsigned)nstages);
+      const uint32_t ph = (i / (unsigned)nstages) & 1u;
+      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 11));
+      if (!ok) break;
+      if (lane == 0) {
+        const unsigned row = blockIdx.x + i * G;
+        const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
+        ring::mbar_expect_tx(full, NIN * row_bytes + (uint32_t)F);
+        auto row_of = [&](const View3& v) { return reinterpret_cast<const __half*>(v.p) + b * v.sB + j * v.sJ; };
+        if (MODE == 0) {
+          ring::bulk_load(dst, row_of(p.y), row_bytes, full);
+          ring::bulk_load(dst + row_bytes, row_of(p.n), row_bytes, full);
+        } else {
+          ring::bulk_load(dst, row_of(p.n), row_bytes, full);
+          ring::bulk_load(dst + row_bytes, row_of(p.r2), row_bytes, full);
+          ring::bulk_load(dst + 2 * row_bytes, row_of(p.w), row_bytes, full);
+          ring::bulk_load(dst + 3 * row_bytes, row_of(p.l2), row_bytes, full);
+        }
+        ring::bulk_load(dst + (NIN - 1) * row_bytes, row_of(p.diff), row_bytes, full);
+        ring::bulk_load(dst + NIN * row_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + b * p.mask.sB + j * p.mask.sJ,
+                        (uint32_t)F, full);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------- consumers: group g takes tokens g, g + 4, ... of this CTA ----------------
+    const int group = tid / kGroupThreads, t = tid % kGroupThreads;
+    const int warp_in_group = t >> 5;
+    const int f = t * 8;
+    const bool active = f < F;
+    const float invn = 1.f / (float)F;
+    float gm[8];
+    if (active) unpack8(load8h_raw(p.gamma, 0, 1, 1, f, F), gm);
+    float acc[NQ][8];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+    const __half* istd = reinterpret_cast<const __half*>(p.istd.p);
+    auto istd_of = [&](unsigned i) {
+      const unsigned row = blockIdx.x + i * G;
+      return istd[(long long)(row / (unsigned)p.d.J) * p.istd.sB + (long long)(row % (unsigned)p.d.J) * p.istd.sJ];
+    };
+    __half s_next = (unsigned)group < n_i ? istd_of(group) : __float2half(0.f);
+    bool ok = true;
+    unsigned iter = 0;
+    for (unsigned i = group; i < n_i && ok; i += kGroups, ++iter) {
+      const int s = (int)(i % (unsigned)nstages);
+      const uint32_t ph = (i / (unsigned)nstages) & 1u;
+      const unsigned row = blockIdx.x + i * G;
+      const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+      const float sd = __half2float(s_next);
+      if (i + kGroups < n_i) s_next = istd_of(i + kGroups);          // in flight while this token is worked on
+      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_full + 8 * s, ph, 12));
+      if (!ok) break;
+      const uint8_t* st = ring_gen + (size_t)s * stage_bytes;
+      uint4 in[NIN];
+      uint2 mk = make_uint2(0, 0);
+      if (active) {
+#pragma unroll
+        for (int k = 0; k < NIN; ++k) in[k] = *reinterpret_cast<const uint4*>(st + (size_t)k * row_bytes + (size_t)t * 16);
+        mk = *reinterpret_cast<const uint2*>(st + (size_t)NIN * row_bytes + (size_t)t * 8);
+      }
+      __syncwarp();
+      if (lane == 0) ring::mbar_arrive(bar_empty + 8 * s);             // this warp has its pieces in registers
+      float g[8], d8[8];
+      float sg = 0.f, sgd = 0.f;
+      if (active) {
+        float a[8], n8[8];
+        unpack8(in[NIN - 1], d8);
+        if (MODE == 0) {
+          unpack8(in[0], a);
+          unpack8(in[1], n8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            g[e] = a[e] * gm[e];
+            acc[0][e] = fmaf(a[e], n8[e], acc[0][e]);
+            acc[1][e] += a[e];
+          }
+        } else {
+          float r2[8], w8[8], l28[8];
+          unpack8(in[0], n8);
+          unpack8(in[1], r2);
+          unpack8(in[2], w8);
+          unpack8(in[3], l28);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            a[e] = r2[e] + w8[e];
+            g[e] = a[e] * gm[e];
+            acc[0][e] = fmaf(a[e], n8[e], acc[0][e]);
+            acc[1][e] += a[e];
+            acc[2][e] += l28[e];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          sg += g[e];
+          sgd = fmaf(g[e], d8[e], sgd);
+        }
+      }
+      sg = warp_sum(sg);
+      sgd = warp_sum(sgd);
+      float* rg = red + ((group * 2 + (iter & 1)) * 4) * 2;
+      if (lane == 0) {
+        rg[warp_in_group * 2] = sg;
+        rg[warp_in_group * 2 + 1] = sgd;
+      }
+      group_barrier(group);
+      sg = rg[0] + rg[2] + rg[4] + rg[6];
+      sgd = rg[1] + rg[3] + rg[5] + rg[7];
+      if (active) {
+        const float c1 = sg * sd * invn, c2 = sgd * sd * sd * sd * invn;
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(g[e], sd, -c1) - d8[e] * c2;
+        const uint4 dres = pack8(o);
+        const uint4 dl = mask_apply(dres, mk);
+        if (p.dln.p) store8h_raw(p.dln.p, b * p.dln.sB + j * p.dln.sJ, 1, 1, f, F, pack8(g));
+        store8h_raw(p.dresid.p, b * p.dresid.sB + j * p.dresid.sJ, 1, 1, f, F, dres);
+        store8h_raw(p.dlin.p, b * p.dlin.sB + j * p.dlin.sJ, 1, 1, f, F, dl);
+        if (MODE == 1) {
+          float dv[8];
+          unpack8(dl, dv);  // the fp16 values just stored: the bias gradient sums exactly them
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[3][e] += dv[e];
+        }
+      }
+    }
+    // the four row groups' accumulators, to be added in group order below
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) colred[(group * NQ + q) * kMaxF + f + e] = acc[q][e];
+  }
+  __syncthreads();
+  for (int i = tid; i < NQ * kMaxF; i += kRingThreads) {
+    const int q = i / kMaxF, ff = i % kMaxF;
+    float v = 0.f;
+#pragma unroll
+    for (int gq = 0; gq < kGroups; ++gq) v += colred[(gq * NQ + q) * kMaxF + ff];
+    p.partial[((long long)q * gridDim.x + blockIdx.x) * kMaxF + ff] = v;
+  }
+}
+
 // out[q][f] = sum over the P partial rows in a fixed order: 16 thread groups take every 16th row each (loads
 // issued eight at a time, then added in row order) and are combined through shared memory in group order.
 constexpr int kFinishParts = 16;
@@ -231,6 +435,148 @@ colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, vo
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Forward: bias + dropout + residual + LayerNorm out of the same kind of ring.  Warps 0-15 consume (token i of the
+// CTA goes to warp i % 16 and stage i % NS), warp 16 produces.  A stage holds IN and RESID (2F bytes each) and,
+// when the mask is an input, the mask row (F bytes).  NV = 128-bit pieces per lane and row (F <= 256 * NV).
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kFwdWarps = 16;
+constexpr int kFwdThreads = (kFwdWarps + 1) * 32;
+
+struct BdrlnParams {
+  Dims3 d;
+  View3 in, resid, mask, lin, diff, ln, out;
+  View2 istd;
+  const void *bias, *gamma, *beta;
+  Rng rng;
+};
+
+template <int NV>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t ring_s = ring::smem_u32(smem);
+  const uint32_t bars = ring_s + (uint32_t)nstages * (uint32_t)stage_bytes;   // full[NS], empty[NS]
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * nstages;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int F = p.d.F;
+  const unsigned R = (unsigned)p.d.B * (unsigned)p.d.J;
+  const unsigned G = gridDim.x;
+  const unsigned n_i = blockIdx.x < R ? (R - blockIdx.x + G - 1) / G : 0;
+  const uint32_t row_bytes = 2u * (uint32_t)F;
+  const bool mask_in = !p.rng.philox;
+
+  if (tid == 0) {
+    for (int s = 0; s < nstages; ++s) {
+      ring::mbar_init(bar_full + 8 * s, 1);
+      ring::mbar_init(bar_empty + 8 * s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  grid_dependency_sync();
+
+  if (warp == kFwdWarps) {
+    bool ok = true;
+    for (unsigned i = 0; i < n_i && ok; ++i) {
+      const int s = (int)(i % (unsigned)nstages);
+      const uint32_t ph = (i / (unsigned)nstages) & 1u;
+      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 13));
+      if (!ok) break;
+      if (lane == 0) {
+        const unsigned row = blockIdx.x + i * G;
+        const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
+        ring::mbar_expect_tx(full, 2 * row_bytes + (mask_in ? (uint32_t)F : 0u));
+        ring::bulk_load(dst, reinterpret_cast<const __half*>(p.in.p) + b * p.in.sB + j * p.in.sJ, row_bytes, full);
+        ring::bulk_load(dst + row_bytes, reinterpret_cast<const __half*>(p.resid.p) + b * p.resid.sB + j * p.resid.sJ,
+                        row_bytes, full);
+        if (mask_in)
+          ring::bulk_load(dst + 2 * row_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + b * p.mask.sB + j * p.mask.sJ,
+                          (uint32_t)F, full);
+      }
+      __syncwarp();
+    }
+    return;
+  }
+  const float invF = 1.f / (float)F;
+  bool ok = true;
+  for (unsigned i = warp; i < n_i && ok; i += kFwdWarps) {
+    const int s = (int)(i % (unsigned)nstages);
+    const uint32_t ph = (i / (unsigned)nstages) & 1u;
+    const unsigned row = blockIdx.x + i * G;
+    const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+    ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_full + 8 * s, ph, 14));
+    if (!ok) break;
+    const uint8_t* st = smem + (size_t)s * stage_bytes;
+    float r[NV][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int piece = lane + kWarp * k;
+      const int f = piece * 8;
+      if (f < F) {
+        uint2 mk;
+        if (mask_in) {
+          mk = *reinterpret_cast<const uint2*>(st + 2 * (size_t)row_bytes + (size_t)piece * 8);
+        } else {
+          uint32_t mm[8];
+          philox_keep8(p.rng, ((unsigned long long)row * F + f) >> 3, mm);
+          mk = mask_pack(mm);
+          store8m_raw(p.mask.p, b * p.mask.sB + j * p.mask.sJ, 1, 1, f, F, mk);
+        }
+        float x[8], bb[8], rs[8];
+        unpack8(*reinterpret_cast<const uint4*>(st + (size_t)piece * 16), x);
+        unpack8(load8h_raw(p.bias, 0, 1, 1, f, F), bb);
+        unpack8(*reinterpret_cast<const uint4*>(st + row_bytes + (size_t)piece * 16), rs);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] += bb[e];
+        if (p.lin.p) store8h_raw(p.lin.p, b * p.lin.sB + j * p.lin.sJ, 1, 1, f, F, pack8(x));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          r[k][e] = (mask_keep(mk, e) ? x[e] : 0.f) + rs[e];
+          sum += r[k][e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[k][e] = 0.f;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ring::mbar_arrive(bar_empty + 8 * s);     // the row has been read: the stage may be refilled
+    const float mean = warp_sum(sum) * invF;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int f = (lane + kWarp * k) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        r[k][e] = (f < F) ? r[k][e] - mean : 0.f;
+        sq = fmaf(r[k][e], r[k][e], sq);
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * invF + kLnEps);
+    if (lane == 0) reinterpret_cast<__half*>(p.istd.p)[b * p.istd.sB + j * p.istd.sJ] = __float2half_rn(rstd);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int f = (lane + kWarp * k) * 8;
+      if (f >= F) continue;
+      float gm[8], bt[8], n[8], o[8];
+      unpack8(load8h_raw(p.gamma, 0, 1, 1, f, F), gm);
+      unpack8(load8h_raw(p.beta, 0, 1, 1, f, F), bt);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        n[e] = r[k][e] * rstd;
+        o[e] = fmaf(n[e], gm[e], bt[e]);
+      }
+      store8h_raw(p.diff.p, b * p.diff.sB + j * p.diff.sJ, 1, 1, f, F, pack8(r[k]));
+      store8h_raw(p.ln.p, b * p.ln.sB + j * p.ln.sJ, 1, 1, f, F, pack8(n));
+      store8h_raw(p.out.p, b * p.out.sB + j * p.out.sJ, 1, 1, f, F, pack8(o));
+    }
+  }
+}
+
 bool eligible(const Dims3& d, std::initializer_list<const View3*> views, const void* gamma) {
   if (d.F > kMaxF || d.F % 8 != 0) return false;
   if ((long long)d.B * d.J > 0x3fffffffLL) return false;
@@ -240,19 +586,45 @@ bool eligible(const Dims3& d, std::initializer_list<const View3*> views, const v
   return true;
 }
 
+bool ring_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SUBSTATION_B200_LN_RING");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// bulk copies move whole rows: 16-byte multiples from 16-byte-aligned addresses (fp16 views that qualify for
+// 128-bit access already are; a byte mask needs the stricter alignment checked here)
+bool mask_rows_bulk_ok(const Dims3& d, const View3& m) {
+  return d.F % 16 == 0 && (reinterpret_cast<uintptr_t>(m.p) & 15u) == 0 && (d.B <= 1 || m.sB % 16 == 0) &&
+         (d.J <= 1 || m.sJ % 16 == 0);
+}
+
 template <int MODE>
 int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4]) {
   constexpr int NQ = MODE == 0 ? 2 : 4;
   LnBwdParams p = p0;
   const long long R = (long long)p.d.B * p.d.J;
   const int sms = device_facts().sms;
-  const int P = (int)std::max<long long>(1, std::min<long long>(sms, (R + kGroups * kRows - 1) / (kGroups * kRows)));
+  const bool use_ring = ring_enabled() && mask_rows_bulk_ok(p.d, p.mask);
+  const int per_cta = use_ring ? kGroups : kGroups * kRows;
+  const int P = (int)std::max<long long>(1, std::min<long long>(sms, (R + per_cta - 1) / per_cta));
   if ((size_t)NQ * P * kMaxF * sizeof(float) > kWsBytes - kWsCounterBytes)
     return fail(SB_ERR_UNSUPPORTED, "fused LayerNorm backward: workspace too small");
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
-  const size_t smem = (size_t)kGroups * NQ * kMaxF * sizeof(float);
-  SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_kernel<MODE>), (int)smem));
-  SB_LAUNCH_OK(launch_k(lnbwd_kernel<MODE>, P, kThreads, smem, s, p));
+  if (use_ring) {
+    using C = RingCfg<MODE>;
+    const int stage_bytes = (C::NIN * 2 * p.d.F + p.d.F + 127) / 128 * 128;
+    const int nstages = std::min(32, C::kBudget / stage_bytes);
+    const size_t smem = (size_t)C::kColredBytes + (size_t)nstages * stage_bytes + 256 + 16 * (size_t)nstages + 64;
+    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_ring_kernel<MODE>), (int)smem));
+    SB_LAUNCH_OK(launch_k(lnbwd_ring_kernel<MODE>, P, kRingThreads, smem, s, p, nstages, stage_bytes));
+  } else {
+    const size_t smem = (size_t)kGroups * NQ * kMaxF * sizeof(float);
+    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_kernel<MODE>), (int)smem));
+    SB_LAUNCH_OK(launch_k(lnbwd_kernel<MODE>, P, kThreads, smem, s, p));
+  }
   SB_CUDA_OK(cudaGetLastError());
   dim3 grid((p.d.F + 63) / 64, NQ);
   SB_LAUNCH_OK(launch_k(colsum_finish_kernel, grid, 64 * kFinishParts, 0, s, p.partial, P, p.d.F, NQ, outs[0], outs[1], outs[2], outs[3]));
@@ -287,6 +659,53 @@ int launch_lnbwd_b(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gam
   p.dln = dln1; p.dresid = dresid1; p.dlin = datt; p.gamma = gamma1;
   void* outs[4] = {dgamma1, dbeta1, dlinb2, dbo};
   return launch<1>(s, ws, p, outs);
+}
+
+// Ring-fed forward LayerNorm; SB_ERR_UNSUPPORTED (nothing launched) when the views do not qualify, the caller then
+// runs the register-resident kernel.
+int launch_bdrln_ring(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma,
+                      const void* beta, View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng) {
+  const long long R = (long long)d.B * d.J;
+  if (!ring_enabled() || d.F % 8 != 0 || d.F > 2048 || R > 0x3fffffffLL || R < 1)
+    return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm: shape not covered");
+  for (const View3* v : {&in, &resid, &mask, &lin, &diff, &ln, &out})
+    if (!v->vec) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm needs feature-innermost views");
+  for (const void* q : {bias, gamma, beta})
+    if (reinterpret_cast<uintptr_t>(q) & 15u) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm needs aligned parameter vectors");
+  if (!rng.philox && !mask_rows_bulk_ok(d, mask)) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm: mask rows are not 16-byte multiples");
+  BdrlnParams p{};
+  p.d = d; p.in = in; p.resid = resid; p.mask = mask; p.lin = lin; p.diff = diff; p.ln = ln; p.out = out;
+  p.istd = istd; p.bias = bias; p.gamma = gamma; p.beta = beta; p.rng = rng;
+  const int stage_bytes = (5 * d.F + 127) / 128 * 128;
+  const int nstages = std::min(32, (232448 - 1024) / stage_bytes);
+  const size_t smem = (size_t)nstages * stage_bytes + 16 * (size_t)nstages + 64;
+  const int P = (int)std::max<long long>(1, std::min<long long>(device_facts().sms, (R + kFwdWarps - 1) / kFwdWarps));
+#define SB_BDRLN_RING(NV)                                                                                    \
+  do {                                                                                                       \
+    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(bdrln_ring_kernel<NV>), (int)smem));        \
+    SB_LAUNCH_OK(launch_k(bdrln_ring_kernel<NV>, P, kFwdThreads, smem, s, p, nstages, stage_bytes));         \
+  } while (0)
+  if (d.F <= 256) SB_BDRLN_RING(1);
+  else if (d.F <= 512) SB_BDRLN_RING(2);
+  else if (d.F <= 1024) SB_BDRLN_RING(4);
+  else SB_BDRLN_RING(8);
+#undef SB_BDRLN_RING
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
+int ring_device_error(cudaStream_t s, int* code) {
+  int v = 0;
+  SB_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, ring::g_ring_error, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+  SB_CUDA_OK(cudaStreamSynchronize(s));
+  *code = v;
+  return SB_OK;
+}
+int ring_device_error_reset(cudaStream_t s) {
+  const int zero = 0;
+  SB_CUDA_OK(cudaStreamSynchronize(s));
+  SB_CUDA_OK(cudaMemcpyToSymbol(ring::g_ring_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice));
+  return SB_OK;
 }
 
 }  // namespace sb

@@ -1022,6 +1022,11 @@ int launch_bdrln(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resi
   if (d.F > 2048) return fail(SB_ERR_UNSUPPORTED, "LayerNorm rows longer than 2048 are not supported");
   if (R > 0x3fffffffLL) return fail(SB_ERR_UNSUPPORTED, "more than 2^30 tokens are not supported");
   const int pvec = param_vec({bias, gamma, beta}, d.F);
+  if (pvec && all_vec(in, resid, mask, lin, diff, ln, out)) {
+    // rows stream through a shared-memory ring when they can be moved with bulk copies
+    const int st = launch_bdrln_ring(s, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out, rng);
+    if (st != SB_ERR_UNSUPPORTED) return st;
+  }
   if (pvec && all_vec(in, resid, mask, lin, diff, ln, out))
     SB_ROW_LAUNCH(bdrln_kernel, true, d.F, d, in, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out, rng, pvec);
   else

@@ -47,6 +47,14 @@ int launch_lnbwd_b(cudaStream_t s, void* ws, Dims3 d, View3 ln1, const void* gam
                    View3 dlin2, View2 istd, View3 diff, View3 mask, View3 dln1, View3 dresid1, View3 datt,
                    void* dgamma1, void* dbeta1, void* dlinb2, void* dbo);
 
+// bias + dropout + residual + LayerNorm with the input rows staged through a shared-memory ring (bulk copies);
+// SB_ERR_UNSUPPORTED, nothing launched, unless every view is feature-innermost with 16-byte-multiple rows.
+int launch_bdrln_ring(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma,
+                      const void* beta, View3 mask, View3 lin, View3 diff, View2 istd, View3 ln, View3 out, Rng rng);
+// Error flag of the ring kernels (a bounded wait ran out: codes 11-14), per device.
+int ring_device_error(cudaStream_t s, int* code);
+int ring_device_error_reset(cudaStream_t s);
+
 // Fused attention scores.  qq/kk/dgamma/vv are [P,H,B,rows] projections passed as View4 whose
 // (sH,sB,sJ,sK) fields hold the (P,H,B,row) strides; d = {H,B,J,K}.  SB_ERR_UNSUPPORTED when
 // the shapes or layouts do not qualify.

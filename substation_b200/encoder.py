@@ -154,10 +154,10 @@ class Encoder(torch.nn.Module):
                 bplan, btotal = outer._bwd_plan
                 gplan, gtotal = outer._grad_plan
                 barena = torch.empty(max(btotal, 1), dtype=torch.uint8, device=DY.device)
-                garena = torch.empty(max(gtotal, 1), dtype=torch.uint8, device=DY.device)
+                garena = outer._next_grad_arena(gtotal, DY.device)
                 outer._backward_ptrs(DY, outer._plan_ptrs(gplan, garena, {}), outer._plan_ptrs(bplan, barena, {}), weights,
                                      outer._plan_ptrs(outer._fwd_plan[0], arena, ctx.masks), X, DX)
-                g16 = garena.view(outer.torch_dtype)
+                g16 = garena[:max(gtotal, 2)].view(outer.torch_dtype)
                 outer._grad_bucket = g16
                 grads = tuple(torch.as_strided(g16, shape, strides, off) for shape, strides, off in outer._grad_views)
                 if outer.enable_debug:
@@ -444,6 +444,32 @@ class Encoder(torch.nn.Module):
                 ev.record()
             handle = ctypes.c_void_p(ev.cuda_event)
         _lib.check(_lib.load().sb_encoder_set_ffn_grads_event(self._handle, handle))
+
+    def set_grad_arenas(self, arenas):
+        """Caller-held storage for the parameter gradients of the autograd path: a list of contiguous uint8 CUDA
+        tensors of at least ``arena_bytes('grads')`` bytes, used in turn by successive backward passes (``None``:
+        back to a fresh allocation per pass).  A data-parallel caller that reduces ``grad_bucket()`` every step
+        then hands the collective the same few buffers again and again; with two arenas the reduction of one
+        step may still run while the next backward fills the other.  The caller must not let a backward pass
+        start on an arena whose reduction is still in flight."""
+        if arenas is not None:
+            need = self.arena_bytes('grads')
+            for a in arenas:
+                if a.dtype != torch.uint8 or not a.is_contiguous() or a.numel() < need or not a.is_cuda:
+                    raise ValueError(f'gradient arenas must be contiguous uint8 CUDA tensors of at least {need} bytes')
+            arenas = list(arenas)
+        self._grad_arenas = arenas
+        self._grad_arena_turn = 0
+
+    def _next_grad_arena(self, total, device):
+        arenas = self.__dict__.get('_grad_arenas')
+        if not arenas:
+            return torch.empty(max(total, 1), dtype=torch.uint8, device=device)
+        a = arenas[self._grad_arena_turn % len(arenas)]
+        self._grad_arena_turn += 1
+        if a.device != device:
+            raise ValueError('gradient arenas must live on the device the pass runs on')
+        return a
 
     def grad_bucket(self):
         """The flat fp16 tensor that holds all 12 parameter gradients of the most recent autograd backward

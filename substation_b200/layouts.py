@@ -125,3 +125,30 @@ def selected_layouts(tag='b8_l512'):
         d[k] = [tuple(x) for x in d[k]]
     d['input'], d['output'] = tuple(d['input']), tuple(d['output'])
     return d
+
+
+def read_json(path):
+    """A configuration stored as JSON (the pickle's dict with tuples written as lists)."""
+    import json
+    with open(path) as f:
+        d = json.load(f)
+    for k in ('params', 'forward_interm', 'backward_interm'):
+        d[k] = [tuple(x) for x in d[k]]
+    d['input'], d['output'] = tuple(d['input']), tuple(d['output'])
+    return d
+
+
+def named_layouts(which):
+    """A configuration by name: a dict (returned as is), 'uniform', 'b200_<tag>' (what the layout search chose for
+    these kernels, see ``selected_layouts``), or the path of a ``.json`` / ``.pickle`` file."""
+    if isinstance(which, dict):
+        return which
+    if which == 'uniform':
+        return uniform_layouts()
+    if which.startswith('b200_'):
+        return selected_layouts(which[5:])
+    if which.endswith('.pickle') or which.endswith('.pkl'):
+        return load_layouts(which)
+    if which.endswith('.json'):
+        return read_json(which)
+    raise LayoutError(f"unknown layout configuration '{which}'")

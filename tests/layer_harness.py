@@ -8,7 +8,6 @@ Tolerance: rel-L2 <= 1e-2 (fp16 storage / fp32 accumulation against float64),
 masks bit-exact.
 """
 
-import json
 import os
 
 import numpy as np
@@ -21,19 +20,11 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden')
 
 
 def get_layouts(which):
-    if isinstance(which, dict):
-        return which
-    if which == 'uniform':
-        return L.uniform_layouts()
-    if which.startswith('b200_'):
-        return L.selected_layouts(which[5:])
-    path = which if which.endswith('.json') else os.path.join(GOLDEN_DIR, f'layouts_{which}.json')
-    with open(path) as f:
-        d = json.load(f)
-    for k in ('params', 'forward_interm', 'backward_interm'):
-        d[k] = [tuple(x) for x in d[k]]
-    d['input'], d['output'] = tuple(d['input']), tuple(d['output'])
-    return d
+    """Package-held configurations by name; 'b8_l512' / 'b96_l128' are the reference's two shipped pickles,
+    kept as JSON fixtures beside the golden vectors."""
+    if isinstance(which, str) and which in ('b8_l512', 'b96_l128'):
+        which = os.path.join(GOLDEN_DIR, f'layouts_{which}.json')
+    return L.named_layouts(which)
 
 
 def to_dev(a, logical, layout, device, dtype=torch.float16):
