@@ -202,9 +202,13 @@ lnbwd_kernel(LnBwdParams p) {
 
 // ---------------------------------------------------------------------------------------------------------
 // The same pass with its inputs staged through a shared-memory ring.  Thread layout: warps 0-15 = four row groups
-// (as above), warp 16 = producer.  Token sequence of a CTA: rows blockIdx.x + i * gridDim.x, i = 0, 1, ...; token
-// i goes to group i % 4 and to ring stage i % NS.  A stage holds the token's input rows back to back:
-//   mode A: DY, LN, DIFF (2F bytes each), mask (F bytes);   mode B: LN1, DRESID2, DLIN1_LINW1, DLIN2, DIFF, mask.
+// (as above), warp 16 = producer.  The tensors must be dense token-major ([tokens][F] with nothing between rows),
+// so that kGroups consecutive tokens are one contiguous piece of every tensor: a ring stage holds such a block of
+// four tokens, fetched with ONE bulk copy per tensor (8 KB at 1024 features; the copy engine keeps few requests
+// in flight, so requests of one row each leave most of the bandwidth unused).  Block sequence of a CTA: blocks
+// blockIdx.x + i * gridDim.x; block i lives in stage i % NS and group g works on its g-th token.  Stage layout:
+//   mode A: DY, LN, DIFF (4 x 2F bytes each), mask (4 x F bytes);   mode B: LN1, DRESID2, DLIN1_LINW1, DLIN2, DIFF, mask.
+// The per-feature accumulators go through the ring's memory once the ring is drained.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kRingThreads = kThreads + 32;
 
@@ -213,9 +217,15 @@ struct RingCfg {
   static constexpr int NQ = MODE == 0 ? 2 : 4;
   static constexpr int NIN = MODE == 0 ? 3 : 5;                 // fp16 input rows per token (incl. DIFF)
   static constexpr int kColredBytes = kGroups * NQ * kMaxF * 4;
-  static constexpr int kMaxStage = NIN * 2 * kMaxF + kMaxF;     // bytes at 1024 features
-  static constexpr int kBudget = 232448 - kColredBytes - 2048;  // ring bytes available
+  static constexpr int kBudget = 232448 - 1024;                 // ring bytes available (barriers and sums follow)
 };
+
+// one lane polls, the warp follows (fewer pollers on the barrier unit than one per thread)
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int code, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = ring::mbar_wait(bar, parity, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(kRingThreads, 1)
@@ -224,11 +234,11 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
   constexpr int NQ = C::NQ;
   constexpr int NIN = C::NIN;
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: colred [kGroups][NQ][1024] floats | ring | red | barriers
-  float* colred = reinterpret_cast<float*>(smem);
-  uint8_t* ring_gen = smem + C::kColredBytes;
+  // layout: ring (reused for the column sums [kGroups][NQ][1024] at the end) | red | barriers
+  uint8_t* ring_gen = smem;
   const uint32_t ring_s = ring::smem_u32(ring_gen);
-  float* red = reinterpret_cast<float*>(ring_gen + (size_t)nstages * stage_bytes);   // [kGroups][2][4][2]
+  const int ring_bytes = max(nstages * stage_bytes, C::kColredBytes);
+  float* red = reinterpret_cast<float*>(ring_gen + ring_bytes);                       // [kGroups][2][4][2]
   const uint32_t bars = ring::smem_u32(red) + kGroups * 2 * 4 * 2 * 4;                 // full[NS], empty[NS]
   const uint32_t bar_full = bars, bar_empty = bars + 8 * nstages;
 
@@ -236,14 +246,16 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
   const int warp = tid >> 5, lane = tid & 31;
   const int F = p.d.F;
   const unsigned R = (unsigned)p.d.B * (unsigned)p.d.J;
+  const unsigned nblocks = (R + kGroups - 1) / kGroups;
   const unsigned G = gridDim.x;
-  const unsigned n_i = blockIdx.x < R ? (R - blockIdx.x + G - 1) / G : 0;   // tokens of this CTA
+  const unsigned n_i = blockIdx.x < nblocks ? (nblocks - blockIdx.x + G - 1) / G : 0;   // blocks of this CTA
   const uint32_t row_bytes = 2u * (uint32_t)F;
+  const uint32_t tensor_bytes = kGroups * row_bytes;       // one tensor's part of a stage
 
   if (tid == 0) {
     for (int s = 0; s < nstages; ++s) {
       ring::mbar_init(bar_full + 8 * s, 1);
-      ring::mbar_init(bar_empty + 8 * s, kGroupThreads / 32);
+      ring::mbar_init(bar_empty + 8 * s, kThreads / 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -251,44 +263,42 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
   grid_dependency_sync();
 
   if (warp == kThreads / 32) {
-    // ---------------- producer: one elected lane issues the copies of token after token ----------------
-    bool ok = true;
-    for (unsigned i = 0; i < n_i && ok; ++i) {
-      const int s = (int)(i % (unsigned)nstages);
-      const uint32_t ph = (i / (unsigned)nstages) & 1u;
-      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 11));
-      if (!ok) break;
-      if (lane == 0) {
-        const unsigned row = blockIdx.x + i * G;
-        const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+    // ---------------- producer: one elected lane issues the copies of block after block ----------------
+    if (lane == 0) {
+      for (unsigned i = 0; i < n_i; ++i) {
+        const int s = (int)(i % (unsigned)nstages);
+        const uint32_t ph = (i / (unsigned)nstages) & 1u;
+        if (!ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 11)) break;
+        const unsigned long long row0 = (unsigned long long)(blockIdx.x + i * G) * kGroups;
+        const uint32_t nrows = (uint32_t)min((unsigned long long)kGroups, R - row0);
         const uint32_t full = bar_full + 8 * s;
         const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
-        ring::mbar_expect_tx(full, NIN * row_bytes + (uint32_t)F);
-        auto row_of = [&](const View3& v) { return reinterpret_cast<const __half*>(v.p) + b * v.sB + j * v.sJ; };
+        const uint32_t nb = nrows * row_bytes;
+        ring::mbar_expect_tx(full, NIN * nb + nrows * (uint32_t)F);
+        auto rows_of = [&](const View3& v) { return reinterpret_cast<const __half*>(v.p) + row0 * F; };
         if (MODE == 0) {
-          ring::bulk_load(dst, row_of(p.y), row_bytes, full);
-          ring::bulk_load(dst + row_bytes, row_of(p.n), row_bytes, full);
+          ring::bulk_load(dst, rows_of(p.y), nb, full);
+          ring::bulk_load(dst + tensor_bytes, rows_of(p.n), nb, full);
         } else {
-          ring::bulk_load(dst, row_of(p.n), row_bytes, full);
-          ring::bulk_load(dst + row_bytes, row_of(p.r2), row_bytes, full);
-          ring::bulk_load(dst + 2 * row_bytes, row_of(p.w), row_bytes, full);
-          ring::bulk_load(dst + 3 * row_bytes, row_of(p.l2), row_bytes, full);
+          ring::bulk_load(dst, rows_of(p.n), nb, full);
+          ring::bulk_load(dst + tensor_bytes, rows_of(p.r2), nb, full);
+          ring::bulk_load(dst + 2 * tensor_bytes, rows_of(p.w), nb, full);
+          ring::bulk_load(dst + 3 * tensor_bytes, rows_of(p.l2), nb, full);
         }
-        ring::bulk_load(dst + (NIN - 1) * row_bytes, row_of(p.diff), row_bytes, full);
-        ring::bulk_load(dst + NIN * row_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + b * p.mask.sB + j * p.mask.sJ,
-                        (uint32_t)F, full);
+        ring::bulk_load(dst + (NIN - 1) * tensor_bytes, rows_of(p.diff), nb, full);
+        ring::bulk_load(dst + NIN * tensor_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + row0 * F, nrows * (uint32_t)F, full);
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
-    // ---------------- consumers: group g takes tokens g, g + 4, ... of this CTA ----------------
+    // ---------------- consumers: group g takes the g-th token of every block ----------------
     const int group = tid / kGroupThreads, t = tid % kGroupThreads;
     const int warp_in_group = t >> 5;
     const int f = t * 8;
-    const bool active = f < F;
+    const bool has_f = f < F;
     const float invn = 1.f / (float)F;
     float gm[8];
-    if (active) unpack8(load8h_raw(p.gamma, 0, 1, 1, f, F), gm);
+    if (has_f) unpack8(load8h_raw(p.gamma, 0, 1, 1, f, F), gm);
     float acc[NQ][8];
 #pragma unroll
     for (int q = 0; q < NQ; ++q)
@@ -296,28 +306,27 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
       for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
     const __half* istd = reinterpret_cast<const __half*>(p.istd.p);
     auto istd_of = [&](unsigned i) {
-      const unsigned row = blockIdx.x + i * G;
+      const unsigned long long row = (unsigned long long)(blockIdx.x + i * G) * kGroups + group;
+      if (row >= R) return __float2half(0.f);
       return istd[(long long)(row / (unsigned)p.d.J) * p.istd.sB + (long long)(row % (unsigned)p.d.J) * p.istd.sJ];
     };
-    __half s_next = (unsigned)group < n_i ? istd_of(group) : __float2half(0.f);
-    bool ok = true;
-    unsigned iter = 0;
-    for (unsigned i = group; i < n_i && ok; i += kGroups, ++iter) {
+    __half s_next = n_i > 0 ? istd_of(0) : __float2half(0.f);
+    for (unsigned i = 0; i < n_i; ++i) {
       const int s = (int)(i % (unsigned)nstages);
       const uint32_t ph = (i / (unsigned)nstages) & 1u;
-      const unsigned row = blockIdx.x + i * G;
-      const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+      const unsigned long long row = (unsigned long long)(blockIdx.x + i * G) * kGroups + group;
+      const bool active = has_f && row < R;
       const float sd = __half2float(s_next);
-      if (i + kGroups < n_i) s_next = istd_of(i + kGroups);          // in flight while this token is worked on
-      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_full + 8 * s, ph, 12));
-      if (!ok) break;
+      if (i + 1 < n_i) s_next = istd_of(i + 1);          // in flight while this token is worked on
+      if (!warp_wait(bar_full + 8 * s, ph, 12, lane)) break;
       const uint8_t* st = ring_gen + (size_t)s * stage_bytes;
       uint4 in[NIN];
       uint2 mk = make_uint2(0, 0);
       if (active) {
 #pragma unroll
-        for (int k = 0; k < NIN; ++k) in[k] = *reinterpret_cast<const uint4*>(st + (size_t)k * row_bytes + (size_t)t * 16);
-        mk = *reinterpret_cast<const uint2*>(st + (size_t)NIN * row_bytes + (size_t)t * 8);
+        for (int k = 0; k < NIN; ++k)
+          in[k] = *reinterpret_cast<const uint4*>(st + (size_t)k * tensor_bytes + (size_t)group * row_bytes + (size_t)t * 16);
+        mk = *reinterpret_cast<const uint2*>(st + (size_t)NIN * tensor_bytes + (size_t)group * F + (size_t)t * 8);
       }
       __syncwarp();
       if (lane == 0) ring::mbar_arrive(bar_empty + 8 * s);             // this warp has its pieces in registers
@@ -358,7 +367,7 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
       }
       sg = warp_sum(sg);
       sgd = warp_sum(sgd);
-      float* rg = red + ((group * 2 + (iter & 1)) * 4) * 2;
+      float* rg = red + ((group * 2 + (i & 1)) * 4) * 2;
       if (lane == 0) {
         rg[warp_in_group * 2] = sg;
         rg[warp_in_group * 2 + 1] = sgd;
@@ -373,9 +382,10 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
         for (int e = 0; e < 8; ++e) o[e] = fmaf(g[e], sd, -c1) - d8[e] * c2;
         const uint4 dres = pack8(o);
         const uint4 dl = mask_apply(dres, mk);
-        if (p.dln.p) store8h_raw(p.dln.p, b * p.dln.sB + j * p.dln.sJ, 1, 1, f, F, pack8(g));
-        store8h_raw(p.dresid.p, b * p.dresid.sB + j * p.dresid.sJ, 1, 1, f, F, dres);
-        store8h_raw(p.dlin.p, b * p.dlin.sB + j * p.dlin.sJ, 1, 1, f, F, dl);
+        const long long off = (long long)row * F;
+        if (p.dln.p) store8h_raw(p.dln.p, off, 1, 1, f, F, pack8(g));
+        store8h_raw(p.dresid.p, off, 1, 1, f, F, dres);
+        store8h_raw(p.dlin.p, off, 1, 1, f, F, dl);
         if (MODE == 1) {
           float dv[8];
           unpack8(dl, dv);  // the fp16 values just stored: the bias gradient sums exactly them
@@ -384,13 +394,18 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
         }
       }
     }
-    // the four row groups' accumulators, to be added in group order below
+    __syncwarp();
+    // every consumer is done with the ring before its memory takes the accumulators (a named barrier over the
+    // 512 consumer threads; the producer warp is not part of it)
+    asm volatile("bar.sync 8, %0;" ::"n"(kThreads) : "memory");
+    float* colred = reinterpret_cast<float*>(smem);
 #pragma unroll
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
       for (int e = 0; e < 8; ++e) colred[(group * NQ + q) * kMaxF + f + e] = acc[q][e];
   }
   __syncthreads();
+  const float* colred = reinterpret_cast<const float*>(smem);
   for (int i = tid; i < NQ * kMaxF; i += kRingThreads) {
     const int q = i / kMaxF, ff = i % kMaxF;
     float v = 0.f;
@@ -436,12 +451,15 @@ colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, vo
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Forward: bias + dropout + residual + LayerNorm out of the same kind of ring.  Warps 0-15 consume (token i of the
-// CTA goes to warp i % 16 and stage i % NS), warp 16 produces.  A stage holds IN and RESID (2F bytes each) and,
-// when the mask is an input, the mask row (F bytes).  NV = 128-bit pieces per lane and row (F <= 256 * NV).
+// Forward: bias + dropout + residual + LayerNorm out of the same kind of ring (dense token-major tensors, blocks of
+// four consecutive tokens, one bulk copy per tensor and block).  Warps 0-15 consume, one warp per token: block i of
+// the CTA lives in stage i % NS and belongs to the warp set i % 4 (warps 4 * set .. 4 * set + 3, one token each).
+// Warp 16 produces.  A stage holds IN and RESID (4 x 2F bytes each) and, when the mask is an input, the mask rows
+// (4 x F bytes).  NV = 128-bit pieces per lane and row (F <= 256 * NV).
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kFwdWarps = 16;
 constexpr int kFwdThreads = (kFwdWarps + 1) * 32;
+constexpr int kFwdRows = 4;                      // tokens per stage
 
 struct BdrlnParams {
   Dims3 d;
@@ -461,15 +479,17 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int F = p.d.F;
   const unsigned R = (unsigned)p.d.B * (unsigned)p.d.J;
+  const unsigned nblocks = (R + kFwdRows - 1) / kFwdRows;
   const unsigned G = gridDim.x;
-  const unsigned n_i = blockIdx.x < R ? (R - blockIdx.x + G - 1) / G : 0;
+  const unsigned n_i = blockIdx.x < nblocks ? (nblocks - blockIdx.x + G - 1) / G : 0;
   const uint32_t row_bytes = 2u * (uint32_t)F;
+  const uint32_t tensor_bytes = kFwdRows * row_bytes;
   const bool mask_in = !p.rng.philox;
 
   if (tid == 0) {
     for (int s = 0; s < nstages; ++s) {
       ring::mbar_init(bar_full + 8 * s, 1);
-      ring::mbar_init(bar_empty + 8 * s, 1);
+      ring::mbar_init(bar_empty + 8 * s, kFwdRows);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -477,62 +497,61 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
   grid_dependency_sync();
 
   if (warp == kFwdWarps) {
-    bool ok = true;
-    for (unsigned i = 0; i < n_i && ok; ++i) {
-      const int s = (int)(i % (unsigned)nstages);
-      const uint32_t ph = (i / (unsigned)nstages) & 1u;
-      ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 13));
-      if (!ok) break;
-      if (lane == 0) {
-        const unsigned row = blockIdx.x + i * G;
-        const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
+    if (lane == 0) {
+      for (unsigned i = 0; i < n_i; ++i) {
+        const int s = (int)(i % (unsigned)nstages);
+        const uint32_t ph = (i / (unsigned)nstages) & 1u;
+        if (!ring::mbar_wait(bar_empty + 8 * s, ph ^ 1u, 13)) break;
+        const unsigned long long row0 = (unsigned long long)(blockIdx.x + i * G) * kFwdRows;
+        const uint32_t nrows = (uint32_t)min((unsigned long long)kFwdRows, R - row0);
         const uint32_t full = bar_full + 8 * s;
         const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
-        ring::mbar_expect_tx(full, 2 * row_bytes + (mask_in ? (uint32_t)F : 0u));
-        ring::bulk_load(dst, reinterpret_cast<const __half*>(p.in.p) + b * p.in.sB + j * p.in.sJ, row_bytes, full);
-        ring::bulk_load(dst + row_bytes, reinterpret_cast<const __half*>(p.resid.p) + b * p.resid.sB + j * p.resid.sJ,
-                        row_bytes, full);
+        const uint32_t nb = nrows * row_bytes;
+        ring::mbar_expect_tx(full, 2 * nb + (mask_in ? nrows * (uint32_t)F : 0u));
+        ring::bulk_load(dst, reinterpret_cast<const __half*>(p.in.p) + row0 * F, nb, full);
+        ring::bulk_load(dst + tensor_bytes, reinterpret_cast<const __half*>(p.resid.p) + row0 * F, nb, full);
         if (mask_in)
-          ring::bulk_load(dst + 2 * row_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + b * p.mask.sB + j * p.mask.sJ,
-                          (uint32_t)F, full);
+          ring::bulk_load(dst + 2 * tensor_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + row0 * F, nrows * (uint32_t)F, full);
       }
-      __syncwarp();
     }
+    __syncwarp();
     return;
   }
   const float invF = 1.f / (float)F;
-  bool ok = true;
-  for (unsigned i = warp; i < n_i && ok; i += kFwdWarps) {
+  const int set = warp >> 2, rsel = warp & 3;          // which blocks, which token of a block
+  for (unsigned i = set; i < n_i; i += kFwdWarps / kFwdRows) {
     const int s = (int)(i % (unsigned)nstages);
     const uint32_t ph = (i / (unsigned)nstages) & 1u;
-    const unsigned row = blockIdx.x + i * G;
-    const long long b = row / (unsigned)p.d.J, j = row % (unsigned)p.d.J;
-    ok = __all_sync(0xffffffffu, ring::mbar_wait(bar_full + 8 * s, ph, 14));
-    if (!ok) break;
-    const uint8_t* st = smem + (size_t)s * stage_bytes;
+    const unsigned long long row = (unsigned long long)(blockIdx.x + i * G) * kFwdRows + rsel;
+    if (!warp_wait(bar_full + 8 * s, ph, 14, lane)) break;
+    const bool valid = row < R;
+    const long long b = (long long)(row / (unsigned)p.d.J), j = (long long)(row % (unsigned)p.d.J);
+    const long long off = (long long)row * F;
+    const uint8_t* st = smem + (size_t)s * stage_bytes + (size_t)rsel * row_bytes;          // this token's IN row
+    const uint8_t* st_m = smem + (size_t)s * stage_bytes + 2 * (size_t)tensor_bytes + (size_t)rsel * F;
     float r[NV][8];
     float sum = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int piece = lane + kWarp * k;
       const int f = piece * 8;
-      if (f < F) {
+      if (valid && f < F) {
         uint2 mk;
         if (mask_in) {
-          mk = *reinterpret_cast<const uint2*>(st + 2 * (size_t)row_bytes + (size_t)piece * 8);
+          mk = *reinterpret_cast<const uint2*>(st_m + (size_t)piece * 8);
         } else {
           uint32_t mm[8];
           philox_keep8(p.rng, ((unsigned long long)row * F + f) >> 3, mm);
           mk = mask_pack(mm);
-          store8m_raw(p.mask.p, b * p.mask.sB + j * p.mask.sJ, 1, 1, f, F, mk);
+          store8m_raw(p.mask.p, off, 1, 1, f, F, mk);
         }
         float x[8], bb[8], rs[8];
         unpack8(*reinterpret_cast<const uint4*>(st + (size_t)piece * 16), x);
         unpack8(load8h_raw(p.bias, 0, 1, 1, f, F), bb);
-        unpack8(*reinterpret_cast<const uint4*>(st + row_bytes + (size_t)piece * 16), rs);
+        unpack8(*reinterpret_cast<const uint4*>(st + tensor_bytes + (size_t)piece * 16), rs);
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] += bb[e];
-        if (p.lin.p) store8h_raw(p.lin.p, b * p.lin.sB + j * p.lin.sJ, 1, 1, f, F, pack8(x));
+        if (p.lin.p) store8h_raw(p.lin.p, off, 1, 1, f, F, pack8(x));
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           r[k][e] = (mask_keep(mk, e) ? x[e] : 0.f) + rs[e];
@@ -545,6 +564,7 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
     }
     __syncwarp();
     if (lane == 0) ring::mbar_arrive(bar_empty + 8 * s);     // the row has been read: the stage may be refilled
+    if (!valid) continue;
     const float mean = warp_sum(sum) * invF;
     float sq = 0.f;
 #pragma unroll
@@ -570,9 +590,9 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
         n[e] = r[k][e] * rstd;
         o[e] = fmaf(n[e], gm[e], bt[e]);
       }
-      store8h_raw(p.diff.p, b * p.diff.sB + j * p.diff.sJ, 1, 1, f, F, pack8(r[k]));
-      store8h_raw(p.ln.p, b * p.ln.sB + j * p.ln.sJ, 1, 1, f, F, pack8(n));
-      store8h_raw(p.out.p, b * p.out.sB + j * p.out.sJ, 1, 1, f, F, pack8(o));
+      store8h_raw(p.diff.p, off, 1, 1, f, F, pack8(r[k]));
+      store8h_raw(p.ln.p, off, 1, 1, f, F, pack8(n));
+      store8h_raw(p.out.p, off, 1, 1, f, F, pack8(o));
     }
   }
 }
@@ -594,11 +614,18 @@ bool ring_enabled() {
   return on;
 }
 
-// bulk copies move whole rows: 16-byte multiples from 16-byte-aligned addresses (fp16 views that qualify for
-// 128-bit access already are; a byte mask needs the stricter alignment checked here)
-bool mask_rows_bulk_ok(const Dims3& d, const View3& m) {
-  return d.F % 16 == 0 && (reinterpret_cast<uintptr_t>(m.p) & 15u) == 0 && (d.B <= 1 || m.sB % 16 == 0) &&
-         (d.J <= 1 || m.sJ % 16 == 0);
+// The ring kernels fetch blocks of consecutive tokens with one bulk copy per tensor: every tensor must be dense
+// token-major ([tokens][F], unit feature stride, nothing between rows) and rows must be 16-byte multiples from a
+// 16-byte-aligned base (for the byte mask that means F % 16 == 0).
+bool dense_rows(const Dims3& d, const View3& v) {
+  return v.sF == 1 && (d.J <= 1 || v.sJ == d.F) && (d.B <= 1 || v.sB == (long long)d.J * d.F) &&
+         (reinterpret_cast<uintptr_t>(v.p) & 15u) == 0;
+}
+bool ring_ok(const Dims3& d, std::initializer_list<const View3*> views, bool with_mask) {
+  if (!ring_enabled() || d.F % 8 != 0 || (with_mask && d.F % 16 != 0)) return false;
+  for (const View3* v : views)
+    if (v->p && !dense_rows(d, *v)) return false;
+  return true;
 }
 
 template <int MODE>
@@ -607,7 +634,8 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   LnBwdParams p = p0;
   const long long R = (long long)p.d.B * p.d.J;
   const int sms = device_facts().sms;
-  const bool use_ring = ring_enabled() && mask_rows_bulk_ok(p.d, p.mask);
+  const bool use_ring = MODE == 0 ? ring_ok(p.d, {&p.y, &p.n, &p.diff, &p.mask, &p.dln, &p.dresid, &p.dlin}, true)
+                                  : ring_ok(p.d, {&p.n, &p.r2, &p.w, &p.l2, &p.diff, &p.mask, &p.dln, &p.dresid, &p.dlin}, true);
   const int per_cta = use_ring ? kGroups : kGroups * kRows;
   const int P = (int)std::max<long long>(1, std::min<long long>(sms, (R + per_cta - 1) / per_cta));
   if ((size_t)NQ * P * kMaxF * sizeof(float) > kWsBytes - kWsCounterBytes)
@@ -615,10 +643,11 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
   if (use_ring) {
     using C = RingCfg<MODE>;
-    const int stage_bytes = (C::NIN * 2 * p.d.F + p.d.F + 127) / 128 * 128;
-    const int nstages = std::min(32, C::kBudget / stage_bytes);
-    const size_t smem = (size_t)C::kColredBytes + (size_t)nstages * stage_bytes + 256 + 16 * (size_t)nstages + 64;
-    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_ring_kernel<MODE>), (int)smem));
+    const int stage_bytes = (kGroups * (C::NIN * 2 * p.d.F + p.d.F) + 127) / 128 * 128;
+    const int nstages = std::max(2, std::min(16, C::kBudget / stage_bytes));
+    const size_t smem = (size_t)std::max(nstages * stage_bytes, C::kColredBytes) + 256 + 16 * (size_t)nstages + 64;
+    // the attribute is set once to the most any launch may ask for (launches differ in their ring size)
+    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(lnbwd_ring_kernel<MODE>), 232448));
     SB_LAUNCH_OK(launch_k(lnbwd_ring_kernel<MODE>, P, kRingThreads, smem, s, p, nstages, stage_bytes));
   } else {
     const size_t smem = (size_t)kGroups * NQ * kMaxF * sizeof(float);
@@ -668,21 +697,20 @@ int launch_bdrln_ring(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3
   const long long R = (long long)d.B * d.J;
   if (!ring_enabled() || d.F % 8 != 0 || d.F > 2048 || R > 0x3fffffffLL || R < 1)
     return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm: shape not covered");
-  for (const View3* v : {&in, &resid, &mask, &lin, &diff, &ln, &out})
-    if (!v->vec) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm needs feature-innermost views");
+  if (!ring_ok(d, {&in, &resid, &lin, &diff, &ln, &out}, false) || !dense_rows(d, mask) || (!rng.philox && d.F % 16 != 0))
+    return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm needs dense token-major tensors with 16-byte-multiple rows");
   for (const void* q : {bias, gamma, beta})
     if (reinterpret_cast<uintptr_t>(q) & 15u) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm needs aligned parameter vectors");
-  if (!rng.philox && !mask_rows_bulk_ok(d, mask)) return fail(SB_ERR_UNSUPPORTED, "ring LayerNorm: mask rows are not 16-byte multiples");
   BdrlnParams p{};
   p.d = d; p.in = in; p.resid = resid; p.mask = mask; p.lin = lin; p.diff = diff; p.ln = ln; p.out = out;
   p.istd = istd; p.bias = bias; p.gamma = gamma; p.beta = beta; p.rng = rng;
-  const int stage_bytes = (5 * d.F + 127) / 128 * 128;
-  const int nstages = std::min(32, (232448 - 1024) / stage_bytes);
+  const int stage_bytes = (kFwdRows * 5 * d.F + 127) / 128 * 128;
+  const int nstages = std::max(2, std::min(16, (232448 - 1024) / stage_bytes));
   const size_t smem = (size_t)nstages * stage_bytes + 16 * (size_t)nstages + 64;
-  const int P = (int)std::max<long long>(1, std::min<long long>(device_facts().sms, (R + kFwdWarps - 1) / kFwdWarps));
+  const int P = (int)std::max<long long>(1, std::min<long long>(device_facts().sms, (R + kFwdRows - 1) / kFwdRows));
 #define SB_BDRLN_RING(NV)                                                                                    \
   do {                                                                                                       \
-    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(bdrln_ring_kernel<NV>), (int)smem));        \
+    SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(bdrln_ring_kernel<NV>), 232448));           \
     SB_LAUNCH_OK(launch_k(bdrln_ring_kernel<NV>, P, kFwdThreads, smem, s, p, nstages, stage_bytes));         \
   } while (0)
   if (d.F <= 256) SB_BDRLN_RING(1);
