@@ -357,7 +357,9 @@ int sb_encoder_backward(sb_encoder* enc, void* stream, const void* dy, void* con
                         const void* x, void* dx);
 /* Per-operator device time of the most recent forward+backward, measured with
  * CUDA events when timing was switched on; writes up to max (name, ms) pairs
- * and returns the count.  Stands in for the NVTX ranges of pytorch_module/encoder.cu:32-53. */
+ * and returns the count.  While timing is on every operator is also an NVTX range
+ * of the same name on the calling thread (the ranges of pytorch_module/encoder.cu:32-53),
+ * and passes are launched plainly rather than replayed as graphs. */
 int sb_encoder_set_timing(sb_encoder* enc, int enabled);
 int sb_encoder_get_timing(sb_encoder* enc, int max, const char** names, float* ms);
 /* Number of operators the most recent forward / backward launched. */

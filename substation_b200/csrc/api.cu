@@ -10,6 +10,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "ops.h"
 
 namespace sb {
@@ -706,6 +708,7 @@ struct sb_encoder {
   // forget the operator just marked (a fused attempt declined before launching anything)
   void unmark() {
     --launches;
+    if (timing) close_range();
     if (timing && !marks.empty()) {
       event_pool.push_back(marks.back().second);
       marks.pop_back();
@@ -713,11 +716,29 @@ struct sb_encoder {
   }
   // rename the operator just marked (a fused attempt fell back to its first separate operator)
   void relabel(const char* name) {
-    if (timing && !marks.empty()) marks.back().first = name;
+    if (timing && !marks.empty()) {
+      marks.back().first = name;
+      close_range();
+      nvtxRangePushA(name);
+      range_open = true;
+    }
+  }
+  // With timing on, every operator is also an NVTX range named like the reference's (pytorch_module/encoder.cu:32-53):
+  // a range opens where the operator is enqueued and closes where the next one opens (or the pass ends), so a
+  // timeline shows the same names the event table reports.  Without a profiler attached the calls do nothing.
+  bool range_open = false;
+  void close_range() {
+    if (range_open) nvtxRangePop();
+    range_open = false;
   }
   void mark(cudaStream_t s, const char* name) {
     ++launches;
     if (!timing) return;
+    close_range();
+    if (name[0]) {
+      nvtxRangePushA(name);
+      range_open = true;
+    }
     cudaEvent_t e;
     if (event_pool.empty()) cudaEventCreate(&e);
     else { e = event_pool.back(); event_pool.pop_back(); }

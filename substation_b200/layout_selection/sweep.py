@@ -1,189 +1,194 @@
-"""Time every operator of the layer under candidate layouts, on the GPU, through
-the C ABI, and write the tables the layout optimizer reads.
+"""Measure the layer's operator groups under candidate layouts, on the GPU, and keep the tables the layout
+optimizer reads.
 
-    python -m substation_b200.layout_selection.sweep --out DIR [--batch 8 --seq 512]
+    python -m substation_b200.layout_selection.sweep --out DIR [--batch 8 --seq 512] [--around CONFIG.json]
+                                                     [--rounds 3] [--tag b8_l512]
 
-Output formats are the reference's:
-  * fused kernels: ``<kernel>-combined.csv`` with one line per configuration,
-    ``NAME = layout ... time = t s`` (pytorch_module/benchmark.py:1440-1444,
-    read back by config_selection/load_data.py:11-41);
-  * contractions: ``<op>-result.csv`` with columns A,B,C,M,N,K,batch,Time,
-    Implementation (subset of config_selection/parse_tc_results.py:15-18,38-62;
-    the cuBLAS-specific columns trans_a/lda/... have no meaning here and are
-    left out).
-Search-space pruning (the reference prunes too, pytorch_module/benchmark.py:365-373):
-contractions take the full product of their operands' candidate layouts; a fused
-kernel is timed with all of its tensors in one common family of layouts and with
-one tensor at a time deviating from it.
+What is timed is what runs: for every candidate configuration an ``Encoder`` is built with those layouts and
+one forward+backward step is run a few times with the library's per-operator CUDA events on, inside the real
+operator sequence (inputs as the previous operator left them in the caches, fused operators where the layouts
+allow them, their separate replacements where they decline).  A group's time is the sum over the operators the
+layer reported for it.  The reference instead benchmarks every kernel and every cuBLAS call in isolation
+(pytorch_module/benchmark.py:1328-1359, tc_profiling/einsum_perms.py:397-470); its table formats are kept:
+  * groups that are one contraction: ``<group>-result.csv`` with columns A,B,C,M,N,K,batch,Time,Implementation
+    (subset of config_selection/parse_tc_results.py:15-18,38-62; cuBLAS-only columns have no meaning here);
+  * all other groups: ``<group>-combined.csv``, one line per configuration,
+    ``NAME = layout ... time = t s`` (pytorch_module/benchmark.py:1440-1444, config_selection/load_data.py:11-41).
+Candidates: the configuration given with ``--around`` (default: every tensor in its logical order) and every
+configuration that differs from it in ONE tensor (or one group of tied tensors), over every permutation of that
+tensor's dims.  Tables are appended to, never rewritten: a configuration whose groups are all present is skipped,
+so an interrupted sweep resumes and a later sweep around another configuration adds to the same files
+(the reference: ``--resume``, pytorch_module/benchmark.py:1388-1399).  With ``--rounds N`` the optimizer runs after
+each sweep and the next sweep goes around what it chose, until nothing changes.
 """
 
 import argparse
-import itertools
+import json
 import os
-
-import torch
+import statistics
 
 from .. import layouts as L
-from .. import ops
-from .spec import DOMAINS, OPS
+from .spec import DOMAINS, OPS, default_table, op_key, tie_groups
 
-H, DEV = 16, 'cuda'
-
-
-def _alloc(name, layout, sizes, kind='h'):
-    shape = L.shape_of(layout, sizes)
-    if name in L.MASKS:
-        t = (torch.rand(shape, device=DEV) >= 0.1).to(torch.uint8)
-    else:
-        t = (torch.randn(shape, device=DEV) * 0.5).half()
-    logical = L.LOGICAL[name]
-    return t.permute([layout.index(c) for c in logical])        # logical-order view
+H = 16
 
 
-def _vec(n):
-    return torch.ones(n, device=DEV).half()
+def table_path(out_dir, op):
+    return os.path.join(out_dir, f"{op['name']}-{'result' if op['kind'] == 'gemm' else 'combined'}.csv")
 
 
-def fused_call(name, T, sizes):
-    """Closure running fused operator ``name`` on logical views ``T`` (dict by tensor name)."""
-    I, U = sizes['I'], sizes['U']
-    vi, vu = _vec(I), _vec(U)
-    if name == 'aib':
-        return lambda: ops.attention_input_biases(T['WKKWQQWVV'], T['BKQV'], T['KKQQVV'])
-    if name == 'softmax':
-        return lambda: ops.softmax_dropout(T['BETA'], T['ALPHA'], T['ATTN_DROP_MASK'], T['ATTN_DROP'], p=0.1)
-    if name == 'bdrln1':
-        return lambda: ops.bias_dropout_residual_layernorm(T['ATT'], vi, T['X'], vi, vi, T['DROP1MASK'], T['ATT'],
-                                                           T['LN1DIFF'], T['LN1STD'], T['LN1'], T['SB1'], p=0.1)
-    if name == 'bdrln2':
-        return lambda: ops.bias_dropout_residual_layernorm(T['DROP2_LINW2'], vi, T['SB1'], vi, vi, T['DROP3MASK'],
-                                                           T['LIN2'], T['LN2DIFF'], T['LN2STD'], T['LN2'], T['SB2'], p=0.1)
-    if name == 'bad':
-        return lambda: ops.bias_activation_dropout(T['SB1_LINW1'], vu, T['DROP2MASK'], T['LIN1'], T['DROP2'], p=0.1)
-    if name == 'bsb':
-        dg, db = _vec(I), _vec(I)
-        return lambda: ops.backward_scale_bias(T['SB2'], T['LN2'], vi, T['DLN2'], dg, db)
-    if name in ('blnrd1', 'blnrd2'):
-        k = ('DLN2', 'LN2STD', 'LN2DIFF', 'DROP3MASK', 'DRESID2', 'DLIN2') if name == 'blnrd1' else \
-            ('DLN1', 'LN1STD', 'LN1DIFF', 'DROP1MASK', 'DRESID1', 'DATT')
-        return lambda: ops.backward_layernorm_residual_dropout(*(T[n] for n in k))
-    if name == 'bdrlb':
-        db = _vec(U)
-        return lambda: ops.backward_dropout_activation_bias(T['DDROP2'], T['DROP2MASK'], T['LIN1'], T['DLIN1'], db)
-    if name == 'ebsb':
-        a, b, c = _vec(I), _vec(I), _vec(I)
-        return lambda: ops.extended_backward_scale_bias(T['LN1'], vi, T['DRESID2'], T['DLIN1_LINW1'], T['DLIN2'],
-                                                        T['DLN1'], a, b, c)
-    if name == 'baob':
-        d = _vec(I)
-        return lambda: ops.backward_attn_out_bias(T['DATT'], d)
-    if name == 'bs':
-        return lambda: ops.backward_softmax(T['ALPHA'], T['ATTN_DROP_MASK'], T['DATTN_DROP'], T['DBETA'])
-    if name == 'baib':
-        return lambda: ops.backward_attention_input_biases(T['DKKQQVV'], T['BKQV'])
-    if name == 'bei':
-        return lambda: ops.backward_encoder_input(T['DXATT'], T['DRESID1'], T['X'])
-    raise KeyError(name)
+def load_keys(out_dir):
+    """{group name: set of layout keys already measured}."""
+    from .optimize import load_tables
+    return {name: set(t) for name, t in load_tables(out_dir).items()}
 
 
-def time_graph(fn, reps=8, replays=3):
-    """Median device time (s) of one call: `reps` calls captured in a CUDA graph (so host
-    launch cost is out of the picture), replayed a few times."""
-    fn()
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    s = torch.cuda.Stream()
-    with torch.cuda.stream(s):
-        fn()
-        with torch.cuda.graph(g, stream=s):
-            for _ in range(reps):
-                fn()
-    torch.cuda.synchronize()
-    times = []
-    for _ in range(replays):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        g.replay()
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b) / reps / 1e3)
-    return sorted(times)[len(times) // 2]
+def _extents(dims, sizes):
+    n = 1
+    for c in dims:
+        n *= sizes[c]
+    return n
 
 
-def fused_configs(op):
-    """Common-family configurations plus single-tensor deviations."""
-    names = op['tensors']
-    doms = [DOMAINS[n] for n in names]
-    width = max(len(d) for d in doms)
-    seen = []
-    for fam in range(width):
-        base = tuple(d[min(fam, len(d) - 1)] for d in doms)
-        if base not in seen:
-            seen.append(base)
-        if fam == 0:
-            for i, d in enumerate(doms):
-                for alt in d[1:]:
-                    cfg = base[:i] + (alt,) + base[i + 1:]
-                    if cfg not in seen:
-                        seen.append(cfg)
-    return seen
-
-
-def sweep(out_dir, batch, seq, heads=H, embed=1024, only=None, verbose=True):
+def append_rows(out_dir, table, times, sizes, have):
+    """Append one line per group whose key is new; ``times``: {group name: seconds}."""
     os.makedirs(out_dir, exist_ok=True)
-    sizes = L.sizes_map(batch, seq, heads, embed)
     for op in OPS:
-        if only and op['name'] not in only:
+        key = op_key(op, table)
+        if key in have.setdefault(op['name'], set()) or op['name'] not in times:
             continue
-        names = op['tensors']
-        if op['kind'] == 'gemm':
-            path = os.path.join(out_dir, f"{op['name']}-result.csv")
-            rows = ['A,B,C,M,N,K,batch,Time,Implementation']
-            for lay in itertools.product(*(DOMAINS[n] for n in names)):
-                if names[0] == names[1] and lay[0] != lay[1]:
-                    continue                      # the same tensor read twice
-                dims = [v(l) for v, l in zip(op['views'], lay)]
-                try:
-                    t = [(torch.randn(L.shape_of(d, sizes), device=DEV) * 0.1).half() for d in dims]
-                    spec = f'{dims[0].lower()},{dims[1].lower()}->{dims[2].lower()}'
-                    impl = ops.einsum(spec, t[0], t[1], t[2])
-                    sec = time_graph(lambda: ops.einsum(spec, t[0], t[1], t[2]))
-                except ops.SubstationError:
-                    continue                      # not a GEMM under these layouts (index groups do not collapse)
-                ks = [c for c in dims[0] if c in dims[1] and c not in dims[2]]
-                bs = [c for c in dims[0] if c in dims[1] and c in dims[2]]
-                ms = [c for c in dims[0] if c not in dims[1]]
-                ns = [c for c in dims[1] if c not in dims[0]]
-                prod = lambda cs: int(torch.tensor([sizes[c] for c in cs]).prod()) if cs else 1
-                rows.append(f'{lay[0]},{lay[1]},{lay[2]},{prod(ms)},{prod(ns)},{prod(ks)},{prod(bs)},{sec:.9f},{impl}')
-                del t
-            with open(path, 'w') as f:
-                f.write('\n'.join(rows) + '\n')
-        else:
-            path = os.path.join(out_dir, f"{op['name']}-combined.csv")
-            lines = []
-            for lay in fused_configs(op):
-                T = {}
-                for n, l in zip(names, lay):
-                    T[n] = _alloc(n, l, sizes)
-                sec = time_graph(fused_call(op['name'], T, sizes))
-                lines.append(' '.join(f'{n} = {l}' for n, l in zip(names, lay)) + f' time = {sec:.9f} s')
-                del T
-            with open(path, 'w') as f:
-                f.write('\n'.join(lines) + '\n')
-        torch.cuda.empty_cache()
-        if verbose:
-            print(op['name'], 'done', flush=True)
+        path = table_path(out_dir, op)
+        new = not os.path.exists(path)
+        with open(path, 'a') as f:
+            if op['kind'] == 'gemm':
+                if new:
+                    f.write('A,B,C,M,N,K,batch,Time,Implementation\n')
+                a, b, c = (L.LOGICAL[t] for t in op['tensors'])
+                batch = [x for x in a if x in b and x in c]
+                ks = [x for x in a if x in b and x not in c]
+                ms = [x for x in a if x not in b]
+                ns = [x for x in b if x not in a]
+                f.write(f'{key[0]},{key[1]},{key[2]},{_extents(ms, sizes)},{_extents(ns, sizes)},{_extents(ks, sizes)},'
+                        f'{_extents(batch, sizes)},{times[op["name"]]:.9f},layer\n')
+            else:
+                f.write(' '.join(f'{n} = {l}' for n, l in zip(op['tensors'], key)) + f' time = {times[op["name"]]:.9f} s\n')
+        have[op['name']].add(key)
+
+
+def candidates(base):
+    """The base table and every single-tensor (tie-group) deviation from it."""
+    yield dict(base)
+    for group in tie_groups():
+        for lay in DOMAINS[group[0]]:
+            if lay == base[group[0]]:
+                continue
+            t = dict(base)
+            for n in group:
+                t[n] = lay
+            yield t
+
+
+def measure_layer(table, batch, seq, heads=H, embed=1024, reps=5, warmup=2, device='cuda'):
+    """{group name: seconds} for one configuration: median over ``reps`` steps of the per-operator event times."""
+    import torch
+    from ..encoder import Encoder
+    from .optimize import to_configuration
+    from .spec import GROUP_OF
+    cfg = to_configuration(table)
+    dev = torch.device(device)
+    enc = Encoder('', batch, seq, heads, embed, cfg, torch.float16, 0.1, 0.1, 0.1, 0.1, profiling=True,
+                  mask_mode='explicit').to(dev)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for prm in enc.params:
+            prm.copy_((torch.randn(prm.shape, device=dev, generator=gen) * 0.02).half())
+    shape_x = L.shape_of(table['X'], enc.sizes)
+    X = torch.randn(shape_x, device=dev, generator=gen).half()
+    DY = torch.randn(shape_x, device=dev, generator=gen).half()
+    masks = {n: (torch.rand(L.shape_of(table[n], enc.sizes), device=dev, generator=gen) >= 0.1).to(torch.uint8)
+             for n in L.MASKS}
+    enc.set_masks(masks)
+    weights = [p.detach() for p in enc.params]
+    fwd = enc._alloc(enc._fwd_plan, dev)
+    fwd.update(masks)
+    bwd = enc._alloc(enc._bwd_plan, dev)
+    grads = enc._alloc(enc._grad_plan, dev)
+    Y, DX = torch.empty_like(X), torch.empty_like(X)
+    per = {}
+    for i in range(warmup + reps):
+        enc.forward_raw(X, weights, fwd, Y)
+        enc.backward_raw(DY, grads, bwd, weights, fwd, X, DX)
+        torch.cuda.synchronize(dev)
+        times = enc.op_times()
+        if i >= warmup:
+            step = {}
+            for name, ms in times:
+                g = GROUP_OF.get(name)
+                if g is not None:
+                    step[g] = step.get(g, 0.0) + ms * 1e-3
+            for g, s in step.items():
+                per.setdefault(g, []).append(s)
+    enc._destroy()
+    del enc, fwd, bwd, grads
+    torch.cuda.empty_cache()
+    return {g: statistics.median(v) for g, v in per.items()}
+
+
+def sweep(out_dir, batch, seq, heads=H, embed=1024, around=None, measure=None, limit=None, verbose=True):
+    """Measure every candidate around ``around`` whose groups are not all in the tables yet; returns how many
+    configurations were run."""
+    base = dict(around or default_table())
+    sizes = L.sizes_map(batch, seq, heads, embed)
+    have = load_keys(out_dir) if os.path.isdir(out_dir) else {}
+    measure = measure or (lambda t: measure_layer(t, batch, seq, heads, embed))
+    done = 0
+    for table in candidates(base):
+        if all(op_key(op, table) in have.get(op['name'], ()) for op in OPS):
+            continue
+        if limit is not None and done >= limit:
+            break
+        try:
+            times = measure(table)
+        except Exception as exc:        # a layout the layer refuses outright: nothing to record
+            if verbose:
+                print('skipped', {n: table[n] for n in table if table[n] != base[n]}, '-', exc, flush=True)
+            continue
+        append_rows(out_dir, table, times, sizes, have)
+        done += 1
+        if verbose and done % 25 == 0:
+            print(done, 'configurations measured', flush=True)
+    return done
 
 
 def main():
+    from . import optimize as opt
     ap = argparse.ArgumentParser()
-    ap.add_argument('--out', required=True)
+    ap.add_argument('--out', required=True, help='directory of the tables (appended to)')
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
-    ap.add_argument('--only', nargs='*')
+    ap.add_argument('--around', help='configuration (.json) to sweep around; default: all tensors in logical order')
+    ap.add_argument('--rounds', type=int, default=1, help='sweep, optimize, sweep around the result, ...')
+    ap.add_argument('--tag', help='write the chosen configuration and report into the package as results_<tag>/')
+    ap.add_argument('--limit', type=int, help='at most this many configurations per sweep')
     a = ap.parse_args()
-    sweep(a.out, a.batch, a.seq, only=a.only)
+    table = L.validate(L.read_json(a.around)) if a.around else default_table()
+    cfg = report = None
+    for r in range(max(1, a.rounds)):
+        n = sweep(a.out, a.batch, a.seq, around=table, limit=a.limit)
+        cfg, report = opt.optimize(a.out, start=table)
+        new = L.validate(cfg)
+        print(f'round {r}: {n} configurations measured; sum of groups {1e6 * report["start_cost_s"]:.1f} us -> '
+              f'{1e6 * report["chosen_cost_s"]:.1f} us; changed: {report["changed"]}', flush=True)
+        if new == table:
+            break
+        table = new
+    if a.tag:
+        d = os.path.join(os.path.dirname(os.path.abspath(__file__)), f'results_{a.tag}')
+        os.makedirs(d, exist_ok=True)
+        with open(os.path.join(d, f'layouts_b200_{a.tag}.json'), 'w') as f:
+            json.dump(cfg, f, indent=1)
+        with open(os.path.join(d, 'report.json'), 'w') as f:
+            json.dump(report, f, indent=1)
 
 
 if __name__ == '__main__':
