@@ -109,26 +109,40 @@ SIGNATURES = {
     'sb_encoder_set_dead_stores': (c_int, [c_void_p, c_int]),
 }
 
-_lib = None
+_libs = {}
 
 
-def lib_path():
-    return _build.LIB_PATH
+def lib_path(dtype='fp16'):
+    return _build.LIB_PATHS[dtype]
 
 
-def load():
-    """Load the library, (re)building it first whenever nvcc is at hand and the sources changed since the
-    last build.  Without nvcc a library whose stamp does not match the sources is refused: results from a
-    stale binary would describe code that no longer exists."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    path = lib_path()
+def dtype_key(dtype):
+    """'fp16' / 'bf16' for a torch dtype (or one of those strings); anything else has no library."""
+    if isinstance(dtype, str):
+        key = dtype
+    else:
+        import torch
+        key = {torch.float16: 'fp16', torch.bfloat16: 'bf16'}.get(dtype)
+    if key not in _build.LIB_PATHS:
+        raise NotImplementedError(
+            f'substation_b200 stores activations and parameters in float16 or bfloat16 (fp32 accumulation); '
+            f'{dtype} is not implemented')
+    return key
+
+
+def load(dtype='fp16'):
+    """Load the library of one storage type, (re)building first whenever nvcc is at hand and the sources changed
+    since the last build.  Without nvcc a library whose stamp does not match the sources is refused: results from
+    a stale binary would describe code that no longer exists."""
+    key = dtype_key(dtype)
+    if key in _libs:
+        return _libs[key]
+    path = lib_path(key)
     if _build.have_nvcc():
-        _build.build()                # returns at once when the digest of the sources matches the stamp
+        _build.build(dtypes=(key,))   # returns at once when the digest of the sources matches the stamp
     elif not os.path.exists(path):
         raise RuntimeError(f'{path} is missing and nvcc is not available to build it')
-    elif not _build.stamp_matches():
+    elif not _build.stamp_matches(key):
         raise RuntimeError(f'{path} was built from other sources than the ones in csrc/ (stamp mismatch) '
                            'and nvcc is not available to rebuild it')
     lib = ctypes.CDLL(path)
@@ -136,13 +150,18 @@ def load():
         fn = getattr(lib, name)      # AttributeError if a declared symbol is missing
         fn.restype = restype
         fn.argtypes = argtypes
-    _lib = lib
+    if key.encode() not in lib.sb_version():
+        raise RuntimeError(f'{path} reports {lib.sb_version()!r}, expected a {key} build')
+    _libs[key] = lib
     return lib
 
 
-def check(status):
+_last_lib = [None]     # library of the most recent failing call (for the error text)
+
+
+def check(status, lib=None):
     if status != SB_OK:
-        raise SubstationError(status, load().sb_last_error().decode())
+        raise SubstationError(status, (lib or load()).sb_last_error().decode())
 
 
 def tensor_desc(t, order=None):

@@ -17,6 +17,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, 'csrc')
 LIB_NAME = 'libsubstation_b200.so'
 LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
+#: one library per storage type (fp16 is the default one; the bf16 build is the same sources with -DSB_BF16)
+LIB_PATHS = {'fp16': LIB_PATH, 'bf16': os.path.join(PKG_DIR, 'libsubstation_b200_bf16.so')}
+DTYPE_FLAGS = {'fp16': [], 'bf16': ['-DSB_BF16']}
 SOURCES = ('api.cu', 'fused_ops.cu', 'fused_lnbwd.cu', 'gemm.cu')
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
               '-Xcompiler', '-fPIC', '-shared', '--threads', '0']
@@ -37,10 +40,11 @@ def have_nvcc():
         return False
 
 
-def stamp_matches():
+def stamp_matches(dtype='fp16'):
     """True when the library on disk was built from the current sources."""
-    stamp = LIB_PATH + '.md5'
-    if not (os.path.exists(LIB_PATH) and os.path.exists(stamp)):
+    path = LIB_PATHS[dtype]
+    stamp = path + '.md5'
+    if not (os.path.exists(path) and os.path.exists(stamp)):
         return False
     with open(stamp) as f:
         return f.read().strip() == source_digest()
@@ -59,25 +63,28 @@ def source_digest():
     return h.hexdigest()
 
 
-def build(force=False, verbose=False, extra_flags=()):
-    """Compile the library if the sources changed since the last build."""
-    stamp = LIB_PATH + '.md5'
+def build(force=False, verbose=False, extra_flags=(), dtypes=('fp16', 'bf16')):
+    """Compile the libraries whose sources changed since their last build (both storage types by default, the two
+    nvcc runs side by side).  Returns the path of the fp16 library."""
     digest = source_digest()
-    if not force and os.path.exists(LIB_PATH) and os.path.exists(stamp):
-        with open(stamp) as f:
-            if f.read().strip() == digest:
-                return LIB_PATH
     srcs = [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra_flags, '-o', LIB_PATH, *srcs]
-    if verbose:
-        print(' '.join(cmd))
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError('nvcc failed:\n' + res.stdout + res.stderr)
-    if verbose and (res.stdout or res.stderr):
-        print(res.stdout + res.stderr)
-    with open(stamp, 'w') as f:
-        f.write(digest)
+    running = []
+    for dt in dtypes:
+        path = LIB_PATHS[dt]
+        if not force and stamp_matches(dt):
+            continue
+        cmd = [_nvcc(), *NVCC_FLAGS, *DTYPE_FLAGS[dt], *extra_flags, '-o', path, *srcs]
+        if verbose:
+            print(' '.join(cmd))
+        running.append((dt, path, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for dt, path, proc in running:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError(f'nvcc failed ({dt}):\n' + out)
+        if verbose and out:
+            print(out)
+        with open(path + '.md5', 'w') as f:
+            f.write(digest)
     return LIB_PATH
 
 

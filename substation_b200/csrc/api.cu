@@ -160,7 +160,7 @@ extern "C" const char* sb_status_string(int status) {
   }
 }
 extern "C" const char* sb_last_error(void) { return g_error.c_str(); }
-extern "C" const char* sb_version(void) { return "0.1 sm_100a"; }
+extern "C" const char* sb_version(void) { return "0.2 sm_100a " SB_DTYPE_NAME; }
 extern "C" size_t sb_workspace_bytes(void) { return kWsBytes; }
 
 // ---------------------------------------------------------------------------
@@ -966,7 +966,7 @@ static int forward_pass(sb_encoder* e, void* stream, const void* x, const void* 
   e->kernel_base = g_kernel_launches;
   const auto& L = e->layout;
   const long long slice = (long long)e->P * e->H * e->B * e->S;  // elements per stacked projection
-  auto q_slice = [&](const char* name, int q) { return (void*)((__half*)T[name] + q * slice); };
+  auto q_slice = [&](const char* name, int q) { return (void*)((sb_half*)T[name] + q * slice); };
   const std::string lKK = L.at("KKQQVV").substr(1);
 
   // F1: stacked K,Q,V projections
@@ -1114,7 +1114,7 @@ static int backward_pass(sb_encoder* e, void* stream, const void* dy, void* cons
   e->kernel_base = g_kernel_launches;
   const auto& L = e->layout;
   const long long slice = (long long)e->P * e->H * e->B * e->S;
-  auto q_slice = [&](void* base, int q) { return (void*)((__half*)base + q * slice); };
+  auto q_slice = [&](void* base, int q) { return (void*)((sb_half*)base + q * slice); };
   const std::string lKK = L.at("KKQQVV").substr(1), lDKK = L.at("DKKQQVV").substr(1);
   void* ws = e->workspace;
   auto v = [&](const char* name) { return e->view(T[name], name); };

@@ -259,7 +259,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (lane == 0) {
           const uint32_t sa = operands, sb_ = sa + kABytes;
           const int width = min(256, L - c * 256);
-          const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) | ((uint32_t)(p.b_mn ? 1 : 0) << 16) |
+          const uint32_t idesc = (1u << 4) | SB_IDESC_AB_FMT | ((uint32_t)(p.a_mn ? 1 : 0) << 15) | ((uint32_t)(p.b_mn ? 1 : 0) << 16) |
                                  ((uint32_t)(width >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -554,7 +554,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               float f[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
-                const float2 da_al = __half22float2(*reinterpret_cast<const __half2*>(&r[v * 8 + e]));
+                const float2 da_al = sb_h22f2(*reinterpret_cast<const sb_half2*>(&r[v * 8 + e]));
                 f[e] = da_al.y * (da_al.x - ssum);
               }
               *stage_ptr(b, hh * 4 + v) = pack8(f);

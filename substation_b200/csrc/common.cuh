@@ -3,6 +3,7 @@
 // counter-based dropout generator.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -11,6 +12,46 @@
 #include <string>
 
 #include "../../include/substation_b200.h"
+
+// ---------------------------------------------------------------------------
+// Storage type of activations and parameters.  The library is built once per type (fp16 by default, bf16 with
+// -DSB_BF16): sb_half / sb_half2 and the handful of conversions below are all that differs; every reduction and
+// accumulation is fp32 in both.  The reference selects the type the same way, at compile time
+// (pytorch_module/encoder.py:13-17, `Real`).
+// ---------------------------------------------------------------------------
+#ifdef SB_BF16
+typedef __nv_bfloat16 sb_half;
+typedef __nv_bfloat162 sb_half2;
+#define SB_ONE_BITS 0x3F80u                      /* 1.0 */
+#define SB_TMAP_DTYPE CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+#define SB_IDESC_AB_FMT ((1u << 7) | (1u << 10)) /* tcgen05 instruction descriptor: A and B are bf16 */
+#define SB_DTYPE_NAME "bf16"
+#else
+typedef __half sb_half;
+typedef __half2 sb_half2;
+#define SB_ONE_BITS 0x3C00u
+#define SB_TMAP_DTYPE CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+#define SB_IDESC_AB_FMT 0u
+#define SB_DTYPE_NAME "fp16"
+#endif
+
+#ifdef __CUDACC__
+#ifdef SB_BF16
+__host__ __device__ __forceinline__ float sb_h2f(sb_half h) { return __bfloat162float(h); }
+__host__ __device__ __forceinline__ sb_half sb_f2h(float f) { return __float2bfloat16_rn(f); }
+__device__ __forceinline__ float2 sb_h22f2(sb_half2 h) { return __bfloat1622float2(h); }
+__device__ __forceinline__ sb_half2 sb_f2h2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+__device__ __forceinline__ sb_half2 sb_f2h2_dup(float a) { return __float2bfloat162_rn(a); }
+__device__ __forceinline__ sb_half2 sb_h2h2(sb_half h) { return __bfloat162bfloat162(h); }
+#else
+__host__ __device__ __forceinline__ float sb_h2f(sb_half h) { return __half2float(h); }
+__host__ __device__ __forceinline__ sb_half sb_f2h(float f) { return __float2half_rn(f); }
+__device__ __forceinline__ float2 sb_h22f2(sb_half2 h) { return __half22float2(h); }
+__device__ __forceinline__ sb_half2 sb_f2h2(float a, float b) { return __floats2half2_rn(a, b); }
+__device__ __forceinline__ sb_half2 sb_f2h2_dup(float a) { return __float2half2_rn(a); }
+__device__ __forceinline__ sb_half2 sb_h2h2(sb_half h) { return __half2half2(h); }
+#endif
+#endif
 
 namespace sb {
 
@@ -184,43 +225,43 @@ __device__ __forceinline__ float group_max(float v) {
 
 // ---- 8-element accessors -------------------------------------------------
 __device__ __forceinline__ void unpack8(const uint4& u, float v[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
+  const sb_half2* h = reinterpret_cast<const sb_half2*>(&u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(h[i]);
+    float2 f = sb_h22f2(h[i]);
     v[2 * i] = f.x;
     v[2 * i + 1] = f.y;
   }
 }
 __device__ __forceinline__ uint4 pack8(const float v[8]) {
   uint4 u;
-  __half2* h = reinterpret_cast<__half2*>(&u);
+  sb_half2* h = reinterpret_cast<sb_half2*>(&u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) h[i] = sb_f2h2(v[2 * i], v[2 * i + 1]);
   return u;
 }
 
 // Load eight fp16 values base[(f..f+7)*sF] as float; elements at or beyond F read as `fill`.
 __device__ __forceinline__ void load8h(const void* base, long long off, long long sF, int vec,
                                        int f, int F, float v[8], float fill = 0.f) {
-  const __half* p = reinterpret_cast<const __half*>(base) + off;
+  const sb_half* p = reinterpret_cast<const sb_half*>(base) + off;
   if (vec) {
     uint4 u = *reinterpret_cast<const uint4*>(p + f);
     unpack8(u, v);
   } else {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (f + e < F) ? __half2float(p[(long long)(f + e) * sF]) : fill;
+    for (int e = 0; e < 8; ++e) v[e] = (f + e < F) ? sb_h2f(p[(long long)(f + e) * sF]) : fill;
   }
 }
 __device__ __forceinline__ void store8h(void* base, long long off, long long sF, int vec, int f,
                                         int F, const float v[8]) {
-  __half* p = reinterpret_cast<__half*>(base) + off;
+  sb_half* p = reinterpret_cast<sb_half*>(base) + off;
   if (vec) {
     *reinterpret_cast<uint4*>(p + f) = pack8(v);
   } else {
 #pragma unroll
     for (int e = 0; e < 8; ++e)
-      if (f + e < F) p[(long long)(f + e) * sF] = __float2half_rn(v[e]);
+      if (f + e < F) p[(long long)(f + e) * sF] = sb_f2h(v[e]);
   }
 }
 __device__ __forceinline__ void load8m(const void* base, long long off, long long sF, int vec,
@@ -256,21 +297,21 @@ __device__ __forceinline__ void store8m(void* base, long long off, long long sF,
 // uint2 until they are used, so data in flight costs 4 (2) registers per access ------------
 __device__ __forceinline__ uint4 load8h_raw(const void* base, long long off, long long sF, int vec,
                                             int f, int F) {
-  const __half* p = reinterpret_cast<const __half*>(base) + off;
+  const sb_half* p = reinterpret_cast<const sb_half*>(base) + off;
   if (vec) return *reinterpret_cast<const uint4*>(p + f);
   uint4 u;
-  __half* h = reinterpret_cast<__half*>(&u);
+  sb_half* h = reinterpret_cast<sb_half*>(&u);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) h[e] = (f + e < F) ? p[(long long)(f + e) * sF] : __float2half_rn(0.f);
+  for (int e = 0; e < 8; ++e) h[e] = (f + e < F) ? p[(long long)(f + e) * sF] : sb_f2h(0.f);
   return u;
 }
 __device__ __forceinline__ void store8h_raw(void* base, long long off, long long sF, int vec, int f,
                                             int F, const uint4& u) {
-  __half* p = reinterpret_cast<__half*>(base) + off;
+  sb_half* p = reinterpret_cast<sb_half*>(base) + off;
   if (vec) {
     *reinterpret_cast<uint4*>(p + f) = u;
   } else {
-    const __half* h = reinterpret_cast<const __half*>(&u);
+    const sb_half* h = reinterpret_cast<const sb_half*>(&u);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
       if (f + e < F) p[(long long)(f + e) * sF] = h[e];
@@ -307,16 +348,16 @@ __device__ __forceinline__ uint2 mask_pack(const uint32_t m[8]) {
 }
 
 // Two mask bytes (0/1) -> half2 of 0.0/1.0: spread the bytes to 16-bit lanes, multiply by 0x3C00.
-__device__ __forceinline__ __half2 mask_half2(uint32_t word, int pair) {
+__device__ __forceinline__ sb_half2 mask_half2(uint32_t word, int pair) {
   const uint32_t spread = __byte_perm(word, 0u, pair ? 0x4342 : 0x4140);  // (b_lo, 0, b_hi, 0)
-  const uint32_t bits = spread * 0x3C00u;
-  return *reinterpret_cast<const __half2*>(&bits);
+  const uint32_t bits = spread * SB_ONE_BITS;
+  return *reinterpret_cast<const sb_half2*>(&bits);
 }
 // out = v (8 packed halves) times the 0/1 mask, lane for lane
 __device__ __forceinline__ uint4 mask_apply(const uint4& v, const uint2& m) {
   uint4 o;
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-  __half2* q = reinterpret_cast<__half2*>(&o);
+  const sb_half2* h = reinterpret_cast<const sb_half2*>(&v);
+  sb_half2* q = reinterpret_cast<sb_half2*>(&o);
   q[0] = __hmul2(h[0], mask_half2(m.x, 0));
   q[1] = __hmul2(h[1], mask_half2(m.x, 1));
   q[2] = __hmul2(h[2], mask_half2(m.y, 0));
@@ -327,9 +368,9 @@ __device__ __forceinline__ uint4 mask_apply(const uint4& v, const uint2& m) {
 // lane-wise sum of 8 packed halves (fp16 arithmetic, one rounding, like the flat elementwise kernels)
 __device__ __forceinline__ uint4 hadd8(const uint4& a, const uint4& b) {
   uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&a);
-  const __half2* y = reinterpret_cast<const __half2*>(&b);
-  __half2* q = reinterpret_cast<__half2*>(&o);
+  const sb_half2* x = reinterpret_cast<const sb_half2*>(&a);
+  const sb_half2* y = reinterpret_cast<const sb_half2*>(&b);
+  sb_half2* q = reinterpret_cast<sb_half2*>(&o);
 #pragma unroll
   for (int i = 0; i < 4; ++i) q[i] = __hadd2(x[i], y[i]);
   return o;

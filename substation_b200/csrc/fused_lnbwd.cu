@@ -103,7 +103,7 @@ lnbwd_kernel(LnBwdParams p) {
         df[r] = load8h_raw(p.diff.p, b * p.diff.sB + j * p.diff.sJ, 1, 1, f, F);
         mk[r] = load8m_raw(p.mask.p, b * p.mask.sB + j * p.mask.sJ, 1, 1, f, F);
       }
-      s[r] = __half2float(reinterpret_cast<const __half*>(p.istd.p)[b * p.istd.sB + j * p.istd.sJ]);
+      s[r] = sb_h2f(reinterpret_cast<const sb_half*>(p.istd.p)[b * p.istd.sB + j * p.istd.sJ]);
       off_out[r][0] = b * p.dln.sB + j * p.dln.sJ;
       off_out[r][1] = b * p.dresid.sB + j * p.dresid.sJ;
       off_out[r][2] = b * p.dlin.sB + j * p.dlin.sJ;
@@ -275,7 +275,7 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
         const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
         const uint32_t nb = nrows * row_bytes;
         ring::mbar_expect_tx(full, NIN * nb + nrows * (uint32_t)F);
-        auto rows_of = [&](const View3& v) { return reinterpret_cast<const __half*>(v.p) + row0 * F; };
+        auto rows_of = [&](const View3& v) { return reinterpret_cast<const sb_half*>(v.p) + row0 * F; };
         if (MODE == 0) {
           ring::bulk_load(dst, rows_of(p.y), nb, full);
           ring::bulk_load(dst + tensor_bytes, rows_of(p.n), nb, full);
@@ -304,19 +304,19 @@ lnbwd_ring_kernel(LnBwdParams p, int nstages, int stage_bytes) {
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
-    const __half* istd = reinterpret_cast<const __half*>(p.istd.p);
+    const sb_half* istd = reinterpret_cast<const sb_half*>(p.istd.p);
     auto istd_of = [&](unsigned i) {
       const unsigned long long row = (unsigned long long)(blockIdx.x + i * G) * kGroups + group;
-      if (row >= R) return __float2half(0.f);
+      if (row >= R) return sb_f2h(0.f);
       return istd[(long long)(row / (unsigned)p.d.J) * p.istd.sB + (long long)(row % (unsigned)p.d.J) * p.istd.sJ];
     };
-    __half s_next = n_i > 0 ? istd_of(0) : __float2half(0.f);
+    sb_half s_next = n_i > 0 ? istd_of(0) : sb_f2h(0.f);
     for (unsigned i = 0; i < n_i; ++i) {
       const int s = (int)(i % (unsigned)nstages);
       const uint32_t ph = (i / (unsigned)nstages) & 1u;
       const unsigned long long row = (unsigned long long)(blockIdx.x + i * G) * kGroups + group;
       const bool active = has_f && row < R;
-      const float sd = __half2float(s_next);
+      const float sd = sb_h2f(s_next);
       if (i + 1 < n_i) s_next = istd_of(i + 1);          // in flight while this token is worked on
       if (!warp_wait(bar_full + 8 * s, ph, 12, lane)) break;
       const uint8_t* st = ring_gen + (size_t)s * stage_bytes;
@@ -446,7 +446,7 @@ colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, vo
 #pragma unroll
     for (int g = 0; g < kFinishParts; ++g) total += sm[g][fl];
     void* outs[4] = {o0, o1, o2, o3};
-    reinterpret_cast<__half*>(outs[q])[f] = __float2half_rn(total);
+    reinterpret_cast<sb_half*>(outs[q])[f] = sb_f2h(total);
   }
 }
 
@@ -508,8 +508,8 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
         const uint32_t dst = ring_s + (uint32_t)s * (uint32_t)stage_bytes;
         const uint32_t nb = nrows * row_bytes;
         ring::mbar_expect_tx(full, 2 * nb + (mask_in ? nrows * (uint32_t)F : 0u));
-        ring::bulk_load(dst, reinterpret_cast<const __half*>(p.in.p) + row0 * F, nb, full);
-        ring::bulk_load(dst + tensor_bytes, reinterpret_cast<const __half*>(p.resid.p) + row0 * F, nb, full);
+        ring::bulk_load(dst, reinterpret_cast<const sb_half*>(p.in.p) + row0 * F, nb, full);
+        ring::bulk_load(dst + tensor_bytes, reinterpret_cast<const sb_half*>(p.resid.p) + row0 * F, nb, full);
         if (mask_in)
           ring::bulk_load(dst + 2 * tensor_bytes, reinterpret_cast<const uint8_t*>(p.mask.p) + row0 * F, nrows * (uint32_t)F, full);
       }
@@ -577,7 +577,7 @@ bdrln_ring_kernel(BdrlnParams p, int nstages, int stage_bytes) {
       }
     }
     const float rstd = rsqrtf(warp_sum(sq) * invF + kLnEps);
-    if (lane == 0) reinterpret_cast<__half*>(p.istd.p)[b * p.istd.sB + j * p.istd.sJ] = __float2half_rn(rstd);
+    if (lane == 0) reinterpret_cast<sb_half*>(p.istd.p)[b * p.istd.sB + j * p.istd.sJ] = sb_f2h(rstd);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int f = (lane + kWarp * k) * 8;

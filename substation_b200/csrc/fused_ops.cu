@@ -45,9 +45,9 @@ __device__ __forceinline__ float act_bwd(float x, float dy, int activation) {
 
 __device__ __forceinline__ uint4 hmul8(const uint4& a, const uint4& b) {
   uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&a);
-  const __half2* y = reinterpret_cast<const __half2*>(&b);
-  __half2* q = reinterpret_cast<__half2*>(&o);
+  const sb_half2* x = reinterpret_cast<const sb_half2*>(&a);
+  const sb_half2* y = reinterpret_cast<const sb_half2*>(&b);
+  sb_half2* q = reinterpret_cast<sb_half2*>(&o);
 #pragma unroll
   for (int i = 0; i < 4; ++i) q[i] = __hmul2(x[i], y[i]);
   return o;
@@ -284,7 +284,7 @@ bdrln_kernel(Dims3 d, View3 in, const void* bias, View3 resid, const void* gamma
       }
     }
     const float rstd = rsqrtf(warp_sum(sq) * invF + kLnEps);
-    if (lane == 0) reinterpret_cast<__half*>(istd.p)[b * istd.sB + j * istd.sJ] = __float2half_rn(rstd);
+    if (lane == 0) reinterpret_cast<sb_half*>(istd.p)[b * istd.sB + j * istd.sJ] = sb_f2h(rstd);
     const long long o_diff = b * diff.sB + j * diff.sJ, o_ln = b * ln.sB + j * ln.sJ;
     const long long o_out = b * out.sB + j * out.sJ;
 #pragma unroll
@@ -334,7 +334,7 @@ blnrd_kernel(Dims3 d, View3 dln, View2 istd, View3 diff, View3 mask, View3 dresi
         mr[i] = make_uint2(0, 0);
       }
     }
-    const float s = __half2float(reinterpret_cast<const __half*>(istd.p)[b * istd.sB + j * istd.sJ]);
+    const float s = sb_h2f(reinterpret_cast<const sb_half*>(istd.p)[b * istd.sB + j * istd.sJ]);
     float sg = 0.f, sgd = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -408,9 +408,9 @@ bad_flat_kernel(unsigned long long ngroups, int groups_per_row, const uint4* __r
       lin1[g] = l;
       uint4 a;
       if (ACT == SB_ACT_RELU) {
-        const __half2* h = reinterpret_cast<const __half2*>(&l);
-        __half2* q = reinterpret_cast<__half2*>(&a);
-        const __half2 zero = __float2half2_rn(0.f);
+        const sb_half2* h = reinterpret_cast<const sb_half2*>(&l);
+        sb_half2* q = reinterpret_cast<sb_half2*>(&a);
+        const sb_half2 zero = sb_f2h2_dup(0.f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) q[i] = __hmax2(h[i], zero);
       } else {
@@ -449,13 +449,13 @@ add_flat_kernel(unsigned long long ngroups, const uint4* __restrict__ a, const u
 // out[r, :] = in[r, :] + bias[r] over dense rows of `groups_per_row` groups of eight
 __global__ void __launch_bounds__(kSmThreads, 4)
 rowbias_flat_kernel(unsigned long long ngroups, unsigned groups_per_row, const uint4* __restrict__ in,
-                    const __half* __restrict__ bias, uint4* __restrict__ out) {
+                    const sb_half* __restrict__ bias, uint4* __restrict__ out) {
   grid_dependency_sync();
   const unsigned long long stride = (unsigned long long)gridDim.x * kSmThreads;
   for (unsigned long long g0 = (unsigned long long)blockIdx.x * kSmThreads + threadIdx.x; g0 < ngroups;
        g0 += stride * kFlatUnr) {
     uint4 x[kFlatUnr];
-    __half bv[kFlatUnr];
+    sb_half bv[kFlatUnr];
 #pragma unroll
     for (int u = 0; u < kFlatUnr; ++u) {
       const unsigned long long g = g0 + u * stride;
@@ -465,10 +465,10 @@ rowbias_flat_kernel(unsigned long long ngroups, unsigned groups_per_row, const u
     for (int u = 0; u < kFlatUnr; ++u) {
       const unsigned long long g = g0 + u * stride;
       if (g >= ngroups) continue;
-      const __half2 b2 = __half2half2(bv[u]);
+      const sb_half2 b2 = sb_h2h2(bv[u]);
       uint4 o;
-      const __half2* h = reinterpret_cast<const __half2*>(&x[u]);
-      __half2* q = reinterpret_cast<__half2*>(&o);
+      const sb_half2* h = reinterpret_cast<const sb_half2*>(&x[u]);
+      sb_half2* q = reinterpret_cast<sb_half2*>(&o);
 #pragma unroll
       for (int i = 0; i < 4; ++i) q[i] = __hadd2(h[i], b2);
       out[g] = o;
@@ -570,7 +570,7 @@ aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long l
   const int n = (int)(row / d.P);
   const long long o_in = n * in.sN + p * in.sP + h * in.sH + b * in.sB;
   const long long o_out = n * out.sN + p * out.sP + h * out.sH + b * out.sB;
-  const float bv = __half2float(reinterpret_cast<const __half*>(bias)[n * bsN + p * bsP + h * bsH]);
+  const float bv = sb_h2f(reinterpret_cast<const sb_half*>(bias)[n * bsN + p * bsP + h * bsH]);
   float x[kEwNV][8];
 #pragma unroll
   for (int i = 0; i < kEwNV; ++i) {
@@ -590,7 +590,7 @@ aib_kernel(Dims5 d, int spans, View5 in, const void* bias, long long bsN, long l
 // Dense rows: out[r] = sum of the `groups` groups of eight of row r; one warp per row, eight
 // 128-bit loads in flight per lane.
 __global__ void __launch_bounds__(kSmThreads)
-rowsum_flat_kernel(unsigned rows, unsigned groups, const uint4* __restrict__ in, __half* __restrict__ out) {
+rowsum_flat_kernel(unsigned rows, unsigned groups, const uint4* __restrict__ in, sb_half* __restrict__ out) {
   grid_dependency_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned nwarps = gridDim.x * (kSmThreads / kWarp);
@@ -613,7 +613,7 @@ rowsum_flat_kernel(unsigned rows, unsigned groups, const uint4* __restrict__ in,
       }
     }
     acc = warp_sum(acc);
-    if (lane == 0) out[r] = __float2half_rn(acc);
+    if (lane == 0) out[r] = sb_f2h(acc);
   }
 }
 
@@ -645,7 +645,7 @@ baib_kernel(Dims5 d, View5 in, void* dbias, long long bsN, long long bsP, long l
     float s = 0.f;
 #pragma unroll
     for (int w = 0; w < kColThreads / kWarp; ++w) s += sm[w];
-    reinterpret_cast<__half*>(dbias)[n * bsN + p * bsP + h * bsH] = __float2half_rn(s);
+    reinterpret_cast<sb_half*>(dbias)[n * bsN + p * bsP + h * bsH] = sb_f2h(s);
   }
 }
 
@@ -748,10 +748,10 @@ struct BdrlbOp {
     if (activation == SB_ACT_RELU) {
       // dlin1 = [lin1 > 0] * mask * ddrop2, all exact selections of fp16 values
       const uint4 g = mask_apply(r.v[0], r.m);
-      const __half2* x = reinterpret_cast<const __half2*>(&r.v[1]);
-      const __half2* gg = reinterpret_cast<const __half2*>(&g);
-      __half2* q = reinterpret_cast<__half2*>(&out);
-      const __half2 zero = __float2half2_rn(0.f);
+      const sb_half2* x = reinterpret_cast<const sb_half2*>(&r.v[1]);
+      const sb_half2* gg = reinterpret_cast<const sb_half2*>(&g);
+      sb_half2* q = reinterpret_cast<sb_half2*>(&out);
+      const sb_half2 zero = sb_f2h2_dup(0.f);
 #pragma unroll
       for (int i = 0; i < 4; ++i) q[i] = __hmul2(gg[i], __hgt2(x[i], zero));
       unpack8(out, o);
@@ -886,7 +886,7 @@ colreduce_kernel(Op op, Dims3 d, int rows_per_chunk, float* partial, unsigned* c
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < NW; ++w) s += sm[w][q][t];
-      reinterpret_cast<__half*>(outs.out[q])[slice * 256 + t] = __float2half_rn(s);
+      reinterpret_cast<sb_half*>(outs.out[q])[slice * 256 + t] = sb_f2h(s);
     }
   }
   if (t == 0) counters[slice] = 0u;
@@ -1116,7 +1116,7 @@ int launch_aib(cudaStream_t s, Dims5 d, View5 in, const void* bias, long long bs
     const unsigned long long ngroups = (unsigned long long)R * (d.J / 8);
     const unsigned long long work = (ngroups + (unsigned long long)kSmThreads * kFlatUnr - 1) / ((unsigned long long)kSmThreads * kFlatUnr);
     SB_LAUNCH_OK(launch_k(rowbias_flat_kernel, persistent_blocks(rowbias_flat_kernel, kSmThreads, work), kSmThreads, 0, s, 
-        ngroups, (unsigned)(BJ / 8), (const uint4*)in.p, (const __half*)bias, (uint4*)out.p));
+        ngroups, (unsigned)(BJ / 8), (const uint4*)in.p, (const sb_half*)bias, (uint4*)out.p));
     SB_CUDA_OK(cudaGetLastError());
     return SB_OK;
   }
@@ -1136,7 +1136,7 @@ int launch_baib(cudaStream_t s, Dims5 d, View5 in, void* dbias, long long bsN, l
   if (in.vec && in.sJ == 1 && in.sB == d.J && in.sH == BJ && in.sP == BJ * d.H && in.sN == BJ * d.H * d.P &&
       bsH == 1 && bsP == d.H && bsN == (long long)d.H * d.P && R < 0x7fffffffLL && BJ / 8 < 0x7fffffffLL) {
     const unsigned blocks = persistent_blocks(rowsum_flat_kernel, kSmThreads, (unsigned long long)((R + 7) / 8));
-    SB_LAUNCH_OK(launch_k(rowsum_flat_kernel, blocks, kSmThreads, 0, s, (unsigned)R, (unsigned)(BJ / 8), (const uint4*)in.p, (__half*)dbias));
+    SB_LAUNCH_OK(launch_k(rowsum_flat_kernel, blocks, kSmThreads, 0, s, (unsigned)R, (unsigned)(BJ / 8), (const uint4*)in.p, (sb_half*)dbias));
     SB_CUDA_OK(cudaGetLastError());
     return SB_OK;
   }

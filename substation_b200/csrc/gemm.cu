@@ -177,9 +177,9 @@ gemm_simt_kernel(GemmProblem g) {
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
   const long long m0 = (long long)blockIdx.y * kSt, n0 = (long long)blockIdx.x * kSt;
-  const __half* A = reinterpret_cast<const __half*>(g.A);
-  const __half* B = reinterpret_cast<const __half*>(g.B);
-  __half* C = reinterpret_cast<__half*>(g.C);
+  const sb_half* A = reinterpret_cast<const sb_half*>(g.A);
+  const sb_half* B = reinterpret_cast<const sb_half*>(g.B);
+  sb_half* C = reinterpret_cast<sb_half*>(g.C);
   for (long long bt = blockIdx.z; bt < g.batch; bt += gridDim.z) {
     float acc[4][4] = {};
     for (long long k0 = 0; k0 < g.K; k0 += kSk) {
@@ -191,8 +191,8 @@ gemm_simt_kernel(GemmProblem g) {
         if (g.sAk == 1) { ak = idx % kSk; am = idx / kSk; } else { am = idx % kSt; ak = idx / kSt; }
         if (g.sBk == 1) { bk = idx % kSk; bn = idx / kSk; } else { bn = idx % kSt; bk = idx / kSt; }
         const long long m = m0 + am, ka = k0 + ak, n = n0 + bn, kb = k0 + bk;
-        As[ak][am] = (m < g.M && ka < g.K) ? __half2float(A[bt * g.sAb + m * g.sAm + ka * g.sAk]) : 0.f;
-        Bs[bk][bn] = (n < g.N && kb < g.K) ? __half2float(B[bt * g.sBb + n * g.sBn + kb * g.sBk]) : 0.f;
+        As[ak][am] = (m < g.M && ka < g.K) ? sb_h2f(A[bt * g.sAb + m * g.sAm + ka * g.sAk]) : 0.f;
+        Bs[bk][bn] = (n < g.N && kb < g.K) ? sb_h2f(B[bt * g.sBb + n * g.sBn + kb * g.sBk]) : 0.f;
       }
       __syncthreads();
 #pragma unroll
@@ -212,7 +212,7 @@ gemm_simt_kernel(GemmProblem g) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const long long m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-        if (m < g.M && n < g.N) C[bt * g.sCb + m * g.sCm + n * g.sCn] = __float2half_rn(acc[i][j] * g.alpha);
+        if (m < g.M && n < g.N) C[bt * g.sCb + m * g.sCm + n * g.sCn] = sb_f2h(acc[i][j] * g.alpha);
       }
   }
 }
@@ -252,8 +252,8 @@ __device__ int g_tc_error = 0;  // first failure code of any tcgen05 kernel on t
 struct EpiParams {
   int kind;
   int vec_along_m;       // bias indexed by the row (m) instead of the column (n)
-  const __half* vec;
-  const __half* resid;   // [M][N], row stride sCm
+  const sb_half* vec;
+  const sb_half* resid;   // [M][N], row stride sCm
   uint8_t* mask;         // [M][N] bytes, row stride sCm; read, or written when rng.philox
   int activation;
   int skip_c;            // C itself is not stored (nothing reads it once the fused outputs exist)
@@ -474,7 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer (whole warp walks the loop, lane 0 issues) ----------------
     // instruction descriptor: fp32 accumulate, fp16 A and B, operand majors, N, M
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+    const uint32_t idesc = (1u << 4) | SB_IDESC_AB_FMT | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
                            ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) |
                            ((uint32_t)(kBM >> 4) << 24);
     // K-major: 8-row groups 1024 B apart, 32 B per K step of 16.
@@ -593,7 +593,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       } else {
-        __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;
+        sb_half* crow = reinterpret_cast<sb_half*>(p.C) + bt * p.sCb + m * p.sCm;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -620,7 +620,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             } else {
 #pragma unroll
               for (int e = 0; e < 32; ++e)
-                if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+                if (nb + e < p.N) crow[(nb + e) * p.sCn] = sb_f2h(__uint_as_float(r[e]) * p.alpha);
             }
           }
         }
@@ -646,7 +646,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // out = alpha * sum over splits of the fp32 partials [split][batch][M][N] (fixed order)
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, long long M, long long N,
-                     __half* out, long long sCb, long long sCm, long long sCn, float alpha) {
+                     sb_half* out, long long sCb, long long sCm, long long sCn, float alpha) {
   grid_dependency_sync();
   const long long total4 = batch * M * N / 4;  // N % 4 == 0
   const long long plane = batch * M * N;
@@ -663,18 +663,18 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
     }
     const long long e = i * 4;
     const long long n = e % N, m = (e / N) % M, b = e / (N * M);
-    __half* o = out + b * sCb + m * sCm + n * sCn;
+    sb_half* o = out + b * sCb + m * sCm + n * sCn;
     if (sCn == 1 && ((reinterpret_cast<uintptr_t>(o) & 7u) == 0)) {
-      __half2 lo = __floats2half2_rn(acc.x * alpha, acc.y * alpha), hi = __floats2half2_rn(acc.z * alpha, acc.w * alpha);
+      sb_half2 lo = sb_f2h2(acc.x * alpha, acc.y * alpha), hi = sb_f2h2(acc.z * alpha, acc.w * alpha);
       uint2 u;
       u.x = *reinterpret_cast<uint32_t*>(&lo);
       u.y = *reinterpret_cast<uint32_t*>(&hi);
       *reinterpret_cast<uint2*>(o) = u;
     } else {
-      o[0] = __float2half_rn(acc.x * alpha);
-      o[sCn] = __float2half_rn(acc.y * alpha);
-      o[2 * sCn] = __float2half_rn(acc.z * alpha);
-      o[3 * sCn] = __float2half_rn(acc.w * alpha);
+      o[0] = sb_f2h(acc.x * alpha);
+      o[sCn] = sb_f2h(acc.y * alpha);
+      o[2 * sCn] = sb_f2h(acc.z * alpha);
+      o[3 * sCn] = sb_f2h(acc.w * alpha);
     }
   }
 }
@@ -729,7 +729,7 @@ bool encode_map(const void* ptr, cuuint64_t n0, cuuint64_t n1, cuuint64_t n2, lo
     if (dim[i] == 0 || dim[i] > 0xffffffffull) { *why = "extent out of range"; return false; }
   cuuint64_t gstr[2] = {(cuuint64_t)(str[1] * esize), (cuuint64_t)(str[2] * esize)};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = g_encode(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  const CUresult r = g_encode(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : SB_TMAP_DTYPE, 3,
                               const_cast<void*>(ptr), dim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               bytes ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -831,7 +831,7 @@ int launch_tc(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const O
     const long long total4 = g.batch * g.M * g.N / 4;
     const unsigned blocks = (unsigned)std::min<long long>((total4 + 255) / 256, (long long)sm_count() * 8);
     SB_LAUNCH_OK(launch_k(splitk_reduce_kernel, blocks, 256, 0, s, reinterpret_cast<const float*>(ws), p.splits, g.batch, g.M, g.N,
-                                                reinterpret_cast<__half*>(g.C), g.sCb, g.sCm, g.sCn, g.alpha));
+                                                reinterpret_cast<sb_half*>(g.C), g.sCb, g.sCm, g.sCn, g.alpha));
     SB_CUDA_OK(cudaGetLastError());
   }
   return SB_OK;
@@ -942,8 +942,8 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
       return fail(SB_ERR_ALIGNMENT, "fused epilogue: the residual must be 16-byte aligned");
     if (epi->kind == 3 && (misaligned(epi->mask) || g.sCm % 16 != 0))
       return fail(SB_ERR_ALIGNMENT, "fused epilogue: the mask must be 16-byte aligned with a row pitch that is a multiple of 16");
-    p.epi.vec = reinterpret_cast<const __half*>(epi->vec);
-    p.epi.resid = reinterpret_cast<const __half*>(epi->resid);
+    p.epi.vec = reinterpret_cast<const sb_half*>(epi->vec);
+    p.epi.resid = reinterpret_cast<const sb_half*>(epi->resid);
     p.epi.mask = reinterpret_cast<uint8_t*>(epi->mask);
     p.epi.activation = epi->activation;
     p.epi.skip_c = epi->skip_c;
@@ -1191,7 +1191,7 @@ int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const Vi
       return fail(SB_ERR_UNSUPPORTED, "score contractions, row operand: " + why);
     mx = m.map; p.x_mn = m.mn; p.x_swap = m.swap;
     if (!unit_stride(*out_r, &su)) return fail(SB_ERR_UNSUPPORTED, "score contractions: head and sample dims of the row output do not collapse");
-    p.out_r = reinterpret_cast<__half*>(out_r->p); p.r_sU = su; p.r_sRow = out_r->sK; p.r_sP = out_r->sH;
+    p.out_r = reinterpret_cast<sb_half*>(out_r->p); p.r_sU = su; p.r_sRow = out_r->sK; p.r_sP = out_r->sH;
   }
   if (y) {
     OperandMap m;
@@ -1199,7 +1199,7 @@ int launch_score_contract(cudaStream_t s, Dims4 d, int P, View4 scores, const Vi
       return fail(SB_ERR_UNSUPPORTED, "score contractions, column operand: " + why);
     my = m.map; p.y_mn = m.mn; p.y_swap = m.swap;
     if (!unit_stride(*out_c, &su)) return fail(SB_ERR_UNSUPPORTED, "score contractions: head and sample dims of the column output do not collapse");
-    p.out_c = reinterpret_cast<__half*>(out_c->p); p.c_sU = su; p.c_sRow = out_c->sK; p.c_sP = out_c->sH;
+    p.out_c = reinterpret_cast<sb_half*>(out_c->p); p.c_sU = su; p.c_sRow = out_c->sK; p.c_sP = out_c->sH;
   }
   // two sets of projections and column accumulators when they fit (L <= 256): the next (head, sample) loads
   // while this one computes, which is what matters when a unit is only one or four tiles long

@@ -178,7 +178,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (rank == 0) {
       // ---------------- MMA issuer (leader CTA only; lane 0 issues) ----------------
       // instruction descriptor: fp32 accumulate, fp16 operands, majors, N = 256, M = 256 across the pair
-      const uint32_t idesc = (1u << 4) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+      const uint32_t idesc = (1u << 4) | SB_IDESC_AB_FMT | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
                              ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(kBN >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
@@ -277,7 +277,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const bool row_ok = m < p.M && nc < p.N;
           if (EPI == 1 || EPI == 3) {
             if (p.epi.vec_along_m) {
-              const __half2 b2 = __half2half2(m < p.M ? p.epi.vec[m] : __float2half(0.f));
+              const sb_half2 b2 = sb_h2h2(m < p.M ? p.epi.vec[m] : sb_f2h(0.f));
               const uint32_t w = *reinterpret_cast<const uint32_t*>(&b2);
 #pragma unroll
               for (int v = 0; v < 8; ++v) side[v] = make_uint4(w, w, w, w);
@@ -287,7 +287,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           if (EPI == 2 && row_ok) {
-            const __half* rp = p.epi.resid + m * p.sCm + nc;
+            const sb_half* rp = p.epi.resid + m * p.sCm + nc;
 #pragma unroll
             for (int v = 0; v < 8; ++v) side[v] = *reinterpret_cast<const uint4*>(rp + 8 * v);
           }
@@ -338,9 +338,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int v = 0; v < 8; ++v) {
               uint4 a;
               if (p.epi.activation == SB_ACT_RELU) {
-                const __half2* h = reinterpret_cast<const __half2*>(&o1[v]);
-                __half2* qq = reinterpret_cast<__half2*>(&a);
-                const __half2 zero = __float2half2_rn(0.f);
+                const sb_half2* h = reinterpret_cast<const sb_half2*>(&o1[v]);
+                sb_half2* qq = reinterpret_cast<sb_half2*>(&a);
+                const sb_half2 zero = sb_f2h2_dup(0.f);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) qq[i] = __hmax2(h[i], zero);
               } else {
@@ -356,7 +356,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       } else {
-        __half* crow = reinterpret_cast<__half*>(p.C) + bt * p.sCb + m * p.sCm;
+        sb_half* crow = reinterpret_cast<sb_half*>(p.C) + bt * p.sCb + m * p.sCm;
 #pragma unroll 1
         for (int c = 2 * c_first; c < 2 * (c_first + kChunks); ++c) {
           uint32_t r[32];
@@ -382,7 +382,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             } else {
 #pragma unroll
               for (int e = 0; e < 32; ++e)
-                if (nb + e < p.N) crow[(nb + e) * p.sCn] = __float2half_rn(__uint_as_float(r[e]) * p.alpha);
+                if (nb + e < p.N) crow[(nb + e) * p.sCn] = sb_f2h(__uint_as_float(r[e]) * p.alpha);
             }
           }
         }

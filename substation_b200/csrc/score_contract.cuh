@@ -31,12 +31,12 @@ struct Params {
   int nstages;
   int nbuf;               // 1 or 2 sets of (X, Y, column accumulators): with 2, the next unit loads while this one computes
   float alpha;
-  __half* out_r; long long r_sU, r_sRow, r_sP;   // strides of R over (unit, j, p)
-  __half* out_c; long long c_sU, c_sRow, c_sP;   // strides of C over (unit, k, p)
+  sb_half* out_r; long long r_sU, r_sRow, r_sP;   // strides of R over (unit, j, p)
+  sb_half* out_c; long long c_sU, c_sRow, c_sP;   // strides of C over (unit, k, p)
 };
 
 // 64 fp32 accumulator columns of this thread's row -> alpha * value as fp16 at ptr[p * sP]
-__device__ __forceinline__ void store_row64(__half* ptr, long long sP, const uint32_t* r, float alpha) {
+__device__ __forceinline__ void store_row64(sb_half* ptr, long long sP, const uint32_t* r, float alpha) {
   if (sP == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) {
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
@@ -47,7 +47,7 @@ __device__ __forceinline__ void store_row64(__half* ptr, long long sP, const uin
     }
   } else {
 #pragma unroll
-    for (int e = 0; e < 64; ++e) ptr[e * sP] = __float2half_rn(__uint_as_float(r[e]) * alpha);
+    for (int e = 0; e < 64; ++e) ptr[e * sP] = sb_f2h(__uint_as_float(r[e]) * alpha);
   }
 }
 
@@ -154,8 +154,8 @@ score_contract_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_cons
     // ---------------- MMA issuer ----------------
     const uint32_t x_lbo = p.x_mn ? 8192u : 16u, x_step = p.x_mn ? 2048u : 32u;
     const uint32_t y_lbo = p.y_mn ? 8192u : 16u, y_step = p.y_mn ? 2048u : 32u;
-    const uint32_t idesc_r = (1u << 4) | ((uint32_t)(p.x_mn ? 1 : 0) << 16) | ((64u >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-    const uint32_t idesc_c = (1u << 4) | (1u << 15) | ((uint32_t)(p.y_mn ? 1 : 0) << 16) | ((64u >> 3) << 17) |
+    const uint32_t idesc_r = (1u << 4) | SB_IDESC_AB_FMT | ((uint32_t)(p.x_mn ? 1 : 0) << 16) | ((64u >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    const uint32_t idesc_c = (1u << 4) | SB_IDESC_AB_FMT | (1u << 15) | ((uint32_t)(p.y_mn ? 1 : 0) << 16) | ((64u >> 3) << 17) |
                              ((uint32_t)(kBM >> 4) << 24);
     uint32_t un = 0, sit = 0, rn = 0;
     bool ok = true;

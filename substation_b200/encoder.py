@@ -8,7 +8,8 @@ ctypes call per pass into the hand-written sm_100a library instead of a
 per-configuration nvcc build (pytorch_module/encoder.py:165-405).
 
 What differs, on purpose:
-  * only ``torch.float16`` is implemented (fp16 storage, fp32 accumulation);
+  * ``torch.float16`` and ``torch.bfloat16`` are implemented (16-bit storage, fp32 accumulation; one build of
+    the library per storage type), ``float32`` / ``float64`` are not;
   * dropout masks are ``uint8``; with ``mask_mode='explicit'`` the four masks
     are caller-supplied inputs (``set_masks``), with ``'philox'`` (default, the
     reference's behaviour) the kernels generate them from ``(seed, offset)``;
@@ -40,6 +41,12 @@ def _round_up(n, a=_ALIGN):
 # to step (measured: one capture per three steps, no gain), unlike the caller-held arenas of the raw passes.
 _AUTOGRAD_GRAPHS = os.environ.get('SUBSTATION_B200_AUTOGRAD_GRAPHS', '0') == '1'
 
+def _to_numpy(t):
+    """numpy copy of a tensor for ``.debug``; numpy has no bfloat16, those come back as float32 (exact)."""
+    t = t.detach()
+    return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
+
+
 class Encoder(torch.nn.Module):
     """Optimized BERT encoder layer (API of pytorch_module/encoder.py:19-25)."""
 
@@ -50,10 +57,9 @@ class Encoder(torch.nn.Module):
                  enable_debug=False, profiling=False, *,
                  activation='relu', mask_mode='philox', seed=0, fuse=True, keep_all_intermediates=None):
         super().__init__()
-        if torch_dtype != torch.float16:
-            raise NotImplementedError(
-                f'substation_b200.Encoder computes in float16 storage with float32 accumulation; '
-                f'{torch_dtype} is not implemented')
+        # float16 or bfloat16 storage, float32 accumulation; anything else (the reference also builds float and
+        # double, pytorch_module/encoder.py:13-17) raises NotImplementedError
+        self._lib_key = _lib.dtype_key(torch_dtype)
         if activation not in ('relu', 'gelu'):
             raise ValueError('Unknown activation ' + str(activation))
         if mask_mode not in ('philox', 'explicit'):
@@ -138,9 +144,9 @@ class Encoder(torch.nn.Module):
                     fwd = outer.views('forward', arena)
                     fwd.update(over)
                     for name in outer._fwd_names:
-                        outer.debug[name] = fwd[name].detach().cpu().numpy()
+                        outer.debug[name] = _to_numpy(fwd[name])
                     for name, w in zip(outer._param_names, weights):
-                        outer.debug[name] = w.detach().cpu().numpy()
+                        outer.debug[name] = _to_numpy(w)
                 return Y
 
             @staticmethod
@@ -164,9 +170,9 @@ class Encoder(torch.nn.Module):
                     torch.cuda.synchronize()
                     bwd = outer.views('backward', barena)
                     for name in outer._bwd_names:
-                        outer.debug[name] = bwd[name].detach().cpu().numpy()
+                        outer.debug[name] = _to_numpy(bwd[name])
                     for name, g in zip(outer._param_names, grads):
-                        outer.debug['D' + name] = g.detach().cpu().numpy()
+                        outer.debug['D' + name] = _to_numpy(g)
                 return (DX, *grads)
 
         self.encoder_func = EncoderFunction
@@ -251,7 +257,7 @@ class Encoder(torch.nn.Module):
             return self._handle
         if self._handle is not None:
             self._destroy()
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         names = list(self._table.keys())
         cfg = _lib.SbEncoderConfig()
         cfg.batch, cfg.seq = self.batch_size, self.max_seq_len
@@ -270,21 +276,24 @@ class Encoder(torch.nn.Module):
         cfg.names, cfg.dims = name_arr, dims_arr
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
-            _lib.check(lib.sb_encoder_create(ctypes.byref(cfg), ctypes.byref(handle)))
+            self._check(lib.sb_encoder_create(ctypes.byref(cfg), ctypes.byref(handle)))
             if self.profiling:
-                _lib.check(lib.sb_encoder_set_timing(handle, 1))
-            _lib.check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
-            _lib.check(lib.sb_encoder_set_dead_stores(handle, 1 if self.keep_all_intermediates else 0))
+                self._check(lib.sb_encoder_set_timing(handle, 1))
+            self._check(lib.sb_encoder_set_fusion(handle, 1 if self.fuse else 0))
+            self._check(lib.sb_encoder_set_dead_stores(handle, 1 if self.keep_all_intermediates else 0))
             self._graphs_state = None
         self._handle, self._handle_device = handle, device
         with torch.cuda.device(device):
             self._apply_ffn_event()
         return handle
 
+    def _check(self, status):
+        _lib.check(status, _lib.load(self._lib_key))
+
     def _destroy(self):
         if self.__dict__.get('_handle') is not None:
             try:
-                _lib.load().sb_encoder_destroy(self._handle)
+                _lib.load(self._lib_key).sb_encoder_destroy(self._handle)
             except Exception:  # interpreter shutdown
                 pass
             self._handle = None
@@ -324,25 +333,25 @@ class Encoder(torch.nn.Module):
         path allocates fresh arenas per step, where capturing would only cost host time."""
         on = bool(on and self.__dict__.get('_graphs', True))
         if self.__dict__.get('_graphs_state') != on:
-            _lib.check(_lib.load().sb_encoder_set_graphs(h, int(on)))
+            self._check(_lib.load(self._lib_key).sb_encoder_set_graphs(h, int(on)))
             self._graphs_state = on
 
     def _forward_ptrs(self, X, weights, fwd_ptrs, Y):
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         h = self._native(X.device)
         self._graphs_now(h, _AUTOGRAD_GRAPHS)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
-        _lib.check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
+        self._check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
                                           ctypes.c_void_p(Y.data_ptr()), mode, self.seed, self.philox_offset))
         self.philox_offset += 4
 
     def _backward_ptrs(self, DY, grad_ptrs, bwd_ptrs, weights, fwd_ptrs, X, DX):
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         h = self._native(DY.device)
         self._graphs_now(h, _AUTOGRAD_GRAPHS)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
-        _lib.check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
+        self._check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
                                            self._ptrs(weights), fwd_ptrs, ctypes.c_void_p(X.data_ptr()),
                                            ctypes.c_void_p(DX.data_ptr())))
 
@@ -368,13 +377,13 @@ class Encoder(torch.nn.Module):
         self._check_input(X, 'X')
         self._check_input(Y, 'Y')
         self._check_raw(X.device, X=X, Y=Y, weights=list(weights), fwd={n: fwd[n] for n in self._fwd_names})
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         h = self._native(X.device)
         self._graphs_now(h, True)
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
         wl = list(weights)
-        _lib.check(lib.sb_encoder_forward(
+        self._check(lib.sb_encoder_forward(
             h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(wl),
             self._ptrs([fwd[n] for n in self._fwd_names]), ctypes.c_void_p(Y.data_ptr()),
             mode, self.seed, self.philox_offset))
@@ -389,12 +398,12 @@ class Encoder(torch.nn.Module):
         self._check_raw(DY.device, DY=DY, DX=DX, X=X, weights=list(weights),
                         grads={n: grads[n] for n in self._param_names}, bwd={n: bwd[n] for n in self._bwd_names},
                         fwd={n: fwd[n] for n in self._fwd_names})
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         h = self._native(DY.device)
         self._graphs_now(h, True)
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
         wl = list(weights)
-        _lib.check(lib.sb_encoder_backward(
+        self._check(lib.sb_encoder_backward(
             h, stream, ctypes.c_void_p(DY.data_ptr()),
             self._ptrs([grads[n] for n in self._param_names]),
             self._ptrs([bwd[n] for n in self._bwd_names]),
@@ -407,7 +416,7 @@ class Encoder(torch.nn.Module):
         Names follow the NVTX ranges of pytorch_module/encoder.cu:89-296."""
         if self._handle is None:
             return []
-        lib = _lib.load()
+        lib = _lib.load(self._lib_key)
         n = 64
         names = (ctypes.c_char_p * n)()
         ms = (ctypes.c_float * n)()
@@ -443,7 +452,7 @@ class Encoder(torch.nn.Module):
             if not ev.cuda_event:      # created lazily: a first record makes the handle exist
                 ev.record()
             handle = ctypes.c_void_p(ev.cuda_event)
-        _lib.check(_lib.load().sb_encoder_set_ffn_grads_event(self._handle, handle))
+        self._check(_lib.load(self._lib_key).sb_encoder_set_ffn_grads_event(self._handle, handle))
 
     def set_grad_arenas(self, arenas):
         """Caller-held storage for the parameter gradients of the autograd path: a list of contiguous uint8 CUDA
@@ -486,16 +495,16 @@ class Encoder(torch.nn.Module):
         if self._handle is None:
             return 0, 0
         c, r = ctypes.c_longlong(0), ctypes.c_longlong(0)
-        _lib.check(_lib.load().sb_encoder_graph_stats(self._handle, ctypes.byref(c), ctypes.byref(r)))
+        self._check(_lib.load(self._lib_key).sb_encoder_graph_stats(self._handle, ctypes.byref(c), ctypes.byref(r)))
         return c.value, r.value
 
     def launch_count(self):
         """Operators launched by the most recent raw pass."""
-        return 0 if self._handle is None else _lib.load().sb_encoder_launch_count(self._handle)
+        return 0 if self._handle is None else _lib.load(self._lib_key).sb_encoder_launch_count(self._handle)
 
     def kernel_count(self):
         """Kernels launched by the most recent forward plus the most recent backward."""
-        return 0 if self._handle is None else _lib.load().sb_encoder_kernel_count(self._handle)
+        return 0 if self._handle is None else _lib.load(self._lib_key).sb_encoder_kernel_count(self._handle)
 
     def forward(self, X):
         """Run the encoder."""

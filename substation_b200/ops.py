@@ -7,13 +7,14 @@ reference's kernel harness drives one generated launcher at a time
 """
 
 import ctypes
+import threading
 
 import torch
 
 from . import _lib
 from ._lib import SubstationError  # noqa: F401
 from ._lib import (SB_ACT_GELU, SB_ACT_RELU, SB_GEMM_AUTO, SB_GEMM_SIMT, SB_GEMM_TCGEN05,
-                   SB_MASK_EXPLICIT, SB_MASK_PHILOX, SbDropout, check, tensor_desc)
+                   SB_MASK_EXPLICIT, SB_MASK_PHILOX, SbDropout, tensor_desc)
 
 _ACT = {'relu': SB_ACT_RELU, 'gelu': SB_ACT_GELU}
 _MODE = {'explicit': SB_MASK_EXPLICIT, 'philox': SB_MASK_PHILOX}
@@ -43,10 +44,29 @@ def _check_cuda(*tensors):
             raise ValueError('substation_b200 operators need CUDA tensors (there is no CPU path)')
 
 
+_tls = threading.local()
+
+
 def _half(*tensors):
+    """All floating-point operands of a call share one storage type, float16 or bfloat16; it selects the library
+    build the call goes to (remembered per thread until the next call)."""
+    dt = tensors[0].dtype
+    if dt not in (torch.float16, torch.bfloat16):
+        raise TypeError(f'expected float16 or bfloat16, got {dt}')
     for t in tensors:
-        if t.dtype != torch.float16:
-            raise TypeError(f'expected float16, got {t.dtype}')
+        if t.dtype != dt:
+            raise TypeError(f'operands mix {dt} and {t.dtype}')
+    _tls.lib = _lib.load(dt)
+
+
+def _cur():
+    """Library of the current call (float16 build unless ``_half`` chose otherwise)."""
+    lib = getattr(_tls, 'lib', None)
+    return lib if lib is not None else _lib.load()
+
+
+def check(status):
+    _lib.check(status, _cur())
 
 
 def _mask(t):
@@ -76,14 +96,14 @@ def _given(*tensors):
 def attention_input_biases(inp, bias, out):
     """out[n,p,h,b,j] = inp[n,p,h,b,j] + bias[n,p,h]."""
     _check_cuda(inp, bias, out); _half(inp, bias, out)
-    check(_lib.load().sb_attention_input_biases(_stream(), _d(inp), _d(bias), _d(out)))
+    check(_cur().sb_attention_input_biases(_stream(), _d(inp), _d(bias), _d(out)))
 
 
 def softmax_dropout(beta, alpha, mask, drop, scale=1.0, p=0.0, mode='explicit', seed=0, offset=0):
     """alpha = softmax_k(scale*beta), drop = mask*alpha; all [H,B,J,K]."""
     _check_cuda(beta, alpha, mask, drop); _half(beta, alpha, drop); _mask(mask)
     d = _dropout(p, mode, seed, offset)
-    check(_lib.load().sb_softmax_dropout(_stream(), _d(beta), _d(alpha), _d(mask), _d(drop),
+    check(_cur().sb_softmax_dropout(_stream(), _d(beta), _d(alpha), _d(mask), _d(drop),
                                          float(scale), ctypes.byref(d)))
 
 
@@ -92,7 +112,7 @@ def attention_scores_softmax(qq, kk, beta, alpha, mask, drop, scale, p=0.0, mode
     ``beta=None``: the scores themselves are not stored."""
     _check_cuda(qq, kk, alpha); _half(qq, kk, alpha, drop, *_given(beta)); _mask(mask)
     d = _dropout(p, mode, seed, offset)
-    check(_lib.load().sb_attention_scores_softmax(_stream(), _d(qq), _d(kk), _opt(beta), _d(alpha), _d(mask), _d(drop),
+    check(_cur().sb_attention_scores_softmax(_stream(), _d(qq), _d(kk), _opt(beta), _d(alpha), _d(mask), _d(drop),
                                                   float(scale), ctypes.byref(d)))
 
 
@@ -100,7 +120,7 @@ def attention_scores_softmax_backward(dgamma, vv, alpha, mask, dattn_drop, dbeta
     """dattn_drop = dgamma.vv and the softmax backward in one kernel; dgamma, vv are [P,H,B,J].
     ``dattn_drop=None``: that intermediate is not stored."""
     _check_cuda(dgamma, vv, alpha); _half(dgamma, vv, alpha, dbeta, *_given(dattn_drop)); _mask(mask)
-    check(_lib.load().sb_attention_scores_softmax_backward(_stream(), _d(dgamma), _d(vv), _d(alpha), _d(mask),
+    check(_cur().sb_attention_scores_softmax_backward(_stream(), _d(dgamma), _d(vv), _d(alpha), _d(mask),
                                                            _opt(dattn_drop), _d(dbeta)))
 
 
@@ -112,13 +132,13 @@ def attention_score_contractions(scores, x=None, out_rows=None, y=None, out_cols
     given = [t for t in (x, out_rows, y, out_cols) if t is not None]
     _check_cuda(scores, *given); _half(scores, *given)
     opt = lambda t: _d(t) if t is not None else None
-    check(_lib.load().sb_attention_score_contractions(_stream(), _d(scores), opt(x), opt(out_rows), opt(y),
+    check(_cur().sb_attention_score_contractions(_stream(), _d(scores), opt(x), opt(out_rows), opt(y),
                                                       opt(out_cols), float(alpha)))
 
 
 def backward_softmax(alpha, mask, dattn_drop, dbeta):
     _check_cuda(alpha, mask, dattn_drop, dbeta); _half(alpha, dattn_drop, dbeta); _mask(mask)
-    check(_lib.load().sb_backward_softmax(_stream(), _d(alpha), _d(mask), _d(dattn_drop), _d(dbeta)))
+    check(_cur().sb_backward_softmax(_stream(), _d(alpha), _d(mask), _d(dattn_drop), _d(dbeta)))
 
 
 def bias_dropout_residual_layernorm(inp, bias, resid, gamma, beta, mask, lin, diff, istd, ln, out,
@@ -126,7 +146,7 @@ def bias_dropout_residual_layernorm(inp, bias, resid, gamma, beta, mask, lin, di
     """``lin=None``: the biased input is not stored."""
     _check_cuda(inp, out); _half(inp, bias, resid, gamma, beta, diff, istd, ln, out, *_given(lin)); _mask(mask)
     d = _dropout(p, mode, seed, offset)
-    check(_lib.load().sb_bias_dropout_residual_layernorm(
+    check(_cur().sb_bias_dropout_residual_layernorm(
         _stream(), _d(inp), _d(bias), _d(resid), _d(gamma), _d(beta), _d(mask), _opt(lin), _d(diff),
         _d(istd), _d(ln), _d(out), ctypes.byref(d)))
 
@@ -135,27 +155,27 @@ def bias_activation_dropout(inp, bias, mask, lin1, drop2, activation='relu', p=0
                             mode='explicit', seed=0, offset=0):
     _check_cuda(inp, drop2); _half(inp, bias, lin1, drop2); _mask(mask)
     d = _dropout(p, mode, seed, offset)
-    check(_lib.load().sb_bias_activation_dropout(_stream(), _d(inp), _d(bias), _d(mask), _d(lin1),
+    check(_cur().sb_bias_activation_dropout(_stream(), _d(inp), _d(bias), _d(mask), _d(lin1),
                                                  _d(drop2), _ACT[activation], ctypes.byref(d)))
 
 
 def backward_scale_bias(dy, ln, gamma, dln, dgamma, dbeta):
     _check_cuda(dy); _half(dy, ln, gamma, dln, dgamma, dbeta)
     ws = workspace(dy.device)
-    check(_lib.load().sb_backward_scale_bias(_stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy),
+    check(_cur().sb_backward_scale_bias(_stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy),
                                              _d(ln), _d(gamma), _d(dln), _d(dgamma), _d(dbeta)))
 
 
 def backward_layernorm_residual_dropout(dln, istd, diff, mask, dresid, dlin):
     _check_cuda(dln); _half(dln, istd, diff, dresid, dlin); _mask(mask)
-    check(_lib.load().sb_backward_layernorm_residual_dropout(
+    check(_cur().sb_backward_layernorm_residual_dropout(
         _stream(), _d(dln), _d(istd), _d(diff), _d(mask), _d(dresid), _d(dlin)))
 
 
 def backward_dropout_activation_bias(ddrop2, mask, lin1, dlin1, dbias, activation='relu'):
     _check_cuda(ddrop2); _half(ddrop2, lin1, dlin1, dbias); _mask(mask)
     ws = workspace(ddrop2.device)
-    check(_lib.load().sb_backward_dropout_activation_bias(
+    check(_cur().sb_backward_dropout_activation_bias(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ddrop2), _d(mask), _d(lin1), _d(dlin1),
         _d(dbias), _ACT[activation]))
 
@@ -164,7 +184,7 @@ def extended_backward_scale_bias(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1,
                                  dlinb2):
     _check_cuda(ln1); _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, dln1, dgamma1, dbeta1, dlinb2)
     ws = workspace(ln1.device)
-    check(_lib.load().sb_extended_backward_scale_bias(
+    check(_cur().sb_extended_backward_scale_bias(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ln1), _d(gamma1), _d(dresid2),
         _d(dlin1_linw1), _d(dlin2), _d(dln1), _d(dgamma1), _d(dbeta1), _d(dlinb2)))
 
@@ -173,7 +193,7 @@ def backward_scale_bias_layernorm(dy, ln, gamma, istd, diff, mask, dln, dresid, 
     """backward_scale_bias + backward_layernorm_residual_dropout in one pass (``dln=None``: not stored)."""
     _check_cuda(dy); _half(dy, ln, gamma, istd, diff, dresid, dlin, dgamma, dbeta, *_given(dln)); _mask(mask)
     ws = workspace(dy.device)
-    check(_lib.load().sb_backward_scale_bias_layernorm(
+    check(_cur().sb_backward_scale_bias_layernorm(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(dy), _d(ln), _d(gamma), _d(istd), _d(diff), _d(mask),
         _opt(dln), _d(dresid), _d(dlin), _d(dgamma), _d(dbeta)))
 
@@ -185,7 +205,7 @@ def extended_backward_scale_bias_layernorm(ln1, gamma1, dresid2, dlin1_linw1, dl
     _check_cuda(ln1); _mask(mask)
     _half(ln1, gamma1, dresid2, dlin1_linw1, dlin2, istd, diff, dresid1, datt, dgamma1, dbeta1, dlinb2, dbo, *_given(dln1))
     ws = workspace(ln1.device)
-    check(_lib.load().sb_extended_backward_scale_bias_layernorm(
+    check(_cur().sb_extended_backward_scale_bias_layernorm(
         _stream(), ctypes.c_void_p(ws.data_ptr()), _d(ln1), _d(gamma1), _d(dresid2), _d(dlin1_linw1), _d(dlin2),
         _d(istd), _d(diff), _d(mask), _opt(dln1), _d(dresid1), _d(datt), _d(dgamma1), _d(dbeta1), _d(dlinb2), _d(dbo)))
 
@@ -193,18 +213,18 @@ def extended_backward_scale_bias_layernorm(ln1, gamma1, dresid2, dlin1_linw1, dl
 def backward_attn_out_bias(datt, dbo):
     _check_cuda(datt); _half(datt, dbo)
     ws = workspace(datt.device)
-    check(_lib.load().sb_backward_attn_out_bias(_stream(), ctypes.c_void_p(ws.data_ptr()),
+    check(_cur().sb_backward_attn_out_bias(_stream(), ctypes.c_void_p(ws.data_ptr()),
                                                 _d(datt), _d(dbo)))
 
 
 def backward_attention_input_biases(d, dbias):
     _check_cuda(d); _half(d, dbias)
-    check(_lib.load().sb_backward_attention_input_biases(_stream(), _d(d), _d(dbias)))
+    check(_cur().sb_backward_attention_input_biases(_stream(), _d(d), _d(dbias)))
 
 
 def backward_encoder_input(dxatt, dresid1, dx):
     _check_cuda(dxatt); _half(dxatt, dresid1, dx)
-    check(_lib.load().sb_backward_encoder_input(_stream(), _d(dxatt), _d(dresid1), _d(dx)))
+    check(_cur().sb_backward_encoder_input(_stream(), _d(dxatt), _d(dresid1), _d(dx)))
 
 
 def einsum(spec, a, b, c, alpha=1.0, impl='auto', workspace=None):
@@ -215,7 +235,7 @@ def einsum(spec, a, b, c, alpha=1.0, impl='auto', workspace=None):
     _check_cuda(a, b, c); _half(a, b, c)
     lhs, cd = spec.replace(' ', '').split('->')
     ad, bd = lhs.split(',')
-    lib = _lib.load()
+    lib = _cur()
     ws_ptr = ctypes.c_void_p(workspace.data_ptr()) if workspace is not None else None
     ws_len = workspace.numel() * workspace.element_size() if workspace is not None else 0
     check(lib.sb_einsum(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
@@ -255,32 +275,45 @@ def einsum_fused(spec, a, b, c, alpha=1.0, *, kind, out2, bias=None, bias_dims=N
     if logical_dims is not None:
         ep.logical_dims = logical_dims.encode()
     ep.discard_c = 1 if discard_c else 0      # c then only gives the geometry; it is not stored
-    check(_lib.load().sb_einsum_fused(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
+    check(_cur().sb_einsum_fused(_stream(), ad.encode(), _d(a), bd.encode(), _d(b), cd.encode(), _d(c),
                                       float(alpha), ctypes.byref(ep)))
 
 
+def _loaded():
+    """Every library build this process has loaded (the float16 one is loaded if none is yet)."""
+    return list(_lib._libs.values()) or [_lib.load()]
+
+
 def device_error():
-    """Code set on the current device when a bounded wait inside a tcgen05 kernel ran out (0 = none since the
-    last ``device_error_reset``)."""
-    code = ctypes.c_int(0)
-    check(_lib.load().sb_device_error(_stream(), ctypes.byref(code)))
-    return code.value
+    """Code set on the current device when a bounded wait inside a kernel ran out (0 = none since the last
+    ``device_error_reset``); every loaded build of the library is asked."""
+    for lib in _loaded():
+        code = ctypes.c_int(0)
+        _lib.check(lib.sb_device_error(_stream(), ctypes.byref(code)), lib)
+        if code.value:
+            return code.value
+    return 0
 
 
 def device_error_reset():
     """Clear that code once the failed pass has been dealt with (while it is set, every tcgen05 kernel on the
     device gives up its waits at once)."""
-    check(_lib.load().sb_device_error_reset(_stream()))
+    for lib in _loaded():
+        _lib.check(lib.sb_device_error_reset(_stream()), lib)
 
 
 def mma_peak_probe(k_blocks, bf16=False):
     """Enqueue one MMA-only launch (see ``sb_mma_peak_probe``) on the current stream; returns its FLOP count."""
     fl = ctypes.c_double(0.0)
-    check(_lib.load().sb_mma_peak_probe(_stream(), int(k_blocks), 1 if bf16 else 0, ctypes.byref(fl)))
+    lib = _lib.load()
+    _lib.check(lib.sb_mma_peak_probe(_stream(), int(k_blocks), 1 if bf16 else 0, ctypes.byref(fl)), lib)
     return fl.value
 
 
 def set_sm_budget(n_sms):
     """Let the persistent contraction kernels occupy only ``n_sms`` SMs (0 = all), leaving the
-    rest to a kernel that runs beside them, e.g. the NCCL allreduce of the data-parallel path."""
-    check(_lib.load().sb_set_sm_budget(int(n_sms)))
+    rest to a kernel that runs beside them, e.g. the NCCL allreduce of the data-parallel path.  Applies to both
+    storage-type builds of the library."""
+    for key in ('fp16', 'bf16'):
+        lib = _lib.load(key)
+        _lib.check(lib.sb_set_sm_budget(int(n_sms)), lib)

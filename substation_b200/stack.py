@@ -21,18 +21,18 @@ from .encoder import Encoder
 class EncoderStack:
     def __init__(self, num_layers, batch_size, max_seq_len, num_heads, embedding_size, layouts,
                  dropout_p=0.1, device='cuda', mask_mode='philox', seed=0, activation='relu',
-                 weight_std=0.02, group=None):
+                 weight_std=0.02, group=None, dtype=torch.float16):
         self.device = torch.device(device)
         self.layers = []
         gen = torch.Generator(device=self.device).manual_seed(seed)
         for l in range(num_layers):
-            enc = Encoder('', batch_size, max_seq_len, num_heads, embedding_size, layouts, torch.float16,
+            enc = Encoder('', batch_size, max_seq_len, num_heads, embedding_size, layouts, dtype,
                           dropout_p, dropout_p, dropout_p, dropout_p, mask_mode=mask_mode, seed=seed + l,
                           activation=activation).to(self.device)
             with torch.no_grad():
                 for (name, _), prm in zip(layouts['params'], enc.params):
                     if name in ('WKQV', 'WO', 'LINW1', 'LINW2'):
-                        prm.copy_((torch.randn(prm.shape, device=self.device, generator=gen) * weight_std).half())
+                        prm.copy_((torch.randn(prm.shape, device=self.device, generator=gen) * weight_std).to(dtype))
                     elif name in ('S1', 'S2'):
                         prm.fill_(1.0)
                     else:
@@ -46,9 +46,9 @@ class EncoderStack:
                     for enc in self.layers]
         self.bwd = e0.views('backward', torch.empty(e0.arena_bytes('backward'), dtype=torch.uint8, device=self.device))
         # activations between layers: acts[l] is the input of layer l, acts[-1] the output
-        self.acts = [torch.empty(shape_x, dtype=torch.float16, device=self.device) for _ in range(num_layers + 1)]
-        self.dacts = [torch.empty(shape_x, dtype=torch.float16, device=self.device) for _ in range(2)]
-        self.reducer = GradientBucketReducer(e0.arena_bytes('grads'), self.device, group=group, buffers=num_layers)
+        self.acts = [torch.empty(shape_x, dtype=dtype, device=self.device) for _ in range(num_layers + 1)]
+        self.dacts = [torch.empty(shape_x, dtype=dtype, device=self.device) for _ in range(2)]
+        self.reducer = GradientBucketReducer(e0.arena_bytes('grads'), self.device, group=group, buffers=num_layers, dtype=dtype)
         self.grads = [enc.views('grads', self.reducer.arenas[l]) for l, enc in enumerate(self.layers)]
         if mask_mode == 'explicit':
             raise NotImplementedError('the stack draws its masks in the kernels (Philox); explicit masks are a '

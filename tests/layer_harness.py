@@ -31,43 +31,48 @@ def to_dev(a, logical, layout, device, dtype=torch.float16):
     return torch.from_numpy(orc.to_layout(np.asarray(a), logical, layout)).to(device=device, dtype=dtype)
 
 
-def make_case(B, J, H, P, seed, p, random_affine=True, w_std=0.02, explicit_masks=True):
-    """Seeded inputs in logical order, rounded to fp16 so that oracle and kernels see
+def round_to(a, dtype):
+    """Round float64 data to the storage type and return it as float64 (what the kernels will see)."""
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dtype).double().numpy()
+
+
+def make_case(B, J, H, P, seed, p, random_affine=True, w_std=0.02, explicit_masks=True, dtype=torch.float16):
+    """Seeded inputs in logical order, rounded to the storage type so that oracle and kernels see
     identical values.  X ~ N(0,1), weights ~ N(0, w_std), dY ~ N(0,1)."""
     rng = np.random.default_rng(seed)
     I, U = H * P, 4 * H * P
     params = orc.make_params(H, P, U, rng, w_std=w_std, random_affine=random_affine)
-    params = {k: v.astype(np.float16).astype(np.float64) for k, v in params.items()}
-    X = rng.normal(0, 1, (B, J, I)).astype(np.float16).astype(np.float64)
-    DY = rng.normal(0, 1, (B, J, I)).astype(np.float16).astype(np.float64)
+    params = {k: round_to(v, dtype) for k, v in params.items()}
+    X = round_to(rng.normal(0, 1, (B, J, I)), dtype)
+    DY = round_to(rng.normal(0, 1, (B, J, I)), dtype)
     masks = orc.make_masks(B, J, H, I, U, p, seed) if explicit_masks else None
     return X, DY, params, masks
 
 
 def run_layer_case(B, J, H, P, layouts='uniform', p=0.1, activation='relu', mask_mode='explicit',
                    seed=0, device='cuda:0', tol=1e-2, random_affine=True, w_std=0.02,
-                   case=None, return_report=False):
+                   case=None, return_report=False, dtype=torch.float16):
     """Returns the worst rel-L2 over all compared tensors (asserts each <= tol)."""
     lay = get_layouts(layouts)
     table = L.validate(lay)
     ps = (p, p, p, p) if np.isscalar(p) else tuple(p)
     if case is None:
         X, DY, params, masks = make_case(B, J, H, P, seed, ps, random_affine, w_std,
-                                         explicit_masks=(mask_mode == 'explicit'))
+                                         explicit_masks=(mask_mode == 'explicit'), dtype=dtype)
     else:
         X, DY, params, masks = case
     I = H * P
-    enc = Encoder('/tmp/substation_b200_unused', B, J, H, I, lay, torch.float16, *ps,
+    enc = Encoder('/tmp/substation_b200_unused', B, J, H, I, lay, dtype, *ps,
                   enable_debug=True, activation=activation, mask_mode=mask_mode, seed=seed)
     enc = enc.to(device)
     enc.train()
     with torch.no_grad():
         for (name, layout), prm in zip(lay['params'], enc.params):
-            prm.copy_(to_dev(params[name], L.LOGICAL[name], layout, device))
+            prm.copy_(to_dev(params[name], L.LOGICAL[name], layout, device, dtype))
     if mask_mode == 'explicit':
         enc.set_masks({n: to_dev(masks[n], L.LOGICAL[n], table[n], device, torch.uint8) for n in L.MASKS})
-    Xd = to_dev(X, 'BJI', table['X'], device).requires_grad_(True)
-    DYd = to_dev(DY, 'BJI', table['SB2'], device)
+    Xd = to_dev(X, 'BJI', table['X'], device, dtype).requires_grad_(True)
+    DYd = to_dev(DY, 'BJI', table['SB2'], device, dtype)
     first_offset = enc.philox_offset
     Y = enc(Xd)
     Y.backward(DYd)
@@ -109,7 +114,7 @@ def run_layer_case(B, J, H, P, layouts='uniform', p=0.1, activation='relu', mask
         assert np.isfinite(got).all(), f'{name}: non-finite values'
         assert r <= tol, f'{name}: rel-L2 {r:.3e} > {tol}'
 
-    cmp('Y', orc.from_layout(Y.detach().cpu().numpy(), table['SB2'], 'BJI'), f['SB2'])
+    cmp('Y', orc.from_layout(Y.detach().float().cpu().numpy(), table['SB2'], 'BJI'), f['SB2'])
     for n in enc._fwd_names:
         if n in L.MASKS:
             continue
@@ -118,7 +123,7 @@ def run_layer_case(B, J, H, P, layouts='uniform', p=0.1, activation='relu', mask
         else:
             want = f[n]
         cmp(n, dbg(n), want)
-    cmp('DX', orc.from_layout(Xd.grad.cpu().numpy(), table['X'], 'BJI'), g['DX'])
+    cmp('DX', orc.from_layout(Xd.grad.float().cpu().numpy(), table['X'], 'BJI'), g['DX'])
     for n in enc._bwd_names:
         got, want = dbg(n), g[n]
         cmp(n, got, want)
@@ -127,6 +132,6 @@ def run_layer_case(B, J, H, P, layouts='uniform', p=0.1, activation='relu', mask
         cmp('D' + n, got, g['D' + n])
         # the same gradient must reach autograd
         ag = getattr(enc, n).grad
-        assert ag is not None and np.array_equal(ag.cpu().numpy(), enc.debug['D' + n]), n
+        assert ag is not None and np.array_equal(ag.float().cpu().numpy(), enc.debug['D' + n].astype(np.float32)), n
     worst = max(report.values())
     return (worst, report) if return_report else worst

@@ -26,9 +26,11 @@ def test_every_declared_symbol_is_exported_and_bound():
         text = re.sub(r'/\*.*?\*/', '', f.read(), flags=re.S)
     declared = set(re.findall(r'\b(sb_[a-z0-9_]+)\s*\(', text))
     assert declared, 'no declarations found'
-    lib = ctypes.CDLL(_lib.lib_path())
-    for name in declared:
-        assert hasattr(lib, name), f'{name} declared in the header but not exported'
+    for key in ('fp16', 'bf16'):                       # one build of the same sources per storage type
+        lib = ctypes.CDLL(_lib.lib_path(key))
+        for name in declared:
+            assert hasattr(lib, name), f'{name} declared in the header but not exported by the {key} build'
+        assert key.encode() in _lib.load(key).sb_version()
     assert declared == set(_lib.SIGNATURES), (declared ^ set(_lib.SIGNATURES))
 
 

@@ -306,3 +306,30 @@ def test_mma_peak_probe_runs_and_reports_its_flops(bf16):
     (t0, f0), (t1, f1) = times
     assert t1 > 4 * t0 and f1 == 16 * f0
     assert 100e12 < f1 / (t1 * 1e-3) < 3000e12, f'{f1 / (t1 * 1e-3) / 1e12:.0f} TFLOP/s is not a plausible tensor rate'
+
+
+def test_bfloat16_build_contractions_and_epilogue():
+    """bfloat16 operands go to the bf16 build of the library (the MMA instruction descriptor and the conversions are
+    all that differs): paired-CTA contraction with a fused bias epilogue, a batched attention-shaped contraction, and
+    the SIMT fall-back, against float64 einsums.  Tolerance 2e-2 (bf16 keeps 8 significant bits)."""
+    ops = _ops()
+    g = torch.Generator(device=DEV).manual_seed(3)
+    rnd = lambda *s, std=1.0: (torch.randn(*s, device=DEV, generator=g) * std).to(torch.bfloat16)
+    f64 = lambda t: t.double().cpu().numpy()
+    B, J, I, U = 4, 512, 256, 1280
+    x, w, bias = rnd(B, J, I), rnd(I, U, std=0.08), rnd(U, std=0.5)
+    c, out2 = (torch.empty(B, J, U, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+    ops.einsum_fused('bji,iu->bju', x, w, c, kind='bias', bias=bias, bias_dims='u', out2=out2)
+    want = np.einsum('bji,iu->bju', f64(x), f64(w))
+    assert orc.rel_l2(f64(c), want) < 2e-2 and orc.rel_l2(f64(out2), want + f64(bias)) < 2e-2
+    q, k = rnd(64, 2, 3, 256), rnd(64, 2, 3, 256)
+    s = torch.empty(2, 3, 256, 256, device=DEV, dtype=torch.bfloat16)
+    assert ops.einsum('phbk,phbj->hbjk', k, q, s, alpha=0.125) == 'tcgen05'
+    assert orc.rel_l2(f64(s), 0.125 * np.einsum('phbk,phbj->hbjk', f64(k), f64(q))) < 2e-2
+    a, b = rnd(37, 21), rnd(13, 21)
+    o = torch.empty(37, 13, device=DEV, dtype=torch.bfloat16)
+    ops.einsum('mk,nk->mn', a, b, o, impl='simt')
+    assert orc.rel_l2(f64(o), f64(a) @ f64(b).T) < 2e-2
+    with pytest.raises(TypeError):
+        ops.einsum('mk,nk->mn', a, b.half(), o)
+    assert ops.device_error() == 0
