@@ -504,16 +504,18 @@ def run_ours(args):
     # feed-forward half, final in the middle of the backward pass, are allreduced beside the attention half of the
     # pass instead: measured slower in steady state (the allreduce then competes with the HBM-bound attention
     # kernels rather than with the next step's tensor-bound projections).
+    # The LAST step of a timed region has no next step to hide behind: there the feed-forward half is started early
+    # (--early-last 1, the default), which shortens the drain that ends the region.
     early = None
-    if world > 1 and args.early_allreduce:
+    if world > 1 and (args.early_allreduce or args.early_last):
         ffn_event = torch.cuda.Event()
         enc.set_ffn_grads_event(ffn_event)
         early = (enc.early_grad_offset(), ffn_event)
 
-    def step(i):
+    def step(i, last=False):
         reducer.wait(i)                                   # this bucket's previous reduction has finished
         lb.run(grad_views[i % len(grad_views)])
-        reducer.reduce_async(i, early=early)
+        reducer.reduce_async(i, early=early if (args.early_allreduce or (last and args.early_last)) else None)
 
     drain = reducer.drain
 
@@ -542,7 +544,7 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(n_steps):
-            step(i)
+            step(i, last=(i == n_steps - 1))
         drain()
         e1.record()
         barrier()
@@ -666,9 +668,10 @@ def run_ours(args):
         works = [None, None]
         for prm in enc.params:
             prm.requires_grad_(True)
-        # the autograd path writes its gradients into these two caller-held buckets in turn, so the collective
-        # sees the same two buffers every step
-        enc.set_grad_arenas([torch.empty(enc.arena_bytes('grads'), dtype=torch.uint8, device=dev) for _ in range(2)])
+        # The module keeps two sets of buffers for its autograd path and uses them in turn (set_buffer_pool): the
+        # pointers of a pass repeat every other step, so passes replay as CUDA graphs, and the collective sees the
+        # same two gradient buckets every step.  Y and dX are copied to the host before their set comes round again.
+        enc.set_buffer_pool(2)
 
         def copy_in(i):
             b = i & 1
@@ -693,9 +696,10 @@ def run_ours(args):
             copy_in(i + 1)
             cur.wait_event(ev_in[b])
             x = xd[b].detach().requires_grad_(True)
-            if works[b] is not None:                           # the bucket this backward writes is free again
+            if works[b] is not None:                           # the bucket this backward writes (used two steps ago) is free again
                 works[b].wait()
                 works[b] = None
+            cur.wait_event(ev_out[b])                          # ... and so are the Y / dX of that set (copied out)
             y = enc(x)
             y.backward(dyd[b])
             ev_free[b].record(cur)
@@ -748,7 +752,7 @@ def run_ours(args):
             copy_only_step(i)
         e2e_drain()
         copy_ms, _ = e2e_region(copy_only_step, first + 2, args.steps)
-        enc.set_grad_arenas(None)
+        enc.set_buffer_pool(0)
         nbytes = hX.numel() * 2
         e2e = {'value': world * B * args.steps / (e2e_ms / 1e3), 'unit': UNIT,
                'h2d_bytes_per_step': 2 * nbytes, 'd2h_bytes_per_step': 2 * nbytes,
@@ -1038,6 +1042,8 @@ def main():
     ap.add_argument('--early-allreduce', type=int, default=0,
                     help='N > 1: sum the feed-forward gradients beside the attention half of backward (1) or the whole '
                          'bucket beside the next step (0)')
+    ap.add_argument('--early-last', type=int, default=1,
+                    help='N > 1: start the allreduce of the feed-forward gradients early on the last step of a timed region')
     ap.add_argument('--layers', type=int, default=1, help='>1: time a stack of layers (the 24-layer configuration uses 24)')
     ap.add_argument('--kernels', action='store_true', help='time every fused operator alone at the kernel-sweep shapes')
     ap.add_argument('--keep-all', type=int, default=0,

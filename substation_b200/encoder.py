@@ -132,9 +132,15 @@ class Encoder(torch.nn.Module):
                 outer._check_input(X, 'X')
                 X = X.contiguous()
                 weights = tuple(w if w.is_contiguous() else w.contiguous() for w in weights)
-                Y = torch.empty_like(X)
                 plan, total = outer._fwd_plan
-                arena = torch.empty(max(total, 1), dtype=torch.uint8, device=X.device)
+                pooled = outer._pool_set(X) if outer.__dict__.get('_pool_n') else None
+                if pooled is not None:
+                    Y, arena = pooled['Y'], pooled['fwd']
+                    ctx.pool_set = pooled
+                else:
+                    Y = torch.empty_like(X)
+                    arena = torch.empty(max(total, 1), dtype=torch.uint8, device=X.device)
+                    ctx.pool_set = None
                 over = outer._explicit_masks(X.device) if outer.mask_mode == 'explicit' else {}
                 outer._forward_ptrs(X, weights, outer._plan_ptrs(plan, arena, over), Y)
                 ctx.save_for_backward(*weights, arena, X)
@@ -156,11 +162,16 @@ class Encoder(torch.nn.Module):
                 weights, arena, X = saved[:np_], saved[np_], saved[-1]
                 outer._check_input(DY, 'DY')
                 DY = DY.contiguous()
-                DX = torch.empty_like(DY)
                 bplan, btotal = outer._bwd_plan
                 gplan, gtotal = outer._grad_plan
-                barena = torch.empty(max(btotal, 1), dtype=torch.uint8, device=DY.device)
-                garena = outer._next_grad_arena(gtotal, DY.device)
+                if ctx.pool_set is not None:
+                    DX, barena = ctx.pool_set['DX'], ctx.pool_set['bwd']
+                    garena = ctx.pool_set['grads'] if not outer.__dict__.get('_grad_arenas') else \
+                        outer._next_grad_arena(gtotal, DY.device)
+                else:
+                    DX = torch.empty_like(DY)
+                    barena = torch.empty(max(btotal, 1), dtype=torch.uint8, device=DY.device)
+                    garena = outer._next_grad_arena(gtotal, DY.device)
                 outer._backward_ptrs(DY, outer._plan_ptrs(gplan, garena, {}), outer._plan_ptrs(bplan, barena, {}), weights,
                                      outer._plan_ptrs(outer._fwd_plan[0], arena, ctx.masks), X, DX)
                 g16 = garena[:max(gtotal, 2)].view(outer.torch_dtype)
@@ -339,7 +350,7 @@ class Encoder(torch.nn.Module):
     def _forward_ptrs(self, X, weights, fwd_ptrs, Y):
         lib = _lib.load(self._lib_key)
         h = self._native(X.device)
-        self._graphs_now(h, _AUTOGRAD_GRAPHS)
+        self._graphs_now(h, _AUTOGRAD_GRAPHS or bool(self.__dict__.get('_pool_n')))
         mode = _lib.SB_MASK_PHILOX if self.mask_mode == 'philox' else _lib.SB_MASK_EXPLICIT
         stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
         self._check(lib.sb_encoder_forward(h, stream, ctypes.c_void_p(X.data_ptr()), self._ptrs(weights), fwd_ptrs,
@@ -349,7 +360,7 @@ class Encoder(torch.nn.Module):
     def _backward_ptrs(self, DY, grad_ptrs, bwd_ptrs, weights, fwd_ptrs, X, DX):
         lib = _lib.load(self._lib_key)
         h = self._native(DY.device)
-        self._graphs_now(h, _AUTOGRAD_GRAPHS)
+        self._graphs_now(h, _AUTOGRAD_GRAPHS or bool(self.__dict__.get('_pool_n')))
         stream = ctypes.c_void_p(torch.cuda.current_stream(DY.device).cuda_stream)
         self._check(lib.sb_encoder_backward(h, stream, ctypes.c_void_p(DY.data_ptr()), grad_ptrs, bwd_ptrs,
                                            self._ptrs(weights), fwd_ptrs, ctypes.c_void_p(X.data_ptr()),
@@ -453,6 +464,34 @@ class Encoder(torch.nn.Module):
                 ev.record()
             handle = ctypes.c_void_p(ev.cuda_event)
         self._check(_lib.load(self._lib_key).sb_encoder_set_ffn_grads_event(self._handle, handle))
+
+    def set_buffer_pool(self, n):
+        """``n`` > 0: the autograd path stops allocating per pass and takes the forward arena, the output, the backward
+        arena, the input gradient and the gradient bucket from ``n`` sets of buffers the module owns, used in turn
+        (allocated on first use).  The pointers of a pass then repeat every ``n`` steps, so passes are replayed as
+        CUDA graphs with one launch each instead of some thirty, which is what an input pipeline that feeds the
+        module from a few rotating device buffers wants.  The price: a tensor returned by ``forward`` (or a
+        gradient produced by ``backward``) is overwritten ``n`` steps later; copy what must live longer.  ``n`` = 0
+        (the default) restores the reference's behaviour, fresh tensors every pass
+        (pytorch_module/encoder.py:80-85, :110-121)."""
+        self._pool_n = int(n)
+        self._pool = []
+        self._pool_turn = 0
+
+    def _pool_set(self, X):
+        if len(self._pool) < self._pool_n:
+            dev = X.device
+            self._pool.append({
+                'Y': torch.empty_like(X), 'DX': torch.empty_like(X),
+                'fwd': torch.empty(max(self._fwd_plan[1], 1), dtype=torch.uint8, device=dev),
+                'bwd': torch.empty(max(self._bwd_plan[1], 1), dtype=torch.uint8, device=dev),
+                'grads': torch.empty(max(self._grad_plan[1], 2), dtype=torch.uint8, device=dev)})
+            return self._pool[-1]
+        s = self._pool[self._pool_turn % self._pool_n]
+        self._pool_turn += 1
+        if s['Y'].device != X.device:
+            raise ValueError('the buffer pool lives on another device than the input; call set_buffer_pool again')
+        return s
 
     def set_grad_arenas(self, arenas):
         """Caller-held storage for the parameter gradients of the autograd path: a list of contiguous uint8 CUDA
