@@ -9,7 +9,10 @@
 // tile is produced by tcgen05.mma into tensor memory (L fp32 columns).  Eight epilogue warps read it
 // back: two per 32-lane quadrant of tensor memory, thread = one query row, the two warps of a
 // quadrant taking alternate 64-key chunks and exchanging their partial row maximum / row sums
-// through shared memory.  The scores never make a second trip through HBM: the forward kernel
+// through shared memory.  The forward softmax is an online one: the first pass exponentiates every
+// 32-key piece against the row maximum seen so far (rescaling the running sum when it rises) and
+// leaves the exponentials in tensor memory, the second brings each piece to the final maximum while
+// it normalises and writes; a separate maximum pass over the tile is not needed.  The scores never make a second trip through HBM: the forward kernel
 // does not read BETA back, the backward kernel does not read DATTN_DROP back (it keeps
 // (mask*dattn_drop, alpha) as an fp16 pair per tensor-memory word between its two passes).
 // Inputs that stream per row (the dropout mask, ALPHA in the backward kernel) arrive through
@@ -27,14 +30,15 @@ constexpr int kNW = 2;                               // epilogue warps per tenso
 constexpr int kEpiWarps = 4 * kNW;
 constexpr int kThreads = 64 + 32 * kEpiWarps;        // producer warp, MMA warp, epilogue warps
 constexpr int kOperandBytes = kABytes + kMaxL * 128; // 128 x 64 queries + up to 512 x 64 keys, fp16
-constexpr int kRedBytes = 2 * kNW * 128 * 4;         // partial row maxima and row sums
+constexpr int kRedBytes = 2 * 2 * kNW * 128 * 4;     // partial row maxima and row sums, two sets used by alternate tiles
+constexpr int kRefBytes = 8 * kEpiWarps * 32 * 4;    // forward: the maximum each 32-column piece of a row was scaled by
 
 template <bool BWD>
 struct Cfg {
   static constexpr int kOutBufs = BWD ? 2 : 3;       // staging buffers (32 rows x 128 B) per warp
   static constexpr int kInSlot = BWD ? 6144 : 2048;  // ALPHA rows (4 KiB) + mask rows (2 KiB) | mask rows
   static constexpr int kStaging = kEpiWarps * kOutBufs * 4096;
-  static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot + kRedBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot + kRedBytes + (BWD ? 0 : kRefBytes) + 1024 + 256;
 };
 
 struct Params {
@@ -145,12 +149,14 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t staging = operands + kOperandBytes;
   const uint32_t inslots = staging + C::kStaging;
   const uint32_t red = inslots + kEpiWarps * C::kInSlot;
-  const uint32_t bars = red + kRedBytes;  // full, empty, tmem_full, tmem_empty, tmem_full[2], tmem_empty[2], in_full[kEpiWarps], epilogue barrier, tmem slot
+  const uint32_t refs = red + kRedBytes;                    // forward only
+  const uint32_t bars = refs + (BWD ? 0 : kRefBytes);  // full, empty, tmem_full, tmem_empty, tmem_full[2], tmem_empty[2], in_full[kEpiWarps], epilogue barrier, tmem slot
   const uint32_t bar_full = bars, bar_empty = bars + 8, bar_tfull = bars + 16, bar_tempty = bars + 32, bar_in = bars + 48;
   const uint32_t bar_epi = bar_in + 8 * kEpiWarps;
   uint8_t* gen_base = smem_raw + (operands - raw);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 64 + 8 * kEpiWarps);
   float* red_gen = reinterpret_cast<float*>(gen_base + (red - operands));
+  float* ref_gen = reinterpret_cast<float*>(gen_base + (refs - operands));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int L = p.L;
@@ -352,27 +358,28 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       auto no_op = [](int) {};
 
       if (!BWD) {
-        // pass 1: row maximum of the raw accumulator (scale > 0)
-        float mx = -INFINITY;
+        // pass 1 (online softmax): e = 2^(t - m) back into tensor memory, where m is the row maximum SO FAR (over
+        // the pieces this warp has seen); when a piece raises m, the running sum is rescaled.  The m each 32-column
+        // piece was scaled by is kept (shared memory, one float per thread and piece) so that the last pass can
+        // bring every piece to the final maximum.  BETA out unless it is not wanted.  (scale > 0.)
+        float mrun = -INFINITY, sum = 0.f;
+        float* my_ref = ref_gen + (ew * 32 + lane);
         if (rows)
-          sweep_halves(trow, h, nc64, wait_half, no_op, [&](int, int, uint32_t* r) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-          });
-        red_gen[h * 128 + rt] = mx;
-        ok = epi_barrier(bar_epi, n_bar, lane) && ok;
-#pragma unroll
-        for (int w = 0; w < kNW; ++w) mx = fmaxf(mx, red_gen[w * 128 + rt]);
-        const float mxs = mx * c2;
-        // pass 2: e = 2^(t - max) back into tensor memory, partial row sum, BETA out
-        float sum = 0.f;
-        if (rows)
-          sweep(trow, h, nc64, [&](int c, int hh, uint32_t* r) {
+          sweep_halves(trow, h, nc64, wait_half, no_op, [&](int c, int hh, uint32_t* r) {
             const uint32_t b = n_out % NB;
             if (hh == 0 && !p.skip_o0) {
               if (lane == 0) bulk_wait_read<NB - 1>();
               __syncwarp();
             }
+            float mx = mrun;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+            if (mx > mrun) {
+              sum *= ex2_approx((mrun - mx) * c2);      // 0 for the first piece (mrun = -inf, sum = 0)
+              mrun = mx;
+            }
+            my_ref[((c / kNW) * 2 + hh) * (kEpiWarps * 32)] = mrun;
+            const float mxs = mrun * c2;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               float f[8];
@@ -395,13 +402,23 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           });
         tmem_st_wait();
-        red_gen[(kNW + h) * 128 + rt] = sum;
+        // the warps of a quadrant combine their (maximum, sum) pairs; alternate tiles use alternate slots, so a
+        // warp already in the next tile never overwrites what a slower one still reads
+        float* rset = red_gen + (it & 1u) * (2 * kNW * 128);
+        rset[h * 128 + rt] = mrun;
+        rset[(kNW + h) * 128 + rt] = sum;
         ok = epi_barrier(bar_epi, n_bar, lane) && ok;
+        float mfin = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) mfin = fmaxf(mfin, rset[w * 128 + rt]);
         sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kNW; ++w) sum += red_gen[(kNW + w) * 128 + rt];
+        for (int w = 0; w < kNW; ++w) {
+          const float mw_ = rset[w * 128 + rt];
+          if (mw_ > -INFINITY) sum = fmaf(rset[(kNW + w) * 128 + rt], ex2_approx((mw_ - mfin) * c2), sum);
+        }
         const float inv = 1.f / sum;
-        // pass 3: ALPHA = e / sum, ATTN_DROP = mask * ALPHA
+        // pass 2: ALPHA = e * 2^(m_piece - m_final) / sum, ATTN_DROP = mask * ALPHA
         uint32_t mall[16];  // the mask bytes of this thread's row for one 64-column chunk
         if (rows)
           sweep_halves(trow, h, nc64, no_op, release_half, [&](int c, int hh, uint32_t* r) {
@@ -446,11 +463,13 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               if (lane == 0) bulk_wait_read<NB - 2>();
               __syncwarp();
             }
+            // bring this piece from the maximum it was scaled by to the row's final one, and normalise
+            const float fac = ex2_approx((my_ref[((c / kNW) * 2 + hh) * (kEpiWarps * 32)] - mfin) * c2) * inv;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               float f[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * inv;
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * fac;
               const uint4 al = pack8(f);
               *stage_ptr(b0, hh * 4 + v) = al;
               *stage_ptr(b1, hh * 4 + v) = mask_apply(al, make_uint2(mw[2 * v], mw[2 * v + 1]));
@@ -536,11 +555,12 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           });
         tmem_st_wait();
-        red_gen[h * 128 + rt] = ssum;
+        float* rset = red_gen + (it & 1u) * (2 * kNW * 128);   // alternate tiles, alternate slots (see forward)
+        rset[h * 128 + rt] = ssum;
         ok = epi_barrier(bar_epi, n_bar, lane) && ok;
         ssum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kNW; ++w) ssum += red_gen[w * 128 + rt];
+        for (int w = 0; w < kNW; ++w) ssum += rset[w * 128 + rt];
         // backward pass 2: DBETA = alpha * (da - s)
         if (rows)
           sweep_halves(trow, h, nc64, no_op, release_half, [&](int c, int hh, uint32_t* r) {
