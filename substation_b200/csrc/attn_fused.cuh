@@ -37,8 +37,9 @@ template <bool BWD>
 struct Cfg {
   static constexpr int kOutBufs = BWD ? 2 : 3;       // staging buffers (32 rows x 128 B) per warp
   static constexpr int kInSlot = BWD ? 6144 : 2048;  // ALPHA rows (4 KiB) + mask rows (2 KiB) | mask rows
+  static constexpr int kSlots = BWD ? 1 : 2;         // input chunks in flight per warp (what shared memory allows)
   static constexpr int kStaging = kEpiWarps * kOutBufs * 4096;
-  static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot + kRedBytes + (BWD ? 0 : kRefBytes) + 1024 + 256;
+  static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot * kSlots + kRedBytes + (BWD ? 0 : kRefBytes) + 1024 + 256;
 };
 
 struct Params {
@@ -148,13 +149,13 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t operands = (raw + 1023u) & ~1023u;
   const uint32_t staging = operands + kOperandBytes;
   const uint32_t inslots = staging + C::kStaging;
-  const uint32_t red = inslots + kEpiWarps * C::kInSlot;
+  const uint32_t red = inslots + kEpiWarps * C::kInSlot * C::kSlots;
   const uint32_t refs = red + kRedBytes;                    // forward only
   const uint32_t bars = refs + (BWD ? 0 : kRefBytes);  // full, empty, tmem_full, tmem_empty, tmem_full[2], tmem_empty[2], in_full[kEpiWarps], epilogue barrier, tmem slot
   const uint32_t bar_full = bars, bar_empty = bars + 8, bar_tfull = bars + 16, bar_tempty = bars + 32, bar_in = bars + 48;
-  const uint32_t bar_epi = bar_in + 8 * kEpiWarps;
+  const uint32_t bar_epi = bar_in + 8 * kEpiWarps * C::kSlots;
   uint8_t* gen_base = smem_raw + (operands - raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 64 + 8 * kEpiWarps);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + (bars - operands) + 64 + 8 * kEpiWarps * C::kSlots);
   float* red_gen = reinterpret_cast<float*>(gen_base + (red - operands));
   float* ref_gen = reinterpret_cast<float*>(gen_base + (refs - operands));
 
@@ -170,7 +171,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, kEpiWarps);
     }
-    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar_in + 8 * w, 1);
+    for (int w = 0; w < kEpiWarps * C::kSlots; ++w) mbar_init(bar_in + 8 * w, 1);
     mbar_init(bar_epi, kEpiWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -288,26 +289,28 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int nc64 = L / 64;
     const uint32_t my_stage = staging + (uint32_t)ew * NB * 4096;
     uint8_t* my_stage_gen = gen_base + (my_stage - operands);
-    const uint32_t my_in = inslots + (uint32_t)ew * C::kInSlot;
-    const uint8_t* my_in_gen = gen_base + (my_in - operands);
-    const uint32_t my_bar = bar_in + 8 * ew;
+    constexpr int NSL = C::kSlots;
+    const uint32_t my_in = inslots + (uint32_t)ew * C::kInSlot * NSL;      // this warp's NSL slots, back to back
+    const uint8_t* my_in_gen0 = gen_base + (my_in - operands);
+    const uint32_t my_bar0 = bar_in + 8 * ew * NSL;
     const float c2 = p.scale * 1.4426950408889634f;
     const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
     const int G = gridDim.x;
 
     auto tile_has_rows = [&](int t) { return (t % p.tiles_j) * 128 + q * 32 < L; };
     // fetch the row inputs of chunk c of tile t into this warp's slot (lane 0)
-    auto fetch_in = [&](int t, int c) {
+    auto fetch_in = [&](int t, int c, uint32_t slot) {
       const int jr = (t % p.tiles_j) * 128 + q * 32;
       const int bt = t / p.tiles_j;
-      mbar_expect_tx(my_bar, (uint32_t)C::kInSlot);
+      const uint32_t bar = my_bar0 + 8 * slot, dst = my_in + slot * (uint32_t)C::kInSlot;
+      mbar_expect_tx(bar, (uint32_t)C::kInSlot);
       if (BWD) {
-        if (p.swap_o) tma_load_3d(my_in, &tmI, my_bar, c * 64, bt, jr);
-        else tma_load_3d(my_in, &tmI, my_bar, c * 64, jr, bt);
+        if (p.swap_o) tma_load_3d(dst, &tmI, bar, c * 64, bt, jr);
+        else tma_load_3d(dst, &tmI, bar, c * 64, jr, bt);
       }
-      const uint32_t md = my_in + (BWD ? 4096u : 0u);
-      if (p.swap_o) tma_load_3d(md, &tmM, my_bar, c * 64, bt, jr);
-      else tma_load_3d(md, &tmM, my_bar, c * 64, jr, bt);
+      const uint32_t md = dst + (BWD ? 4096u : 0u);
+      if (p.swap_o) tma_load_3d(md, &tmM, bar, c * 64, bt, jr);
+      else tma_load_3d(md, &tmM, bar, c * 64, jr, bt);
     };
     // successor of (t, c) in this warp's sequence of input chunks
     auto next_in = [&](int& t, int& c) {
@@ -318,14 +321,30 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (tile_has_rows(t)) return true;
       return false;
     };
-    uint32_t n_in = 0;    // input chunks consumed (slot phase)
+    uint32_t n_in = 0;    // input chunks consumed (slot = n_in % NSL, phase = (n_in / NSL) & 1)
     uint32_t n_out = 0;   // staging buffers filled (buffer = n_out % NB)
     uint32_t n_bar = 0;   // uses of the epilogue barrier
+    // lane 0 keeps the cursor of the next chunk to fetch: NSL chunks are requested up front, and every chunk taken
+    // out of its slot lets the one NSL positions further in
+    int ft = blockIdx.x, fc = h;
+    bool fmore = false;
+    uint32_t n_f = 0;
     if (mask_in && h < nc64 && lane == 0) {
-      int t0 = blockIdx.x;
-      while (t0 < p.tiles && !tile_has_rows(t0)) t0 += G;
-      if (t0 < p.tiles) fetch_in(t0, h);
+      while (ft < p.tiles && !tile_has_rows(ft)) ft += G;
+      fmore = ft < p.tiles;
+      for (int i = 0; i < NSL && fmore; ++i) {
+        fetch_in(ft, fc, n_f % NSL);
+        ++n_f;
+        fmore = next_in(ft, fc);
+      }
     }
+    auto refill = [&]() {                  // lane 0, after the slot just read is free again
+      if (fmore) {
+        fetch_in(ft, fc, n_f % NSL);
+        ++n_f;
+        fmore = next_in(ft, fc);
+      }
+    };
 
     // staging: 16-byte piece i (0..7) of this thread's row in buffer b
     auto stage_ptr = [&](uint32_t b, int i) {
@@ -427,7 +446,9 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (!p.rng.philox) {
               if (hh == 0) {
                 // take the whole chunk out of the slot at once, so that the next fetch starts early
-                ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
+                const uint32_t slot = n_in % NSL;
+                const uint8_t* my_in_gen = my_in_gen0 + slot * C::kInSlot;
+                ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar0 + 8 * slot, (n_in / NSL) & 1u, 5));
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   uint4 m = make_uint4(0, 0, 0, 0);
@@ -437,11 +458,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ++n_in;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0 && ok) {
-                  int tn = t;
-                  int cn = c;
-                  if (next_in(tn, cn)) fetch_in(tn, cn);
-                }
+                if (lane == 0 && ok) refill();
               }
 #pragma unroll
               for (int i = 0; i < 8; ++i) mw[i] = mall[hh * 8 + i];
@@ -494,7 +511,9 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           sweep_halves(trow, h, nc64, wait_half, no_op, [&](int c, int hh, uint32_t* r) {
             if (hh == 0) {
               // take the whole chunk (ALPHA and mask rows) out of the slot, then refill it at once
-              ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar, n_in & 1u, 5));
+              const uint32_t slot = n_in % NSL;
+              const uint8_t* my_in_gen = my_in_gen0 + slot * C::kInSlot;
+              ok = ok && __all_sync(0xffffffffu, mbar_wait(my_bar0 + 8 * slot, (n_in / NSL) & 1u, 5));
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 aall[i] = make_uint4(0, 0, 0, 0);
@@ -509,11 +528,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               ++n_in;
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
-              if (lane == 0 && ok) {
-                int tn = t;
-                int cn = c;
-                if (next_in(tn, cn)) fetch_in(tn, cn);
-              }
+              if (lane == 0 && ok) refill();
             }
             uint4 araw[4];
             uint32_t mw[8];

@@ -272,8 +272,6 @@ struct TcParams {
   int tiles_m, tiles_n, batch;
   int splits, kt_per_split;  // split-K: K stages per split
   long long tiles;     // tiles_m * tiles_n * batch * splits
-  float* partials;     // paired-CTA split-K: fp32 partial tiles [split][batch][M][N]
-  unsigned* tickets;   // ... and two counters per (tile, CTA rank), zero before and after the launch
   EpiParams epi;       // paired-CTA kernel only
 };
 
@@ -848,8 +846,6 @@ int pair_epi_warps() {
   return ew;
 }
 
-constexpr size_t kPairTicketBytes = 4096;   // head of the split-K workspace: two counters per (tile, CTA rank)
-
 // Paired-CTA launch: 256 x 256 tiles, one cluster of two CTAs per tile.
 int pair_clusters() {
   static thread_local int cached_dev = -1, cached = 0;
@@ -883,14 +879,6 @@ int pair_clusters() {
   return cached;
 }
 
-bool pair_splitk_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("SUBSTATION_B200_PAIR_SPLITK");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 bool pair_enabled() {
   static const bool on = [] {
     const char* e = getenv("SUBSTATION_B200_PAIR");
@@ -899,14 +887,10 @@ bool pair_enabled() {
   return on;
 }
 
-// splits > 1: K is dealt out to that many clusters per tile (fp32 partials and counters in `ws`, reduced inside
-// the kernel); the caller has checked that all tiles * splits items are resident at once.
 int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b, int clusters,
-                   const GemmEpilogue* epi = nullptr, bool vec_flipped = false, int splits = 1, void* ws = nullptr) {
+                   const GemmEpilogue* epi = nullptr, bool vec_flipped = false) {
   TcParams p;
   memset(&p.epi, 0, sizeof(p.epi));
-  p.partials = nullptr;
-  p.tickets = nullptr;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
   p.C = g.C;
@@ -915,23 +899,15 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
   p.tiles_n = (int)((g.N + 255) / 256);
   p.tiles_m = (int)((g.M + 255) / 256);
   p.batch = (int)g.batch;
-  const int KT_all = (int)((g.K + kBK - 1) / kBK);
-  p.splits = splits;
-  p.kt_per_split = (KT_all + splits - 1) / splits;
-  p.splits = (KT_all + p.kt_per_split - 1) / p.kt_per_split;   // no split may be left without work
-  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch * p.splits;
+  p.splits = 1;
+  p.kt_per_split = (int)((g.K + kBK - 1) / kBK);
+  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
   CUtensorMap cmap;
   memset(&cmap, 0, sizeof(cmap));
   const bool c_vec = g.sCn == 1 && g.N % 8 == 0 && g.sCm % 8 == 0 && (g.batch == 1 || g.sCb % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0;
   p.c_mode = c_vec ? 1 : 0;
-  if (p.splits > 1) {
-    p.c_mode = 3;
-    p.tickets = reinterpret_cast<unsigned*>(ws);
-    p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kPairTicketBytes);
-    // the counters start at zero (the kernel leaves them at zero, but the workspace may be fresh)
-    SB_CUDA_OK(cudaMemsetAsync(ws, 0, kPairTicketBytes, s));
-  } else if (c_vec) {
+  if (c_vec) {
     std::string why;
     int swapped = 0;
     if (encode_map(g.C, (cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch, g.sCm, g.sCb, 64, 32, &cmap, &swapped, &why)) {
@@ -1059,25 +1035,6 @@ int launch_gemm_tcgen05_epi(cudaStream_t s, const GemmProblem& g0, void* ws, siz
     }
   }
   if (epi) return fail(SB_ERR_UNSUPPORTED, "fused epilogue: only the paired-CTA kernel (large single-batch problems) has it");
-  // Few output tiles, long K (the attention-output weight gradient): the paired-CTA kernel with K dealt out to up to
-  // four clusters per tile, every item resident at once, partials reduced inside the same launch.
-  if (ws && bn == 256 && g.batch == 1 && g.M >= 256 && g.N >= 256 && g.N % 8 == 0 && pair_enabled() && pair_splitk_enabled()) {
-    const int avail = std::min(pair_clusters(), sm_count() / 2);
-    const long long tiles2 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
-    const int KT = (int)((g.K + kBK - 1) / kBK);
-    int splits = (int)std::min<long long>(4, tiles2 > 0 ? avail / tiles2 : 0);
-    while (splits > 1 && KT / splits < 8) --splits;
-    if (splits > 1 && tiles2 * 4 * sizeof(unsigned) <= kPairTicketBytes &&
-        kPairTicketBytes + (size_t)splits * g.M * g.N * sizeof(float) <= ws_bytes) {
-      if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
-        return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
-      if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, 128, &b, &why))
-        return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand B: " + why);
-      const int st2 = launch_tc_pair(s, g, a, b, avail, nullptr, false, splits, ws);
-      if (st2 == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
-      return st2;
-    }
-  }
   if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
     return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
   if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))

@@ -102,7 +102,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t rank = cluster_rank();          // 0 = leader
   const unsigned cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
   const int KT = (int)((p.K + kBK - 1) / kBK);
-  const long long per_split = (long long)p.tiles_n * p.tiles_m * p.batch;   // items per K split (all of them when unsplit)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -138,12 +137,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t it = 0;
     bool ok = true;
     for (long long t = cluster_id; t < p.tiles && ok; t += nclusters) {
-      const long long tt = t % per_split;                                // item = (K split, tile)
-      const int kb_begin = (int)(t / per_split) * p.kt_per_split, kb_end = min(KT, kb_begin + p.kt_per_split);
-      const int n0 = (int)(tt % p.tiles_n) * kBN + (int)rank * 128;      // this CTA's half of B
-      const int m0 = (int)((tt / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
-      const int bt = (int)(tt / ((long long)p.tiles_n * p.tiles_m));
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+      const int n0 = (int)(t % p.tiles_n) * kBN + (int)rank * 128;       // this CTA's half of B
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
+      const int bt = (int)(t / ((long long)p.tiles_n * p.tiles_m));
+      for (int kb = 0; kb < KT; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, 1));
@@ -201,8 +198,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!ok) break;
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + buf * kBN;
-          const int kb_begin = (int)(t / per_split) * p.kt_per_split, kb_end = min(KT, kb_begin + p.kt_per_split);
-          for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          for (int kb = 0; kb < KT; ++kb, ++it) {
             const uint32_t s = it % S;
             const uint32_t ph = (it / S) & 1u;
             ok = mbar_wait(bar_full + 8 * s, ph, 2);
@@ -211,7 +207,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t da = da_base + s * stage_inc, db = db_base + s * stage_inc;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              umma_f16_pair(tmem_d, da + k * a_inc, db + k * b_inc, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+              umma_f16_pair(tmem_d, da + k * a_inc, db + k * b_inc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             // the stage is free in both CTAs once these MMAs have read it
             umma_commit_pair(bar_empty + 8 * s);
             umma_commit_pair(peer_empty + 8 * s);
@@ -228,20 +224,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue (both CTAs; each stores its own 128 rows) ----------------
     const int q = warp & 3;                    // the 32-lane quadrant of tensor memory this warp may read
     const int c_first = ((warp - 2) >> 2) * kChunks;   // its share of the tile's four 64-column chunks
-    // barrier over this CTA's epilogue warps only (split-K reduction) and a flag they share
-    auto epi_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory"); };
-    volatile int* epi_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t leader_acce = map_to_rank(bar_acce, 0);
     const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
     uint8_t* my_stage_gen = gen_base + kTileBytes + (warp - 2) * 8192;
     uint32_t lt = 0, nstore = 0;
     bool ok = true;
     for (long long t = cluster_id; t < p.tiles && ok; t += nclusters, ++lt) {
-      const long long tt = t % per_split;
-      const int split = (int)(t / per_split);
-      const int n0 = (int)(tt % p.tiles_n) * kBN;
-      const int m0 = (int)((tt / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
-      const long long bt = tt / ((long long)p.tiles_n * p.tiles_m);
+      const int n0 = (int)(t % p.tiles_n) * kBN;
+      const int m0 = (int)((t / p.tiles_n) % p.tiles_m) * 256 + (int)rank * 128;
+      const long long bt = t / ((long long)p.tiles_n * p.tiles_m);
       const uint32_t buf = lt & 1u, aph = (lt >> 1) & 1u;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_accf + 8 * buf, aph, 3));
       if (!ok) break;
@@ -362,91 +353,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               o1[v] = mask_apply(a, mk[v]);
             }
             put(&tmC3, o1);
-          }
-        }
-      } else if (p.c_mode == 3) {
-        // ---- K split over several clusters: fp32 partial tile to the workspace, then the CTAs that worked on this
-        // half-tile (one per split, same rank) each reduce a share of its 128 rows once all partials are there.
-        // Partials [split][batch][M][N]; tickets[2 * tile + rank] counts arrivals, done[...] counts finished
-        // reducers (the last one puts both back to zero).  All items of the launch are resident at once (the host
-        // only splits when items <= clusters), so the wait below cannot starve; it is bounded all the same.
-        float* part = p.partials + (((long long)split * p.batch + bt) * p.M + m) * p.N;
-#pragma unroll 1
-        for (int c = 2 * c_first; c < 2 * (c_first + kChunks); ++c) {
-          uint32_t r[32];
-          tmem_ld32_nowait(tsrc + (uint32_t)(c * 32), r);
-          tmem_ld_wait();
-          if (c == 2 * (c_first + kChunks) - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acce + 8 * buf);
-          }
-          if (m < p.M) {
-            const long long nb = (long long)n0 + c * 32;
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              if (nb + v * 4 < p.N)  // N % 4 == 0 in this mode
-                *reinterpret_cast<uint4*>(part + nb + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-          }
-        }
-        __threadfence();
-        epi_sync();
-        unsigned* ticket = p.tickets + 2 * (2 * tt + rank);
-        if (warp == 2 && lane == 0) {
-          atomicAdd(ticket, 1u);
-          const unsigned long long t0 = globaltimer_ns();
-          bool seen = true;
-          while (*reinterpret_cast<volatile unsigned*>(ticket) < (unsigned)p.splits) {
-            __nanosleep(200);
-            if (globaltimer_ns() - t0 > kWaitNs || *reinterpret_cast<volatile int*>(&g_tc_error) != 0) {
-              atomicCAS(&g_tc_error, 0, 8);
-              seen = false;
-              break;
-            }
-          }
-          *epi_flag = seen ? 1 : 0;
-          __threadfence();
-        }
-        epi_sync();
-        ok = *epi_flag != 0;
-        if (ok) {
-          // rows of this CTA's half-tile are dealt out to the splits; within a share, one warp per row at a time,
-          // a lane sums eight columns of every partial in split order (fixed order: deterministic)
-          const int rows_per = (128 + p.splits - 1) / p.splits;
-          const int r_begin = split * rows_per, r_end = min(128, r_begin + rows_per);
-          for (int rr = r_begin + (warp - 2); rr < r_end; rr += EW) {
-            const long long mm = (long long)m0 + rr;
-            if (mm >= p.M) break;
-            const long long nn = (long long)n0 + lane * 8;
-            if (nn < p.N) {
-              float acc[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-              for (int sp = 0; sp < p.splits; ++sp) {
-                const float4* src = reinterpret_cast<const float4*>(p.partials + (((long long)sp * p.batch + bt) * p.M + mm) * p.N + nn);
-                const float4 u = __ldcg(src), v = __ldcg(src + 1);
-                acc[0] += u.x; acc[1] += u.y; acc[2] += u.z; acc[3] += u.w;
-                acc[4] += v.x; acc[5] += v.y; acc[6] += v.z; acc[7] += v.w;
-              }
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[e] *= p.alpha;
-              sb_half* dst = reinterpret_cast<sb_half*>(p.C) + bt * p.sCb + mm * p.sCm + nn * p.sCn;
-              if (p.sCn == 1 && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) && nn + 8 <= p.N) {
-                *reinterpret_cast<uint4*>(dst) = pack8(acc);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (nn + e < p.N) dst[e * p.sCn] = sb_f2h(acc[e]);
-              }
-            }
-          }
-          epi_sync();
-          if (warp == 2 && lane == 0) {
-            if (atomicAdd(ticket + 1, 1u) == (unsigned)p.splits - 1) {   // last reducer: leave the counters at zero
-              ticket[0] = 0u;
-              ticket[1] = 0u;
-              __threadfence();
-            }
           }
         }
       } else {
