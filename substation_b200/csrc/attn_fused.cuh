@@ -125,42 +125,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Two fp32 values in one 64-bit register, and arithmetic on both at once (one instruction per pair): the softmax
-// passes are bound by instruction issue (two warps per scheduler), not by any pipe.
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
-  return d;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
 // Ask for a box to be brought into L2 (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
@@ -418,7 +382,6 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // piece was scaled by is kept (shared memory, one float per thread and piece) so that the last pass can
         // bring every piece to the final maximum.  BETA out unless it is not wanted.  (scale > 0.)
         float mrun = -INFINITY, sum = 0.f;
-        uint64_t sum2 = 0ull;                                // two partial row sums (even and odd columns of a piece)
         float* my_ref = ref_gen + (ew * 32 + lane);
         if (rows)
           sweep_halves(trow, h, nc64, wait_half, no_op, [&](int c, int hh, uint32_t* r) {
@@ -429,33 +392,25 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
             float mx = mrun;
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
             if (mx > mrun) {
-              const float resc = ex2_approx((mrun - mx) * c2);   // 0 for the first piece (mrun = -inf, sums = 0)
-              sum2 = f2_mul(sum2, f2_pack(resc, resc));
+              sum *= ex2_approx((mrun - mx) * c2);      // 0 for the first piece (mrun = -inf, sum = 0)
               mrun = mx;
             }
             my_ref[((c / kNW) * 2 + hh) * (kEpiWarps * 32)] = mrun;
             const float mxs = mrun * c2;
-            const uint64_t c2_2 = f2_pack(c2, c2), nmxs_2 = f2_pack(-mxs, -mxs);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              if (!p.skip_o0) {
-                float f[8];
+              float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.scale;
-                *stage_ptr(b, hh * 4 + v) = pack8(f);
+              for (int e = 0; e < 8; ++e) {
+                const float a = __uint_as_float(r[v * 8 + e]);
+                f[e] = a * p.scale;
+                const float ex = ex2_approx(fmaf(a, c2, -mxs));
+                sum += ex;
+                r[v * 8 + e] = __float_as_uint(ex);
               }
-#pragma unroll
-              for (int e = 0; e < 8; e += 2) {
-                float x0, x1;
-                f2_unpack(f2_fma(f2_pack_bits(r[v * 8 + e], r[v * 8 + e + 1]), c2_2, nmxs_2), x0, x1);
-                x0 = ex2_approx(x0);
-                x1 = ex2_approx(x1);
-                sum2 = f2_add(sum2, f2_pack(x0, x1));
-                r[v * 8 + e] = __float_as_uint(x0);
-                r[v * 8 + e + 1] = __float_as_uint(x1);
-              }
+              if (!p.skip_o0) *stage_ptr(b, hh * 4 + v) = pack8(f);
             }
             tmem_st32(trow + c * 64 + hh * 32, r);
             if (hh == 1 && !p.skip_o0) {
@@ -466,11 +421,6 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           });
         tmem_st_wait();
-        {
-          float s0, s1;
-          f2_unpack(sum2, s0, s1);
-          sum = s0 + s1;
-        }
         // the warps of a quadrant combine their (maximum, sum) pairs; alternate tiles use alternate slots, so a
         // warp already in the next tile never overwrites what a slower one still reads
         float* rset = red_gen + (it & 1u) * (2 * kNW * 128);
@@ -533,13 +483,10 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             // bring this piece from the maximum it was scaled by to the row's final one, and normalise
             const float fac = ex2_approx((my_ref[((c / kNW) * 2 + hh) * (kEpiWarps * 32)] - mfin) * c2) * inv;
 #pragma unroll
-            const uint64_t fac_2 = f2_pack(fac, fac);
-#pragma unroll
             for (int v = 0; v < 4; ++v) {
               float f[8];
 #pragma unroll
-              for (int e = 0; e < 8; e += 2)
-                f2_unpack(f2_mul(f2_pack_bits(r[v * 8 + e], r[v * 8 + e + 1]), fac_2), f[e], f[e + 1]);
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * fac;
               const uint4 al = pack8(f);
               *stage_ptr(b0, hh * 4 + v) = al;
               *stage_ptr(b1, hh * 4 + v) = mask_apply(al, make_uint2(mw[2 * v], mw[2 * v + 1]));
@@ -558,7 +505,6 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // backward pass 1: DATTN_DROP out; (da, alpha) with da = mask * DATTN_DROP kept as an fp16
         // pair per tensor-memory word; partial s = sum da * alpha
         float ssum = 0.f;
-        uint64_t ssum2 = 0ull;   // two partial sums (even and odd columns)
         uint4 aall[8];      // ALPHA of this thread's row for one 64-column chunk
         uint32_t mall[16];  // and its mask bytes
         if (rows)
@@ -607,7 +553,7 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               unpack8(da, f);
               unpack8(araw[v], a8);
 #pragma unroll
-              for (int e = 0; e < 8; e += 2) ssum2 = f2_fma(f2_pack(f[e], f[e + 1]), f2_pack(a8[e], a8[e + 1]), ssum2);
+              for (int e = 0; e < 8; ++e) ssum = fmaf(f[e], a8[e], ssum);
               const uint32_t dw[4] = {da.x, da.y, da.z, da.w}, aw[4] = {araw[v].x, araw[v].y, araw[v].z, araw[v].w};
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
@@ -624,11 +570,6 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           });
         tmem_st_wait();
-        {
-          float s0, s1;
-          f2_unpack(ssum2, s0, s1);
-          ssum = s0 + s1;
-        }
         float* rset = red_gen + (it & 1u) * (2 * kNW * 128);   // alternate tiles, alternate slots (see forward)
         rset[h * 128 + rt] = ssum;
         ok = epi_barrier(bar_epi, n_bar, lane) && ok;
@@ -643,15 +584,13 @@ attn_scores_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               if (lane == 0) bulk_wait_read<NB - 1>();
               __syncwarp();
             }
-            const uint64_t nss_2 = f2_pack(-ssum, -ssum);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               float f[8];
 #pragma unroll
-              for (int e = 0; e < 8; e += 2) {
-                const float2 p0 = sb_h22f2(*reinterpret_cast<const sb_half2*>(&r[v * 8 + e]));       // (da, alpha)
-                const float2 p1 = sb_h22f2(*reinterpret_cast<const sb_half2*>(&r[v * 8 + e + 1]));
-                f2_unpack(f2_mul(f2_add(f2_pack(p0.x, p1.x), nss_2), f2_pack(p0.y, p1.y)), f[e], f[e + 1]);
+              for (int e = 0; e < 8; ++e) {
+                const float2 da_al = sb_h22f2(*reinterpret_cast<const sb_half2*>(&r[v * 8 + e]));
+                f[e] = da_al.y * (da_al.x - ssum);
               }
               *stage_ptr(b, hh * 4 + v) = pack8(f);
             }

@@ -142,7 +142,9 @@ class Encoder(torch.nn.Module):
                     arena = torch.empty(max(total, 1), dtype=torch.uint8, device=X.device)
                     ctx.pool_set = None
                 over = outer._explicit_masks(X.device) if outer.mask_mode == 'explicit' else {}
-                outer._forward_ptrs(X, weights, outer._plan_ptrs(plan, arena, over), Y)
+                ptrs = outer._pooled_ptrs('fwd', plan, arena, over) if pooled is not None else \
+                    outer._plan_ptrs(plan, arena, over)
+                outer._forward_ptrs(X, weights, ptrs, Y)
                 ctx.save_for_backward(*weights, arena, X)
                 ctx.masks = over
                 if outer.enable_debug:
@@ -172,8 +174,10 @@ class Encoder(torch.nn.Module):
                     DX = torch.empty_like(DY)
                     barena = torch.empty(max(btotal, 1), dtype=torch.uint8, device=DY.device)
                     garena = outer._next_grad_arena(gtotal, DY.device)
-                outer._backward_ptrs(DY, outer._plan_ptrs(gplan, garena, {}), outer._plan_ptrs(bplan, barena, {}), weights,
-                                     outer._plan_ptrs(outer._fwd_plan[0], arena, ctx.masks), X, DX)
+                tab = outer._pooled_ptrs if ctx.pool_set is not None else \
+                    (lambda which, plan, a, over: outer._plan_ptrs(plan, a, over))
+                outer._backward_ptrs(DY, tab('grads', gplan, garena, {}), tab('bwd', bplan, barena, {}), weights,
+                                     tab('fwd', outer._fwd_plan[0], arena, ctx.masks), X, DX)
                 g16 = garena[:max(gtotal, 2)].view(outer.torch_dtype)
                 outer._grad_bucket = g16
                 grads = tuple(torch.as_strided(g16, shape, strides, off) for shape, strides, off in outer._grad_views)
@@ -339,6 +343,19 @@ class Encoder(torch.nn.Module):
             arr[i] = base + off if t is None else t.data_ptr()
         return arr
 
+    def _pooled_ptrs(self, which, plan, arena, overrides):
+        """``_plan_ptrs`` remembered per (plan, arena, override pointers): with a buffer pool the same few arenas
+        come back every step, and building a 50-entry pointer table three times per step is host time the
+        end-to-end path can do without."""
+        cache = self.__dict__.setdefault('_ptr_cache', {})
+        key = (which, arena.data_ptr(), tuple(t.data_ptr() for t in overrides.values()) if overrides else ())
+        arr = cache.get(key)
+        if arr is None:
+            if len(cache) > 64:
+                cache.clear()
+            arr = cache[key] = self._plan_ptrs(plan, arena, overrides)
+        return arr
+
     def _graphs_now(self, h, on):
         """Graph replay pays when the buffers of a pass repeat (raw passes into caller-held arenas); the autograd
         path allocates fresh arenas per step, where capturing would only cost host time."""
@@ -477,6 +494,7 @@ class Encoder(torch.nn.Module):
         self._pool_n = int(n)
         self._pool = []
         self._pool_turn = 0
+        self._ptr_cache = {}
 
     def _pool_set(self, X):
         if len(self._pool) < self._pool_n:
