@@ -338,6 +338,31 @@ def event_time_ms(fn, n, torch):
     return e0.elapsed_time(e1)
 
 
+def graph_time_ms(fn, n, torch):
+    """The same n calls captured once into a CUDA graph and replayed: the device time of back-to-back launches,
+    whatever the host needs to issue one (a Python call with a dozen tensor arguments costs 20-60 us, more than
+    the shorter operators run).  None when the calls cannot be captured; the caller then times them eagerly."""
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        del g
+        return ms
+    except Exception as exc:  # capture refused (an operator that synchronises or allocates): eager timing instead
+        sys.stderr.write(f'kernel sweep: graph capture not possible ({type(exc).__name__}: {exc}); timing eagerly\n')
+        torch.cuda.synchronize()
+        return None
+
+
 def cublas_anchors(T, dev, torch, reps=20, nset=4):
     """torch.matmul (cuBLAS) fp16 time of the twelve large contractions at the layer's shapes, both operands
     K-major, over rotating operand sets so that every call starts cold in L2.  A yardstick only."""
@@ -382,7 +407,8 @@ def fused_kernel_sweep(dev, torch, warmup=20, reps=200, Hh=16, B=96, L=128, nset
     """Each fused operator and its backward counterpart alone at H=16, B=96, J=K=128, E=1024, U=4096: scores
     ~ N(0,4) with scale 1/8 and dropout p=0.1, bdrln over [B,J,E] with bias ~ N(0,0.02) and residual ~ N(0,1),
     bad over [B,J,U], gradients ~ N(0,1), saved tensors from the matching forward.  20 + 200 launches over
-    rotating buffer sets (a set is 50-350 MB, above the 126 MB L2), CUDA events, GB/s = algorithmic bytes / time.
+    rotating buffer sets (a set is 50-350 MB, above the 126 MB L2), the 200 replayed as one CUDA graph between two
+    CUDA events so that the host's issue rate does not enter, GB/s = algorithmic bytes / time.
     Mirrors the reference's per-kernel harness (pytorch_module/benchmark.py:375-393, :1475-1493)."""
     from substation_b200 import ops
     peaks, _ = load_peaks()
@@ -398,9 +424,12 @@ def fused_kernel_sweep(dev, torch, warmup=20, reps=200, Hh=16, B=96, L=128, nset
         for i in range(warmup):
             calls[i % len(calls)]()
         torch.cuda.synchronize()
-        ms = event_time_ms(lambda i: calls[i % len(calls)](), reps, torch)
+        ms = graph_time_ms(lambda i: calls[i % len(calls)](), reps, torch)
+        how = 'graph replay'
+        if ms is None:
+            ms, how = event_time_ms(lambda i: calls[i % len(calls)](), reps, torch), 'eager'
         us = 1e3 * ms / reps
-        results[name] = {'us': round(us, 2), 'gbs': round(nbytes / us / 1e3, 1),
+        results[name] = {'us': round(us, 2), 'launch': how, 'gbs': round(nbytes / us / 1e3, 1),
                          'frac_of_measured_copy': round(nbytes / us / 1e3 / hbm, 3),
                          'frac_of_8tbs': round(nbytes / us / 1e3 / NOMINAL_HBM_GBS, 3)}
 
