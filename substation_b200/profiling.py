@@ -26,7 +26,7 @@ KERNEL_METRICS = (
     ('dram__bytes_write.sum', 'dram_write_bytes'),
     ('gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed', 'dram_pct'),
     ('sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active', 'tensor_pipe_pct'),
-    ('smsp__issue_active.avg.pct', 'issue_active_pct'),
+    ('sm__issue_active.avg.pct_of_peak_sustained_elapsed', 'issue_active_pct'),
     ('lts__t_sector_hit_rate.pct', 'l2_hit_pct'),
     ('launch__registers_per_thread', 'registers'),
     ('launch__grid_size', 'grid'),
