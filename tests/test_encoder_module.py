@@ -78,3 +78,24 @@ def test_early_gradient_part_is_a_suffix_of_the_bucket():
     names = [n for n, _, _, o, _ in plan if o >= off]
     assert names == ['BO', 'S1', 'B1', 'LINB1', 'LINW1', 'S2', 'B2', 'LINB2', 'LINW2']
     assert 0 < off < total and off % 2 == 0
+
+
+def test_pointer_tables_are_remembered_per_arena():
+    """With a buffer pool the same arenas return every step: their pointer tables are built once, hold the plan's
+    offsets, follow the caller's masks, and are forgotten when the pool is set up again."""
+    enc = Encoder('/tmp/unused', 2, 8, 2, 16, L.uniform_layouts(), torch.float16, 0, 0, 0, 0)
+    plan, total = enc._fwd_plan
+    a = torch.empty(max(total, 1), dtype=torch.uint8)
+    b = torch.empty(max(total, 1), dtype=torch.uint8)
+    t1 = enc._pooled_ptrs('fwd', plan, a, {})
+    assert enc._pooled_ptrs('fwd', plan, a, {}) is t1
+    t2 = enc._pooled_ptrs('fwd', plan, b, {})
+    assert t2 is not t1
+    for i, (_, _, _, off, _) in enumerate(plan):
+        assert t1[i] == a.data_ptr() + off and t2[i] == b.data_ptr() + off
+    name = plan[0][0]
+    m = torch.empty(4, dtype=torch.uint8)
+    t3 = enc._pooled_ptrs('fwd', plan, a, {name: m})
+    assert t3 is not t1 and t3[0] == m.data_ptr() and t3[1] == t1[1]
+    enc.set_buffer_pool(2)
+    assert enc._pooled_ptrs('fwd', plan, a, {}) is not t1
