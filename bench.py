@@ -1026,6 +1026,20 @@ def stack_record(args, world, rank, dev, barrier, max_over_ranks, layers=24, ste
     rec = {'layers': layers, 'per_gpu_batch': 8, 'seq_len': 512, 'ms_per_step': ms, 'ms_per_layer': ms / layers,
            'value': world * 8 / (ms / 1e3), 'unit': UNIT, 'memory_gb': round(st.memory_bytes() / 2 ** 30, 2),
            'masks': 'in-kernel Philox'}
+    if world > 1:
+        # one more step, traced (outside the timed region): when each layer's backward and each bucket's allreduce
+        # ended on this rank.  The reduction of layer l is hidden when it ends before the backward of layer l-1 does.
+        st.forward(X)
+        trace = []
+        st.backward(DY, trace=trace)
+        st.wait_gradients()
+        torch.cuda.synchronize(dev)
+        rows = st.overlap_trace(trace)
+        hidden = sum(1 for a, b in zip(rows, rows[1:]) if a[2] is not None and a[2] <= b[1])
+        rec['overlap_trace'] = {
+            'columns': ['layer', 'backward_done_ms', 'allreduce_done_ms'], 'rank': rank, 'rows': rows,
+            'reductions_hidden_behind_next_backward': hidden, 'of': len(rows) - 1,
+            'exposed_after_last_backward_ms': None if rows[-1][2] is None else round(rows[-1][2] - rows[-1][1], 3)}
     del st
     torch.cuda.empty_cache()
     return rec

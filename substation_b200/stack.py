@@ -64,16 +64,49 @@ class EncoderStack:
             enc.forward_raw(self.acts[l], self.weights[l], self.fwd[l], self.acts[l + 1])
         return self.acts[-1]
 
-    def backward(self, DY):
-        """Returns dX; gradients of layer l are in ``self.grads[l]`` once ``wait_gradients`` returns."""
+    def backward(self, DY, trace=None):
+        """Returns dX; gradients of layer l are in ``self.grads[l]`` once ``wait_gradients`` returns.
+
+        ``trace``: an empty list to be filled with one (layer, event at the end of that layer's backward, event at
+        the end of its bucket's allreduce or None) per layer, plus a leading ('start', event, None): what
+        ``overlap_trace`` turns into times.  The allreduce events are recorded on a stream of their own that
+        waits for each reduction in turn, so tracing does not change what the compute stream waits for."""
         cur = DY
+        tracing = trace is not None and self.device.type == 'cuda'
+        if tracing:
+            if self.__dict__.get('_trace_stream') is None:
+                self._trace_stream = torch.cuda.Stream(self.device)
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            trace.append(('start', ev, None))
         for l in range(len(self.layers) - 1, -1, -1):
             self.reducer.wait(l)                         # bucket l free again (previous step's reduction done)
             out = self.dacts[l & 1]
             self.layers[l].backward_raw(cur, self.grads[l], self.bwd, self.weights[l], self.fwd[l], self.acts[l], out)
+            if tracing:
+                done = torch.cuda.Event(enable_timing=True)
+                done.record()
             self.reducer.reduce_async(l)
+            if tracing:
+                reduced = None
+                works = self.reducer.pending[l % len(self.reducer.arenas)]
+                if works:
+                    with torch.cuda.stream(self._trace_stream):
+                        for w in works:
+                            w.wait()
+                        reduced = torch.cuda.Event(enable_timing=True)
+                        reduced.record()
+                trace.append((l, done, reduced))
             cur = out
         return cur
+
+    @staticmethod
+    def overlap_trace(trace):
+        """Times in ms since the start of the traced backward: [[layer, backward done, allreduce done or None], ...]
+        in the order the layers ran (last layer first).  Call after the device has finished the step."""
+        start = trace[0][1]
+        return [[l, round(start.elapsed_time(done), 3), None if red is None else round(start.elapsed_time(red), 3)]
+                for l, done, red in trace[1:]]
 
     def wait_gradients(self):
         self.reducer.drain()
