@@ -35,9 +35,13 @@ constexpr int kRefBytes = 8 * kEpiWarps * 32 * 4;    // forward: the maximum eac
 
 template <bool BWD>
 struct Cfg {
-  static constexpr int kOutBufs = BWD ? 2 : 3;       // staging buffers (32 rows x 128 B) per warp
+  // Shared memory left after the operands is split between output staging and input slots where the kernel
+  // stalls most: the forward kernel issues two stores per chunk and reads 2 KiB of mask, the backward kernel reads
+  // 6 KiB (ALPHA and mask) per chunk and issues one store; a second input slot bought the backward kernel 4.5 us
+  // of 51, the second staging buffer it gave up cost 1 us.
+  static constexpr int kOutBufs = BWD ? 1 : 3;       // staging buffers (32 rows x 128 B) per warp
   static constexpr int kInSlot = BWD ? 6144 : 2048;  // ALPHA rows (4 KiB) + mask rows (2 KiB) | mask rows
-  static constexpr int kSlots = BWD ? 1 : 2;         // input chunks in flight per warp (what shared memory allows)
+  static constexpr int kSlots = 2;                   // input chunks in flight per warp
   static constexpr int kStaging = kEpiWarps * kOutBufs * 4096;
   static constexpr int kSmemBytes = kOperandBytes + kStaging + kEpiWarps * kInSlot * kSlots + kRedBytes + (BWD ? 0 : kRefBytes) + 1024 + 256;
 };
