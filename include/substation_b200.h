@@ -306,10 +306,11 @@ int sb_device_error_reset(void* stream);
  * tensor-pipe rate these kernels could reach if nothing but the MMAs cost time.  Stands in for the reference's
  * tensor-core microbenchmark (tc_profiling/microbenchmark/tensorcores.cu:16-40). */
 int sb_mma_peak_probe(void* stream, int k_blocks, int bf16, double* flops);
-/* The contraction kernels are persistent: one CTA per SM walks the output tiles.  When
- * another kernel must run next to them (the NCCL gradient allreduce of the data-parallel
- * path), tell the library to occupy only n_sms SMs so that no CTA of a contraction waits
- * behind it (0 = use every SM, the default).  Process-wide.  No counterpart in the
+/* The contraction, attention and LayerNorm kernels are persistent: one CTA per SM (or a
+ * fixed number per SM) walks the work.  When another kernel must run next to them (the NCCL
+ * gradient allreduce of the data-parallel path), tell the library to size every such grid
+ * for n_sms SMs only, so that no CTA waits behind the other kernel and then runs its share
+ * as a second round (0 = use every SM, the default).  Process-wide.  No counterpart in the
  * reference, which has no multi-GPU path. */
 int sb_set_sm_budget(int n_sms);
 

@@ -633,7 +633,7 @@ int launch(cudaStream_t s, void* ws, const LnBwdParams& p0, void* const outs[4])
   constexpr int NQ = MODE == 0 ? 2 : 4;
   LnBwdParams p = p0;
   const long long R = (long long)p.d.B * p.d.J;
-  const int sms = device_facts().sms;
+  const int sms = usable_sms(device_facts().sms);
   const bool use_ring = MODE == 0 ? ring_ok(p.d, {&p.y, &p.n, &p.diff, &p.mask, &p.dln, &p.dresid, &p.dlin}, true)
                                   : ring_ok(p.d, {&p.n, &p.r2, &p.w, &p.l2, &p.diff, &p.mask, &p.dln, &p.dresid, &p.dlin}, true);
   const int per_cta = use_ring ? kGroups : kGroups * kRows;
@@ -707,7 +707,7 @@ int launch_bdrln_ring(cudaStream_t s, Dims3 d, View3 in, const void* bias, View3
   const int stage_bytes = (kFwdRows * 5 * d.F + 127) / 128 * 128;
   const int nstages = std::max(2, std::min(16, (232448 - 1024) / stage_bytes));
   const size_t smem = (size_t)nstages * stage_bytes + 16 * (size_t)nstages + 64;
-  const int P = (int)std::max<long long>(1, std::min<long long>(device_facts().sms, (R + kFwdRows - 1) / kFwdRows));
+  const int P = (int)std::max<long long>(1, std::min<long long>(usable_sms(device_facts().sms), (R + kFwdRows - 1) / kFwdRows));
 #define SB_BDRLN_RING(NV)                                                                                    \
   do {                                                                                                       \
     SB_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(bdrln_ring_kernel<NV>), 232448));           \

@@ -902,7 +902,7 @@ int launch_colreduce(cudaStream_t s, void* ws, Dims3 d, const Op& op, ColOut<Op:
   if (R > 0x7fffffffLL) return fail(SB_ERR_UNSUPPORTED, "token reductions over more than 2^31-1 tokens are not supported");
   const long long Fp = (long long)slices * 256;
   // as many 8-warp CTAs per SM as the kernel's register budget allows; bounded by rows and by the workspace
-  long long P = ((long long)device_facts().sms * Op::MINB + slices - 1) / slices;
+  long long P = ((long long)usable_sms(device_facts().sms) * Op::MINB + slices - 1) / slices;
   const long long cap = (long long)((kWsBytes - kWsCounterBytes) / (Op::NQ * Fp * sizeof(float)));
   if (cap < 1) return fail(SB_ERR_UNSUPPORTED, "feature dim too large for the workspace");
   if (P > cap) P = cap;
@@ -940,7 +940,7 @@ bool all_vec(const V&... v) {
 template <class K>
 unsigned persistent_blocks(K kernel, int threads, unsigned long long work_blocks) {
   const int per_sm = cached_blocks_per_sm(reinterpret_cast<const void*>(kernel), threads);
-  const unsigned long long cap = (unsigned long long)device_facts().sms * per_sm;
+  const unsigned long long cap = (unsigned long long)usable_sms(device_facts().sms) * per_sm;
   return (unsigned)std::max<unsigned long long>(1, std::min(work_blocks, cap));
 }
 
@@ -1245,7 +1245,7 @@ extern "C" int sb_backward_attn_out_bias_noalloc(void* stream, const sb_tensor* 
   const long long R = B * J, Fp = (long long)slices * 256;
   if (R > 0x7fffffffLL)   // the kernel indexes tokens with 32-bit arithmetic
     return fail(SB_ERR_UNSUPPORTED, "baob (no-alloc): more than 2^31-1 tokens (B*J) are not supported");
-  long long P = ((long long)device_facts().sms * 4 + slices - 1) / slices;
+  long long P = ((long long)usable_sms(device_facts().sms) * 4 + slices - 1) / slices;
   const long long cap = (long long)(kStaticPartialBytes / (Fp * sizeof(float)));  // >= 16 for F <= 16384
   if (P > cap) P = cap;
   if (P > (R + 7) / 8) P = (R + 7) / 8;

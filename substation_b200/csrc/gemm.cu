@@ -680,6 +680,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long batch, 
 }
 
 #include "gemm_pair.cuh"
+#include "gemm_pair_splitk.cuh"
 #include "attn_fused.cuh"
 #include "score_contract.cuh"
 #include "peak_probe.cuh"
@@ -968,6 +969,75 @@ int launch_tc_pair(cudaStream_t s, const GemmProblem& g, const OperandMap& a, co
   return SB_OK;
 }
 
+// Split-K clusters (SK CTA pairs per 256 x 256 tile, partials reduced through distributed shared memory).
+// SUBSTATION_B200_PAIR_SPLITK: 0 switches the form off, 2..4 force that many pairs; unset, the launcher takes the
+// largest number of pairs whose clusters are all resident at once.
+int pair_splitk_forced() {
+  static const int sk = [] {
+    const char* e = getenv("SUBSTATION_B200_PAIR_SPLITK");
+    if (!e) return -1;
+    const int v = atoi(e);
+    return (v >= 2 && v <= 4) ? v : 0;
+  }();
+  return sk;
+}
+
+template <int SK>
+int splitk_clusters_resident() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cached_dev = dev;
+    cached = 0;
+    const void* fn = reinterpret_cast<const void*>(pair::gemm_tc_pair_splitk_kernel<8, SK>);
+    const int smem = pair::Cfg<8>::kSmemBytes;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2 * SK * 16);
+      cfg.blockDim = dim3(pair::Cfg<8>::kThreads);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2 * SK; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess) cached = n;
+      else cudaGetLastError();
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return cached;
+}
+
+template <int SK>
+int launch_tc_pair_splitk(cudaStream_t s, const GemmProblem& g, const OperandMap& a, const OperandMap& b) {
+  TcParams p;
+  memset(&p.epi, 0, sizeof(p.epi));
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.sCb = g.sCb; p.sCm = g.sCm; p.sCn = g.sCn;
+  p.C = g.C;
+  p.alpha = g.alpha;
+  p.a_mn = a.mn; p.b_mn = b.mn; p.a_swap = a.swap; p.b_swap = b.swap; p.c_swap = 0;
+  p.tiles_n = (int)((g.N + 255) / 256);
+  p.tiles_m = (int)((g.M + 255) / 256);
+  p.batch = (int)g.batch;
+  const int KT = (int)((g.K + kBK - 1) / kBK);
+  p.splits = SK;
+  p.kt_per_split = (KT + SK - 1) / SK;
+  p.tiles = (long long)p.tiles_m * p.tiles_n * g.batch;
+  p.c_mode = 1;
+  const void* fn = reinterpret_cast<const void*>(pair::gemm_tc_pair_splitk_kernel<8, SK>);
+  SB_CUDA_OK(ensure_dynamic_smem(fn, pair::Cfg<8>::kSmemBytes));
+  SB_LAUNCH_OK(launch_k(pair::gemm_tc_pair_splitk_kernel<8, SK>, (unsigned)(2 * SK * p.tiles), pair::Cfg<8>::kThreads,
+                        pair::Cfg<8>::kSmemBytes, s, a.map, b.map, p));
+  SB_CUDA_OK(cudaGetLastError());
+  return SB_OK;
+}
+
 int pick_bn(long long M, long long N, long long batch) {
   // 128 x 256 moves the fewest operand bytes per flop (each CTA fetches its own tiles), so it is
   // used whenever N fills most of it and the persistent grid still covers about half the SMs
@@ -1035,6 +1105,33 @@ int launch_gemm_tcgen05_epi(cudaStream_t s, const GemmProblem& g0, void* ws, siz
     }
   }
   if (epi) return fail(SB_ERR_UNSUPPORTED, "fused epilogue: only the paired-CTA kernel (large single-batch problems) has it");
+  // Few output tiles and a long K: several CTA pairs per tile share K and add their partials up inside the
+  // cluster.  Every cluster must be resident at once (a second round would double the time): on a B200, 22 clusters
+  // of six CTAs are, 15 of eight, 33 of four.
+  if (bn == 256 && g.batch == 1 && g.M >= 256 && g.N >= 256 && pair_enabled() && pair_splitk_forced() != 0) {
+    const long long tiles2 = ((g.M + 255) / 256) * ((g.N + 255) / 256);
+    const long long KT = (g.K + kBK - 1) / kBK;
+    const bool c_ok = g.sCn == 1 && g.N % 4 == 0 && g.sCm % 4 == 0 && (reinterpret_cast<uintptr_t>(g.C) & 7u) == 0;
+    int sk = 0;
+    if (c_ok && tiles2 * 4 <= sm_count()) {
+      for (int cand : {4, 3, 2}) {
+        if (pair_splitk_forced() > 0 && cand != pair_splitk_forced()) continue;
+        const int resident = cand == 4 ? splitk_clusters_resident<4>() : cand == 3 ? splitk_clusters_resident<3>()
+                                                                                   : splitk_clusters_resident<2>();
+        if (KT >= 8 * cand && tiles2 * 2 * cand <= sm_count() && resident >= tiles2) {
+          sk = cand;
+          break;
+        }
+      }
+    }
+    if (sk && make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why) &&
+        make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, 128, &b, &why)) {
+      const int st2 = sk == 4 ? launch_tc_pair_splitk<4>(s, g, a, b)
+                              : sk == 3 ? launch_tc_pair_splitk<3>(s, g, a, b) : launch_tc_pair_splitk<2>(s, g, a, b);
+      if (st2 == SB_OK) g_last_gemm_impl = SB_GEMM_TCGEN05;
+      return st2;
+    }
+  }
   if (!make_operand_map(g.A, g.M, g.K, g.batch, g.sAm, g.sAk, g.sAb, kBM, &a, &why))
     return fail(SB_ERR_ALIGNMENT, "tcgen05 contraction, operand A: " + why);
   if (!make_operand_map(g.B, g.N, g.K, g.batch, g.sBn, g.sBk, g.sBb, bn, &b, &why))

@@ -111,6 +111,12 @@ extern thread_local int g_last_gemm_impl;
 // Number of SMs the persistent contraction kernels may occupy (0 = all).
 void set_gemm_sm_budget(int n);
 int gemm_sm_budget();
+// SMs a persistent grid may count on: all of them, or the budget set through sb_set_sm_budget when a concurrent
+// kernel (a collective) holds the rest.  A grid sized for SMs it cannot get runs its last CTAs as a second round.
+inline int usable_sms(int sms) {
+  const int b = gemm_sm_budget();
+  return (b > 0 && b < sms) ? b : sms;
+}
 // Non-zero once a tcgen05 kernel on the current device reported a bounded wait running out (until reset).
 int gemm_device_error(cudaStream_t s, int* code);
 int gemm_device_error_reset(cudaStream_t s);

@@ -168,6 +168,48 @@ def test_split_k_with_workspace_matches_unsplit(M, N, K, c_mn):
     assert ops.device_error() == 0
 
 
+def test_split_k_with_workspace_for_batched_problems():
+    """Batched problems with few tiles keep the workspace form of split-K (fp32 partials, fixed-order reduce
+    kernel): two batches of 256 x 256 over K = 4096, reproducible bit for bit."""
+    ops = _ops()
+    rng = np.random.default_rng(11)
+    A, dA = _operand(rng, 2, 256, 4096, True)
+    B, dB = _operand(rng, 2, 256, 4096, True)
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=DEV)
+    outs = []
+    for _ in range(2):
+        dC = torch.full((2, 256, 256), float('nan'), dtype=torch.float16, device=DEV)
+        assert ops.einsum('bmk,bnk->bmn', dA, dB, dC, alpha=0.25, impl='tcgen05', workspace=ws) == 'tcgen05'
+        assert_close(dC, 0.25 * np.einsum('bmk,bnk->bmn', A, B), tol=2e-3, what='batched split-K C')
+        outs.append(dC)
+    assert torch.equal(outs[0], outs[1])
+    assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize('M,N,K', [(1024, 1024, 4096), (304, 520, 2080), (512, 768, 16384)])
+@pytest.mark.parametrize('a_mn,b_mn', [(0, 0), (1, 1), (1, 0)])
+def test_split_k_inside_a_cluster(M, N, K, a_mn, b_mn):
+    """Few 256 x 256 tiles and a long K without a workspace: four CTA pairs per tile share K and add their
+    partial accumulators up through distributed shared memory.  Ragged M and N, a K that does not divide into four
+    equal parts, both operand majors; the result must match fp32 and repeat bit for bit."""
+    ops = _ops()
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    A = (torch.randn(1, M, K, device=DEV, generator=g) / K ** 0.5).half()
+    B = torch.randn(1, N, K, device=DEV, generator=g).half()
+    dA = A.transpose(1, 2).contiguous().transpose(1, 2) if a_mn else A
+    dB = B.transpose(1, 2).contiguous().transpose(1, 2) if b_mn else B
+    ref = 0.5 * torch.einsum('bmk,bnk->bmn', A.float(), B.float())
+    outs = []
+    for _ in range(2):
+        dC = torch.full((1, M, N), float('nan'), dtype=torch.float16, device=DEV)
+        assert ops.einsum('bmk,bnk->bmn', dA, dB, dC, alpha=0.5, impl='tcgen05') == 'tcgen05'
+        assert ops.device_error() == 0
+        assert torch.isfinite(dC).all()
+        assert ((dC.float() - ref).norm() / ref.norm()).item() < 1e-3
+        outs.append(dC)
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize('M,N,K', [(4096, 4096, 1024), (2000, 1544, 520), (4096, 1024, 4096)])
 @pytest.mark.parametrize('a_mn,b_mn,c_mn', [(0, 0, 0), (1, 0, 0), (0, 1, 0), (1, 1, 1)])
 def test_paired_cta_kernel_on_large_problems(M, N, K, a_mn, b_mn, c_mn):
