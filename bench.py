@@ -997,7 +997,7 @@ def strong_scaling_record(args, world, rank, dev, barrier, max_over_ranks, globa
     return rec
 
 
-def stack_record(args, world, rank, dev, barrier, max_over_ranks, layers=24, steps=4):
+def stack_record(args, world, rank, dev, barrier, max_over_ranks, layers=24, steps=10):
     """24 layers with independent weights, per-GPU batch 8 at L=512: forward through all layers, backward through all
     layers, each layer's gradient bucket allreduced while the next layer's backward runs."""
     import torch
@@ -1114,7 +1114,8 @@ def main():
                          'b8_l512 / b96_l128 (the reference\'s shipped configurations) or a .json path')
     ap.add_argument('--batch', type=int, default=8)
     ap.add_argument('--seq', type=int, default=512)
-    ap.add_argument('--comm-ctas', type=int, default=4, help='SMs left to NCCL when N > 1')
+    ap.add_argument('--comm-ctas', type=int, default=12,
+                    help='SMs left to NCCL when N > 1 (every persistent grid of the library is sized for the rest)')
     ap.add_argument('--early-allreduce', type=int, default=0,
                     help='N > 1: sum the feed-forward gradients beside the attention half of backward (1) or the whole '
                          'bucket beside the next step (0)')
