@@ -154,12 +154,13 @@ gemm_tc_pair_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       const uint32_t tsrc = tmem_base + ((uint32_t)(q * 32) << 16);
       uint8_t* prow = gen_base + (q * 32 + lane) * kPartialPitch;
 #pragma unroll 1
-      for (int c = col0; c < col0 + 128; c += 32) {
-        uint32_t r[32];
+      for (int c = col0; c < col0 + 128; c += 64) {
+        uint32_t r[64];
         tmem_ld32_nowait(tsrc + (uint32_t)c, r);
+        tmem_ld32_nowait(tsrc + (uint32_t)(c + 32), r + 32);
         tmem_ld_wait();
 #pragma unroll
-        for (int v = 0; v < 8; ++v)
+        for (int v = 0; v < 16; ++v)
           *reinterpret_cast<uint4*>(prow + (c + 4 * v) * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
       }
     }
@@ -173,27 +174,38 @@ gemm_tc_pair_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 #pragma unroll
     for (int j = 0; j < SK; ++j) src[j] = map_to_rank(tiles, half + 2u * (uint32_t)j);
     sb_half* cbase = reinterpret_cast<sb_half*>(p.C) + (long long)bt * p.sCb;
-#pragma unroll 2
-    // the row half's 128 x 64 pieces of four columns are dealt out to the SK CTAs that hold it, a contiguous range each
-    constexpr int kItems = 128 * (kBN / 4), kPer = (kItems + SK - 1) / SK;
+    // the row half's 128 x 64 pieces of four columns are dealt out to the SK CTAs that hold it, a contiguous range
+    // each; a thread asks for the SK parts of four pieces before it adds any, so that 4 SK remote loads are in flight
+    constexpr int kItems = 128 * (kBN / 4), kPer = (kItems + SK - 1) / SK, kBatch = 4;
     const int first = (int)pi * kPer, last = min(kItems, first + kPer);
-    for (int item = first + tid; item < last; item += 256) {
-      const int row = item / (kBN / 4), col = (item % (kBN / 4)) * 4;
-      const uint32_t off = (uint32_t)(row * kPartialPitch + col * 4);
-      float4 acc = ld_cluster_f4(src[0] + off);
+    for (int base = first + tid; base < last; base += 256 * kBatch) {
+      float4 v[kBatch][SK];
 #pragma unroll
-      for (int j = 1; j < SK; ++j) {
-        const float4 v = ld_cluster_f4(src[j] + off);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      for (int u = 0; u < kBatch; ++u) {
+        const int item = min(base + u * 256, last - 1);       // past the end: a valid address, result unused
+        const uint32_t off = (uint32_t)((item / (kBN / 4)) * kPartialPitch + (item % (kBN / 4)) * 16);
+#pragma unroll
+        for (int j = 0; j < SK; ++j) v[u][j] = ld_cluster_f4(src[j] + off);
       }
-      const long long m = (long long)m_tile + half * 128 + row, n = (long long)n_tile + col;
-      if (m < p.M && n < p.N) {
-        const sb_half2 lo = sb_f2h2(acc.x * p.alpha, acc.y * p.alpha);
-        const sb_half2 hi = sb_f2h2(acc.z * p.alpha, acc.w * p.alpha);
-        uint2 o;
-        o.x = *reinterpret_cast<const uint32_t*>(&lo);
-        o.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(cbase + m * p.sCm + n) = o;
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int item = base + u * 256;
+        if (item >= last) break;
+        const int row = item / (kBN / 4), col = (item % (kBN / 4)) * 4;
+        float4 acc = v[u][0];
+#pragma unroll
+        for (int j = 1; j < SK; ++j) {
+          acc.x += v[u][j].x; acc.y += v[u][j].y; acc.z += v[u][j].z; acc.w += v[u][j].w;
+        }
+        const long long m = (long long)m_tile + half * 128 + row, n = (long long)n_tile + col;
+        if (m < p.M && n < p.N) {
+          const sb_half2 lo = sb_f2h2(acc.x * p.alpha, acc.y * p.alpha);
+          const sb_half2 hi = sb_f2h2(acc.z * p.alpha, acc.w * p.alpha);
+          uint2 o;
+          o.x = *reinterpret_cast<const uint32_t*>(&lo);
+          o.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(cbase + m * p.sCm + n) = o;
+        }
       }
     }
   }
