@@ -126,9 +126,16 @@ class Encoder(torch.nn.Module):
 
         class EncoderFunction(torch.autograd.Function):
             @staticmethod
-            def forward(ctx, X, *weights):
+            def forward(ctx, X, anchor, *weights):
                 # Hot path: one arena per pass, pointers computed from the plan's offsets; tensor views
                 # over the arena are only built when somebody asks for them (debug, or a caller of views()).
+                # ``anchor`` is None on the ordinary path (``weights`` are the sixteen parameters, and autograd routes
+                # their gradients).  With a buffer pool it is a one-element leaf that keeps the node in the graph,
+                # ``weights`` is ONE tuple of detached parameters that autograd does not look into, and backward
+                # writes every ``.grad`` itself: sixteen inputs and sixteen accumulation nodes less per step.
+                ctx.direct = anchor is not None
+                if ctx.direct:
+                    weights = weights[0]
                 outer._check_input(X, 'X')
                 X = X.contiguous()
                 weights = tuple(w if w.is_contiguous() else w.contiguous() for w in weights)
@@ -145,7 +152,11 @@ class Encoder(torch.nn.Module):
                 ptrs = outer._pooled_ptrs('fwd', plan, arena, over) if pooled is not None else \
                     outer._plan_ptrs(plan, arena, over)
                 outer._forward_ptrs(X, weights, ptrs, Y)
-                ctx.save_for_backward(*weights, arena, X)
+                if ctx.direct:
+                    ctx.weights = weights
+                    ctx.save_for_backward(arena, X)
+                else:
+                    ctx.save_for_backward(*weights, arena, X)
                 ctx.masks = over
                 if outer.enable_debug:
                     torch.cuda.synchronize()
@@ -161,7 +172,10 @@ class Encoder(torch.nn.Module):
             def backward(ctx, DY):
                 saved = ctx.saved_tensors
                 np_ = len(outer._param_names)
-                weights, arena, X = saved[:np_], saved[np_], saved[-1]
+                if ctx.direct:
+                    weights, arena, X = ctx.weights, saved[0], saved[1]
+                else:
+                    weights, arena, X = saved[:np_], saved[np_], saved[-1]
                 outer._check_input(DY, 'DY')
                 DY = DY.contiguous()
                 bplan, btotal = outer._bwd_plan
@@ -188,7 +202,12 @@ class Encoder(torch.nn.Module):
                         outer.debug[name] = _to_numpy(bwd[name])
                     for name, g in zip(outer._param_names, grads):
                         outer.debug['D' + name] = _to_numpy(g)
-                return (DX, *grads)
+                if ctx.direct:
+                    for prm, g in zip(outer.params, grads):
+                        if prm.requires_grad:
+                            prm.grad = g
+                    return DX, None, None
+                return (DX, None, *grads)
 
         self.encoder_func = EncoderFunction
 
@@ -482,15 +501,19 @@ class Encoder(torch.nn.Module):
             handle = ctypes.c_void_p(ev.cuda_event)
         self._check(_lib.load(self._lib_key).sb_encoder_set_ffn_grads_event(self._handle, handle))
 
-    def set_buffer_pool(self, n):
+    def set_buffer_pool(self, n, direct_grads=True):
         """``n`` > 0: the autograd path stops allocating per pass and takes the forward arena, the output, the backward
         arena, the input gradient and the gradient bucket from ``n`` sets of buffers the module owns, used in turn
         (allocated on first use).  The pointers of a pass then repeat every ``n`` steps, so passes are replayed as
         CUDA graphs with one launch each instead of some thirty, which is what an input pipeline that feeds the
         module from a few rotating device buffers wants.  The price: a tensor returned by ``forward`` (or a
-        gradient produced by ``backward``) is overwritten ``n`` steps later; copy what must live longer.  ``n`` = 0
-        (the default) restores the reference's behaviour, fresh tensors every pass
-        (pytorch_module/encoder.py:80-85, :110-121)."""
+        gradient produced by ``backward``) is overwritten ``n`` steps later; copy what must live longer.
+        ``direct_grads``: backward sets every parameter's ``.grad`` itself (a view into the pooled bucket, replacing
+        what was there) instead of handing sixteen gradients to autograd, which takes a third off the host's time per
+        step; parameter hooks do not fire and ``torch.autograd.grad`` with respect to a parameter is not available
+        on that path (pass ``direct_grads=False`` to keep autograd's routing).  ``n`` = 0 (the default) restores the
+        reference's behaviour, fresh tensors every pass (pytorch_module/encoder.py:80-85, :110-121)."""
+        self._pool_direct = bool(direct_grads)
         self._pool_n = int(n)
         self._pool = []
         self._pool_turn = 0
@@ -565,4 +588,9 @@ class Encoder(torch.nn.Module):
 
     def forward(self, X):
         """Run the encoder."""
-        return self.encoder_func.apply(X, *self.params)
+        if self.__dict__.get('_pool_n') and self.__dict__.get('_pool_direct') and torch.is_grad_enabled():
+            anchor = self.__dict__.get('_anchor')
+            if anchor is None or anchor.device != X.device:
+                anchor = self._anchor = torch.zeros(1, device=X.device, requires_grad=True)
+            return self.encoder_func.apply(X, anchor, tuple(p.detach() for p in self.params))
+        return self.encoder_func.apply(X, None, *self.params)
