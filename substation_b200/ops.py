@@ -311,9 +311,9 @@ def mma_peak_probe(k_blocks, bf16=False):
 
 
 def set_sm_budget(n_sms):
-    """Let the persistent contraction kernels occupy only ``n_sms`` SMs (0 = all), leaving the
-    rest to a kernel that runs beside them, e.g. the NCCL allreduce of the data-parallel path.  Applies to both
-    storage-type builds of the library."""
+    """Size every persistent grid of the library (contractions, attention, LayerNorm, reductions) for ``n_sms``
+    SMs (0 = all), leaving the rest to a kernel that runs beside them, e.g. the NCCL allreduce of the
+    data-parallel path.  Applies to both storage-type builds of the library."""
     for key in ('fp16', 'bf16'):
         lib = _lib.load(key)
         _lib.check(lib.sb_set_sm_budget(int(n_sms)), lib)
