@@ -363,21 +363,53 @@ def graph_time_ms(fn, n, torch):
         return None
 
 
-def cublas_anchors(T, dev, torch, reps=20, nset=4):
-    """torch.matmul (cuBLAS) fp16 time of the twelve large contractions at the layer's shapes, both operands
-    K-major, over rotating operand sets so that every call starts cold in L2.  A yardstick only."""
+def cublas_anchors(T, dev, torch, reps=100, nset=4):
+    """The twelve large contractions at the layer's shapes, alone: this library's kernel (with the epilogue the layer
+    fuses into it) and torch.matmul (cuBLAS), both operands K-major, rotating operand sets so that every launch
+    starts cold in L2, the `reps` launches replayed as one CUDA graph between two events (no host in the loop, no
+    event between launches).  name -> (this kernel us, cuBLAS us).  A yardstick only: never on the product path."""
+    from substation_b200 import ops
+    g = torch.Generator(device=dev).manual_seed(3)
+    rnd = lambda *s, std=1.0: (torch.randn(*s, device=dev, generator=g) * std).half()
     out = {}
     for name, shape in GEMM_SHAPES.items():
         M, N, K = shape(T)
-        As = [torch.randn(M, K, device=dev, dtype=torch.float16) for _ in range(nset)]
-        Bs = [torch.randn(N, K, device=dev, dtype=torch.float16) for _ in range(nset)]
-        Cs = [torch.empty(M, N, device=dev, dtype=torch.float16) for _ in range(nset)]
-        f = lambda i: torch.matmul(As[i % nset], Bs[i % nset].t(), out=Cs[i % nset])
-        for i in range(nset + 2):
-            f(i)
-        torch.cuda.synchronize()
-        out[name] = 1e3 * event_time_ms(f, reps, torch) / reps
+        As = [rnd(1, M, K, std=K ** -0.5) for _ in range(nset)]
+        Bs = [rnd(1, N, K) for _ in range(nset)]
+        Cs = [torch.empty(1, M, N, device=dev, dtype=torch.float16) for _ in range(nset)]
+        if name == 'QKV-fused':      # + bias, C itself not stored
+            O2 = [torch.empty_like(c) for c in Cs]
+            bias = rnd(N, std=0.02)
+            ours = lambda i: ops.einsum_fused('bmk,bnk->bmn', As[i % nset], Bs[i % nset], Cs[i % nset], kind='bias',
+                                              out2=O2[i % nset], bias=bias, bias_dims='n', discard_c=True)
+        elif name == 'dXQKV-fused':  # + residual, C itself not stored
+            O2 = [torch.empty_like(c) for c in Cs]
+            R = [rnd(1, M, N) for _ in range(nset)]
+            ours = lambda i: ops.einsum_fused('bmk,bnk->bmn', As[i % nset], Bs[i % nset], Cs[i % nset], kind='residual',
+                                              out2=O2[i % nset], resid=R[i % nset], discard_c=True)
+        elif name == 'lin1':         # + bias, activation, dropout: two outputs, C itself not stored
+            O2 = [torch.empty_like(c) for c in Cs]
+            O3 = [torch.empty_like(c) for c in Cs]
+            bias = rnd(N, std=0.02)
+            mask = [(torch.rand(1, M, N, device=dev, generator=g) >= P_DROP).to(torch.uint8) for _ in range(nset)]
+            ours = lambda i: ops.einsum_fused('bmk,bnk->bmn', As[i % nset], Bs[i % nset], Cs[i % nset],
+                                              kind='bias_act_dropout', out2=O2[i % nset], out3=O3[i % nset], bias=bias,
+                                              bias_dims='n', mask=mask[i % nset], p=P_DROP, discard_c=True)
+        else:
+            ours = lambda i: ops.einsum('bmk,bnk->bmn', As[i % nset], Bs[i % nset], Cs[i % nset], impl='tcgen05')
+        lib = lambda i: torch.matmul(As[i % nset][0], Bs[i % nset][0].t(), out=Cs[i % nset][0])
+        res = []
+        for f in (ours, lib):
+            for i in range(nset + 2):
+                f(i)
+            torch.cuda.synchronize()
+            ms = graph_time_ms(f, reps, torch)
+            if ms is None:
+                ms = event_time_ms(f, reps, torch)
+            res.append(1e3 * ms / reps)
+        out[name] = tuple(res)
         del As, Bs, Cs
+    torch.cuda.empty_cache()
     return out
 
 
@@ -648,7 +680,11 @@ def run_ours(args):
                 ideal = max(ideal, by / (hbm * 1e3))
             base = name.split('+')[0]
             if base in anchors:
-                rec['cublas_us'] = round(anchors[base], 2)      # the plain contraction of the same shape
+                # alone, back to back under graph replay: this kernel with its fused epilogue, and cuBLAS on the plain
+                # contraction of the same shape (`us` above carries the per-operator events' 5-10 us)
+                rec['replay_us'] = round(anchors[base][0], 2)
+                rec['frac_tensor_replay'] = round(fl / anchors[base][0] / 1e6 / tf_burst, 3)
+                rec['cublas_us'] = round(anchors[base][1], 2)
         else:
             by = fused_bytes[name](B, S)
             rec['gbs'] = round(by / us / 1e3, 1)
