@@ -452,12 +452,13 @@ colsum_finish_kernel(const float* __restrict__ partial, int P, int F, int NQ, vo
 
 // ---------------------------------------------------------------------------------------------------------
 // Forward: bias + dropout + residual + LayerNorm out of the same kind of ring (dense token-major tensors, blocks of
-// four consecutive tokens, one bulk copy per tensor and block).  Warps 0-15 consume, one warp per token: block i of
-// the CTA lives in stage i % NS and belongs to the warp set i % 4 (warps 4 * set .. 4 * set + 3, one token each).
-// Warp 16 produces.  A stage holds IN and RESID (4 x 2F bytes each) and, when the mask is an input, the mask rows
+// four consecutive tokens, one bulk copy per tensor and block).  Warps 0-27 consume, one warp per token: block i of
+// the CTA lives in stage i % NS and belongs to the warp set i % 7 (warps 4 * set .. 4 * set + 3, one token each), so
+// the seven blocks a CTA gets at 4096 tokens on 148 SMs are one round (sixteen warps took two: 18.3 against 16.5 us).
+// Warp 28 produces.  A stage holds IN and RESID (4 x 2F bytes each) and, when the mask is an input, the mask rows
 // (4 x F bytes).  NV = 128-bit pieces per lane and row (F <= 256 * NV).
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kFwdWarps = 16;
+constexpr int kFwdWarps = 28;
 constexpr int kFwdThreads = (kFwdWarps + 1) * 32;
 constexpr int kFwdRows = 4;                      // tokens per stage
 
